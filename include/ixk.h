@@ -1,0 +1,182 @@
+/* ixk.h — C ABI of libixk.so: the B200 (sm_100a) kernel library that stands in
+ * for the kernel layer of intel-extension-for-openxla's PJRT plugin.
+ *
+ * The reference isolates its kernels behind two seams:
+ *   - sycl_onednn.so, entered through RunGemmCustomCall
+ *     (xla/service/gpu/sycl_onednn.h:31-37, xla/service/gpu/sycl_onednn.cc:38-54), and
+ *   - the XeTLA attention entry points fmha_forward_kernel_{bf16,fp16}
+ *     (xla/service/gpu/xetla/sdp/sdp_forward.h:22-36).
+ * Every function below replaces one of those, with plain pointers and sizes
+ * only.  All buffers are caller-owned device memory; nothing is retained past
+ * the call; kernels are enqueued on the caller's stream and never synchronised.
+ * No entry point except the *_workspace_bytes queries is valid without a
+ * B200-class GPU: there is no CPU fallback.
+ */
+#ifndef IXK_H_
+#define IXK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ status */
+/* Replaces absl::Status at the boundary (xetla_gpu_fused_mha_runner.cc:60,
+ * :145, :217 return Unimplemented / Internal; the reference CHECK-aborts on
+ * layout violations at :114-116 — this library returns a code instead). */
+typedef enum ixk_status {
+  IXK_OK = 0,
+  IXK_INVALID_ARGUMENT = 1,   /* malformed descriptor, null pointer, misalignment */
+  IXK_UNIMPLEMENTED = 2,      /* valid request outside what the kernels cover      */
+  IXK_WORKSPACE_TOO_SMALL = 3,
+  IXK_CUDA_ERROR = 4,         /* a CUDA runtime/driver call failed                 */
+  IXK_NO_DEVICE = 5,          /* no sm_100 device is current                       */
+  IXK_DEVICE_TIMEOUT = 6      /* a bounded device-side wait gave up (see ixk_device_status) */
+} ixk_status;
+
+const char* ixk_status_string(int status);
+/* Text of the last failure on the calling thread ("" if none). */
+const char* ixk_last_error(void);
+/* Library version, "major.minor.patch". */
+const char* ixk_version(void);
+
+/* ------------------------------------------------------------------- types */
+/* Element types the reference dispatches on (onednn_matmul_utils.cc:605-610,
+ * xetla_gpu_fused_mha_runner.cc:209-217), plus the two fp8 kinds of the scaled GEMM. */
+typedef enum ixk_dtype {
+  IXK_BF16 = 0,
+  IXK_F16 = 1,
+  IXK_F32 = 2,
+  IXK_F8E4M3 = 3, /* e4m3fn: no inf, max 448   */
+  IXK_F8E5M2 = 4  /* e5m2: IEEE-like, max 57344 */
+} ixk_dtype;
+
+/* MatrixLayout::Order as read from the "*_order" attributes
+ * (onednn_matmul_utils.cc:543-551). */
+typedef enum ixk_order { IXK_ROW_MAJOR = 0, IXK_COL_MAJOR = 1 } ixk_order;
+
+/* SYCLGemm::GemmBackendEpilogue, same names and order
+ * (onednn_matmul_utils.h:35-44). */
+typedef enum ixk_epilogue {
+  IXK_EPILOGUE_DEFAULT = 0,
+  IXK_EPILOGUE_RELU = 1,
+  IXK_EPILOGUE_GELU = 2,
+  IXK_EPILOGUE_BIAS = 3,
+  IXK_EPILOGUE_BIAS_RELU = 4,
+  IXK_EPILOGUE_BIAS_GELU = 5,
+  IXK_EPILOGUE_GELU_AUX = 6,     /* rejected, as in the reference (onednn_matmul_utils.cc:321-322) */
+  IXK_EPILOGUE_BIAS_GELU_AUX = 7 /* rejected, as above */
+} ixk_epilogue;
+
+/* One operand of the GEMM custom call: the six "{lhs,rhs,output}_*" attributes
+ * RunGemm reads from the FFI dictionary (onednn_matmul_utils.cc:543-590).
+ * num_rows/num_cols are the LOGICAL matrix shape; order says which of the two
+ * is contiguous; leading_dim_stride is the pitch, in elements, of the other. */
+typedef struct ixk_matrix_layout {
+  int32_t order;              /* ixk_order */
+  int32_t dtype;              /* ixk_dtype */
+  int64_t num_rows;
+  int64_t num_cols;
+  int64_t batch_stride;       /* elements between consecutive batch members   */
+  int64_t leading_dim_stride; /* elements between consecutive rows (row-major) or columns (col-major) */
+} ixk_matrix_layout;
+
+/* The attribute dictionary of "__cublas$gemm" / "__cublas$lt$matmul"
+ * (sycl_custom_call.cc:154-205, onednn_matmul_utils.cc:533-621). */
+typedef struct ixk_gemm_desc {
+  ixk_matrix_layout lhs;    /* A: [M, K] */
+  ixk_matrix_layout rhs;    /* B: [K, N] */
+  ixk_matrix_layout output; /* D (and C, which XLA aliases with D when beta != 0): [M, N] */
+  int64_t batch_size;
+  float alpha;              /* must be 1, as in the reference (onednn_matmul_utils.cc:438) */
+  float beta;               /* D = epi(A.B + bias) + beta*C; any real value (the reference's
+                               XeTLA path only takes 0 or 1, onednn_matmul_utils.cc:262-270) */
+  int32_t epilogue;         /* ixk_epilogue */
+  int32_t reserved;         /* must be 0 */
+} ixk_gemm_desc;
+
+/* ---------------------------------------------------------------- GEMM call */
+/* Replaces RunGemmCustomCall (sycl_onednn.cc:38-54) → RunGemm
+ * (onednn_matmul_utils.cc:533-621) → hgemm_* kernels
+ * (xetla/gemm/hgemm_impl.h:101-459) / dnnl::matmul (onednn_matmul_utils.cc:394-491).
+ *
+ *   D = act(A.B + bias[n]) + beta*C          fp32 accumulate, one rounding to D's type
+ *
+ * act = identity | relu | gelu_tanh by `epilogue`.  bias is a length-N vector
+ * of A's type, N being the column count AFTER a column-major output has been
+ * rewritten as D^T = B^T.A^T (onednn_matmul_utils.cc:520-530, bias dims :363-365).
+ * c may be NULL iff beta == 0; c may alias d.  bias must be non-NULL exactly for
+ * the BIAS* epilogues.  Type triples: (BF16,BF16,BF16) (F16,F16,F16)
+ * (BF16,BF16,F32) (F16,F16,F32); others → IXK_UNIMPLEMENTED.
+ * Requirements (else IXK_INVALID_ARGUMENT / IXK_UNIMPLEMENTED): pointers 16-byte
+ * aligned, leading_dim_stride * sizeof(element) a multiple of 16 for A and B.
+ * workspace is unused by the present kernels (ixk_gemm_workspace_bytes returns 0)
+ * but kept in the signature because the reference hands its scratch allocator
+ * down this path (sycl_onednn.h:37). */
+int ixk_gemm(const ixk_gemm_desc* desc, const void* a, const void* b,
+             const void* c, const void* bias, void* d, void* workspace,
+             size_t workspace_bytes, void* cuda_stream);
+size_t ixk_gemm_workspace_bytes(const ixk_gemm_desc* desc);
+
+/* fp8 scaled GEMM.  No counterpart kernel exists in the reference (its RunGemm
+ * has no fp8 case, onednn_matmul_utils.cc:605-610); the contract is the one of
+ * the fp8 example (example/fp8/run.py:120-121): operands quantised per tensor,
+ *   D = cast( (sum_k Aq.Bq in fp32) * inv_scale_a * inv_scale_b ) [+ bias, act, beta*C as above]
+ * lhs.dtype / rhs.dtype ∈ {F8E4M3, F8E5M2}; output.dtype ∈ {BF16, F16, F32}.
+ * inv_scale_a / inv_scale_b are HOST floats (1/scale used at quantisation).
+ * bias, if any, has D's type. */
+int ixk_gemm_fp8(const ixk_gemm_desc* desc, const void* a, const void* b,
+                 const void* c, const void* bias, void* d, float inv_scale_a,
+                 float inv_scale_b, void* workspace, size_t workspace_bytes,
+                 void* cuda_stream);
+
+/* --------------------------------------------------------------- attention */
+/* Arguments of fmha_forward_kernel_{bf16,fp16} (sdp_forward.h:22-36) plus the
+ * strides the runner derives them from (xetla_gpu_fused_mha_runner.cc:96-123).
+ * Strides are in ELEMENTS; the innermost (head_size) stride is 1, as the
+ * runner CHECKs (:114-116).  Logical shapes: q,o [B,N,F,H]; k,v [B,N,T,H];
+ * bias [B,N,F,T] with stride 0 on B and/or N meaning broadcast (the reference
+ * wants it materialised per head, fmha_forward.h:229-242); lse [B,N,F] fp32. */
+typedef struct ixk_fmha_desc {
+  int32_t dtype;        /* IXK_BF16 or IXK_F16: q, k, v, bias, out */
+  int32_t causal;       /* keep t <= f, diagonal anchored top-left (fmha_utils.h:45-96) */
+  int32_t num_batches;  /* B */
+  int32_t num_heads;    /* N */
+  int32_t head_size;    /* H  (<= 256, multiple of 8) */
+  int32_t num_queries;  /* F */
+  int32_t num_keys;     /* T */
+  float head_scale;     /* multiplies Q.K^T before the bias is added (fmha_forward.h:256-282) */
+  float dropout_prob;   /* must be 0 (xetla_gpu_fused_mha_runner.cc:56-62) */
+  int32_t reserved;     /* must be 0 */
+  int64_t q_strides[3]; /* B, N, F */
+  int64_t k_strides[3]; /* B, N, T */
+  int64_t v_strides[3]; /* B, N, T */
+  int64_t o_strides[3]; /* B, N, F */
+  int64_t bias_strides[3]; /* B, N, F (innermost T stride is 1); ignored if bias == NULL */
+} ixk_fmha_desc;
+
+/* Replaces fmha_forward_kernel_bf16 / _fp16 (sdp_forward.cc:34-84):
+ *   O[b,n,f,:] = softmax_t( head_scale * Q[b,n,f,:].K[b,n,t,:] + bias[b,n,f,t] ) . V[b,n,t,:]
+ * with the softmax statistics in fp32.  lse (may be NULL) receives
+ * m + ln(l) per row — the reference's "activation" output when is_training
+ * (fmha_forward.h:433-450).  workspace must hold ixk_fmha_fwd_workspace_bytes(desc)
+ * bytes (non-zero only for the split-key decode path, F <= 16). */
+int ixk_fmha_fwd(const ixk_fmha_desc* desc, const void* q, const void* k,
+                 const void* v, const void* bias, void* out, float* lse,
+                 void* workspace, size_t workspace_bytes, void* cuda_stream);
+size_t ixk_fmha_fwd_workspace_bytes(const ixk_fmha_desc* desc);
+
+/* ------------------------------------------------------------ diagnostics */
+/* Every device-side wait in the tensor-core kernels is bounded; a wait that
+ * gives up records a code in a per-device status word and the kernel drains and
+ * returns.  Reads and clears that word (synchronises the device).  0 = clean. */
+int ixk_device_status(int* status_word);
+/* Number of kernels this library has launched from this process (all threads). */
+uint64_t ixk_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IXK_H_ */

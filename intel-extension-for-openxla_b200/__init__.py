@@ -1,0 +1,345 @@
+"""Host-side mirror of the reference's kernel-layer interface, over libixk.so's C ABI.
+
+The reference reaches its kernels through
+  * RunGemmCustomCall(lhs, rhs, add, output, bias, stream, dict, epilogue, scratch)
+    (xla/service/gpu/sycl_onednn.h:31-37), fed by the "__cublas$gemm" / "__cublas$lt$matmul"
+    FFI handlers (xla/service/gpu/sycl_custom_call.cc:154-226), and
+  * fmha_forward_kernel_{bf16,fp16}(queue, q, k, v, bias, dropout, dropout_prob, out, activation,
+    B, N, H, F, T, head_scale, is_training) (xla/service/gpu/xetla/sdp/sdp_forward.h:22-36), called by
+    RunXetlaGpuFMHA (xla/service/gpu/xetla_gpu_fused_mha_runner.cc:195-221).
+The functions here keep those names, argument meanings and error behaviour; torch is used only
+to hold device memory and streams.  There is no CPU path: every call needs the CUDA library and
+raises IxkError otherwise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+__all__ = [
+    "IxkError", "library_path", "load_library", "version", "launch_count", "device_status",
+    "EPILOGUES", "run_gemm_custom_call", "gemm_attrs_for", "gemm", "gemm_fp8",
+    "fmha_forward_kernel", "fmha_forward_kernel_bf16", "fmha_forward_kernel_fp16", "fmha_workspace_bytes",
+    "quantize_fp8",
+]
+
+# ----------------------------------------------------------------------------- ABI mirror
+
+IXK_OK, IXK_INVALID_ARGUMENT, IXK_UNIMPLEMENTED, IXK_WORKSPACE_TOO_SMALL = 0, 1, 2, 3
+IXK_CUDA_ERROR, IXK_NO_DEVICE, IXK_DEVICE_TIMEOUT = 4, 5, 6
+IXK_BF16, IXK_F16, IXK_F32, IXK_F8E4M3, IXK_F8E5M2 = 0, 1, 2, 3, 4
+ROW_MAJOR, COL_MAJOR = 0, 1
+# SYCLGemm::GemmBackendEpilogue (xla/service/gpu/onednn_matmul_utils.h:35-44)
+EPILOGUES = ("DEFAULT", "RELU", "GELU", "BIAS", "BIAS_RELU", "BIAS_GELU", "GELU_AUX", "BIAS_GELU_AUX")
+
+_TORCH_TO_IXK = {
+    torch.bfloat16: IXK_BF16, torch.float16: IXK_F16, torch.float32: IXK_F32,
+    torch.float8_e4m3fn: IXK_F8E4M3, torch.float8_e5m2: IXK_F8E5M2,
+}
+
+
+class IxkError(RuntimeError):
+    """A non-OK status from libixk.so; .status holds the ixk_status code."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+
+
+class _MatrixLayout(ctypes.Structure):
+    _fields_ = [("order", ctypes.c_int32), ("dtype", ctypes.c_int32), ("num_rows", ctypes.c_int64),
+                ("num_cols", ctypes.c_int64), ("batch_stride", ctypes.c_int64),
+                ("leading_dim_stride", ctypes.c_int64)]
+
+
+class _GemmDesc(ctypes.Structure):
+    _fields_ = [("lhs", _MatrixLayout), ("rhs", _MatrixLayout), ("output", _MatrixLayout),
+                ("batch_size", ctypes.c_int64), ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
+                ("epilogue", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
+class _FmhaDesc(ctypes.Structure):
+    _fields_ = [("dtype", ctypes.c_int32), ("causal", ctypes.c_int32), ("num_batches", ctypes.c_int32),
+                ("num_heads", ctypes.c_int32), ("head_size", ctypes.c_int32), ("num_queries", ctypes.c_int32),
+                ("num_keys", ctypes.c_int32), ("head_scale", ctypes.c_float), ("dropout_prob", ctypes.c_float),
+                ("reserved", ctypes.c_int32), ("q_strides", ctypes.c_int64 * 3), ("k_strides", ctypes.c_int64 * 3),
+                ("v_strides", ctypes.c_int64 * 3), ("o_strides", ctypes.c_int64 * 3),
+                ("bias_strides", ctypes.c_int64 * 3)]
+
+
+_LIB: Optional[ctypes.CDLL] = None
+
+# Every symbol include/ixk.h declares: name -> (restype, argtypes)
+_vp, _sz = ctypes.c_void_p, ctypes.c_size_t
+ABI_SYMBOLS = {
+    "ixk_status_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "ixk_last_error": (ctypes.c_char_p, []),
+    "ixk_version": (ctypes.c_char_p, []),
+    "ixk_gemm": (ctypes.c_int, [ctypes.POINTER(_GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "ixk_gemm_workspace_bytes": (_sz, [ctypes.POINTER(_GemmDesc)]),
+    "ixk_gemm_fp8": (ctypes.c_int, [ctypes.POINTER(_GemmDesc), _vp, _vp, _vp, _vp, _vp, ctypes.c_float,
+                                    ctypes.c_float, _vp, _sz, _vp]),
+    "ixk_fmha_fwd": (ctypes.c_int, [ctypes.POINTER(_FmhaDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "ixk_fmha_fwd_workspace_bytes": (_sz, [ctypes.POINTER(_FmhaDesc)]),
+    "ixk_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
+    "ixk_launch_count": (ctypes.c_uint64, []),
+}
+
+
+def library_path() -> str:
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libixk.so")
+
+
+def load_library() -> ctypes.CDLL:
+    """dlopen libixk.so and bind the ABI.  Raises IxkError if it has not been built — there is
+    deliberately nothing to fall back to."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = library_path()
+    if not os.path.exists(path):
+        raise IxkError(IXK_NO_DEVICE, f"{path} is missing: build it with "
+                       f"`python {os.path.join(os.path.dirname(path), os.pardir, 'build.py')}` "
+                       "(there is no CPU fallback)")
+    lib = ctypes.CDLL(path)
+    for name, (restype, argtypes) in ABI_SYMBOLS.items():
+        fn = getattr(lib, name)  # AttributeError if the library does not export it
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _LIB = lib
+    return lib
+
+
+def _check(status: int) -> None:
+    if status != IXK_OK:
+        lib = load_library()
+        name = lib.ixk_status_string(status).decode()
+        raise IxkError(status, f"{name}: {lib.ixk_last_error().decode()}")
+
+
+def version() -> str:
+    return load_library().ixk_version().decode()
+
+
+def launch_count() -> int:
+    return int(load_library().ixk_launch_count())
+
+
+def device_status() -> int:
+    """Synchronises the device; returns the status word (0 = clean) and raises IxkError on a
+    recorded device-side timeout."""
+    word = ctypes.c_int(0)
+    _check(load_library().ixk_device_status(ctypes.byref(word)))
+    return word.value
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream_ptr(stream) -> ctypes.c_void_p:
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return ctypes.c_void_p(stream.cuda_stream)
+
+
+def _require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise IxkError(IXK_NO_DEVICE, "operands must be CUDA tensors: libixk has no CPU path")
+
+
+# ----------------------------------------------------------------------------- GEMM
+
+def run_gemm_custom_call(lhs: torch.Tensor, rhs: torch.Tensor, add: Optional[torch.Tensor],
+                         output: torch.Tensor, bias: Optional[torch.Tensor], stream, attrs: dict,
+                         epilogue: str, *, inv_scale_a: Optional[float] = None,
+                         inv_scale_b: Optional[float] = None) -> None:
+    """RunGemmCustomCall (xla/service/gpu/sycl_onednn.cc:38-54): buffers + the FFI attribute
+    dictionary RunGemm reads (xla/service/gpu/onednn_matmul_utils.cc:543-595).  `attrs` keys:
+    {lhs,rhs,output}_{order,num_rows,num_cols,batch_stride,leading_dim_stride,layout_dtype},
+    batch_size, alpha, beta.  `add` is the C operand read when beta != 0 (it may be `output`).
+    With inv_scale_a/b given the operands are fp8 and the scaled-GEMM entry point is used."""
+    if epilogue not in EPILOGUES:
+        raise IxkError(IXK_INVALID_ARGUMENT, "Unknown Epilogue.")  # onednn_matmul_utils.cc:52-54
+    _require_cuda(lhs, rhs, add, output, bias)
+    lib = load_library()
+    d = _GemmDesc()
+    for name, field in (("lhs", d.lhs), ("rhs", d.rhs), ("output", d.output)):
+        field.order = int(attrs[f"{name}_order"])
+        field.dtype = int(attrs[f"{name}_layout_dtype"])
+        field.num_rows = int(attrs[f"{name}_num_rows"])
+        field.num_cols = int(attrs[f"{name}_num_cols"])
+        field.batch_stride = int(attrs[f"{name}_batch_stride"])
+        field.leading_dim_stride = int(attrs[f"{name}_leading_dim_stride"])
+    d.batch_size = int(attrs["batch_size"])
+    d.alpha = float(attrs.get("alpha", 1.0))
+    d.beta = float(attrs.get("beta", 0.0))
+    d.epilogue = EPILOGUES.index(epilogue)
+    d.reserved = 0
+    sp = _stream_ptr(stream)
+    if inv_scale_a is not None or inv_scale_b is not None:
+        st = lib.ixk_gemm_fp8(ctypes.byref(d), _ptr(lhs), _ptr(rhs), _ptr(add), _ptr(bias), _ptr(output),
+                              float(inv_scale_a), float(inv_scale_b), None, 0, sp)
+    else:
+        st = lib.ixk_gemm(ctypes.byref(d), _ptr(lhs), _ptr(rhs), _ptr(add), _ptr(bias), _ptr(output), None, 0, sp)
+    _check(st)
+
+
+def _matrix_attrs(prefix: str, t: torch.Tensor) -> dict:
+    """Layout attributes of a 2-D or 3-D (batched) tensor view: whichever of the last two
+    dimensions has stride 1 decides the order."""
+    if t.dim() not in (2, 3):
+        raise IxkError(IXK_INVALID_ARGUMENT, f"{prefix}: expected a 2-D or 3-D tensor")
+    rows, cols = t.shape[-2], t.shape[-1]
+    sr, sc = t.stride(-2), t.stride(-1)
+    if sc == 1 and (sr >= cols or rows == 1):
+        order, ld = ROW_MAJOR, (sr if rows > 1 else max(sr, cols))
+    elif sr == 1 and (sc >= rows or cols == 1):
+        order, ld = COL_MAJOR, (sc if cols > 1 else max(sc, rows))
+    else:
+        raise IxkError(IXK_INVALID_ARGUMENT, f"{prefix}: neither of the last two dimensions is contiguous")
+    bs = t.stride(0) if t.dim() == 3 else rows * cols
+    return {f"{prefix}_order": order, f"{prefix}_num_rows": rows, f"{prefix}_num_cols": cols,
+            f"{prefix}_batch_stride": bs, f"{prefix}_leading_dim_stride": ld,
+            f"{prefix}_layout_dtype": _TORCH_TO_IXK[t.dtype]}
+
+
+def gemm_attrs_for(lhs: torch.Tensor, rhs: torch.Tensor, output: torch.Tensor, beta: float = 0.0) -> dict:
+    """The attribute dictionary XLA's GEMM rewriter would attach for these three tensor views."""
+    attrs = {}
+    attrs.update(_matrix_attrs("lhs", lhs))
+    attrs.update(_matrix_attrs("rhs", rhs))
+    attrs.update(_matrix_attrs("output", output))
+    attrs["batch_size"] = output.shape[0] if output.dim() == 3 else 1
+    attrs["alpha"] = 1.0
+    attrs["beta"] = float(beta)
+    attrs["algorithm"] = 0
+    return attrs
+
+
+def gemm(lhs: torch.Tensor, rhs: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+         c: Optional[torch.Tensor] = None, beta: float = 0.0, epilogue: str = "DEFAULT",
+         out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+         stream=None) -> torch.Tensor:
+    """out = act(lhs @ rhs + bias + beta*c) through "__cublas$lt$matmul"'s path.  Any mix of
+    row-/column-major 2-D (or batched 3-D) views is passed through as-is, never copied."""
+    if out is None:
+        shape = (*lhs.shape[:-1], rhs.shape[-1])
+        out = torch.empty(shape, device=lhs.device, dtype=out_dtype or lhs.dtype)
+    attrs = gemm_attrs_for(lhs, rhs, out, beta)
+    run_gemm_custom_call(lhs, rhs, c, out, bias, stream, attrs, epilogue)
+    return out
+
+
+def quantize_fp8(x: torch.Tensor, dtype: torch.dtype):
+    """Per-tensor scaled, saturating quantisation used by the fp8 configuration:
+    scale = max_finite / amax(x); returns (fp8 tensor, scale).  Works on any device (it is
+    input preparation, not part of the timed path)."""
+    fmax = torch.finfo(dtype).max
+    amax = x.abs().max().item()
+    scale = fmax / amax if amax > 0 else 1.0
+    q = (x.float() * scale).clamp_(-fmax, fmax).to(dtype)
+    return q, scale
+
+
+def gemm_fp8(lhs_q: torch.Tensor, rhs_q: torch.Tensor, inv_scale_a: float, inv_scale_b: float, *,
+             bias: Optional[torch.Tensor] = None, epilogue: str = "DEFAULT",
+             out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+             stream=None) -> torch.Tensor:
+    """out = cast((lhs_q @ rhs_q in fp32) * inv_scale_a * inv_scale_b [+ bias, act])."""
+    if out is None:
+        out = torch.empty((*lhs_q.shape[:-1], rhs_q.shape[-1]), device=lhs_q.device, dtype=out_dtype)
+    attrs = gemm_attrs_for(lhs_q, rhs_q, out, 0.0)
+    run_gemm_custom_call(lhs_q, rhs_q, None, out, bias, stream, attrs, epilogue,
+                         inv_scale_a=inv_scale_a, inv_scale_b=inv_scale_b)
+    return out
+
+
+# ----------------------------------------------------------------------------- attention
+
+def _fmha_desc(query, key, value, bias, out, head_scale, causal, dropout_prob) -> _FmhaDesc:
+    if query.dim() != 4 or key.dim() != 4 or value.dim() != 4 or out.dim() != 4:
+        raise IxkError(IXK_INVALID_ARGUMENT, "q, k, v, out must be 4-D [B,N,S,H] views")
+    B, N, F, H = query.shape
+    T = key.shape[2]
+    d = _FmhaDesc()
+    d.dtype = _TORCH_TO_IXK[query.dtype]
+    d.causal = 1 if causal else 0
+    d.num_batches, d.num_heads, d.head_size, d.num_queries, d.num_keys = B, N, H, F, T
+    d.head_scale = float(head_scale)
+    d.dropout_prob = float(dropout_prob)
+    d.reserved = 0
+    for name, t in (("q", query), ("k", key), ("v", value), ("o", out)):
+        if t.stride(3) != 1 and t.shape[3] > 1:
+            # xetla_gpu_fused_mha_runner.cc:114-116 CHECKs the same
+            raise IxkError(IXK_INVALID_ARGUMENT, f"{name}: head_size must be the contiguous dimension")
+        getattr(d, f"{name}_strides")[:] = [t.stride(0), t.stride(1), t.stride(2)]
+    if bias is not None:
+        if bias.dim() != 4 or bias.shape[3] != T or bias.shape[2] != F:
+            raise IxkError(IXK_INVALID_ARGUMENT, "bias must be [B|1, N|1, F, T]")
+        if bias.stride(3) != 1:
+            raise IxkError(IXK_INVALID_ARGUMENT, "bias: the key dimension must be contiguous")
+        d.bias_strides[:] = [bias.stride(0) if bias.shape[0] > 1 else 0,
+                             bias.stride(1) if bias.shape[1] > 1 else 0, bias.stride(2)]
+    return d
+
+
+def fmha_workspace_bytes(query, key, value, bias, out, head_scale, causal=False) -> int:
+    d = _fmha_desc(query, key, value, bias, out, head_scale, causal, 0.0)
+    return int(load_library().ixk_fmha_fwd_workspace_bytes(ctypes.byref(d)))
+
+
+def fmha_forward_kernel(stream, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                        bias: Optional[torch.Tensor], dropout, dropout_prob: float, out: torch.Tensor,
+                        activation: Optional[torch.Tensor], head_scale: float, is_training: bool = False,
+                        *, causal: bool = False, workspace: Optional[torch.Tensor] = None) -> None:
+    """fmha_forward_kernel_{bf16,fp16} (xla/service/gpu/xetla/sdp/sdp_forward.cc:34-84), the dtype
+    taken from `query`.  q/out are [B,N,F,H] views, k/v [B,N,T,H] views (any strides with H
+    contiguous, so [B,S,N,H] storage is passed as a permuted view); `activation` receives the
+    log-sum-exp rows when is_training (xla/service/gpu/xetla/sdp/fmha_forward.h:433-450).
+    `dropout` must be None: the runner rejects dropout (xetla_gpu_fused_mha_runner.cc:56-62).
+    `causal` is a real flag here; the reference compiles it out (sdp_forward.cc:41) and expects
+    callers to fold the mask into `bias`."""
+    _require_cuda(query, key, value, bias, out, activation)
+    if dropout is not None:
+        raise IxkError(IXK_UNIMPLEMENTED, "Unimplemented dropout")
+    if is_training and activation is None:
+        raise IxkError(IXK_INVALID_ARGUMENT, "is_training needs the activation (log-sum-exp) buffer")
+    lib = load_library()
+    d = _fmha_desc(query, key, value, bias, out, head_scale, causal, 0.0 if dropout_prob in (None, 1.0) else dropout_prob)
+    need = int(lib.ixk_fmha_fwd_workspace_bytes(ctypes.byref(d)))
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=query.device)
+    ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    st = lib.ixk_fmha_fwd(ctypes.byref(d), _ptr(query), _ptr(key), _ptr(value), _ptr(bias), _ptr(out),
+                          _ptr(activation if is_training else None), _ptr(workspace), ws_bytes, _stream_ptr(stream))
+    _check(st)
+
+
+def fmha_forward_kernel_bf16(stream, query, key, value, bias, dropout, dropout_prob, out, activation,
+                             num_batches, num_heads, head_size, num_queries, num_keys, head_scale,
+                             is_training, *, causal=False):
+    """Positional twin of the reference declaration (xla/service/gpu/xetla/sdp/sdp_forward.h:30-36);
+    the sizes must agree with the tensor views."""
+    if query.dtype != torch.bfloat16:
+        raise IxkError(IXK_INVALID_ARGUMENT, "Invalid MHA datatype")  # xetla_gpu_fused_mha_runner.cc:145
+    if tuple(query.shape) != (num_batches, num_heads, num_queries, head_size) or key.shape[2] != num_keys:
+        raise IxkError(IXK_INVALID_ARGUMENT, "sizes do not match the tensor views")
+    fmha_forward_kernel(stream, query, key, value, bias, dropout, dropout_prob, out, activation, head_scale,
+                        is_training, causal=causal)
+
+
+def fmha_forward_kernel_fp16(stream, query, key, value, bias, dropout, dropout_prob, out, activation,
+                             num_batches, num_heads, head_size, num_queries, num_keys, head_scale,
+                             is_training, *, causal=False):
+    """fp16 twin (xla/service/gpu/xetla/sdp/sdp_forward.h:22-28)."""
+    if query.dtype != torch.float16:
+        raise IxkError(IXK_INVALID_ARGUMENT, "Invalid MHA datatype")
+    if tuple(query.shape) != (num_batches, num_heads, num_queries, head_size) or key.shape[2] != num_keys:
+        raise IxkError(IXK_INVALID_ARGUMENT, "sizes do not match the tensor views")
+    fmha_forward_kernel(stream, query, key, value, bias, dropout, dropout_prob, out, activation, head_scale,
+                        is_training, causal=causal)

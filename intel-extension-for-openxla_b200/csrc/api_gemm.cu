@@ -1,0 +1,208 @@
+// GEMM entry points: the host logic of RunGemm (xla/service/gpu/onednn_matmul_utils.cc:533-621)
+// — attribute dictionary → matrix descriptors → column-major-output rewrite → typed dispatch —
+// restated over the C ABI, in front of the tcgen05 kernel.
+#include <cmath>
+#include <cstdlib>
+#include <utility>
+
+#include "gemm_sm100.h"
+
+namespace ixk {
+namespace {
+
+// MatrixDescriptor of the reference (xla/service/gpu/matrix_descriptor.h:31-47): storage is
+// always read as row-major [num_rows, num_cols] with pitch leading_dim_stride; `transpose`
+// says the logical matrix is the transpose of that storage.
+struct MatrixDesc {
+  const void* data;
+  bool transpose;
+  int64_t num_rows, num_cols, batch_stride, leading_dim_stride;
+  int64_t reduced_dim() const { return transpose ? num_rows : num_cols; }
+};
+
+// onednn_matmul_utils.cc:547-590: a column-major layout becomes a transposed descriptor
+// whose stored shape has rows and columns exchanged.
+MatrixDesc make_desc(const ixk_matrix_layout& l, const void* data) {
+  const bool t = l.order == IXK_COL_MAJOR;
+  return MatrixDesc{data, t, t ? l.num_cols : l.num_rows, t ? l.num_rows : l.num_cols,
+                    l.batch_stride, l.leading_dim_stride};
+}
+
+// onednn_matmul_utils.cc:520-530: D^T = B^T . A^T when the output is column-major.
+void make_blas_compatible(MatrixDesc& lhs, MatrixDesc& rhs, MatrixDesc& out) {
+  if (out.transpose) {
+    std::swap(lhs, rhs);
+    lhs.transpose = !lhs.transpose;
+    rhs.transpose = !rhs.transpose;
+    out.transpose = !out.transpose;
+  }
+}
+
+bool is_fp8(int t) { return t == IXK_F8E4M3 || t == IXK_F8E5M2; }
+int elem_bytes(int t) { return t == IXK_F32 ? 4 : (is_fp8(t) ? 1 : 2); }
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_layout(const ixk_matrix_layout& l, const char* name) {
+  if (l.order != IXK_ROW_MAJOR && l.order != IXK_COL_MAJOR)
+    return fail(IXK_INVALID_ARGUMENT, std::string(name) + "_order must be 0 (row-major) or 1 (column-major)");
+  if (l.num_rows < 0 || l.num_cols < 0)
+    return fail(IXK_INVALID_ARGUMENT, std::string(name) + " has a negative dimension");
+  const int64_t contiguous = l.order == IXK_ROW_MAJOR ? l.num_cols : l.num_rows;
+  if (l.leading_dim_stride < contiguous)
+    return fail(IXK_INVALID_ARGUMENT, std::string(name) + "_leading_dim_stride is smaller than the contiguous dimension");
+  return IXK_OK;
+}
+
+int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, const void* bias,
+        void* d, bool fp8_call, float inv_scale_a, float inv_scale_b, void* stream) {
+  clear_error();
+  if (desc == nullptr) return fail(IXK_INVALID_ARGUMENT, "desc is NULL");
+  if (desc->reserved != 0) return fail(IXK_INVALID_ARGUMENT, "desc.reserved must be 0");
+  int rc;
+  if ((rc = check_layout(desc->lhs, "lhs")) != IXK_OK) return rc;
+  if ((rc = check_layout(desc->rhs, "rhs")) != IXK_OK) return rc;
+  if ((rc = check_layout(desc->output, "output")) != IXK_OK) return rc;
+  if (desc->batch_size < 1) return fail(IXK_INVALID_ARGUMENT, "batch_size must be >= 1");
+
+  // Epilogue → (vector bias?, activation).  onednn_matmul_utils.cc:90-136, :434-455.
+  bool wants_bias = false;
+  int act = gemm::kActNone;
+  switch (desc->epilogue) {
+    case IXK_EPILOGUE_DEFAULT: break;
+    case IXK_EPILOGUE_RELU: act = gemm::kActRelu; break;
+    case IXK_EPILOGUE_GELU: act = gemm::kActGelu; break;
+    case IXK_EPILOGUE_BIAS: wants_bias = true; break;
+    case IXK_EPILOGUE_BIAS_RELU: wants_bias = true; act = gemm::kActRelu; break;
+    case IXK_EPILOGUE_BIAS_GELU: wants_bias = true; act = gemm::kActGelu; break;
+    case IXK_EPILOGUE_GELU_AUX:
+    case IXK_EPILOGUE_BIAS_GELU_AUX:
+      // onednn_matmul_utils.cc:321-322, :452-453: "Unsupported Activation mode".
+      return fail(IXK_UNIMPLEMENTED, "Unsupported Activation mode: *_AUX epilogues have no auxiliary output here");
+    default: return fail(IXK_INVALID_ARGUMENT, "Unknown Epilogue.");
+  }
+  if (wants_bias != (bias != nullptr))
+    return fail(IXK_INVALID_ARGUMENT, "bias must be given exactly for the BIAS* epilogues");
+  if (std::fabs(desc->alpha - 1.0f) >= 1e-6f)
+    return fail(IXK_UNIMPLEMENTED, "alpha must be 1 (onednn_matmul_utils.cc:438 CHECKs the same)");
+  const bool has_c = desc->beta != 0.0f;
+  if (has_c && c == nullptr) return fail(IXK_INVALID_ARGUMENT, "beta != 0 needs the C operand");
+  if (a == nullptr || b == nullptr || d == nullptr)
+    return fail(IXK_INVALID_ARGUMENT, "a, b and d must be non-NULL");
+
+  // Type triples of RunGemm's TYPED_GEMM list (onednn_matmul_utils.cc:605-610) that the
+  // tensor-core kernel covers, plus the fp8 operand kinds of the scaled GEMM.
+  const int ta = desc->lhs.dtype, tb = desc->rhs.dtype, tc = desc->output.dtype;
+  gemm::Problem p;
+  if (fp8_call) {
+    if (!is_fp8(ta) || !is_fp8(tb))
+      return fail(IXK_INVALID_ARGUMENT, "ixk_gemm_fp8 needs F8E4M3/F8E5M2 operands");
+    if (tc != IXK_BF16 && tc != IXK_F16 && tc != IXK_F32)
+      return fail(IXK_UNIMPLEMENTED, "fp8 GEMM output must be BF16, F16 or F32");
+    p.fp8 = true;
+    p.a_fmt = ta == IXK_F8E4M3 ? 0u : 1u;
+    p.b_fmt = tb == IXK_F8E4M3 ? 0u : 1u;
+    p.acc_scale = inv_scale_a * inv_scale_b;
+    p.bias_dtype = tc;
+  } else {
+    const bool ok = (ta == IXK_BF16 && tb == IXK_BF16 && (tc == IXK_BF16 || tc == IXK_F32)) ||
+                    (ta == IXK_F16 && tb == IXK_F16 && (tc == IXK_F16 || tc == IXK_F32));
+    if (!ok) {
+      if (is_fp8(ta) || is_fp8(tb)) return fail(IXK_INVALID_ARGUMENT, "fp8 operands go through ixk_gemm_fp8");
+      return fail(IXK_UNIMPLEMENTED,
+                  "Unexpected GEMM lhs/rhs/output types: the tensor-core path takes (BF16,BF16,BF16|F32) and "
+                  "(F16,F16,F16|F32)");
+    }
+    p.fp8 = false;
+    p.ab_dtype = ta;
+    p.a_fmt = p.b_fmt = (ta == IXK_BF16) ? 1u : 0u;
+    p.bias_dtype = ta;
+  }
+
+  MatrixDesc lhs = make_desc(desc->lhs, a);
+  MatrixDesc rhs = make_desc(desc->rhs, b);
+  MatrixDesc out = make_desc(desc->output, d);
+  const bool swapped = out.transpose;
+  make_blas_compatible(lhs, rhs, out);
+
+  // After the rewrite: D is row-major [M,N]; the logical lhs is [M,K], the logical rhs [K,N].
+  p.M = out.num_rows;
+  p.N = out.num_cols;
+  p.K = lhs.reduced_dim();
+  const int64_t lhs_m = lhs.transpose ? lhs.num_cols : lhs.num_rows;
+  const int64_t rhs_k = rhs.transpose ? rhs.num_cols : rhs.num_rows;
+  const int64_t rhs_n = rhs.transpose ? rhs.num_rows : rhs.num_cols;
+  if (lhs_m != p.M || rhs_n != p.N || rhs_k != p.K)
+    return fail(IXK_INVALID_ARGUMENT, "lhs [M,K], rhs [K,N] and output [M,N] shapes do not agree");
+  p.batch = desc->batch_size;
+  if (p.M == 0 || p.N == 0) return IXK_OK;
+  if (p.K == 0) return fail(IXK_UNIMPLEMENTED, "K == 0 is not supported");
+  if (p.M > INT32_MAX || p.N > INT32_MAX || p.K > INT32_MAX)
+    return fail(IXK_UNIMPLEMENTED, "dimensions above 2^31-1 are not supported");
+
+  // lhs stored [rows, cols] row-major: not transposed → K contiguous (K-major);
+  // transposed → stored [K, M] → M contiguous (MN-major).
+  p.a = lhs.data;
+  p.a_mn_major = lhs.transpose;
+  p.lda = lhs.leading_dim_stride;
+  p.a_batch_stride = lhs.batch_stride;
+  // rhs stored row-major [K, N] when not transposed → N contiguous (MN-major);
+  // transposed → stored [N, K] → K-major.
+  p.b = rhs.data;
+  p.b_mn_major = !rhs.transpose;
+  p.ldb = rhs.leading_dim_stride;
+  p.b_batch_stride = rhs.batch_stride;
+  p.d = d;
+  p.ldd = out.leading_dim_stride;
+  p.d_batch_stride = out.batch_stride;
+  p.c = has_c ? c : nullptr;
+  p.ldc = p.ldd;
+  p.c_batch_stride = p.d_batch_stride;
+  p.bias = bias;
+  p.out_dtype = tc;
+  p.act = act;
+  p.beta = desc->beta;
+  (void)swapped;
+
+  const int es = elem_bytes(ta);
+  if (!aligned16(p.a) || !aligned16(p.b))
+    return fail(IXK_INVALID_ARGUMENT, "a and b must be 16-byte aligned (TMA)");
+  if ((p.lda * es) % 16 != 0 || (p.ldb * es) % 16 != 0)
+    return fail(IXK_UNIMPLEMENTED, "leading_dim_stride * element size must be a multiple of 16 bytes for lhs and rhs (TMA)");
+  if (p.batch > 1 && ((p.a_batch_stride * es) % 16 != 0 || (p.b_batch_stride * es) % 16 != 0))
+    return fail(IXK_UNIMPLEMENTED, "batch_stride * element size must be a multiple of 16 bytes for lhs and rhs (TMA)");
+  if ((reinterpret_cast<uintptr_t>(p.d) % elem_bytes(tc)) != 0)
+    return fail(IXK_INVALID_ARGUMENT, "d is not aligned to its element size");
+
+  if (const char* env = std::getenv("IXK_GEMM_BLOCK_N")) p.force_block_n = std::atoi(env);
+
+  DeviceInfo dev;
+  if ((rc = get_device_info(&dev)) != IXK_OK) return rc;
+  return gemm::launch(p, dev, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+}  // namespace ixk
+
+extern "C" {
+
+int ixk_gemm(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c,
+             const void* bias, void* d, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  return ixk::run(desc, a, b, c, bias, d, /*fp8_call=*/false, 1.0f, 1.0f, cuda_stream);
+}
+
+size_t ixk_gemm_workspace_bytes(const ixk_gemm_desc* desc) {
+  (void)desc;
+  return 0;
+}
+
+int ixk_gemm_fp8(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c,
+                 const void* bias, void* d, float inv_scale_a, float inv_scale_b, void* workspace,
+                 size_t workspace_bytes, void* cuda_stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  return ixk::run(desc, a, b, c, bias, d, /*fp8_call=*/true, inv_scale_a, inv_scale_b, cuda_stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,43 @@
+// Interface between the attention entry point and the two attention kernels.
+#pragma once
+
+#include "host_common.h"
+
+namespace ixk {
+namespace fmha {
+
+// Validated attention problem; strides in elements, innermost (head_size) stride 1.
+struct Problem {
+  int dtype = IXK_BF16;
+  bool causal = false;
+  int B = 0, N = 0, H = 0, F = 0, T = 0;
+  float head_scale = 1.0f;
+  const void* q = nullptr;
+  const void* k = nullptr;
+  const void* v = nullptr;
+  const void* bias = nullptr;
+  void* out = nullptr;
+  float* lse = nullptr;
+  int64_t q_strides[3] = {0, 0, 0};
+  int64_t k_strides[3] = {0, 0, 0};
+  int64_t v_strides[3] = {0, 0, 0};
+  int64_t o_strides[3] = {0, 0, 0};
+  int64_t bias_strides[3] = {0, 0, 0};
+};
+
+// Queries-per-(batch,head) at or below which the bandwidth-bound split-key kernel is used.
+constexpr int kDecodeMaxQueries = 16;
+
+// ---- tcgen05 prefill kernel (fmha_prefill_sm100.cu)
+int launch_prefill(const Problem& p, const DeviceInfo& dev, cudaStream_t stream);
+
+// ---- split-key decode kernel (fmha_decode_sm100.cu)
+// Number of key splits chosen for a problem, and the scratch it needs:
+// splits * B*N*F * (H + 2) floats (partial O, running max, running sum).
+int decode_splits(const Problem& p, int sm_count);
+size_t decode_workspace_bytes(const Problem& p, int splits);
+int launch_decode(const Problem& p, const DeviceInfo& dev, void* workspace, size_t workspace_bytes,
+                  cudaStream_t stream);
+
+}  // namespace fmha
+}  // namespace ixk

@@ -1,0 +1,496 @@
+// Persistent, warp-specialised tcgen05 GEMM with a fused epilogue for sm_100a.
+//
+//   D[M,N] = act( acc_scale * (A[M,K] . B[K,N]) + bias[n] + beta * C[M,N] )
+//
+// Replaces the XeTLA hgemm_* kernels (xla/service/gpu/xetla/gemm/hgemm_impl.h:101-459)
+// and the oneDNN matmul + post-ops call (xla/service/gpu/onednn_matmul_utils.cc:394-491).
+//
+// One CTA per SM, 192 threads:
+//   warp 0      TMA producer: A/B k-slabs of 128 bytes into a 128B-swizzled shared-memory ring
+//   warp 1      TMEM allocation + single-thread tcgen05.mma issue (128 x BLOCK_N x 32 bytes of K)
+//   warps 2-5   epilogue: tcgen05.ld of the fp32 accumulator, bias/activation/residual in fp32,
+//               one rounding, 16-byte global stores
+// The accumulator is double-buffered in TMEM (2 x BLOCK_N columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1.  Either operand may be K-major or MN-major in global
+// memory; the TMA box shape and the UMMA descriptors follow the operand's major-ness, so no
+// transposed copy is ever made.  Operands are 16-bit (kind::f16) or 8-bit (kind::f8f6f4).
+#include "gemm_sm100.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
+
+namespace ixk {
+namespace gemm {
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kSlabBytes = 128;  // bytes of K per shared-memory row (one swizzle span)
+constexpr int kThreads = 192;
+constexpr int kATileBytes = kBlockM * kSlabBytes;  // 16 KiB
+
+template <int kBlockN>
+struct Cfg {
+  static constexpr int kBTileBytes = kBlockN * kSlabBytes;
+  static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+  static constexpr int kStages = (192 * 1024) / kStageBytes;
+  static constexpr int kTmemCols = 2 * kBlockN;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + align slack
+};
+
+// Site codes written to the status word by a wait that gave up.
+enum : int { kSiteProducer = 101, kSiteMmaFull = 102, kSiteMmaAcc = 103, kSiteEpilogue = 104 };
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  // 0.5 x (1 + tanh(u)) == x / (1 + exp(-2u)),  u = sqrt(2/pi) (x + 0.044715 x^3)
+  const float u = 0.7978845608028654f * x * fmaf(0.044715f * x, x, 1.0f);
+  const float e = ptx::ex2_approx(-2.885390081777927f * u);  // exp(-2u) = 2^(-2u log2 e)
+  return __fdividef(x, 1.0f + e);
+}
+
+__device__ __forceinline__ void load_row16(const void* base, int64_t elem_off, int dtype, int count,
+                                           bool vec_ok, float (&out)[32]) {
+  // Reads `count` (<= 32) consecutive elements of type `dtype` starting at elem_off into out[].
+  if (dtype == IXK_F32) {
+    const float* p = static_cast<const float*>(base) + elem_off;
+    if (vec_ok && count == 32) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(p) + i);
+        out[4 * i + 0] = v.x;
+        out[4 * i + 1] = v.y;
+        out[4 * i + 2] = v.z;
+        out[4 * i + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) out[i] = i < count ? __ldg(p + i) : 0.0f;
+    }
+  } else {
+    const uint16_t* p = static_cast<const uint16_t*>(base) + elem_off;
+    uint32_t w[16];
+    if (vec_ok && count == 32) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(p) + i);
+        w[4 * i + 0] = v.x;
+        w[4 * i + 1] = v.y;
+        w[4 * i + 2] = v.z;
+        w[4 * i + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t lo = (2 * i) < count ? __ldg(p + 2 * i) : 0u;
+        const uint32_t hi = (2 * i + 1) < count ? __ldg(p + 2 * i + 1) : 0u;
+        w[i] = lo | (hi << 16);
+      }
+    }
+    if (dtype == IXK_BF16) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        out[2 * i] = __uint_as_float(w[i] << 16);
+        out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void store_row(void* base, int64_t elem_off, int dtype, int count,
+                                          bool vec_ok, const float (&v)[32]) {
+  if (dtype == IXK_F32) {
+    float* p = static_cast<float*>(base) + elem_off;
+    if (vec_ok && count == 32) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4*>(p)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < count) p[i] = v[i];
+    }
+  } else {
+    uint32_t w[16];
+    if (dtype == IXK_BF16) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    uint16_t* p = static_cast<uint16_t*>(base) + elem_off;
+    if (vec_ok && count == 32) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        reinterpret_cast<uint4*>(p)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        if (2 * i < count) p[2 * i] = static_cast<uint16_t>(w[i] & 0xffffu);
+        if (2 * i + 1 < count) p[2 * i + 1] = static_cast<uint16_t>(w[i] >> 16);
+      }
+    }
+  }
+}
+
+// Grouped raster: consecutive tile ids walk down a band of `kGroupM` row-blocks before moving
+// to the next column-block, so the CTAs running at the same time share A and B slabs in L2.
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& bz, int& bm,
+                                            int& bn) {
+  constexpr int kGroupM = 8;
+  const int per_batch = tiles_m * tiles_n;
+  bz = t / per_batch;
+  t -= bz * per_batch;
+  const int band = kGroupM * tiles_n;
+  const int g = t / band;
+  const int first_m = g * kGroupM;
+  const int rows = min(tiles_m - first_m, kGroupM);
+  const int r = t - g * band;
+  bm = first_m + r % rows;
+  bn = r / rows;
+}
+
+template <int kBlockN, bool kFp8>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const KernelArgs args) {
+  using C = Cfg<kBlockN>;
+  constexpr int kStages = C::kStages;
+  constexpr int kElemBytes = kFp8 ? 1 : 2;
+  constexpr int kSlabElems = kSlabBytes / kElemBytes;  // K elements per pipeline stage
+  constexpr int kUmmaK = 32 / kElemBytes;              // K elements per tcgen05.mma
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + kStages * C::kStageBytes;
+  // barrier slots (8 bytes each): full[kStages], empty[kStages], acc_full[2], acc_empty[2]
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
+  uint8_t* tail = smem_gen + kStages * C::kStageBytes + 8 * (2 * kStages + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  ptx::AbortCtl ctl{abort_flag, args.status_word};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(acc_full_bar(b), 1);
+      ptx::mbar_init(acc_empty_bar(b), 128);
+    }
+    ptx::fence_mbar_init();
+    ptx::prefetch_tmap(&tmap_a);
+    ptx::prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_kb = (args.K + kSlabElems - 1) / kSlabElems;
+  const int num_tiles = args.tiles_m * args.tiles_n * args.batch;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+        int bz, bm, bn;
+        tile_coords(t, args.tiles_m, args.tiles_n, bz, bm, bn);
+        const int m0 = bm * kBlockM;
+        const int n0 = bn * kBlockN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, ctl, kSiteProducer)) {
+            alive = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * C::kStageBytes;
+          const uint32_t b_dst = a_dst + kATileBytes;
+          const uint32_t bar = full_bar(stage);
+          ptx::mbar_expect_tx(bar, C::kStageBytes);
+          const int k0 = kb * kSlabElems;
+          if (args.a_mn_major) {
+            // box = [kSlabElems k-rows][128 bytes of M]; one box per 128-byte column block
+#pragma unroll
+            for (int i = 0; i < kBlockM / kSlabElems; ++i)
+              ptx::tma_load_3d(a_dst + i * (kSlabElems * kSlabBytes), &tmap_a, bar,
+                               m0 + i * kSlabElems, k0, bz);
+          } else {
+            ptx::tma_load_3d(a_dst, &tmap_a, bar, k0, m0, bz);
+          }
+          if (args.b_mn_major) {
+#pragma unroll
+            for (int i = 0; i < kBlockN / kSlabElems; ++i)
+              ptx::tma_load_3d(b_dst + i * (kSlabElems * kSlabBytes), &tmap_b, bar,
+                               n0 + i * kSlabElems, k0, bz);
+          } else {
+            ptx::tma_load_3d(b_dst, &tmap_b, bar, k0, n0, bz);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t acc_phase = 0;
+      bool alive = true;
+      // K-major: 8-row groups are 1024 B apart, a k-step moves 32 B inside the swizzle span.
+      // MN-major: 8-k groups are 1024 B apart, 128-byte column blocks are a whole slab apart,
+      //           a k-step moves kUmmaK rows of 128 B.
+      const uint32_t a_lbo = args.a_mn_major ? kSlabElems * kSlabBytes : 16;
+      const uint32_t b_lbo = args.b_mn_major ? kSlabElems * kSlabBytes : 16;
+      const uint32_t a_kstep = args.a_mn_major ? kUmmaK * kSlabBytes : 32;
+      const uint32_t b_kstep = args.b_mn_major ? kUmmaK * kSlabBytes : 32;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+        if (!ptx::mbar_wait(acc_empty_bar(buf), acc_phase ^ 1u, ctl, kSiteMmaAcc)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * kBlockN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(full_bar(stage), phase, ctl, kSiteMmaFull)) {
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_src = smem_base + stage * C::kStageBytes;
+          const uint32_t b_src = a_src + kATileBytes;
+#pragma unroll
+          for (int ks = 0; ks < kSlabElems / kUmmaK; ++ks) {
+            const uint64_t da = ptx::umma_smem_desc(a_src + ks * a_kstep, a_lbo, 1024);
+            const uint64_t db = ptx::umma_smem_desc(b_src + ks * b_kstep, b_lbo, 1024);
+            ptx::umma_ss<kFp8>(d_tmem, da, db, args.idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(empty_bar(stage));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!alive) break;
+        ptx::umma_commit(acc_full_bar(buf));
+        buf ^= 1;
+        if (buf == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const int row_in_tile = quarter * 32 + lane;
+    int buf = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_d = args.d_vec_ok != 0;
+    const bool vec_c = args.c_vec_ok != 0;
+    const bool vec_bias = args.bias_vec_ok != 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int bz, bm, bn;
+      tile_coords(t, args.tiles_m, args.tiles_n, bz, bm, bn);
+      if (!ptx::mbar_wait(acc_full_bar(buf), acc_phase, ctl, kSiteEpilogue)) break;
+      ptx::tc_fence_after_sync();
+      const int m = bm * kBlockM + row_in_tile;
+      const bool row_ok = m < args.M;
+      const int64_t d_row = bz * args.d_batch_stride + static_cast<int64_t>(m) * args.ldd;
+      const int64_t c_row = bz * args.c_batch_stride + static_cast<int64_t>(m) * args.ldc;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kBlockN; c0 += 32) {
+        const int n = bn * kBlockN + c0;
+        if (n >= args.N) break;  // warp-uniform
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBlockN + c0, r);
+        ptx::tmem_ld_wait();
+        const int count = min(32, args.N - n);
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * args.acc_scale;
+        if (args.bias != nullptr) {
+          float b[32];
+          load_row16(args.bias, n, args.bias_dtype, count, vec_bias, b);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] += b[i];
+        }
+        if (args.c != nullptr && row_ok) {
+          float cc[32];
+          load_row16(args.c, c_row + n, args.out_dtype, count, vec_c, cc);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = fmaf(args.beta, cc[i], v[i]);
+        }
+        if (args.act == kActRelu) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
+        } else if (args.act == kActGelu) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+        }
+        if (row_ok) store_row(args.d, d_row + n, args.out_dtype, count, vec_d, v);
+      }
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(acc_empty_bar(buf));
+      buf ^= 1;
+      if (buf == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // Teardown.  On the abort path give copies still in flight time to land before the
+  // shared memory they target is released.
+  if (*abort_flag != 0) __nanosleep(2000000);
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <int kBlockN, bool kFp8>
+int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const KernelArgs& args, int grid,
+               cudaStream_t stream) {
+  using C = Cfg<kBlockN>;
+  auto* fn = &gemm_kernel<kBlockN, kFp8>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  IXK_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    IXK_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    configured_device = dev;
+  }
+  fn<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, args);
+  IXK_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return IXK_OK;
+}
+
+}  // namespace
+
+int pick_block_n(int64_t M, int64_t N, int64_t batch, int sm_count) {
+  // Largest N-tile that still gives every SM a tile; wide tiles halve the shared-memory
+  // traffic per flop, narrow ones keep skinny (weight-streaming) problems spread over the chip.
+  const int64_t tiles_m = (M + kBlockM - 1) / kBlockM;
+  for (int bn : {256, 128}) {
+    const int64_t tiles = tiles_m * ((N + bn - 1) / bn) * batch;
+    if (tiles >= sm_count) return bn;
+  }
+  return 64;
+}
+
+int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
+  const int es = p.fp8 ? 1 : 2;
+  const int slab_elems = kSlabBytes / es;
+  int bn = p.force_block_n > 0 ? p.force_block_n : pick_block_n(p.M, p.N, p.batch, dev.sm_count);
+  if (bn != 64 && bn != 128 && bn != 256) return fail(IXK_INVALID_ARGUMENT, "block_n must be 64, 128 or 256");
+
+  const CUtensorMapDataType dt = p.fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                       : (p.ab_dtype == IXK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  // A is [M,K]: K-major when K is contiguous.  B is [K,N]: MN-major when N is contiguous.
+  auto make_map = [&](CUtensorMap* out, const void* base, bool mn_major, int64_t mn, int64_t ld,
+                      int64_t batch_stride, int block_mn) -> int {
+    TmapSpec s{};
+    s.dtype = dt;
+    s.rank = 3;
+    s.swizzle128 = true;
+    if (mn_major) {
+      s.dims[0] = mn;
+      s.dims[1] = p.K;
+      s.box[0] = slab_elems;  // 128 bytes of M/N
+      s.box[1] = slab_elems;  // k rows of one stage
+    } else {
+      s.dims[0] = p.K;
+      s.dims[1] = mn;
+      s.box[0] = slab_elems;
+      s.box[1] = block_mn;
+    }
+    s.dims[2] = p.batch;
+    s.box[2] = 1;
+    s.strides_bytes[0] = static_cast<uint64_t>(ld) * es;
+    // A batch of one still needs a legal (16-byte multiple, non-zero) stride.
+    s.strides_bytes[1] = p.batch > 1 ? static_cast<uint64_t>(batch_stride) * es
+                                     : s.strides_bytes[0] * s.dims[1];
+    return encode_tmap(out, base, s);
+  };
+  CUtensorMap ta, tb;
+  int rc = make_map(&ta, p.a, p.a_mn_major, p.M, p.lda, p.a_batch_stride, kBlockM);
+  if (rc != IXK_OK) return rc;
+  rc = make_map(&tb, p.b, p.b_mn_major, p.N, p.ldb, p.b_batch_stride, bn);
+  if (rc != IXK_OK) return rc;
+
+  KernelArgs k{};
+  k.M = static_cast<int>(p.M);
+  k.N = static_cast<int>(p.N);
+  k.K = static_cast<int>(p.K);
+  k.batch = static_cast<int>(p.batch);
+  k.tiles_m = static_cast<int>((p.M + kBlockM - 1) / kBlockM);
+  k.tiles_n = static_cast<int>((p.N + bn - 1) / bn);
+  k.a_mn_major = p.a_mn_major;
+  k.b_mn_major = p.b_mn_major;
+  k.idesc = ptx::umma_idesc(p.a_fmt, p.b_fmt, p.a_mn_major ? 1 : 0, p.b_mn_major ? 1 : 0, kBlockM, bn);
+  k.bias = p.bias;
+  k.c = (p.beta != 0.0f) ? p.c : nullptr;
+  k.d = p.d;
+  k.ldd = p.ldd;
+  k.ldc = p.ldc;
+  k.d_batch_stride = p.d_batch_stride;
+  k.c_batch_stride = p.c_batch_stride;
+  k.out_dtype = p.out_dtype;
+  k.bias_dtype = p.bias_dtype;
+  k.act = p.act;
+  k.acc_scale = p.acc_scale;
+  k.beta = p.beta;
+  k.status_word = dev.status_word;
+  const int out_es = p.out_dtype == IXK_F32 ? 4 : 2;
+  const int bias_es = p.bias_dtype == IXK_F32 ? 4 : 2;
+  auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+  k.d_vec_ok = aligned16(p.d) && (p.ldd * out_es) % 16 == 0 && (p.d_batch_stride * out_es) % 16 == 0;
+  k.c_vec_ok = k.c && aligned16(p.c) && (p.ldc * out_es) % 16 == 0 && (p.c_batch_stride * out_es) % 16 == 0;
+  k.bias_vec_ok = p.bias && aligned16(p.bias);
+  (void)bias_es;
+
+  const int64_t tiles = static_cast<int64_t>(k.tiles_m) * k.tiles_n * k.batch;
+  const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
+  if (p.fp8) {
+    if (bn == 256) return launch_one<256, true>(ta, tb, k, grid, stream);
+    if (bn == 128) return launch_one<128, true>(ta, tb, k, grid, stream);
+    return launch_one<64, true>(ta, tb, k, grid, stream);
+  }
+  if (bn == 256) return launch_one<256, false>(ta, tb, k, grid, stream);
+  if (bn == 128) return launch_one<128, false>(ta, tb, k, grid, stream);
+  return launch_one<64, false>(ta, tb, k, grid, stream);
+}
+
+}  // namespace gemm
+}  // namespace ixk

@@ -1,0 +1,56 @@
+// Interface between the GEMM entry points (validation, normalisation) and the
+// tcgen05 kernel launcher.
+#pragma once
+
+#include "host_common.h"
+
+namespace ixk {
+namespace gemm {
+
+enum : int { kActNone = 0, kActRelu = 1, kActGelu = 2 };
+
+// A GEMM after normalisation: D is row-major [M,N]; A is [M,K], B is [K,N], each with
+// either dimension contiguous.
+struct Problem {
+  int64_t M = 0, N = 0, K = 0, batch = 1;
+  bool fp8 = false;
+  int ab_dtype = IXK_BF16;  // 16-bit operand type when !fp8
+  uint32_t a_fmt = 0, b_fmt = 0;  // tcgen05 operand format codes
+  bool a_mn_major = false;  // A stored with M contiguous (column-major A)
+  bool b_mn_major = false;  // B stored with N contiguous (row-major B)
+  const void* a = nullptr;
+  const void* b = nullptr;
+  int64_t lda = 0, ldb = 0, a_batch_stride = 0, b_batch_stride = 0;
+  const void* c = nullptr;
+  const void* bias = nullptr;
+  void* d = nullptr;
+  int64_t ldc = 0, ldd = 0, c_batch_stride = 0, d_batch_stride = 0;
+  int out_dtype = IXK_BF16;
+  int bias_dtype = IXK_BF16;
+  int act = kActNone;
+  float acc_scale = 1.0f;
+  float beta = 0.0f;
+  int force_block_n = 0;  // tuning override; 0 = heuristic
+};
+
+// Kernel parameter block (passed by value).
+struct KernelArgs {
+  int M, N, K, batch;
+  int tiles_m, tiles_n;
+  int a_mn_major, b_mn_major;
+  uint32_t idesc;
+  const void* bias;
+  const void* c;
+  void* d;
+  int64_t ldd, ldc, d_batch_stride, c_batch_stride;
+  int out_dtype, bias_dtype, act;
+  float acc_scale, beta;
+  int d_vec_ok, c_vec_ok, bias_vec_ok;
+  int* status_word;
+};
+
+int pick_block_n(int64_t M, int64_t N, int64_t batch, int sm_count);
+int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream);
+
+}  // namespace gemm
+}  // namespace ixk

@@ -1,0 +1,128 @@
+"""CPU: libixk.so loads without a GPU, exports every symbol include/ixk.h declares, and its
+structs have the layout the Python mirror assumes.  No compute call is made."""
+import ctypes
+import os
+import re
+import subprocess
+import sys
+import tempfile
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "ixk.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ixk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_functions_are_all_bound_and_exported(pkg):
+    names = declared_functions()
+    assert len(names) >= 10
+    lib = ctypes.CDLL(pkg.library_path())
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in ixk.h but not exported"
+    assert sorted(pkg.ABI_SYMBOLS) == names, "python mirror and header disagree"
+
+
+def test_struct_layout_matches_c(pkg):
+    """Compile a probe with the real header and compare sizeof/offsetof with ctypes."""
+    src = r'''
+#include <stdio.h>
+#include <stddef.h>
+#include "ixk.h"
+int main(void) {
+  printf("%zu %zu %zu\n", sizeof(ixk_matrix_layout), sizeof(ixk_gemm_desc), sizeof(ixk_fmha_desc));
+  printf("%zu %zu %zu %zu\n", offsetof(ixk_gemm_desc, output), offsetof(ixk_gemm_desc, batch_size),
+         offsetof(ixk_gemm_desc, beta), offsetof(ixk_gemm_desc, epilogue));
+  printf("%zu %zu %zu\n", offsetof(ixk_fmha_desc, head_scale), offsetof(ixk_fmha_desc, q_strides),
+         offsetof(ixk_fmha_desc, bias_strides));
+  return 0;
+}
+'''
+    with tempfile.TemporaryDirectory() as d:
+        c = os.path.join(d, "probe.c")
+        exe = os.path.join(d, "probe")
+        open(c, "w").write(src)
+        subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), c, "-o", exe],
+                       check=True)
+        out = subprocess.run([exe], check=True, capture_output=True, text=True).stdout.split()
+    got = [int(x) for x in out]
+    G, F = pkg._GemmDesc, pkg._FmhaDesc
+    want = [ctypes.sizeof(pkg._MatrixLayout), ctypes.sizeof(G), ctypes.sizeof(F),
+            G.output.offset, G.batch_size.offset, G.beta.offset, G.epilogue.offset,
+            F.head_scale.offset, F.q_strides.offset, F.bias_strides.offset]
+    assert got == want
+
+
+def test_status_strings_and_version(pkg):
+    lib = pkg.load_library()
+    names = [lib.ixk_status_string(i).decode() for i in range(7)]
+    assert names == ["OK", "INVALID_ARGUMENT", "UNIMPLEMENTED", "WORKSPACE_TOO_SMALL", "CUDA_ERROR", "NO_DEVICE",
+                     "DEVICE_TIMEOUT"]
+    assert lib.ixk_status_string(99).decode() == "UNKNOWN"
+    assert re.fullmatch(r"\d+\.\d+\.\d+", pkg.version())
+
+
+def test_workspace_queries_need_no_gpu(pkg):
+    lib = pkg.load_library()
+    d = pkg._FmhaDesc()
+    d.dtype, d.num_batches, d.num_heads, d.head_size, d.num_queries, d.num_keys = 0, 64, 16, 256, 1, 4096
+    # decode: ceil(16*148 / 1024) = 3 key splits, each a partial of (H + 2) floats per row
+    assert lib.ixk_fmha_fwd_workspace_bytes(ctypes.byref(d)) == 3 * 64 * 16 * 1 * 258 * 4
+    d.num_queries = 2048  # prefill keeps everything on chip
+    assert lib.ixk_fmha_fwd_workspace_bytes(ctypes.byref(d)) == 0
+    assert lib.ixk_gemm_workspace_bytes(None) == 0
+
+
+def test_argument_errors_come_back_as_codes_not_aborts(pkg):
+    """Validation happens on the host before any launch (the reference CHECK-aborts instead,
+    xetla_gpu_fused_mha_runner.cc:114-116)."""
+    lib = pkg.load_library()
+    assert lib.ixk_gemm(None, None, None, None, None, None, None, 0, None) == pkg.IXK_INVALID_ARGUMENT
+    assert b"desc is NULL" in lib.ixk_last_error()
+    g = pkg._GemmDesc()
+    g.batch_size, g.alpha, g.epilogue = 1, 1.0, 6  # GELU_AUX
+    assert lib.ixk_gemm(ctypes.byref(g), None, None, None, None, None, None, 0, None) == pkg.IXK_UNIMPLEMENTED
+    g.epilogue = 42
+    assert lib.ixk_gemm(ctypes.byref(g), None, None, None, None, None, None, 0, None) == pkg.IXK_INVALID_ARGUMENT
+    g.epilogue, g.alpha = 0, 2.0
+    assert lib.ixk_gemm(ctypes.byref(g), None, None, None, None, None, None, 0, None) == pkg.IXK_UNIMPLEMENTED
+    f = pkg._FmhaDesc()
+    f.dtype, f.dropout_prob = 0, 0.1
+    assert lib.ixk_fmha_fwd(ctypes.byref(f), None, None, None, None, None, None, None, 0, None) == pkg.IXK_UNIMPLEMENTED
+    assert b"dropout" in lib.ixk_last_error()
+    f.dropout_prob, f.head_size = 0.0, 512
+    assert lib.ixk_fmha_fwd(ctypes.byref(f), None, None, None, None, None, None, None, 0, None) == pkg.IXK_UNIMPLEMENTED
+    f.head_size, f.dtype = 64, 2  # F32
+    assert lib.ixk_fmha_fwd(ctypes.byref(f), None, None, None, None, None, None, None, 0, None) == pkg.IXK_UNIMPLEMENTED
+
+
+def test_missing_library_fails_loudly(pkg, monkeypatch):
+    """No silent fallback: without libixk.so the package raises."""
+    monkeypatch.setattr(pkg, "_LIB", None)
+    monkeypatch.setattr(pkg, "library_path", lambda: "/nonexistent/libixk.so")
+    with pytest.raises(pkg.IxkError, match="no CPU fallback"):
+        pkg.load_library()
+
+
+def test_cpu_tensors_are_rejected(pkg):
+    import torch
+    x = torch.zeros(8, 8, dtype=torch.bfloat16)
+    with pytest.raises(pkg.IxkError, match="no CPU path"):
+        pkg.gemm(x, x)
+    q = torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16)
+    with pytest.raises(pkg.IxkError, match="no CPU path"):
+        pkg.fmha_forward_kernel(None, q, q, q, None, None, 0.0, q.clone(), None, 1.0, False)
+
+
+def test_oracle_is_not_imported_by_the_product(pkg):
+    """The package must not reach into oracle/ (the oracle is test infrastructure)."""
+    pkg_dir = os.path.dirname(pkg.__file__)
+    for dirpath, _, files in os.walk(pkg_dir):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                assert "oracle" not in open(os.path.join(dirpath, f)).read().lower(), f
