@@ -413,6 +413,9 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   const int slab_elems = kSlabBytes / es;
   int bn = p.force_block_n > 0 ? p.force_block_n : pick_block_n(p.M, p.N, p.batch, dev.sm_count);
   if (bn != 64 && bn != 128 && bn != 256) return fail(IXK_INVALID_ARGUMENT, "block_n must be 64, 128 or 256");
+  // An MN-major 8-bit B tile is loaded in 128-column boxes (one swizzle span), so it cannot be
+  // narrower than 128 columns.
+  if (p.fp8 && p.b_mn_major && bn < 128) bn = 128;
 
   const CUtensorMapDataType dt = p.fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                        : (p.ab_dtype == IXK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
