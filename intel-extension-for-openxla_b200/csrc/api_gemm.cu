@@ -86,8 +86,6 @@ int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, 
     return fail(IXK_UNIMPLEMENTED, "alpha must be 1 (onednn_matmul_utils.cc:438 CHECKs the same)");
   const bool has_c = desc->beta != 0.0f;
   if (has_c && c == nullptr) return fail(IXK_INVALID_ARGUMENT, "beta != 0 needs the C operand");
-  if (a == nullptr || b == nullptr || d == nullptr)
-    return fail(IXK_INVALID_ARGUMENT, "a, b and d must be non-NULL");
 
   // Type triples of RunGemm's TYPED_GEMM list (onednn_matmul_utils.cc:605-610) that the
   // tensor-core kernel covers, plus the fp8 operand kinds of the scaled GEMM.
@@ -134,7 +132,9 @@ int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, 
   if (lhs_m != p.M || rhs_n != p.N || rhs_k != p.K)
     return fail(IXK_INVALID_ARGUMENT, "lhs [M,K], rhs [K,N] and output [M,N] shapes do not agree");
   p.batch = desc->batch_size;
-  if (p.M == 0 || p.N == 0) return IXK_OK;
+  if (p.M == 0 || p.N == 0) return IXK_OK;  // nothing to write; pointers may be NULL
+  if (a == nullptr || b == nullptr || d == nullptr)
+    return fail(IXK_INVALID_ARGUMENT, "a, b and d must be non-NULL");
   if (p.K == 0) return fail(IXK_UNIMPLEMENTED, "K == 0 is not supported");
   if (p.M > INT32_MAX || p.N > INT32_MAX || p.K > INT32_MAX)
     return fail(IXK_UNIMPLEMENTED, "dimensions above 2^31-1 are not supported");
