@@ -20,6 +20,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "fmha_sm100.h"
 #include "ptx.cuh"
 
@@ -81,7 +83,7 @@ __device__ __forceinline__ float unpack_hi(uint32_t w, bool bf16) {
   return bf16 ? __uint_as_float(w & 0xffff0000u) : __half2float(__ushort_as_half(static_cast<uint16_t>(w >> 16)));
 }
 
-template <int kHeadDim, int kQTiles>
+template <int kHeadDim, int kQTiles, int kPolyOf4>
 __global__ void __launch_bounds__(kThreads, 1)
 fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const KernelArgs args) {
@@ -283,13 +285,17 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32(s_addr + c * 32, r[c]);
         ptx::tmem_ld_wait();
         const int kv0 = j * kBlockKV;
-        // x = s * scale * log2(e) (+ bias * log2(e))
+        // Scores enter the exponential as x = r * mult - m.  Fast path: r is the raw Q.K^T and
+        // mult = head_scale * log2(e) (> 0, so the row maximum can be taken on r).  With a bias
+        // or a non-positive scale, r is first rewritten as the full log2-domain score and mult = 1.
+        float mult = args.scale_log2;
+        if (args.bias != nullptr || !(args.scale_log2 > 0.0f)) {
+          mult = 1.0f;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 4; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__uint_as_float(r[c][i]) * args.scale_log2);
-        }
-        if (args.bias != nullptr) {
+            for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__uint_as_float(r[c][i]) * args.scale_log2);
+          }
           if (bias_row != nullptr) {
             const uint16_t* bp = bias_row + kv0;
             const int count = min(kBlockKV, args.T - kv0);
@@ -336,12 +342,16 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
               if (c * 32 + i >= limit) r[c][i] = 0xff800000u;  // -inf
           }
         }
-        float mx = -INFINITY;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[c][i]));
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = ptx::max3(mx0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+            mx1 = ptx::max3(mx1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
+          }
         }
+        const float mx = fmaxf(mx0, mx1) * mult;
         float alpha = 1.0f;
         if (mx - m_run > kRescaleThreshold) {  // also true on the first block (m_run = -inf)
           alpha = ptx::ex2_approx(m_run - mx);  // 0 on the first block
@@ -349,22 +359,36 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
         // Rows that are entirely masked so far keep m_run = -inf; use 0 to avoid inf - inf.
         const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
-        float sum = 0.0f;
+        const uint64_t mult2 = ptx::f32x2(mult, mult);
+        const uint64_t negm2 = ptx::f32x2(-m_use, -m_use);
+        uint64_t sum_a = ptx::f32x2(0.0f, 0.0f), sum_b = ptx::f32x2(0.0f, 0.0f);
         // P (16-bit pairs) overwrites the first 64 columns of this tile's S: the 32 scores of
         // chunk c become 16 packed columns at [16 c, 16 c + 16), already read by this thread.
+        // Of every four pairs, kPolyOf4 take their 2^x from the FMA pipe, the rest from the
+        // special-function unit, so that neither pipe alone bounds the softmax.
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float p0 = ptx::ex2_approx(__uint_as_float(r[c][i]) - m_use);
-            const float p1 = ptx::ex2_approx(__uint_as_float(r[c][i + 1]) - m_use);
-            sum += p0 + p1;
+            const uint64_t x2 = ptx::fma2(ptx::f32x2(__uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1])), mult2, negm2);
+            float x0, x1, p0, p1;
+            ptx::f32x2_split(x2, x0, x1);
+            if (((i >> 1) & 3) < kPolyOf4) {
+              ptx::ex2_poly2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f), p0, p1);
+              sum_b = ptx::add2(sum_b, ptx::f32x2(p0, p1));
+            } else {
+              p0 = ptx::ex2_approx(x0);
+              p1 = ptx::ex2_approx(x1);
+              sum_a = ptx::add2(sum_a, ptx::f32x2(p0, p1));
+            }
             pk[i >> 1] = pack2(p0, p1, bf16);
           }
           ptx::tmem_st_32x16(s_addr + c * 16, pk);
         }
-        l_run = l_run * alpha + sum;
+        float s0, s1;
+        ptx::f32x2_split(ptx::add2(sum_a, sum_b), s0, s1);
+        l_run = l_run * alpha + (s0 + s1);
         // Rescale O when any row of the warp raised its maximum.  s_full(j) was committed after
         // P.V of block j-1, so O is quiescent here.
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
@@ -430,7 +454,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   }
 }
 
-template <int kHeadDim, int kQTiles>
+template <int kHeadDim, int kQTiles, int kPolyOf4>
 int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   using C = Cfg<kHeadDim, kQTiles>;
   const CUtensorMapDataType dt = p.dtype == IXK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -487,7 +511,7 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   a.bias_vec_ok = bias_vec ? 1 : 0;
   a.out_vec_ok = out_vec ? 1 : 0;
 
-  auto* fn = &fmha_prefill_kernel<kHeadDim, kQTiles>;
+  auto* fn = &fmha_prefill_kernel<kHeadDim, kQTiles, kPolyOf4>;
   static thread_local int configured_device = -1;
   if (configured_device != dev.device) {
     IXK_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
@@ -506,9 +530,22 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
 int launch_prefill(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   if (p.N > 65535 || p.B > 65535) return fail(IXK_UNIMPLEMENTED, "num_heads and num_batches must be <= 65535");
   // Head-size buckets follow the reference's policy pick (fmha_forward.h:621-646): <=64, <=128, <=256.
-  if (p.H <= 64) return p.F > kBlockQ ? launch_cfg<64, 2>(p, dev, stream) : launch_cfg<64, 1>(p, dev, stream);
-  if (p.H <= 128) return p.F > kBlockQ ? launch_cfg<128, 2>(p, dev, stream) : launch_cfg<128, 1>(p, dev, stream);
-  return launch_cfg<256, 1>(p, dev, stream);
+  constexpr int kPoly = 2;  // pairs of every four whose 2^x runs on the FMA pipe
+  if (p.H <= 64) return p.F > kBlockQ ? launch_cfg<64, 2, kPoly>(p, dev, stream) : launch_cfg<64, 1, kPoly>(p, dev, stream);
+  if (p.H <= 128) {
+    if (p.F <= kBlockQ) return launch_cfg<128, 1, kPoly>(p, dev, stream);
+    // Tuning override for the main configuration: IXK_FMHA_POLY = 0..3.
+    if (const char* env = std::getenv("IXK_FMHA_POLY")) {
+      switch (std::atoi(env)) {
+        case 0: return launch_cfg<128, 2, 0>(p, dev, stream);
+        case 1: return launch_cfg<128, 2, 1>(p, dev, stream);
+        case 3: return launch_cfg<128, 2, 3>(p, dev, stream);
+        default: break;
+      }
+    }
+    return launch_cfg<128, 2, kPoly>(p, dev, stream);
+  }
+  return launch_cfg<256, 1, kPoly>(p, dev, stream);
 }
 
 }  // namespace fmha

@@ -270,6 +270,56 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt, uint32_t b_fmt
          ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+// ---------------------------------------------------------------- packed fp32 math
+// sm_100 issues two fp32 operations per instruction on a register pair.
+__device__ __forceinline__ uint64_t f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f32x2_split(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// 2^x for a pair, on the FMA pipe instead of the special-function unit: x = n + f with
+// n = round(x), |f| <= 1/2; 2^f by a degree-3 minimax polynomial (relative error 7.5e-5, well
+// inside the 2^-9 of a 16-bit P); 2^n by adding n to the exponent field.  Inputs must be
+// >= -126 (callers clamp) and below 127.
+__device__ __forceinline__ void ex2_poly2(float x0, float x1, float& y0, float& y1) {
+  const uint64_t magic = f32x2(12582912.0f, 12582912.0f);  // 1.5 * 2^23: the add rounds to an integer
+  const uint64_t x = f32x2(x0, x1);
+  const uint64_t xr = add2(x, magic);
+  const uint64_t f = sub2(x, sub2(xr, magic));
+  uint64_t p = fma2(f, f32x2(0.0551716685f, 0.0551716685f), f32x2(0.242611125f, 0.242611125f));
+  p = fma2(p, f, f32x2(0.693260968f, 0.693260968f));
+  p = fma2(p, f, f32x2(0.999928057f, 0.999928057f));
+  float p0, p1, r0, r1;
+  f32x2_split(p, p0, p1);
+  f32x2_split(xr, r0, r1);
+  y0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(r0) << 23));
+  y1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(r1) << 23));
+}
+
 // ---------------------------------------------------------------- misc math
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
