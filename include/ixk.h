@@ -168,6 +168,29 @@ int ixk_fmha_fwd(const ixk_fmha_desc* desc, const void* q, const void* k,
                  void* workspace, size_t workspace_bytes, void* cuda_stream);
 size_t ixk_fmha_fwd_workspace_bytes(const ixk_fmha_desc* desc);
 
+/* Attention forward for callers that can neither pass scratch memory nor allocate any.
+ * No counterpart in the reference (its runner always receives scratch from XLA's buffer
+ * assignment, xetla_gpu_fused_mha_runner.h:36-41); added for hosts where that is not so: a
+ * custom-call handler bound without a scratch allocator, or a process whose framework has already
+ * reserved HBM for its own pool so that a library-side cudaMalloc would fail or stall the device.
+ *
+ * Same arguments and results as ixk_fmha_fwd, minus the workspace: the split-key decode path
+ * keeps its partial results in an array of IXK_STATIC_SCRATCH_BYTES that is part of the library's
+ * device image (each GPU that loads libixk.so holds that much memory until the process exits).
+ * The call allocates nothing and frees nothing.
+ *   - A problem whose ixk_fmha_fwd_workspace_bytes(desc) exceeds IXK_STATIC_SCRATCH_BYTES is
+ *     refused with IXK_WORKSPACE_TOO_SMALL and nothing is launched; use ixk_fmha_fwd then.
+ *   - The first call on each device looks up the array's device address (a host-side query, no
+ *     allocation).  Make that first call outside any stream capture.
+ *   - All calls on a device share the one array, which still holds the previous call's partials:
+ *     the kernels overwrite every element they later read, so nothing needs clearing, but two
+ *     calls that may overlap on the GPU (different streams, no ordering between them) race on it.
+ *     Order them, or give the concurrent ones their own workspace through ixk_fmha_fwd. */
+#define IXK_STATIC_SCRATCH_BYTES (4u << 20)
+int ixk_fmha_fwd_static_scratch(const ixk_fmha_desc* desc, const void* q, const void* k,
+                                const void* v, const void* bias, void* out, float* lse,
+                                void* cuda_stream);
+
 /* ------------------------------------------------------------ diagnostics */
 /* Every device-side wait in the tensor-core kernels is bounded; a wait that
  * gives up records a code in a per-device status word and the kernel drains and

@@ -23,6 +23,7 @@ __all__ = [
     "IxkError", "library_path", "load_library", "version", "launch_count", "device_status",
     "EPILOGUES", "run_gemm_custom_call", "gemm_attrs_for", "gemm", "gemm_fp8",
     "fmha_forward_kernel", "fmha_forward_kernel_bf16", "fmha_forward_kernel_fp16", "fmha_workspace_bytes",
+    "fmha_forward_kernel_static_scratch", "STATIC_SCRATCH_BYTES",
     "quantize_fp8",
 ]
 
@@ -84,6 +85,7 @@ ABI_SYMBOLS = {
                                     ctypes.c_float, _vp, _sz, _vp]),
     "ixk_fmha_fwd": (ctypes.c_int, [ctypes.POINTER(_FmhaDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "ixk_fmha_fwd_workspace_bytes": (_sz, [ctypes.POINTER(_FmhaDesc)]),
+    "ixk_fmha_fwd_static_scratch": (ctypes.c_int, [ctypes.POINTER(_FmhaDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ixk_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
     "ixk_launch_count": (ctypes.c_uint64, []),
 }
@@ -317,6 +319,25 @@ def fmha_forward_kernel(stream, query: torch.Tensor, key: torch.Tensor, value: t
     ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     st = lib.ixk_fmha_fwd(ctypes.byref(d), _ptr(query), _ptr(key), _ptr(value), _ptr(bias), _ptr(out),
                           _ptr(activation if is_training else None), _ptr(workspace), ws_bytes, _stream_ptr(stream))
+    _check(st)
+
+
+STATIC_SCRATCH_BYTES = 4 << 20  # IXK_STATIC_SCRATCH_BYTES in include/ixk.h
+
+
+def fmha_forward_kernel_static_scratch(stream, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                                       bias: Optional[torch.Tensor], out: torch.Tensor,
+                                       activation: Optional[torch.Tensor], head_scale: float, *,
+                                       causal: bool = False) -> None:
+    """fmha_forward_kernel for a caller that cannot provide (or allocate) scratch memory: the
+    decode path's partial results go to a fixed array inside the library instead
+    (ixk_fmha_fwd_static_scratch).  Nothing is allocated here either — not even through torch.
+    Problems needing more than STATIC_SCRATCH_BYTES raise IxkError(WORKSPACE_TOO_SMALL).  Calls on
+    one device share that array: do not let two of them overlap on the GPU."""
+    _require_cuda(query, key, value, bias, out, activation)
+    d = _fmha_desc(query, key, value, bias, out, head_scale, causal, 0.0)
+    st = load_library().ixk_fmha_fwd_static_scratch(ctypes.byref(d), _ptr(query), _ptr(key), _ptr(value), _ptr(bias),
+                                                    _ptr(out), _ptr(activation), _stream_ptr(stream))
     _check(st)
 
 
