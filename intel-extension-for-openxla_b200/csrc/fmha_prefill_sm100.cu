@@ -6,14 +6,21 @@
 // XeTLA kernel keeps Q in shared local memory, re-normalises P on every key block and reduces
 // rows across sub-groups through shared memory, this one is built on the Blackwell units:
 //
-//   warp 0        TMA producer: Q once, then K_0, V_0, K_1, V_1 ... through a shared-memory ring
-//   warp 1        tcgen05.mma issuer:  S_t = Q_t.K_j^T  (A, B from shared memory, S in TMEM)
+//   warps 0-3     softmax for query tile 0: one thread owns one row of S (a TMEM lane), so
+//   warps 4-7     softmax for query tile 1  row max / row sum need no cross-thread traffic
+//   warp 8        TMA producer: Q per work item, then K_0, V_0, K_1, V_1 ... through a shared-memory ring
+//   warp 9        tcgen05.mma issuer (one thread, polling both tiles' hand-over barriers and serving
+//                 whichever is ready):  S_t = Q_t.K_j^T  (A, B from shared memory, S in TMEM)
 //                                      O_t += P_t.V_j   (A = P from TMEM, B = V from shared memory)
-//   warps 4-7     softmax for query tile 0: one thread owns one row of S (a TMEM lane), so
-//   warps 8-11    softmax for query tile 1  row max / row sum need no cross-thread traffic
+// The two softmax warpgroups take 216 registers per thread (a whole row of S lives in registers),
+// the control warpgroup gives its share up (setmaxnreg).
 //
-// A CTA carries kQTiles tiles of 128 query rows; with two tiles the tensor core works on one
-// tile's S / P.V while the other tile's softmax runs.  P overwrites S in place in TMEM as
+// CTAs are persistent: each walks a static list of (batch, head, query block) work items, heaviest
+// first, and every barrier keeps counting across items, so the loads and the first S of the next
+// item are issued while the current item's last softmax and its epilogue still run.
+// A work item carries kQTiles tiles of 128 query rows; with two tiles the tensor core works on one
+// tile's S / P.V while the other tile's softmax runs.  P is handed to the MMA issuer in four quarters
+// so that P.V starts on the first 32 keys while the rest is still being exponentiated.  P overwrites S in place in TMEM as
 // packed 16-bit pairs.  The running maximum is only raised when it moved by more than 2^8
 // (exact: the same stale maximum scales P, the row sum and O), which keeps the O rescale off
 // the common path.  exp is evaluated as exp2 with head_scale*log2(e) folded in.
@@ -34,12 +41,18 @@ constexpr int kBlockQ = 128;   // query rows per tile (= TMEM lanes)
 constexpr int kBlockKV = 128;  // keys per block
 constexpr int kChunkElems = 64;                       // 16-bit elements per 128-byte swizzle row
 constexpr int kChunkBytes = kBlockKV * 128;           // one 128-row x 128-byte box
-constexpr int kThreads = 384;
+constexpr int kThreads = 384;  // warpgroups: softmax tile 0, softmax tile 1, {producer, MMA issuer, 2 idle}
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kParts = 2;  // pieces in which a block of P is handed to the MMA issuer (1, 2 or 4)
+constexpr int kSoftmaxRegs = 216;  // per-thread register budgets after re-partitioning
+constexpr int kControlRegs = 64;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
-enum : int { kSiteLoad = 201, kSiteMmaQ = 202, kSiteMmaKV = 203, kSiteMmaP = 204, kSiteSoftmaxS = 205, kSiteEpilogueO = 206 };
+enum : int { kSiteLoad = 201, kSiteMmaQ = 202, kSiteMmaKV = 203, kSiteMmaP = 204, kSiteSoftmaxS = 205, kSiteEpilogueO = 206,
+              kSiteLoadQ = 207, kSiteMmaO = 208 };
 
 template <int kHeadDim, int kQTiles>
 struct Cfg {
@@ -66,6 +79,8 @@ struct KernelArgs {
   int out_vec_ok;
   float* lse;
   int* status_word;
+  int num_qblocks;  // query blocks of kBlockQ * kQTiles rows per (batch, head)
+  int num_items;    // num_qblocks * N * B
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
@@ -83,6 +98,95 @@ __device__ __forceinline__ float unpack_hi(uint32_t w, bool bf16) {
   return bf16 ? __uint_as_float(w & 0xffff0000u) : __half2float(__ushort_as_half(static_cast<uint16_t>(w >> 16)));
 }
 
+// Optional self-timing (compiled in only with -DIXK_FMHA_TRACE, for pipeline studies): CTA 0
+// stamps clock64() at the hand-over points of its first work item into a device array that
+// ixk_debug_fmha_trace() copies out.
+#ifdef IXK_FMHA_TRACE
+__device__ long long g_fmha_trace[9 * 32 * 8];
+#define IXK_TRACE(kind, j, ev)                                                              \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && (j) < 32 && trace_on) g_fmha_trace[((kind)*32 + (j)) * 8 + (ev)] = clock64(); \
+  } while (0)
+#else
+#define IXK_TRACE(kind, j, ev) \
+  do {                         \
+  } while (0)
+#endif
+
+// One unit of work: a (batch, head, query block) triple and how many key blocks each of its
+// query tiles visits.
+struct Item {
+  int q0, head, batch;
+  int nblk[2];
+  int nblk_max;
+};
+
+template <int kQTiles>
+__device__ __forceinline__ Item get_item(const KernelArgs& args, int w) {
+  // Items are ordered heaviest first: under a causal mask the last query block sees the most keys.
+  const int pairs = args.N * args.B;
+  const int rank = w / pairs;
+  const int rest = w - rank * pairs;
+  Item it;
+  it.head = rest % args.N;
+  it.batch = rest / args.N;
+  const int qb = args.causal ? (args.num_qblocks - 1 - rank) : rank;
+  it.q0 = qb * (kBlockQ * kQTiles);
+  const int kv_blocks_all = (args.T + kBlockKV - 1) / kBlockKV;
+  it.nblk[0] = it.nblk[1] = 0;
+#pragma unroll
+  for (int t = 0; t < kQTiles; ++t) {
+    const int row0 = it.q0 + t * kBlockQ;
+    if (row0 < args.F) {
+      int n = kv_blocks_all;
+      if (args.causal) n = min(n, (row0 + kBlockQ - 1) / kBlockKV + 1);
+      it.nblk[t] = n;
+    }
+  }
+  it.nblk_max = max(it.nblk[0], it.nblk[1]);
+  return it;
+}
+
+// The i-th work item of a CTA.  Items are dealt in rounds of gridDim.x, alternating direction
+// (0..G-1, then G-1..0, ...), so that a CTA that drew a heavy item in one round draws a light one
+// in the next: with items sorted by weight this keeps the per-CTA totals within a few percent.
+__device__ __forceinline__ int item_of(uint32_t round) {
+  const int g = static_cast<int>(gridDim.x);
+  const int c = static_cast<int>(blockIdx.x);
+  return static_cast<int>(round) * g + ((round & 1u) ? (g - 1 - c) : c);
+}
+
+// tcgen05.mma with the shared-memory descriptors passed as (lo, hi) halves: the high half is a
+// per-operand constant and the low half is a base plus a compile-time offset, which keeps the
+// single issuing thread at a handful of instructions per MMA.
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 template <int kHeadDim, int kQTiles, int kPolyOf4>
 __global__ void __launch_bounds__(kThreads, 1)
 fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -96,14 +200,16 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t q_smem = smem_base;
   const uint32_t kv_smem = smem_base + C::kQBytes;
   const uint32_t bar_base = kv_smem + kSlots * C::kTileBytes;
-  // barriers: q_full, kv_full[kSlots], kv_empty[kSlots], s_full[2], p_ready[2], o_final[2]
+  // barriers (8 bytes each)
   const uint32_t q_full = bar_base;
-  auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bar_base + 8u * (1 + kSlots + s); };
-  auto s_full = [&](int t) { return bar_base + 8u * (1 + 2 * kSlots + t); };
-  auto p_ready = [&](int t) { return bar_base + 8u * (3 + 2 * kSlots + t); };
-  auto o_final = [&](int t) { return bar_base + 8u * (5 + 2 * kSlots + t); };
-  uint8_t* tail = smem_gen + C::kQBytes + kSlots * C::kTileBytes + 8 * (7 + 2 * kSlots);
+  const uint32_t q_empty = bar_base + 8u;
+  auto kv_full = [&](int s) { return bar_base + 8u * (2 + s); };
+  auto kv_empty = [&](int s) { return bar_base + 8u * (2 + kSlots + s); };
+  auto s_full = [&](int t) { return bar_base + 8u * (2 + 2 * kSlots + t); };
+  auto p_part = [&](int t, int quarter) { return bar_base + 8u * (4 + 2 * kSlots + t * 4 + quarter); };
+  auto o_final = [&](int t) { return bar_base + 8u * (12 + 2 * kSlots + t); };
+  auto o_free = [&](int t) { return bar_base + 8u * (14 + 2 * kSlots + t); };
+  uint8_t* tail = smem_gen + C::kQBytes + kSlots * C::kTileBytes + 8 * (16 + 2 * kSlots);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
@@ -111,42 +217,26 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int lane = threadIdx.x & 31;
   ptx::AbortCtl ctl{abort_flag, args.status_word};
 
-  // Heaviest query blocks (most visible keys under a causal mask) are scheduled first.
-  const int qb = gridDim.x - 1 - blockIdx.x;
-  const int head = blockIdx.y;
-  const int batch = blockIdx.z;
-  const int q0 = qb * (kBlockQ * kQTiles);
-  const int kv_blocks_all = (args.T + kBlockKV - 1) / kBlockKV;
-  int nblk[2] = {0, 0};
-#pragma unroll
-  for (int t = 0; t < kQTiles; ++t) {
-    const int row0 = q0 + t * kBlockQ;
-    if (row0 < args.F) {
-      int n = kv_blocks_all;
-      if (args.causal) n = min(n, (row0 + kBlockQ - 1) / kBlockKV + 1);
-      nblk[t] = n;
-    }
-  }
-  const int nblk_max = max(nblk[0], nblk[1]);
-
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     ptx::mbar_init(q_full, 1);
+    ptx::mbar_init(q_empty, kQTiles);  // every issuer releases Q and each K/V slot
     for (int s = 0; s < kSlots; ++s) {
       ptx::mbar_init(kv_full(s), 1);
-      ptx::mbar_init(kv_empty(s), 1);
+      ptx::mbar_init(kv_empty(s), kQTiles);
     }
     for (int t = 0; t < 2; ++t) {
       ptx::mbar_init(s_full(t), 1);
-      ptx::mbar_init(p_ready(t), 128);
+      for (int quarter = 0; quarter < 4; ++quarter) ptx::mbar_init(p_part(t, quarter), 128);
       ptx::mbar_init(o_final(t), 1);
+      ptx::mbar_init(o_free(t), 128);
     }
     ptx::fence_mbar_init();
     ptx::prefetch_tmap(&tmap_q);
     ptx::prefetch_tmap(&tmap_k);
     ptx::prefetch_tmap(&tmap_v);
   }
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
     ptx::tmem_relinquish();
   }
@@ -155,284 +245,383 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
+    ptx::setmaxnreg_dec<kControlRegs>();
     if (lane == 0) {
-      int valid_tiles = 0;
-      for (int t = 0; t < kQTiles; ++t) valid_tiles += nblk[t] > 0 ? 1 : 0;
-      ptx::mbar_expect_tx(q_full, valid_tiles * C::kTileBytes);
-      for (int t = 0; t < kQTiles; ++t) {
-        if (nblk[t] == 0) continue;
+      uint32_t load_idx = 0;  // position in the CTA-wide K_0, V_0, K_1, V_1, ... sequence
+      bool alive = true;
+      uint32_t it = 0;
+      for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
+        const Item item = get_item<kQTiles>(args, w);
+        if (!ptx::mbar_wait(q_empty, (it & 1u) ^ 1u, ctl, kSiteLoadQ)) break;
+        int valid_tiles = 0;
+        for (int t = 0; t < kQTiles; ++t) valid_tiles += item.nblk[t] > 0 ? 1 : 0;
+        ptx::mbar_expect_tx(q_full, valid_tiles * C::kTileBytes);
+        for (int t = 0; t < kQTiles; ++t) {
+          if (item.nblk[t] == 0) continue;
 #pragma unroll
-        for (int c = 0; c < C::kChunks; ++c)
-          ptx::tma_load_4d(q_smem + t * C::kTileBytes + c * kChunkBytes, &tmap_q, q_full, c * kChunkElems,
-                           q0 + t * kBlockQ, head, batch);
-      }
-      // load order: K_0, V_0, K_1, V_1, ...
-      const int loads = 2 * nblk_max;
-      for (int i = 0; i < loads; ++i) {
-        const int slot = i % kSlots;
-        const uint32_t use = i / kSlots;
-        if (!ptx::mbar_wait(kv_empty(slot), (use & 1u) ^ 1u, ctl, kSiteLoad)) break;
-        const int j = i >> 1;
-        const CUtensorMap* map = (i & 1) ? &tmap_v : &tmap_k;
-        ptx::mbar_expect_tx(kv_full(slot), C::kTileBytes);
+          for (int c = 0; c < C::kChunks; ++c)
+            ptx::tma_load_4d(q_smem + t * C::kTileBytes + c * kChunkBytes, &tmap_q, q_full, c * kChunkElems,
+                             item.q0 + t * kBlockQ, item.head, item.batch);
+        }
+        const int loads = 2 * item.nblk_max;
+        for (int i = 0; i < loads; ++i, ++load_idx) {
+          const int slot = load_idx % kSlots;
+          const uint32_t use = load_idx / kSlots;
+          if (!ptx::mbar_wait(kv_empty(slot), (use & 1u) ^ 1u, ctl, kSiteLoad)) {
+            alive = false;
+            break;
+          }
+          const CUtensorMap* map = (i & 1) ? &tmap_v : &tmap_k;
+          ptx::mbar_expect_tx(kv_full(slot), C::kTileBytes);
 #pragma unroll
-        for (int c = 0; c < C::kChunks; ++c)
-          ptx::tma_load_4d(kv_smem + slot * C::kTileBytes + c * kChunkBytes, map, kv_full(slot), c * kChunkElems,
-                           j * kBlockKV, head, batch);
+          for (int c = 0; c < C::kChunks; ++c)
+            ptx::tma_load_4d(kv_smem + slot * C::kTileBytes + c * kChunkBytes, map, kv_full(slot), c * kChunkElems,
+                             (i >> 1) * kBlockKV, item.head, item.batch);
+        }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && nblk_max > 0) {
+    ptx::setmaxnreg_dec<kControlRegs>();
+    if (lane == 0) {
       const uint32_t fmt = args.is_bf16 ? 1u : 0u;
       // S = Q.K^T : M=128, N=128 keys, both operands K-major (head dim contiguous)
       const uint32_t idesc_s = ptx::umma_idesc(fmt, fmt, 0, 0, kBlockQ, kBlockKV);
       // O += P.V  : M=128, N=kHeadDim, A = P in TMEM, B = V with the head dim contiguous (MN-major)
       const uint32_t idesc_o = ptx::umma_idesc(fmt, fmt, 0, 1, kBlockQ, kHeadDim);
+      // descriptor halves: K-major (Q, K): LBO 16 B (unused), SBO 1024 B; MN-major (V): LBO = one
+      // 128-byte column block of the tile, SBO 1024 B
+      const uint64_t kmajor = ptx::umma_smem_desc(0, 16, 1024);
+      const uint64_t mnmajor = ptx::umma_smem_desc(0, kChunkBytes, 1024);
+      const uint32_t k_lo = static_cast<uint32_t>(kmajor), k_hi = static_cast<uint32_t>(kmajor >> 32);
+      const uint32_t v_lo = static_cast<uint32_t>(mnmajor), v_hi = static_cast<uint32_t>(mnmajor >> 32);
       auto issue_s = [&](int t, int slot) {
-        const uint32_t qa = q_smem + t * C::kTileBytes;
-        const uint32_t kb = kv_smem + slot * C::kTileBytes;
+        const uint32_t qa = k_lo + ((q_smem + t * C::kTileBytes) >> 4);
+        const uint32_t kb = k_lo + ((kv_smem + slot * C::kTileBytes) >> 4);
+        const uint32_t d = tmem_base + C::kTmemS + t * 128;
 #pragma unroll
         for (int ks = 0; ks < kHeadDim / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * kChunkBytes + (ks & 3) * 32;
-          ptx::umma_ss<false>(tmem_base + C::kTmemS + t * 128, ptx::umma_smem_desc(qa + off, 16, 1024),
-                              ptx::umma_smem_desc(kb + off, 16, 1024), idesc_s, ks != 0 ? 1u : 0u);
+          const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
+          mma_ss(d, qa + off, k_hi, kb + off, k_hi, idesc_s, ks != 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int t, int slot, bool accumulate) {
-        const uint32_t vb = kv_smem + slot * C::kTileBytes;
+      // quarter q covers keys [32 q, 32 q + 32) of the block = P columns [16 q, 16 q + 16)
+      auto issue_pv = [&](int t, int slot, int quarter, bool accumulate) {
+        const uint32_t vb = v_lo + ((kv_smem + slot * C::kTileBytes) >> 4);
+        const uint32_t d = tmem_base + C::kTmemO + t * kHeadDim;
+        const uint32_t a = tmem_base + C::kTmemS + t * 128;
 #pragma unroll
-        for (int ks = 0; ks < kBlockKV / 16; ++ks) {
-          // 16 keys = 16 rows of 128 bytes; head-dim column blocks are kChunkBytes apart
-          ptx::umma_ts_f16(tmem_base + C::kTmemO + t * kHeadDim, tmem_base + C::kTmemS + t * 128 + ks * 8,
-                           ptx::umma_smem_desc(vb + ks * 2048, kChunkBytes, 1024), idesc_o,
-                           (accumulate || ks != 0) ? 1u : 0u);
+        for (int k2 = 0; k2 < 2; ++k2) {
+          const int ks = quarter * 2 + k2;  // 16 keys = 16 rows of 128 bytes
+          mma_ts(d, a + ks * 8, vb + ((ks * 2048) >> 4), v_hi, idesc_o, (accumulate || k2 != 0) ? 1u : 0u);
         }
       };
-      bool alive = ptx::mbar_wait(q_full, 0, ctl, kSiteMmaQ);
-      int load_idx = 0;  // index into the K_0, V_0, K_1, ... sequence
-      if (alive) alive = ptx::mbar_wait(kv_full(0), 0, ctl, kSiteMmaKV);
-      if (alive) {
-        ptx::tc_fence_after_sync();
-        for (int t = 0; t < kQTiles; ++t) {
-          if (nblk[t] > 0) {
-            issue_s(t, 0);
-            ptx::umma_commit(s_full(t));
-          }
+      // A K/V slot (and Q) is released once per tile: through tcgen05.commit when the tile's MMAs
+      // read it, by a plain arrive when the tile had no work on it.
+      auto release = [&](uint32_t bar, bool used) {
+        if (used) {
+          ptx::umma_commit(bar);
+        } else {
+          ptx::mbar_arrive(bar);
         }
-        ptx::umma_commit(kv_empty(0));
-        load_idx = 1;
-      }
-      for (int j = 0; j < nblk_max && alive; ++j) {
-        const int v_idx = load_idx;         // V_j
-        const int k_idx = load_idx + 1;     // K_{j+1}
-        const int v_slot = v_idx % kSlots;
-        const int k_slot = k_idx % kSlots;
-        const bool more = (j + 1) < nblk_max;
-        if (!ptx::mbar_wait(kv_full(v_slot), (v_idx / kSlots) & 1u, ctl, kSiteMmaKV)) break;
-        if (more && !ptx::mbar_wait(kv_full(k_slot), (k_idx / kSlots) & 1u, ctl, kSiteMmaKV)) break;
-        for (int t = 0; t < kQTiles; ++t) {
-          if (j >= nblk[t]) continue;
-          if (!ptx::mbar_wait(p_ready(t), j & 1u, ctl, kSiteMmaP)) {
-            alive = false;
-            break;
-          }
+      };
+
+      uint32_t cons_idx = 0;                      // position in the K_0, V_0, K_1, ... sequence
+      uint32_t n_p[2] = {0, 0}, n_item[2] = {0, 0};  // per tile: P blocks consumed, items taken part in
+      uint32_t it = 0;
+      bool alive = true;
+      auto wait = [&](uint32_t bar, uint32_t parity, int site) {
+        if (!ptx::mbar_wait(bar, parity, ctl, site)) alive = false;
+        return alive;
+      };
+      for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
+        const Item item = get_item<kQTiles>(args, w);
+        [[maybe_unused]] const bool trace_on = it == 1;
+        if (!wait(q_full, it & 1u, kSiteMmaQ)) break;
+        {
+          const int slot = cons_idx % kSlots;
+          if (!wait(kv_full(slot), (cons_idx / kSlots) & 1u, kSiteMmaKV)) break;
           ptx::tc_fence_after_sync();
-          issue_pv(t, v_slot, j > 0);
-          if (j + 1 < nblk[t]) {
-            issue_s(t, k_slot);
-            ptx::umma_commit(s_full(t));
-          } else {
-            ptx::umma_commit(o_final(t));
+          for (int t = 0; t < kQTiles; ++t) {
+            if (item.nblk[t] > 0) {
+              issue_s(t, slot);
+              ptx::umma_commit(s_full(t));
+            }
+            release(kv_empty(slot), item.nblk[t] > 0);
+            if (item.nblk_max == 1) release(q_empty, item.nblk[t] > 0);
           }
+          ++cons_idx;
         }
-        if (!alive) break;
-        ptx::umma_commit(kv_empty(v_slot));
-        if (more) ptx::umma_commit(kv_empty(k_slot));
-        load_idx += 2;
+        for (int j = 0; j < item.nblk_max && alive; ++j) {
+          const bool more = (j + 1) < item.nblk_max;
+          const int v_slot = cons_idx % kSlots;
+          const uint32_t k_idx = cons_idx + 1;  // K_{j+1}, present when `more`
+          const int k_slot = k_idx % kSlots;
+          // Every tile waits for the data even when it skips the block, so that its plain
+          // arrive cannot land in the slot's previous release phase.
+          if (!wait(kv_full(v_slot), (cons_idx / kSlots) & 1u, kSiteMmaKV)) break;
+          bool k_ready = false;
+          for (int t = 0; t < kQTiles && alive; ++t) {
+            const bool active = j < item.nblk[t];
+            const bool next_s = (j + 1) < item.nblk[t];
+            if (active) {
+              // O_t of the previous item must have been read out before it is overwritten
+              if (j == 0 && !wait(o_free(t), (n_item[t] & 1u) ^ 1u, kSiteMmaO)) break;
+              for (int part = 0; part < kParts; ++part) {
+                if (!wait(p_part(t, part), n_p[t] & 1u, kSiteMmaP)) break;
+                ptx::tc_fence_after_sync();
+                IXK_TRACE(8, j, t * 4 + (part == 0 ? 0 : 1));
+#pragma unroll
+                for (int q4 = 0; q4 < 4 / kParts; ++q4) {
+                  const int quarter = part * (4 / kParts) + q4;
+                  issue_pv(t, v_slot, quarter, j > 0 || quarter > 0);
+                }
+              }
+              if (!alive) break;
+              ++n_p[t];
+            }
+            release(kv_empty(v_slot), active);
+            if (more) {
+              if (!k_ready) {  // K_{j+1} is first needed here
+                if (!wait(kv_full(k_slot), (k_idx / kSlots) & 1u, kSiteMmaKV)) break;
+                ptx::tc_fence_after_sync();
+                k_ready = true;
+              }
+              if (next_s) {
+                issue_s(t, k_slot);
+                ptx::umma_commit(s_full(t));
+                IXK_TRACE(8, j, t * 4 + 2);
+              }
+              release(kv_empty(k_slot), next_s);
+            }
+            if (active && !next_s) {
+              ptx::umma_commit(o_final(t));
+              ++n_item[t];
+            }
+            if (j == item.nblk_max - 2) release(q_empty, next_s);  // the item's last S has been issued
+          }
+          cons_idx += more ? 2 : 1;
+        }
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp > kMmaWarp) {
+    ptx::setmaxnreg_dec<kControlRegs>();  // idle warps of the control warpgroup
+  } else {
     // ------------------------------------------------------------------ softmax + epilogue
-    const int t = (warp - 4) >> 2;  // query tile of this warpgroup
+    ptx::setmaxnreg_inc<kSoftmaxRegs>();
+    const int t = warp >> 2;  // query tile of this warpgroup (warps 0-3: tile 0, warps 4-7: tile 1)
     const int quarter = warp & 3;
-    if (t < kQTiles && nblk[t] > 0) {
+    if (t < kQTiles) {
       const bool bf16 = args.is_bf16 != 0;
       const int row_in_tile = quarter * 32 + lane;
-      const int f = q0 + t * kBlockQ + row_in_tile;
-      const bool row_ok = f < args.F;
       const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
       const uint32_t s_addr = tmem_base + lane_addr + C::kTmemS + t * 128;
       const uint32_t o_addr = tmem_base + lane_addr + C::kTmemO + t * kHeadDim;
-      const uint16_t* bias_row = nullptr;
-      if (args.bias != nullptr && row_ok)
-        bias_row = args.bias + batch * args.bias_strides[0] + head * args.bias_strides[1] +
-                   static_cast<int64_t>(f) * args.bias_strides[2];
-      float m_run = -INFINITY;
-      float l_run = 0.0f;
+      uint32_t n_s = 0;  // S tiles consumed
+      uint32_t n_o = 0;  // items finished
       bool alive = true;
-      const int my_blocks = nblk[t];
-      for (int j = 0; j < my_blocks; ++j) {
-        if (!ptx::mbar_wait(s_full(t), j & 1u, ctl, kSiteSoftmaxS)) {
+      uint32_t it = 0;
+      for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
+        const Item item = get_item<kQTiles>(args, w);
+        [[maybe_unused]] const bool trace_on = it == 1 && lane == 0;
+        const int my_blocks = item.nblk[t];
+        if (my_blocks == 0) continue;
+        const int q0 = item.q0, head = item.head, batch = item.batch;
+        const int f = q0 + t * kBlockQ + row_in_tile;
+        const bool row_ok = f < args.F;
+        const uint16_t* bias_row = nullptr;
+        if (args.bias != nullptr && row_ok)
+          bias_row = args.bias + batch * args.bias_strides[0] + head * args.bias_strides[1] +
+                     static_cast<int64_t>(f) * args.bias_strides[2];
+        float m_run = -INFINITY;
+        float l_run = 0.0f;
+        for (int j = 0; j < my_blocks; ++j) {
+          if (!ptx::mbar_wait(s_full(t), n_s & 1u, ctl, kSiteSoftmaxS)) {
+            alive = false;
+            break;
+          }
+          ++n_s;
+          ptx::tc_fence_after_sync();
+          IXK_TRACE(warp, j, 0);
+          uint32_t r[4][32];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32(s_addr + c * 32, r[c]);
+          ptx::tmem_ld_wait();
+          IXK_TRACE(warp, j, 1);
+          const int kv0 = j * kBlockKV;
+          // Scores enter the exponential as x = r * mult - m.  Fast path: r is the raw Q.K^T and
+          // mult = head_scale * log2(e) (> 0, so the row maximum can be taken on r).  With a bias
+          // or a non-positive scale, r is first rewritten as the full log2-domain score and mult = 1.
+          float mult = args.scale_log2;
+          if (args.bias != nullptr || !(args.scale_log2 > 0.0f)) {
+            mult = 1.0f;
+  #pragma unroll
+            for (int c = 0; c < 4; ++c) {
+  #pragma unroll
+              for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__uint_as_float(r[c][i]) * args.scale_log2);
+            }
+            if (bias_row != nullptr) {
+              const uint16_t* bp = bias_row + kv0;
+              const int count = min(kBlockKV, args.T - kv0);
+              if (args.bias_vec_ok && count == kBlockKV) {
+  #pragma unroll
+                for (int c = 0; c < 4; ++c) {
+  #pragma unroll
+                  for (int g = 0; g < 4; ++g) {
+                    const uint4 w = __ldg(reinterpret_cast<const uint4*>(bp + c * 32) + g);
+                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+  #pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      const int i = g * 8 + e * 2;
+                      r[c][i] = __float_as_uint(fmaf(unpack_lo(ww[e], bf16), kLog2e, __uint_as_float(r[c][i])));
+                      r[c][i + 1] = __float_as_uint(fmaf(unpack_hi(ww[e], bf16), kLog2e, __uint_as_float(r[c][i + 1])));
+                    }
+                  }
+                }
+              } else {
+  #pragma unroll
+                for (int c = 0; c < 4; ++c) {
+  #pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    const int col = c * 32 + i;
+                    if (col < count) {
+                      const uint32_t w = __ldg(bp + col);
+                      r[c][i] = __float_as_uint(fmaf(unpack_lo(w, bf16), kLog2e, __uint_as_float(r[c][i])));
+                    }
+                  }
+                }
+              }
+            }
+          }
+          // masks: keys past T (tile padding) and, under causal, keys after the query
+          const bool tail_block = kv0 + kBlockKV > args.T;
+          const bool diag_block = args.causal && (kv0 + kBlockKV - 1 > q0 + t * kBlockQ);
+          if (tail_block || diag_block) {
+            int limit = args.T - kv0;                             // first masked column from the tail
+            if (args.causal) limit = min(limit, f - kv0 + 1);     // columns > f - kv0 are masked
+  #pragma unroll
+            for (int c = 0; c < 4; ++c) {
+  #pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (c * 32 + i >= limit) r[c][i] = 0xff800000u;  // -inf
+            }
+          }
+          // eight independent chains keep the row maximum off the latency-bound path
+          float mxs[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) mxs[i] = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 16) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                mxs[e] = ptx::max3(mxs[e], __uint_as_float(r[c][i + 2 * e]), __uint_as_float(r[c][i + 2 * e + 1]));
+            }
+          }
+          const float mx0 = fmaxf(ptx::max3(mxs[0], mxs[1], mxs[2]), mxs[3]);
+          const float mx1 = fmaxf(ptx::max3(mxs[4], mxs[5], mxs[6]), mxs[7]);
+          const float mx = fmaxf(mx0, mx1) * mult;
+          float alpha = 1.0f;
+          if (mx - m_run > kRescaleThreshold) {  // also true on the first block (m_run = -inf)
+            alpha = ptx::ex2_approx(m_run - mx);  // 0 on the first block
+            m_run = mx;
+          }
+          // Rows that are entirely masked so far keep m_run = -inf; use 0 to avoid inf - inf.
+          // Rescale O when any row of the warp raised its maximum.  s_full was committed after
+          // P.V of the previous block, so O is quiescent here; P.V of this block waits for p_lo.
+          if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+            for (int c = 0; c < kHeadDim / 32; ++c) {
+              uint32_t o[32];
+              ptx::tmem_ld_32x32(o_addr + c * 32, o);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              ptx::tmem_st_32x32(o_addr + c * 32, o);
+            }
+          }
+          IXK_TRACE(warp, j, 2);
+          const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
+          const uint64_t mult2 = ptx::f32x2(mult, mult);
+          const uint64_t negm2 = ptx::f32x2(-m_use, -m_use);
+          uint64_t sum_a = ptx::f32x2(0.0f, 0.0f), sum_b = ptx::f32x2(0.0f, 0.0f);
+          // P (16-bit pairs) overwrites the first 64 columns of this tile's S: the 32 scores of
+          // chunk c become 16 packed columns at [16 c, 16 c + 16), already read by this thread.
+          // Of every four pairs, kPolyOf4 take their 2^x from the FMA pipe, the rest from the
+          // special-function unit, so that neither pipe alone bounds the softmax.
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const uint64_t x2 =
+                  ptx::fma2(ptx::f32x2(__uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1])), mult2, negm2);
+              float x0, x1, p0, p1;
+              ptx::f32x2_split(x2, x0, x1);
+              if (((i >> 1) & 3) < kPolyOf4) {
+                ptx::ex2_poly2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f), p0, p1);
+                sum_b = ptx::add2(sum_b, ptx::f32x2(p0, p1));
+              } else {
+                p0 = ptx::ex2_approx(x0);
+                p1 = ptx::ex2_approx(x1);
+                sum_a = ptx::add2(sum_a, ptx::f32x2(p0, p1));
+              }
+              pk[i >> 1] = pack2(p0, p1, bf16);
+            }
+            ptx::tmem_st_32x16(s_addr + c * 16, pk);
+            if ((c + 1) % (4 / kParts) == 0) {
+              // hand over this part of P
+              ptx::tmem_st_wait();
+              ptx::tc_fence_before_sync();
+              ptx::mbar_arrive(p_part(t, c / (4 / kParts)));
+              IXK_TRACE(warp, j, 3 + c);
+            }
+          }
+          float s0, s1;
+          ptx::f32x2_split(ptx::add2(sum_a, sum_b), s0, s1);
+          l_run = l_run * alpha + (s0 + s1);
+        }
+        if (!alive) break;
+        // ---- epilogue: O / l, one rounding, 16-byte stores
+        if (!ptx::mbar_wait(o_final(t), n_o & 1u, ctl, kSiteEpilogueO)) {
           alive = false;
           break;
         }
-        ptx::tc_fence_after_sync();
-        uint32_t r[4][32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32(s_addr + c * 32, r[c]);
-        ptx::tmem_ld_wait();
-        const int kv0 = j * kBlockKV;
-        // Scores enter the exponential as x = r * mult - m.  Fast path: r is the raw Q.K^T and
-        // mult = head_scale * log2(e) (> 0, so the row maximum can be taken on r).  With a bias
-        // or a non-positive scale, r is first rewritten as the full log2-domain score and mult = 1.
-        float mult = args.scale_log2;
-        if (args.bias != nullptr || !(args.scale_log2 > 0.0f)) {
-          mult = 1.0f;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__uint_as_float(r[c][i]) * args.scale_log2);
-          }
-          if (bias_row != nullptr) {
-            const uint16_t* bp = bias_row + kv0;
-            const int count = min(kBlockKV, args.T - kv0);
-            if (args.bias_vec_ok && count == kBlockKV) {
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                  const uint4 w = __ldg(reinterpret_cast<const uint4*>(bp + c * 32) + g);
-                  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const int i = g * 8 + e * 2;
-                    r[c][i] = __float_as_uint(fmaf(unpack_lo(ww[e], bf16), kLog2e, __uint_as_float(r[c][i])));
-                    r[c][i + 1] = __float_as_uint(fmaf(unpack_hi(ww[e], bf16), kLog2e, __uint_as_float(r[c][i + 1])));
-                  }
-                }
-              }
-            } else {
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                  const int col = c * 32 + i;
-                  if (col < count) {
-                    const uint32_t w = __ldg(bp + col);
-                    r[c][i] = __float_as_uint(fmaf(unpack_lo(w, bf16), kLog2e, __uint_as_float(r[c][i])));
-                  }
-                }
-              }
-            }
-          }
-        }
-        // masks: keys past T (tile padding) and, under causal, keys after the query
-        const bool tail_block = kv0 + kBlockKV > args.T;
-        const bool diag_block = args.causal && (kv0 + kBlockKV - 1 > q0 + t * kBlockQ);
-        if (tail_block || diag_block) {
-          int limit = args.T - kv0;                             // first masked column from the tail
-          if (args.causal) limit = min(limit, f - kv0 + 1);     // columns > f - kv0 are masked
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (c * 32 + i >= limit) r[c][i] = 0xff800000u;  // -inf
-          }
-        }
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            mx0 = ptx::max3(mx0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
-            mx1 = ptx::max3(mx1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
-          }
-        }
-        const float mx = fmaxf(mx0, mx1) * mult;
-        float alpha = 1.0f;
-        if (mx - m_run > kRescaleThreshold) {  // also true on the first block (m_run = -inf)
-          alpha = ptx::ex2_approx(m_run - mx);  // 0 on the first block
-          m_run = mx;
-        }
-        // Rows that are entirely masked so far keep m_run = -inf; use 0 to avoid inf - inf.
-        const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
-        const uint64_t mult2 = ptx::f32x2(mult, mult);
-        const uint64_t negm2 = ptx::f32x2(-m_use, -m_use);
-        uint64_t sum_a = ptx::f32x2(0.0f, 0.0f), sum_b = ptx::f32x2(0.0f, 0.0f);
-        // P (16-bit pairs) overwrites the first 64 columns of this tile's S: the 32 scores of
-        // chunk c become 16 packed columns at [16 c, 16 c + 16), already read by this thread.
-        // Of every four pairs, kPolyOf4 take their 2^x from the FMA pipe, the rest from the
-        // special-function unit, so that neither pipe alone bounds the softmax.
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const uint64_t x2 = ptx::fma2(ptx::f32x2(__uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1])), mult2, negm2);
-            float x0, x1, p0, p1;
-            ptx::f32x2_split(x2, x0, x1);
-            if (((i >> 1) & 3) < kPolyOf4) {
-              ptx::ex2_poly2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f), p0, p1);
-              sum_b = ptx::add2(sum_b, ptx::f32x2(p0, p1));
-            } else {
-              p0 = ptx::ex2_approx(x0);
-              p1 = ptx::ex2_approx(x1);
-              sum_a = ptx::add2(sum_a, ptx::f32x2(p0, p1));
-            }
-            pk[i >> 1] = pack2(p0, p1, bf16);
-          }
-          ptx::tmem_st_32x16(s_addr + c * 16, pk);
-        }
-        float s0, s1;
-        ptx::f32x2_split(ptx::add2(sum_a, sum_b), s0, s1);
-        l_run = l_run * alpha + (s0 + s1);
-        // Rescale O when any row of the warp raised its maximum.  s_full(j) was committed after
-        // P.V of block j-1, so O is quiescent here.
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll 1
-          for (int c = 0; c < kHeadDim / 32; ++c) {
-            uint32_t o[32];
-            ptx::tmem_ld_32x32(o_addr + c * 32, o);
-            ptx::tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            ptx::tmem_st_32x32(o_addr + c * 32, o);
-          }
-        }
-        ptx::tmem_st_wait();
-        ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(p_ready(t));
-      }
-      // ---- epilogue: O / l, one rounding, 16-byte stores
-      if (alive && ptx::mbar_wait(o_final(t), 0, ctl, kSiteEpilogueO)) {
+        ++n_o;
         ptx::tc_fence_after_sync();
         const float inv_l = 1.0f / l_run;
         uint16_t* orow = args.out + batch * args.o_strides[0] + head * args.o_strides[1] +
                          static_cast<int64_t>(f) * args.o_strides[2];
+        constexpr int kOChunks = kHeadDim / 32;
 #pragma unroll 1
-        for (int c = 0; c < kHeadDim / 32; ++c) {
-          if (c * 32 >= args.H) break;  // padded head-dim columns
+        for (int c = 0; c < kOChunks; ++c) {
           uint32_t o[32];
           ptx::tmem_ld_32x32(o_addr + c * 32, o);
           ptx::tmem_ld_wait();
-          if (row_ok) {
-            uint32_t w[16];
+          if (c == kOChunks - 1) {
+            // O_t is in registers: the next item's P.V may overwrite it
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(o_free(t));
+          }
+          if (row_ok && c * 32 < args.H) {
+            uint32_t wv[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-              w[i] = pack2(__uint_as_float(o[2 * i]) * inv_l, __uint_as_float(o[2 * i + 1]) * inv_l, bf16);
+              wv[i] = pack2(__uint_as_float(o[2 * i]) * inv_l, __uint_as_float(o[2 * i + 1]) * inv_l, bf16);
             const int count = min(32, args.H - c * 32);
             if (args.out_vec_ok && count == 32) {
 #pragma unroll
               for (int g = 0; g < 4; ++g)
-                reinterpret_cast<uint4*>(orow + c * 32)[g] = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
+                reinterpret_cast<uint4*>(orow + c * 32)[g] =
+                    make_uint4(wv[4 * g], wv[4 * g + 1], wv[4 * g + 2], wv[4 * g + 3]);
             } else {
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                if (2 * i < count) orow[c * 32 + 2 * i] = static_cast<uint16_t>(w[i] & 0xffffu);
-                if (2 * i + 1 < count) orow[c * 32 + 2 * i + 1] = static_cast<uint16_t>(w[i] >> 16);
+                if (2 * i < count) orow[c * 32 + 2 * i] = static_cast<uint16_t>(wv[i] & 0xffffu);
+                if (2 * i + 1 < count) orow[c * 32 + 2 * i + 1] = static_cast<uint16_t>(wv[i] >> 16);
               }
             }
           }
@@ -448,7 +637,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   if (*abort_flag != 0) __nanosleep(2000000);
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, 512);
   }
@@ -517,8 +706,12 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
     IXK_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     configured_device = dev.device;
   }
-  const int rows_per_cta = kBlockQ * kQTiles;
-  dim3 grid((p.F + rows_per_cta - 1) / rows_per_cta, p.N, p.B);
+  const int rows_per_item = kBlockQ * kQTiles;
+  a.num_qblocks = (p.F + rows_per_item - 1) / rows_per_item;
+  const int64_t items = static_cast<int64_t>(a.num_qblocks) * p.N * p.B;
+  if (items > 0x7fffffff) return fail(IXK_UNIMPLEMENTED, "too many (batch, head, query block) work items");
+  a.num_items = static_cast<int>(items);
+  const int grid = a.num_items < dev.sm_count ? a.num_items : dev.sm_count;
   fn<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, a);
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
@@ -528,18 +721,16 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
 }  // namespace
 
 int launch_prefill(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
-  if (p.N > 65535 || p.B > 65535) return fail(IXK_UNIMPLEMENTED, "num_heads and num_batches must be <= 65535");
   // Head-size buckets follow the reference's policy pick (fmha_forward.h:621-646): <=64, <=128, <=256.
-  constexpr int kPoly = 2;  // pairs of every four whose 2^x runs on the FMA pipe
+  constexpr int kPoly = 0;  // pairs of every four whose 2^x runs on the FMA pipe instead of the special-function unit
   if (p.H <= 64) return p.F > kBlockQ ? launch_cfg<64, 2, kPoly>(p, dev, stream) : launch_cfg<64, 1, kPoly>(p, dev, stream);
   if (p.H <= 128) {
     if (p.F <= kBlockQ) return launch_cfg<128, 1, kPoly>(p, dev, stream);
-    // Tuning override for the main configuration: IXK_FMHA_POLY = 0..3.
+    // Tuning override for the main configuration: IXK_FMHA_POLY = 0..2.
     if (const char* env = std::getenv("IXK_FMHA_POLY")) {
       switch (std::atoi(env)) {
-        case 0: return launch_cfg<128, 2, 0>(p, dev, stream);
         case 1: return launch_cfg<128, 2, 1>(p, dev, stream);
-        case 3: return launch_cfg<128, 2, 3>(p, dev, stream);
+        case 2: return launch_cfg<128, 2, 2>(p, dev, stream);
         default: break;
       }
     }
@@ -550,3 +741,9 @@ int launch_prefill(const Problem& p, const DeviceInfo& dev, cudaStream_t stream)
 
 }  // namespace fmha
 }  // namespace ixk
+
+#ifdef IXK_FMHA_TRACE
+extern "C" int ixk_debug_fmha_trace(long long* host_out, int count) {
+  return cudaMemcpyFromSymbol(host_out, ixk::fmha::g_fmha_trace, sizeof(long long) * count) == cudaSuccess ? 0 : 1;
+}
+#endif
