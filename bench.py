@@ -224,6 +224,7 @@ WORKLOADS = {
     "gemm_fp8_e5m2": lambda: Fp8GemmWorkload(True),
     "decode_attn": lambda: DecodeWorkload(),
 }
+LAYER_WORKLOADS = ("gptj_layer", "gemma_decode")   # tensor-parallel over --gpus N, strong scaling
 DEFAULT_WORKLOAD = "fmha_causal"
 OTHERS = ["fmha_bias", "gemm_bias_gelu", "gemm_fp8", "gemm_fp8_e5m2", "decode_attn"]
 
@@ -491,13 +492,192 @@ def run_reference(args, rank, world):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------------------- layer configs
+
+def _layer_weights(name, seed=7):
+    """Random-init weights ~ N(0, 0.02) in bf16, identical on every rank (same seed)."""
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *shape: (torch.randn(*shape, generator=g) * 0.02).bfloat16()
+    if name == "gptj_layer":   # hidden 4096, 16 heads x 256, MLP 16384
+        return {"wqkv": r(4096, 12288), "wo": r(4096, 4096), "w1": r(4096, 16384), "b1": r(16384),
+                "w2": r(16384, 4096), "b2": r(4096)}
+    return {"wqkv": r(3072, 12288), "wo": r(4096, 3072), "wgate": r(3072, 24576), "wup": r(3072, 24576),
+            "wdown": r(24576, 3072)}   # Gemma-7B shape: hidden 3072, 16 heads x 256, GeGLU 24576
+
+
+def run_layer(args, rank, world):
+    """Configurations 4 and 5: one decoder layer, tensor-parallel over `world` GPUs by heads / MLP
+    columns, NCCL all-reduce after the row-parallel projections.  Total work is fixed (strong scaling).
+      gptj_layer    prefill, batch 4 x seq 2048, reported in TFLOP/s of the layer's GEMM+attention FLOPs
+      gemma_decode  one token for 64 sequences against a 4096-entry KV cache, reported in GB/s of the
+                    algorithmic bytes (K, V and every weight once)"""
+    import importlib
+    pkg = entry.load_package()
+    pkg.load_library()
+    layers = importlib.import_module(entry.PKG_NAME + ".layers")
+    if args.impl == "reference":
+        if rank == 0:
+            run_layer_reference(args, layers)
+        return
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+    ops = layers.KernelOps(pkg)
+    full = _layer_weights(args.workload)
+    g = torch.Generator().manual_seed(11)
+    flush_buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=dev)
+    if args.workload == "gptj_layer":
+        B, S = 4, 2048
+        w = layers.GptJLayerWeights.shard(full, 16, 256, 64, rank, world)
+        for k, v in vars(w).items():
+            if torch.is_tensor(v):
+                setattr(w, k, v.to(dev))
+        x_host = torch.randn(B, S, 4096, generator=g).bfloat16().pin_memory()
+        x = x_host.to(dev)
+        step = lambda: layers.gptj_layer_prefill(x, w, ops)
+        work, div, unit, bound = layers.gptj_layer_flops(B, S), 1e12, "TFLOP/s", "tensor"
+        metric = "GPT-J-6B-shaped decoder layer prefill TFLOP/s (bf16, tensor-parallel)"
+        name = f"gptj_layer_prefill_B{B}_S{S}_hidden4096_heads16x256_mlp16384_tp{world}"
+        peak = peaks["bf16_tflops"] * world
+    else:
+        B, T = 64, 4096
+        w = layers.GemmaLayerWeights.shard(full, 16, 256, rank, world)
+        for k, v in vars(w).items():
+            if torch.is_tensor(v):
+                setattr(w, k, v.to(dev))
+        hl = 16 // world
+        x_host = torch.randn(B, 1, 3072, generator=g).bfloat16().pin_memory()
+        x = x_host.to(dev)
+        gk = torch.Generator(device=dev).manual_seed(13 + rank)
+        k_cache = torch.randn(B, T, hl, 256, generator=gk, device=dev).bfloat16()
+        v_cache = torch.randn(B, T, hl, 256, generator=gk, device=dev).bfloat16()
+        ws = torch.empty(8 << 20, dtype=torch.uint8, device=dev)
+        step = lambda: layers.gemma_decode_step(x, w, k_cache, v_cache, T - 1, ops, workspace=ws)
+        work, div, unit, bound = layers.gemma_decode_bytes(B, T), 1e9, "GB/s", "hbm"
+        metric = "Gemma-7B-shaped decode step GB/s of algorithmic bytes (bf16, tensor-parallel)"
+        name = f"gemma_decode_B{B}_T{T}_hidden3072_heads16x256_mlp24576_tp{world}"
+        peak = peaks["hbm_gbs"] * world
+    del full
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        y = step()
+        flush_l2(flush_buf)
+    barrier()
+    n0 = pkg.launch_count()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    with ClockSampler(local) as clk:
+        for i in range(args.steps):
+            starts[i].record()
+            y = step()
+            ends[i].record()
+            flush_l2(flush_buf)
+        torch.cuda.synchronize()
+    launches = pkg.launch_count() - n0
+    total_ms = float(sum(s.elapsed_time(e) for s, e in zip(starts, ends)))
+    # end to end: host x in, host y out
+    y_host = torch.empty(y.shape, dtype=y.dtype).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+    s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    s_ev.record()
+    for _ in range(e2e_steps):
+        x.copy_(x_host, non_blocking=True)
+        y = step()
+        y_host.copy_(y, non_blocking=True)
+    e_ev.record()
+    torch.cuda.synchronize()
+    e2e_ms = s_ev.elapsed_time(e_ev) / e2e_steps
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([total_ms, e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms = float(t[0].item()), float(t[1].item())
+    status = pkg.device_status()
+    ms_per_step = total_ms / args.steps
+    value = work / (ms_per_step * 1e-3) / div
+    line = {
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (random-init weights ~N(0,0.02), activations ~N(0,1), seeded)",
+        "config": {"workload": name, "parallelism": f"tp{world} by heads / MLP columns, all-reduce after row-parallel GEMMs",
+                   "l2": "L2 flushed (512 MB read+write) between timed steps"},
+        "clocks": clk.summary(),
+        "e2e": {"value": work / (e2e_ms * 1e-3) / div, "unit": unit, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": int(x_host.numel() * 2), "d2h_bytes_per_step": int(y_host.numel() * 2)},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": bound, "achieved": value, "peak": peak, "unit": unit, "frac": value / peak, "traffic": None,
+                     "kernel": "whole layer step (libixk GEMM + attention kernels, torch glue, NCCL)",
+                     "peak_source": f"{world} x {peaks['source']} single-GPU peak"},
+        "device_status": status,
+    }
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
+
+def run_layer_reference(args, layers):
+    """Reference arm of the layer configurations: the un-sharded numpy layer oracle on the host
+    cores, on a bounded sample (one sequence of the batch)."""
+    from oracle import layers_oracle
+    full = {k: v.float().numpy() for k, v in _layer_weights(args.workload).items()}
+    g = torch.Generator().manual_seed(11)
+    times = []
+    if args.workload == "gptj_layer":
+        B, S = 4, 2048
+        x = torch.randn(B, S, 4096, generator=g).bfloat16().float().numpy()[:1]
+        work, div, unit, frac = layers.gptj_layer_flops(1, S), 1e12, "TFLOP/s", "1 of 4 sequences"
+        fn = lambda: layers_oracle.gptj_layer_prefill(x, full, 16, 256, 64)
+        metric = "GPT-J-6B-shaped decoder layer prefill TFLOP/s (bf16, tensor-parallel)"
+    else:
+        B, T = 64, 4096
+        nb = 8
+        x = torch.randn(B, 1, 3072, generator=g).bfloat16().float().numpy()[:nb]
+        kc = np.random.default_rng(0).standard_normal((nb, T, 16, 256), dtype=np.float32)
+        vc = np.random.default_rng(1).standard_normal((nb, T, 16, 256), dtype=np.float32)
+        work, div, unit, frac = layers.gemma_decode_bytes(nb, T), 1e9, "GB/s", f"{nb} of 64 sequences (weights read once per sample)"
+        fn = lambda: layers_oracle.gemma_decode_step(x, full, kc, vc, T - 1, 16, 256)
+        metric = "Gemma-7B-shaped decode step GB/s of algorithmic bytes (bf16, tensor-parallel)"
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        fn()
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+        if sum(times) > 120:
+            break
+    dt = float(np.mean(times))
+    value = work / dt / div
+    cores = os.cpu_count() or 1
+    print(json.dumps({
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": int(os.environ.get("WORLD_SIZE", 1)),
+        "steps": len(times), "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic (random-init weights ~N(0,0.02), activations ~N(0,1), seeded)",
+        "config": {"workload": args.workload, "note": "each step is a bounded sample of the workload: " + frac},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": frac},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + list(LAYER_WORKLOADS))
     ap.add_argument("--no-others", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-timed steps only (no e2e, no CPU baseline): the command profiled under ncu")
@@ -505,7 +685,9 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.impl == "reference":
+    if args.workload in LAYER_WORKLOADS:
+        run_layer(args, rank, world)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
         if world != args.gpus and world == 1 and args.gpus > 1:

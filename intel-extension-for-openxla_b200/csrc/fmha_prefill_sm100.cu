@@ -9,8 +9,8 @@
 //   warps 0-3     softmax for query tile 0: one thread owns one row of S (a TMEM lane), so
 //   warps 4-7     softmax for query tile 1  row max / row sum need no cross-thread traffic
 //   warp 8        TMA producer: Q per work item, then K_0, V_0, K_1, V_1 ... through a shared-memory ring
-//   warp 9        tcgen05.mma issuer (one thread, polling both tiles' hand-over barriers and serving
-//                 whichever is ready):  S_t = Q_t.K_j^T  (A, B from shared memory, S in TMEM)
+//   warp 9        tcgen05.mma issuer (one thread, alternating between the tiles):
+//                                      S_t = Q_t.K_j^T  (A, B from shared memory, S in TMEM)
 //                                      O_t += P_t.V_j   (A = P from TMEM, B = V from shared memory)
 // The two softmax warpgroups take 216 registers per thread (a whole row of S lives in registers),
 // the control warpgroup gives its share up (setmaxnreg).
@@ -19,9 +19,9 @@
 // first, and every barrier keeps counting across items, so the loads and the first S of the next
 // item are issued while the current item's last softmax and its epilogue still run.
 // A work item carries kQTiles tiles of 128 query rows; with two tiles the tensor core works on one
-// tile's S / P.V while the other tile's softmax runs.  P is handed to the MMA issuer in four quarters
-// so that P.V starts on the first 32 keys while the rest is still being exponentiated.  P overwrites S in place in TMEM as
-// packed 16-bit pairs.  The running maximum is only raised when it moved by more than 2^8
+// tile's S / P.V while the other tile's softmax runs.  P is handed to the MMA issuer in two halves
+// so that P.V starts on the first 64 keys while the rest is still being exponentiated.  P overwrites
+// S in place in TMEM as packed 16-bit pairs.  The running maximum is only raised when it moved by more than 2^8
 // (exact: the same stale maximum scales P, the row sum and O), which keeps the O rescale off
 // the common path.  exp is evaluated as exp2 with head_scale*log2(e) folded in.
 #include <cuda_bf16.h>

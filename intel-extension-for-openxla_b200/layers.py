@@ -1,0 +1,222 @@
+"""Decoder-layer drivers built from the three custom calls: the shapes the reference's examples
+run (GPT-J prefill, example/gptj/jax_gptj.py; Gemma decode with a [B,T,N,H] KV cache,
+example/gemma/keras_nlp.patch:53-63), tensor-parallel the way the Gemma example lays it out
+(example/gemma/finetune.py:136-153): QKV and the MLP up-projection split by heads / columns with
+no exchange, attention by heads, the row-parallel projections (attention output, MLP down) ending
+in one all-reduce.
+
+The GEMMs and the attention go through libixk (`KernelOps`); layer norm, rotary embedding,
+residual adds and the GeGLU product are the glue XLA would emit as fusions and are plain torch.
+`ops` is injectable so that the sharding and reduction logic can be exercised on CPU ranks with
+a stand-in implementation of the two calls.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+# ----------------------------------------------------------------------------- kernel calls
+
+class KernelOps:
+    """The custom calls as the layers use them, bound to libixk.so."""
+
+    def __init__(self, pkg):
+        self.pkg = pkg
+
+    def gemm(self, x, w, *, bias=None, c=None, beta=0.0, epilogue="DEFAULT", out=None):
+        return self.pkg.gemm(x, w, bias=bias, c=c, beta=beta, epilogue=epilogue, out=out)
+
+    def attention(self, q, k, v, out, *, scale, causal, workspace=None):
+        """q/out [B,N,F,H] views, k/v [B,N,T,H] views."""
+        self.pkg.fmha_forward_kernel(None, q, k, v, None, None, 0.0, out, None, scale, False, causal=causal,
+                                     workspace=workspace)
+        return out
+
+
+# ----------------------------------------------------------------------------- sharding
+
+def shard_range(total: int, rank: int, world: int):
+    """Contiguous [begin, end) share of `total` units for `rank`; total must divide evenly."""
+    if total % world != 0:
+        raise ValueError(f"{total} units do not split evenly over {world} ranks")
+    per = total // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_qkv_weight(wqkv: torch.Tensor, num_heads: int, head_dim: int, rank: int, world: int) -> torch.Tensor:
+    """Fused QKV weight [hidden, 3*num_heads*head_dim] (q | k | v blocks, heads inside each) →
+    the columns of this rank's heads, still as q | k | v."""
+    hidden = wqkv.shape[0]
+    h0, h1 = shard_range(num_heads, rank, world)
+    w = wqkv.view(hidden, 3, num_heads, head_dim)[:, :, h0:h1, :]
+    return w.reshape(hidden, 3 * (h1 - h0) * head_dim).contiguous()
+
+
+def shard_columns(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    c0, c1 = shard_range(w.shape[-1], rank, world)
+    return w[..., c0:c1].contiguous()
+
+
+def shard_rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    r0, r1 = shard_range(w.shape[0], rank, world)
+    return w[r0:r1].contiguous()
+
+
+def all_reduce_sum(t: torch.Tensor, group=None) -> torch.Tensor:
+    """Sum of the row-parallel partials over the tensor-parallel group (NCCL on GPUs)."""
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+    return t
+
+
+# ----------------------------------------------------------------------------- glue
+
+def layer_norm(x: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """LayerNorm with unit gain and zero shift (the benchmark's random-init convention)."""
+    xf = x.float()
+    mu = xf.mean(-1, keepdim=True)
+    var = xf.var(-1, keepdim=True, unbiased=False)
+    return ((xf - mu) * torch.rsqrt(var + eps)).to(x.dtype)
+
+
+def rms_norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+def rotary_tables(positions: torch.Tensor, rotary_dim: int, base: float = 10000.0):
+    """cos/sin [len(positions), rotary_dim/2] in fp32."""
+    inv = 1.0 / (base ** (torch.arange(0, rotary_dim, 2, device=positions.device, dtype=torch.float32) / rotary_dim))
+    ang = positions.float()[:, None] * inv[None, :]
+    return ang.cos(), ang.sin()
+
+
+def apply_rotary_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rotary_dim: int) -> torch.Tensor:
+    """In place, GPT-J convention: interleaved pairs (2i, 2i+1) of the first rotary_dim elements of
+    every head.  x [..., S, heads, head_dim]; cos/sin [S, rotary_dim/2]."""
+    rot = x[..., :rotary_dim].float()
+    x1, x2 = rot[..., 0::2], rot[..., 1::2]
+    c, s = cos[:, None, :], sin[:, None, :]
+    out = torch.stack((x1 * c - x2 * s, x1 * s + x2 * c), dim=-1).flatten(-2)
+    x[..., :rotary_dim] = out.to(x.dtype)
+    return x
+
+
+# ----------------------------------------------------------------------------- GPT-J prefill layer
+
+@dataclass
+class GptJLayerWeights:
+    """This rank's shard.  Full shapes: wqkv [4096, 12288], wo [4096, 4096], w1 [4096, 16384],
+    b1 [16384], w2 [16384, 4096], b2 [4096]."""
+    wqkv: torch.Tensor
+    wo: torch.Tensor
+    w1: torch.Tensor
+    b1: torch.Tensor
+    w2: torch.Tensor
+    b2: torch.Tensor
+    heads_local: int
+    head_dim: int
+    rotary_dim: int
+
+    @staticmethod
+    def shard(full: dict, num_heads: int, head_dim: int, rotary_dim: int, rank: int, world: int):
+        return GptJLayerWeights(
+            wqkv=shard_qkv_weight(full["wqkv"], num_heads, head_dim, rank, world),
+            wo=shard_rows(full["wo"], rank, world),          # rows follow the heads
+            w1=shard_columns(full["w1"], rank, world),
+            b1=shard_columns(full["b1"], rank, world),
+            w2=shard_rows(full["w2"], rank, world),
+            b2=full["b2"],
+            heads_local=num_heads // world, head_dim=head_dim, rotary_dim=rotary_dim)
+
+
+def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None) -> torch.Tensor:
+    """GPT-J block, prefill: y = x + Attn(LN(x)) + MLP(LN(x)), x [B, S, hidden] replicated on every
+    rank.  The attention-output and MLP-down partial sums are added locally (the second GEMM takes
+    the first as its C operand with beta = 1), so the block needs ONE all-reduce."""
+    B, S, hidden = x.shape
+    hl, hd = w.heads_local, w.head_dim
+    h = layer_norm(x).view(B * S, hidden)
+    qkv = ops.gemm(h, w.wqkv).view(B, S, 3, hl, hd)
+    cos, sin = rotary_tables(torch.arange(S, device=x.device), w.rotary_dim)
+    apply_rotary_(qkv[:, :, 0], cos, sin, w.rotary_dim)
+    apply_rotary_(qkv[:, :, 1], cos, sin, w.rotary_dim)
+    q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))        # [B, hl, S, hd] views, no copies
+    ctx = torch.empty(B, S, hl, hd, dtype=x.dtype, device=x.device)
+    ops.attention(q, k, v, ctx.permute(0, 2, 1, 3), scale=1.0 / math.sqrt(hd), causal=True)
+    attn_partial = ops.gemm(ctx.view(B * S, hl * hd), w.wo)
+    up = ops.gemm(h, w.w1, bias=w.b1, epilogue="BIAS_GELU")
+    partial = ops.gemm(up, w.w2, c=attn_partial, beta=1.0, out=attn_partial)   # in place: C aliases D
+    partial = all_reduce_sum(partial, group)
+    return x + (partial.float() + w.b2.float()).to(x.dtype).view(B, S, hidden)
+
+
+def gptj_layer_flops(B, S, hidden=4096, heads=16, head_dim=256, ffn=16384):
+    m = B * S
+    return (2.0 * m * hidden * 3 * heads * head_dim + 4.0 * B * heads * head_dim * S * (S + 1) / 2 +
+            2.0 * m * heads * head_dim * hidden + 2.0 * m * hidden * ffn * 2)
+
+
+# ----------------------------------------------------------------------------- Gemma decode step
+
+@dataclass
+class GemmaLayerWeights:
+    """This rank's shard.  Full shapes: wqkv [3072, 12288], wo [4096, 3072], wgate/wup [3072, 24576],
+    wdown [24576, 3072]."""
+    wqkv: torch.Tensor
+    wo: torch.Tensor
+    wgate: torch.Tensor
+    wup: torch.Tensor
+    wdown: torch.Tensor
+    heads_local: int
+    head_dim: int
+
+    @staticmethod
+    def shard(full: dict, num_heads: int, head_dim: int, rank: int, world: int):
+        return GemmaLayerWeights(
+            wqkv=shard_qkv_weight(full["wqkv"], num_heads, head_dim, rank, world),
+            wo=shard_rows(full["wo"], rank, world),
+            wgate=shard_columns(full["wgate"], rank, world),
+            wup=shard_columns(full["wup"], rank, world),
+            wdown=shard_rows(full["wdown"], rank, world),
+            heads_local=num_heads // world, head_dim=head_dim)
+
+
+def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      position: int, ops, group=None, workspace=None) -> torch.Tensor:
+    """One new token per sequence: x [B, 1, hidden]; k_cache / v_cache [B, T, heads_local, head_dim]
+    (this rank's heads) are updated in place at `position` and attended over [0, position].
+    Two all-reduces: after the attention output projection and after the MLP down projection."""
+    B, _, hidden = x.shape
+    hl, hd = w.heads_local, w.head_dim
+    h = rms_norm(x).view(B, hidden)
+    qkv = ops.gemm(h, w.wqkv).view(B, 1, 3, hl, hd)
+    cos, sin = rotary_tables(torch.tensor([position], device=x.device), hd)
+    apply_rotary_(qkv[:, :, 0], cos, sin, hd)
+    apply_rotary_(qkv[:, :, 1], cos, sin, hd)
+    k_cache[:, position] = qkv[:, 0, 1]
+    v_cache[:, position] = qkv[:, 0, 2]
+    T = position + 1
+    q = qkv[:, :, 0].permute(0, 2, 1, 3)                                   # [B, hl, 1, hd]
+    ctx = torch.empty(B, 1, hl, hd, dtype=x.dtype, device=x.device)
+    ops.attention(q, k_cache[:, :T].permute(0, 2, 1, 3), v_cache[:, :T].permute(0, 2, 1, 3),
+                  ctx.permute(0, 2, 1, 3), scale=1.0 / math.sqrt(hd), causal=False, workspace=workspace)
+    attn = all_reduce_sum(ops.gemm(ctx.view(B, hl * hd), w.wo), group)
+    x1 = x + attn.view(B, 1, hidden)
+    h2 = rms_norm(x1).view(B, hidden)
+    gate = ops.gemm(h2, w.wgate, epilogue="GELU")
+    up = ops.gemm(h2, w.wup)
+    down = all_reduce_sum(ops.gemm(gate * up, w.wdown), group)
+    return x1 + down.view(B, 1, hidden)
+
+
+def gemma_decode_bytes(B, T, hidden=3072, heads=16, head_dim=256, ffn=24576, elem=2):
+    """Algorithmic HBM bytes of one decode step: K and V once, every weight once."""
+    attn = 2.0 * B * heads * T * head_dim * elem + 2.0 * B * heads * head_dim * elem
+    weights = (hidden * 3 * heads * head_dim + heads * head_dim * hidden + 2 * hidden * ffn + ffn * hidden) * elem
+    return attn + weights
