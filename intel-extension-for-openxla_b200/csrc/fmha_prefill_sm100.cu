@@ -52,15 +52,20 @@ constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 enum : int { kSiteLoad = 201, kSiteMmaQ = 202, kSiteMmaKV = 203, kSiteMmaP = 204, kSiteSoftmaxS = 205, kSiteEpilogueO = 206,
-              kSiteLoadQ = 207, kSiteMmaO = 208 };
+              kSiteLoadQ = 207, kSiteMmaO = 208, kSiteLoadBias = 209, kSiteSoftmaxBias = 210 };
 
-template <int kHeadDim, int kQTiles>
+constexpr int kBiasTileBytes = 2 * kChunkBytes;  // 128 query rows x 128 keys, 16-bit, as two swizzled boxes
+
+template <int kHeadDim, int kQTiles, bool kBias>
 struct Cfg {
   static constexpr int kChunks = kHeadDim / kChunkElems;          // 128-byte column blocks per row
   static constexpr int kTileBytes = kChunks * kChunkBytes;        // a 128-row Q, K or V tile
-  static constexpr int kKvSlots = (kHeadDim == 256) ? 2 : 4;
+  // with a TMA-fed bias tile per query tile the K/V ring gives up one slot to make room
+  static constexpr int kKvSlots = (kHeadDim == 256) ? 2 : (kBias ? 3 : 4);
   static constexpr int kQBytes = kQTiles * kTileBytes;
-  static constexpr int kSmemBytes = kQBytes + kKvSlots * kTileBytes + 256 + 1024;
+  static constexpr int kBiasBytes = kBias ? kQTiles * kBiasTileBytes : 0;
+  static constexpr int kSmemBytes = kQBytes + kKvSlots * kTileBytes + kBiasBytes + 256 + 1024;
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
   static constexpr int kTmemS = 0;                                // S_t at columns [128 t, 128 t + 128)
   static constexpr int kTmemO = 128 * kQTiles;                    // O_t at kTmemO + t * kHeadDim
   static_assert(kTmemO + kQTiles * kHeadDim <= 512, "TMEM budget");
@@ -187,11 +192,12 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_
       : "memory");
 }
 
-template <int kHeadDim, int kQTiles, int kPolyOf4>
+template <int kHeadDim, int kQTiles, int kPolyOf4, bool kBias>
 __global__ void __launch_bounds__(kThreads, 1)
 fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                    const __grid_constant__ CUtensorMap tmap_v, const KernelArgs args) {
-  using C = Cfg<kHeadDim, kQTiles>;
+                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_bias,
+                    const KernelArgs args) {
+  using C = Cfg<kHeadDim, kQTiles, kBias>;
   constexpr int kSlots = C::kKvSlots;
 
   extern __shared__ uint8_t smem_raw[];
@@ -199,7 +205,8 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   const uint32_t q_smem = smem_base;
   const uint32_t kv_smem = smem_base + C::kQBytes;
-  const uint32_t bar_base = kv_smem + kSlots * C::kTileBytes;
+  const uint32_t bias_smem = kv_smem + kSlots * C::kTileBytes;  // kQTiles tiles when kBias
+  const uint32_t bar_base = bias_smem + C::kBiasBytes;
   // barriers (8 bytes each)
   const uint32_t q_full = bar_base;
   const uint32_t q_empty = bar_base + 8u;
@@ -209,7 +216,9 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   auto p_part = [&](int t, int quarter) { return bar_base + 8u * (4 + 2 * kSlots + t * 4 + quarter); };
   auto o_final = [&](int t) { return bar_base + 8u * (12 + 2 * kSlots + t); };
   auto o_free = [&](int t) { return bar_base + 8u * (14 + 2 * kSlots + t); };
-  uint8_t* tail = smem_gen + C::kQBytes + kSlots * C::kTileBytes + 8 * (16 + 2 * kSlots);
+  auto bias_full = [&](int t) { return bar_base + 8u * (16 + 2 * kSlots + t); };
+  auto bias_empty = [&](int t) { return bar_base + 8u * (18 + 2 * kSlots + t); };
+  uint8_t* tail = smem_gen + C::kQBytes + kSlots * C::kTileBytes + C::kBiasBytes + 8 * (20 + 2 * kSlots);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
@@ -230,11 +239,14 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       for (int quarter = 0; quarter < 4; ++quarter) ptx::mbar_init(p_part(t, quarter), 128);
       ptx::mbar_init(o_final(t), 1);
       ptx::mbar_init(o_free(t), 128);
+      ptx::mbar_init(bias_full(t), 1);
+      ptx::mbar_init(bias_empty(t), 128);
     }
     ptx::fence_mbar_init();
     ptx::prefetch_tmap(&tmap_q);
     ptx::prefetch_tmap(&tmap_k);
     ptx::prefetch_tmap(&tmap_v);
+    if (kBias) ptx::prefetch_tmap(&tmap_bias);
   }
   if (warp == kMmaWarp) {
     ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
@@ -250,6 +262,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     ptx::setmaxnreg_dec<kControlRegs>();
     if (lane == 0) {
       uint32_t load_idx = 0;  // position in the CTA-wide K_0, V_0, K_1, V_1, ... sequence
+      [[maybe_unused]] uint32_t n_bias[2] = {0, 0};  // bias tiles loaded per query tile
       bool alive = true;
       uint32_t it = 0;
       for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
@@ -279,6 +292,26 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           for (int c = 0; c < C::kChunks; ++c)
             ptx::tma_load_4d(kv_smem + slot * C::kTileBytes + c * kChunkBytes, map, kv_full(slot), c * kChunkElems,
                              (i >> 1) * kBlockKV, item.head, item.batch);
+          if (kBias && (i & 1) == 0) {
+            // right behind K_j: the bias tile of key block j for each query tile (one buffer per
+            // tile, handed back by the softmax warpgroup as soon as it has read it)
+            const int j = i >> 1;
+            for (int t = 0; t < kQTiles && alive; ++t) {
+              if (j >= item.nblk[t]) continue;
+              if (!ptx::mbar_wait(bias_empty(t), (n_bias[t] & 1u) ^ 1u, ctl, kSiteLoadBias)) {
+                alive = false;
+                break;
+              }
+              ++n_bias[t];
+              ptx::mbar_expect_tx(bias_full(t), kBiasTileBytes);
+#pragma unroll
+              for (int c = 0; c < 2; ++c)
+                ptx::tma_load_4d(bias_smem + t * kBiasTileBytes + c * kChunkBytes, &tmap_bias, bias_full(t),
+                                 j * kBlockKV + c * kChunkElems, item.q0 + t * kBlockQ,
+                                 args.bias_strides[1] == 0 ? 0 : item.head, args.bias_strides[0] == 0 ? 0 : item.batch);
+            }
+            if (!alive) break;
+          }
         }
       }
     }
@@ -421,6 +454,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const uint32_t o_addr = tmem_base + lane_addr + C::kTmemO + t * kHeadDim;
       uint32_t n_s = 0;  // S tiles consumed
       uint32_t n_o = 0;  // items finished
+      [[maybe_unused]] uint32_t n_bias = 0;  // bias tiles consumed
       bool alive = true;
       uint32_t it = 0;
       for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
@@ -462,7 +496,34 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   #pragma unroll
               for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__uint_as_float(r[c][i]) * args.scale_log2);
             }
-            if (bias_row != nullptr) {
+            if (kBias) {
+              // The bias tile was brought in by TMA as two 128-byte-swizzled boxes of 64 keys; this
+              // thread reads its own row, 16 bytes at a time (8 consecutive rows touch 8 different
+              // 16-byte columns, so the reads are bank-conflict free).
+              if (!ptx::mbar_wait(bias_full(t), n_bias & 1u, ctl, kSiteSoftmaxBias)) {
+                alive = false;
+                break;
+              }
+              ++n_bias;
+              const uint8_t* tile = smem_gen + (bias_smem - smem_base) + t * kBiasTileBytes + row_in_tile * 128;
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const int grp = c * 4 + g;  // 16-byte group of 8 keys
+                  const uint4 w = *reinterpret_cast<const uint4*>(tile + (grp >> 3) * kChunkBytes +
+                                                                  (((grp & 7) ^ (row_in_tile & 7)) << 4));
+                  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const int i = g * 8 + e * 2;
+                    r[c][i] = __float_as_uint(fmaf(unpack_lo(ww[e], bf16), kLog2e, __uint_as_float(r[c][i])));
+                    r[c][i + 1] = __float_as_uint(fmaf(unpack_hi(ww[e], bf16), kLog2e, __uint_as_float(r[c][i + 1])));
+                  }
+                }
+              }
+              ptx::mbar_arrive(bias_empty(t));  // release semantics: the reads above are done
+            } else if (bias_row != nullptr) {
               const uint16_t* bp = bias_row + kv0;
               const int count = min(kBlockKV, args.T - kv0);
               if (args.bias_vec_ok && count == kBlockKV) {
@@ -643,9 +704,9 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   }
 }
 
-template <int kHeadDim, int kQTiles, int kPolyOf4>
+template <int kHeadDim, int kQTiles, int kPolyOf4, bool kBias>
 int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
-  using C = Cfg<kHeadDim, kQTiles>;
+  using C = Cfg<kHeadDim, kQTiles, kBias>;
   const CUtensorMapDataType dt = p.dtype == IXK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   auto make_map = [&](CUtensorMap* out, const void* base, const int64_t* strides, int rows) -> int {
     TmapSpec s{};
@@ -670,11 +731,32 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
     s.box[3] = 1;
     return encode_tmap(out, base, s);
   };
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, tbias;
   int rc;
   if ((rc = make_map(&tq, p.q, p.q_strides, p.F)) != IXK_OK) return rc;
   if ((rc = make_map(&tk, p.k, p.k_strides, p.T)) != IXK_OK) return rc;
   if ((rc = make_map(&tv, p.v, p.v_strides, p.T)) != IXK_OK) return rc;
+  tbias = tq;  // placeholder, never dereferenced unless kBias
+  if (kBias) {
+    // bias [B|1, N|1, F, T]: a broadcast dimension becomes extent 1 (coordinate always 0)
+    TmapSpec s{};
+    s.dtype = dt;
+    s.rank = 4;
+    s.swizzle128 = true;
+    s.dims[0] = p.T;
+    s.dims[1] = p.F;
+    s.dims[2] = p.bias_strides[1] == 0 ? 1 : p.N;
+    s.dims[3] = p.bias_strides[0] == 0 ? 1 : p.B;
+    const uint64_t row_pitch = static_cast<uint64_t>(p.bias_strides[2]) * 2;
+    s.strides_bytes[0] = row_pitch;
+    s.strides_bytes[1] = p.bias_strides[1] == 0 ? row_pitch * p.F : static_cast<uint64_t>(p.bias_strides[1]) * 2;
+    s.strides_bytes[2] = p.bias_strides[0] == 0 ? row_pitch * p.F * s.dims[2] : static_cast<uint64_t>(p.bias_strides[0]) * 2;
+    s.box[0] = kChunkElems;
+    s.box[1] = kBlockQ;
+    s.box[2] = 1;
+    s.box[3] = 1;
+    if ((rc = encode_tmap(&tbias, p.bias, s)) != IXK_OK) return rc;
+  }
 
   KernelArgs a{};
   a.B = p.B;
@@ -700,7 +782,7 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   a.bias_vec_ok = bias_vec ? 1 : 0;
   a.out_vec_ok = out_vec ? 1 : 0;
 
-  auto* fn = &fmha_prefill_kernel<kHeadDim, kQTiles, kPolyOf4>;
+  auto* fn = &fmha_prefill_kernel<kHeadDim, kQTiles, kPolyOf4, kBias>;
   static thread_local int configured_device = -1;
   if (configured_device != dev.device) {
     IXK_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
@@ -712,7 +794,7 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   if (items > 0x7fffffff) return fail(IXK_UNIMPLEMENTED, "too many (batch, head, query block) work items");
   a.num_items = static_cast<int>(items);
   const int grid = a.num_items < dev.sm_count ? a.num_items : dev.sm_count;
-  fn<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, a);
+  fn<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tbias, a);
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
   return IXK_OK;
@@ -720,23 +802,38 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
 
 }  // namespace
 
+// A bias whose rows start on 16-byte boundaries can be fetched by TMA; any other goes through
+// per-thread global loads in the softmax warps.
+bool bias_fits_tma(const Problem& p) {
+  if (p.bias == nullptr) return false;
+  if ((reinterpret_cast<uintptr_t>(p.bias) & 15u) != 0) return false;
+  if (p.bias_strides[2] % 8 != 0 || p.bias_strides[2] < p.T) return false;
+  return p.bias_strides[1] % 8 == 0 && p.bias_strides[0] % 8 == 0;
+}
+
+template <int kHeadDim, int kQTiles, int kPolyOf4>
+int launch_bias(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
+  if (bias_fits_tma(p)) return launch_cfg<kHeadDim, kQTiles, kPolyOf4, true>(p, dev, stream);
+  return launch_cfg<kHeadDim, kQTiles, kPolyOf4, false>(p, dev, stream);
+}
+
 int launch_prefill(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   // Head-size buckets follow the reference's policy pick (fmha_forward.h:621-646): <=64, <=128, <=256.
   constexpr int kPoly = 0;  // pairs of every four whose 2^x runs on the FMA pipe instead of the special-function unit
-  if (p.H <= 64) return p.F > kBlockQ ? launch_cfg<64, 2, kPoly>(p, dev, stream) : launch_cfg<64, 1, kPoly>(p, dev, stream);
+  if (p.H <= 64) return p.F > kBlockQ ? launch_bias<64, 2, kPoly>(p, dev, stream) : launch_bias<64, 1, kPoly>(p, dev, stream);
   if (p.H <= 128) {
-    if (p.F <= kBlockQ) return launch_cfg<128, 1, kPoly>(p, dev, stream);
+    if (p.F <= kBlockQ) return launch_bias<128, 1, kPoly>(p, dev, stream);
     // Tuning override for the main configuration: IXK_FMHA_POLY = 0..2.
     if (const char* env = std::getenv("IXK_FMHA_POLY")) {
       switch (std::atoi(env)) {
-        case 1: return launch_cfg<128, 2, 1>(p, dev, stream);
-        case 2: return launch_cfg<128, 2, 2>(p, dev, stream);
+        case 1: return launch_cfg<128, 2, 1, false>(p, dev, stream);
+        case 2: return launch_cfg<128, 2, 2, false>(p, dev, stream);
         default: break;
       }
     }
-    return launch_cfg<128, 2, kPoly>(p, dev, stream);
+    return launch_bias<128, 2, kPoly>(p, dev, stream);
   }
-  return launch_cfg<256, 1, kPoly>(p, dev, stream);
+  return launch_bias<256, 1, kPoly>(p, dev, stream);
 }
 
 }  // namespace fmha
