@@ -538,7 +538,8 @@ def run_layer(args, rank, world):
                 setattr(w, k, v.to(dev))
         x_host = torch.randn(B, S, 4096, generator=g).bfloat16().pin_memory()
         x = x_host.to(dev)
-        step = lambda: layers.gptj_layer_prefill(x, w, ops)
+        rope = layers.rotary_tables(torch.arange(S, device=dev), 64)
+        step = lambda: layers.gptj_layer_prefill(x, w, ops, rope=rope)
         work, div, unit, bound = layers.gptj_layer_flops(B, S), 1e12, "TFLOP/s", "tensor"
         metric = "GPT-J-6B-shaped decoder layer prefill TFLOP/s (bf16, tensor-parallel)"
         name = f"gptj_layer_prefill_B{B}_S{S}_hidden4096_heads16x256_mlp16384_tp{world}"
@@ -556,7 +557,8 @@ def run_layer(args, rank, world):
         k_cache = torch.randn(B, T, hl, 256, generator=gk, device=dev).bfloat16()
         v_cache = torch.randn(B, T, hl, 256, generator=gk, device=dev).bfloat16()
         ws = torch.empty(8 << 20, dtype=torch.uint8, device=dev)
-        step = lambda: layers.gemma_decode_step(x, w, k_cache, v_cache, T - 1, ops, workspace=ws)
+        rope = layers.rotary_tables(torch.tensor([T - 1], device=dev), 256)
+        step = lambda: layers.gemma_decode_step(x, w, k_cache, v_cache, T - 1, ops, workspace=ws, rope=rope)
         work, div, unit, bound = layers.gemma_decode_bytes(B, T), 1e9, "GB/s", "hbm"
         metric = "Gemma-7B-shaped decode step GB/s of algorithmic bytes (bf16, tensor-parallel)"
         name = f"gemma_decode_B{B}_T{T}_hidden3072_heads16x256_mlp24576_tp{world}"
@@ -574,6 +576,26 @@ def run_layer(args, rank, world):
         y = step()
         flush_l2(flush_buf)
     barrier()
+    # A layer step is a fixed sequence of ~10 library kernels and ~30 small glue kernels: on one GPU
+    # it is captured once into a CUDA graph and replayed, which removes the launch gaps (the decode
+    # step is launch-bound otherwise).  Multi-GPU runs launch eagerly (NCCL inside the step).
+    launches_per_step = None
+    use_graph = world == 1 and not args.no_graph
+    if use_graph:
+        n_before = pkg.launch_count()
+        cap_stream = torch.cuda.Stream()
+        cap_stream.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(cap_stream):
+            with torch.cuda.graph(graph, stream=cap_stream):
+                y = step()
+        torch.cuda.current_stream().wait_stream(cap_stream)
+        launches_per_step = pkg.launch_count() - n_before
+        eager_step = step
+        step = lambda: (graph.replay(), y)[1]
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
     n0 = pkg.launch_count()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -585,6 +607,8 @@ def run_layer(args, rank, world):
             flush_l2(flush_buf)
         torch.cuda.synchronize()
     launches = pkg.launch_count() - n0
+    if launches_per_step is not None:
+        launches = launches_per_step * args.steps   # replayed from the graph
     total_ms = float(sum(s.elapsed_time(e) for s, e in zip(starts, ends)))
     # end to end: host x in, host y out
     y_host = torch.empty(y.shape, dtype=y.dtype).pin_memory()
@@ -612,7 +636,8 @@ def run_layer(args, rank, world):
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (random-init weights ~N(0,0.02), activations ~N(0,1), seeded)",
         "config": {"workload": name, "parallelism": f"tp{world} by heads / MLP columns, all-reduce after row-parallel GEMMs",
-                   "l2": "L2 flushed (512 MB read+write) between timed steps"},
+                   "l2": "L2 flushed (512 MB read+write) between timed steps",
+                   "launch": "CUDA graph replay" if use_graph else "eager"},
         "clocks": clk.summary(),
         "e2e": {"value": work / (e2e_ms * 1e-3) / div, "unit": unit, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(x_host.numel() * 2), "d2h_bytes_per_step": int(y_host.numel() * 2)},
@@ -679,6 +704,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + list(LAYER_WORKLOADS))
     ap.add_argument("--no-others", action="store_true", help="skip the secondary workloads")
+    ap.add_argument("--no-graph", action="store_true", help="layer workloads: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-timed steps only (no e2e, no CPU baseline): the command profiled under ncu")
     args = ap.parse_args()

@@ -135,15 +135,17 @@ class GptJLayerWeights:
             heads_local=num_heads // world, head_dim=head_dim, rotary_dim=rotary_dim)
 
 
-def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None) -> torch.Tensor:
+def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None, rope=None) -> torch.Tensor:
     """GPT-J block, prefill: y = x + Attn(LN(x)) + MLP(LN(x)), x [B, S, hidden] replicated on every
     rank.  The attention-output and MLP-down partial sums are added locally (the second GEMM takes
-    the first as its C operand with beta = 1), so the block needs ONE all-reduce."""
+    the first as its C operand with beta = 1), so the block needs ONE all-reduce.  `rope` may carry
+    precomputed (cos, sin) tables for positions 0..S-1, which keeps the step free of host work (and
+    capturable in a CUDA graph)."""
     B, S, hidden = x.shape
     hl, hd = w.heads_local, w.head_dim
     h = layer_norm(x).view(B * S, hidden)
     qkv = ops.gemm(h, w.wqkv).view(B, S, 3, hl, hd)
-    cos, sin = rotary_tables(torch.arange(S, device=x.device), w.rotary_dim)
+    cos, sin = rope if rope is not None else rotary_tables(torch.arange(S, device=x.device), w.rotary_dim)
     apply_rotary_(qkv[:, :, 0], cos, sin, w.rotary_dim)
     apply_rotary_(qkv[:, :, 1], cos, sin, w.rotary_dim)
     q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))        # [B, hl, S, hd] views, no copies
@@ -188,15 +190,16 @@ class GemmaLayerWeights:
 
 
 def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                      position: int, ops, group=None, workspace=None) -> torch.Tensor:
+                      position: int, ops, group=None, workspace=None, rope=None) -> torch.Tensor:
     """One new token per sequence: x [B, 1, hidden]; k_cache / v_cache [B, T, heads_local, head_dim]
     (this rank's heads) are updated in place at `position` and attended over [0, position].
-    Two all-reduces: after the attention output projection and after the MLP down projection."""
+    Two all-reduces: after the attention output projection and after the MLP down projection.
+    `rope` may carry the precomputed (cos, sin) row for `position` (no host work in the step)."""
     B, _, hidden = x.shape
     hl, hd = w.heads_local, w.head_dim
     h = rms_norm(x).view(B, hidden)
     qkv = ops.gemm(h, w.wqkv).view(B, 1, 3, hl, hd)
-    cos, sin = rotary_tables(torch.tensor([position], device=x.device), hd)
+    cos, sin = rope if rope is not None else rotary_tables(torch.tensor([position], device=x.device), hd)
     apply_rotary_(qkv[:, :, 0], cos, sin, hd)
     apply_rotary_(qkv[:, :, 1], cos, sin, hd)
     k_cache[:, position] = qkv[:, 0, 1]
