@@ -526,7 +526,7 @@ def run_layer(args, rank, world):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
-    ops = layers.KernelOps(pkg)
+    ops = layers.KernelOps(pkg, gemm_workspace=torch.empty(32 << 20, dtype=torch.uint8, device=dev))
     full = _layer_weights(args.workload)
     g = torch.Generator().manual_seed(11)
     flush_buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=dev)

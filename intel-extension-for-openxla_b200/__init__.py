@@ -21,7 +21,7 @@ import torch
 
 __all__ = [
     "IxkError", "library_path", "load_library", "version", "launch_count", "device_status",
-    "EPILOGUES", "run_gemm_custom_call", "gemm_attrs_for", "gemm", "gemm_fp8",
+    "EPILOGUES", "run_gemm_custom_call", "gemm_attrs_for", "gemm", "gemm_fp8", "gemm_workspace_bytes",
     "fmha_forward_kernel", "fmha_forward_kernel_bf16", "fmha_forward_kernel_fp16", "fmha_workspace_bytes",
     "fmha_forward_kernel_static_scratch", "STATIC_SCRATCH_BYTES",
     "quantize_fp8",
@@ -159,12 +159,14 @@ def _require_cuda(*tensors) -> None:
 def run_gemm_custom_call(lhs: torch.Tensor, rhs: torch.Tensor, add: Optional[torch.Tensor],
                          output: torch.Tensor, bias: Optional[torch.Tensor], stream, attrs: dict,
                          epilogue: str, *, inv_scale_a: Optional[float] = None,
-                         inv_scale_b: Optional[float] = None) -> None:
+                         inv_scale_b: Optional[float] = None, workspace: Optional[torch.Tensor] = None) -> None:
     """RunGemmCustomCall (xla/service/gpu/sycl_onednn.cc:38-54): buffers + the FFI attribute
     dictionary RunGemm reads (xla/service/gpu/onednn_matmul_utils.cc:543-595).  `attrs` keys:
     {lhs,rhs,output}_{order,num_rows,num_cols,batch_stride,leading_dim_stride,layout_dtype},
     batch_size, alpha, beta.  `add` is the C operand read when beta != 0 (it may be `output`).
-    With inv_scale_a/b given the operands are fp8 and the scaled-GEMM entry point is used."""
+    With inv_scale_a/b given the operands are fp8 and the scaled-GEMM entry point is used.
+    `workspace` is the scratch the reference's handler passes down (sycl_onednn.h:37): skinny
+    problems (M <= 128) use it to split K over more SMs; see gemm_workspace_bytes()."""
     if epilogue not in EPILOGUES:
         raise IxkError(IXK_INVALID_ARGUMENT, "Unknown Epilogue.")  # onednn_matmul_utils.cc:52-54
     _require_cuda(lhs, rhs, add, output, bias)
@@ -183,12 +185,26 @@ def run_gemm_custom_call(lhs: torch.Tensor, rhs: torch.Tensor, add: Optional[tor
     d.epilogue = EPILOGUES.index(epilogue)
     d.reserved = 0
     sp = _stream_ptr(stream)
+    ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     if inv_scale_a is not None or inv_scale_b is not None:
         st = lib.ixk_gemm_fp8(ctypes.byref(d), _ptr(lhs), _ptr(rhs), _ptr(add), _ptr(bias), _ptr(output),
-                              float(inv_scale_a), float(inv_scale_b), None, 0, sp)
+                              float(inv_scale_a), float(inv_scale_b), _ptr(workspace), ws_bytes, sp)
     else:
-        st = lib.ixk_gemm(ctypes.byref(d), _ptr(lhs), _ptr(rhs), _ptr(add), _ptr(bias), _ptr(output), None, 0, sp)
+        st = lib.ixk_gemm(ctypes.byref(d), _ptr(lhs), _ptr(rhs), _ptr(add), _ptr(bias), _ptr(output),
+                          _ptr(workspace), ws_bytes, sp)
     _check(st)
+
+
+def gemm_workspace_bytes(lhs: torch.Tensor, rhs: torch.Tensor, out_shape=None) -> int:
+    """Scratch bytes ixk_gemm can make use of for lhs @ rhs (0 unless the problem is skinny)."""
+    d = _GemmDesc()
+    m, k = lhs.shape[-2], lhs.shape[-1]
+    n = rhs.shape[-1]
+    d.lhs.num_rows, d.lhs.num_cols, d.lhs.dtype = m, k, _TORCH_TO_IXK[lhs.dtype]
+    d.rhs.num_rows, d.rhs.num_cols = k, n
+    d.output.num_rows, d.output.num_cols = m, n
+    d.batch_size = lhs.shape[0] if lhs.dim() == 3 else 1
+    return int(load_library().ixk_gemm_workspace_bytes(ctypes.byref(d)))
 
 
 def _matrix_attrs(prefix: str, t: torch.Tensor) -> dict:
@@ -226,14 +242,14 @@ def gemm_attrs_for(lhs: torch.Tensor, rhs: torch.Tensor, output: torch.Tensor, b
 def gemm(lhs: torch.Tensor, rhs: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
          c: Optional[torch.Tensor] = None, beta: float = 0.0, epilogue: str = "DEFAULT",
          out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-         stream=None) -> torch.Tensor:
+         stream=None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = act(lhs @ rhs + bias + beta*c) through "__cublas$lt$matmul"'s path.  Any mix of
     row-/column-major 2-D (or batched 3-D) views is passed through as-is, never copied."""
     if out is None:
         shape = (*lhs.shape[:-1], rhs.shape[-1])
         out = torch.empty(shape, device=lhs.device, dtype=out_dtype or lhs.dtype)
     attrs = gemm_attrs_for(lhs, rhs, out, beta)
-    run_gemm_custom_call(lhs, rhs, c, out, bias, stream, attrs, epilogue)
+    run_gemm_custom_call(lhs, rhs, c, out, bias, stream, attrs, epilogue, workspace=workspace)
     return out
 
 

@@ -54,7 +54,8 @@ int check_layout(const ixk_matrix_layout& l, const char* name) {
 }
 
 int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, const void* bias,
-        void* d, bool fp8_call, float inv_scale_a, float inv_scale_b, void* stream) {
+        void* d, bool fp8_call, float inv_scale_a, float inv_scale_b, void* workspace, size_t workspace_bytes,
+        void* stream) {
   clear_error();
   if (desc == nullptr) return fail(IXK_INVALID_ARGUMENT, "desc is NULL");
   if (desc->reserved != 0) return fail(IXK_INVALID_ARGUMENT, "desc.reserved must be 0");
@@ -177,7 +178,25 @@ int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, 
 
   DeviceInfo dev;
   if ((rc = get_device_info(&dev)) != IXK_OK) return rc;
+  // Skinny problems are cut along K when the caller handed over enough scratch for the partials;
+  // without it they run un-split (same result, fewer SMs busy).
+  const int splits = p.force_block_n > 0 ? 1 : gemm::split_k_factor(p.M, p.N, p.K, p.batch, p.fp8);
+  if (splits > 1 && workspace != nullptr && aligned16(workspace) &&
+      workspace_bytes >= gemm::split_k_workspace_bytes(p.M, p.N, splits))
+    return gemm::launch_split_k(p, splits, workspace, dev, static_cast<cudaStream_t>(stream));
   return gemm::launch(p, dev, static_cast<cudaStream_t>(stream));
+}
+
+// Shape of the problem after the column-major-output rewrite, for the workspace query.
+size_t workspace_query(const ixk_gemm_desc* desc) {
+  if (desc == nullptr) return 0;
+  const bool swap = desc->output.order == IXK_COL_MAJOR;
+  const int64_t M = swap ? desc->output.num_cols : desc->output.num_rows;
+  const int64_t N = swap ? desc->output.num_rows : desc->output.num_cols;
+  const int64_t K = desc->lhs.num_cols;
+  const bool fp8 = is_fp8(desc->lhs.dtype);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  return gemm::split_k_workspace_bytes(M, N, gemm::split_k_factor(M, N, K, desc->batch_size, fp8));
 }
 
 }  // namespace
@@ -187,22 +206,16 @@ extern "C" {
 
 int ixk_gemm(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c,
              const void* bias, void* d, void* workspace, size_t workspace_bytes, void* cuda_stream) {
-  (void)workspace;
-  (void)workspace_bytes;
-  return ixk::run(desc, a, b, c, bias, d, /*fp8_call=*/false, 1.0f, 1.0f, cuda_stream);
+  return ixk::run(desc, a, b, c, bias, d, /*fp8_call=*/false, 1.0f, 1.0f, workspace, workspace_bytes, cuda_stream);
 }
 
-size_t ixk_gemm_workspace_bytes(const ixk_gemm_desc* desc) {
-  (void)desc;
-  return 0;
-}
+size_t ixk_gemm_workspace_bytes(const ixk_gemm_desc* desc) { return ixk::workspace_query(desc); }
 
 int ixk_gemm_fp8(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c,
                  const void* bias, void* d, float inv_scale_a, float inv_scale_b, void* workspace,
                  size_t workspace_bytes, void* cuda_stream) {
-  (void)workspace;
-  (void)workspace_bytes;
-  return ixk::run(desc, a, b, c, bias, d, /*fp8_call=*/true, inv_scale_a, inv_scale_b, cuda_stream);
+  return ixk::run(desc, a, b, c, bias, d, /*fp8_call=*/true, inv_scale_a, inv_scale_b, workspace, workspace_bytes,
+                  cuda_stream);
 }
 
 }  // extern "C"

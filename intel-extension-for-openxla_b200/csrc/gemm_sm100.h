@@ -52,5 +52,12 @@ struct KernelArgs {
 int pick_block_n(int64_t M, int64_t N, int64_t batch, int sm_count);
 int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream);
 
+// Split-K for skinny problems (gemm_splitk.cu): number of K chunks for a problem (1 = do not
+// split; depends on the shape only, so the workspace query needs no device), the fp32 scratch it
+// takes, and the two-kernel launch (partial GEMMs as a batch, then reduce + epilogue).
+int split_k_factor(int64_t M, int64_t N, int64_t K, int64_t batch, bool fp8);
+size_t split_k_workspace_bytes(int64_t M, int64_t N, int splits);
+int launch_split_k(const Problem& p, int splits, void* workspace, const DeviceInfo& dev, cudaStream_t stream);
+
 }  // namespace gemm
 }  // namespace ixk

@@ -1,0 +1,132 @@
+// Split-K for skinny GEMMs (M <= 128: decode-time projections, where the whole problem is one
+// stream of the weight matrix through the chip).  With a single row of output tiles there are too
+// few tiles to occupy 148 SMs, so the K range is cut into `splits` chunks that run as the batch
+// dimension of the tensor-core kernel (each chunk writes an fp32 partial [M, N] into the caller's
+// workspace), and this file's second kernel sums the partials and applies the epilogue once.
+// The reference reaches the same end with shared-local-memory k-slicing inside a work-group
+// (SLM_KS in xla/service/gpu/xetla/gemm/gemm_dispatch.h:183-214); here the slices are CTAs.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gemm_sm100.h"
+#include "ptx.cuh"
+
+namespace ixk {
+namespace gemm {
+
+namespace {
+
+constexpr int kAssumedSms = 148;
+constexpr int kSlabElems16 = 64;   // K elements per pipeline stage, 16-bit operands
+constexpr int kMinChunk = 512;     // smallest K chunk worth a CTA
+
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float u = 0.7978845608028654f * x * fmaf(0.044715f * x, x, 1.0f);
+  const float e = ptx::ex2_approx(-2.885390081777927f * u);
+  return __fdividef(x, 1.0f + e);
+}
+__device__ __forceinline__ float load_as_f32(const void* p, int64_t i, int dtype) {
+  if (dtype == IXK_F32) return static_cast<const float*>(p)[i];
+  const uint16_t h = static_cast<const uint16_t*>(p)[i];
+  return dtype == IXK_BF16 ? __uint_as_float(static_cast<uint32_t>(h) << 16) : __half2float(__ushort_as_half(h));
+}
+__device__ __forceinline__ void store_from_f32(void* p, int64_t i, int dtype, float v) {
+  if (dtype == IXK_F32) {
+    static_cast<float*>(p)[i] = v;
+  } else if (dtype == IXK_BF16) {
+    static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  } else {
+    static_cast<__half*>(p)[i] = __float2half_rn(v);
+  }
+}
+
+struct ReduceArgs {
+  const float* partial;  // [splits][M][N]
+  int splits, M, N;
+  const void* bias;
+  const void* c;
+  void* d;
+  int64_t ldc, ldd;
+  int out_dtype, bias_dtype, act;
+  float beta;
+};
+
+__global__ void splitk_reduce_kernel(const ReduceArgs a) {
+  const int64_t total = static_cast<int64_t>(a.M) * a.N;
+  const int64_t plane = total;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int m = static_cast<int>(i / a.N);
+    const int n = static_cast<int>(i - static_cast<int64_t>(m) * a.N);
+    float v = 0.0f;
+    for (int s = 0; s < a.splits; ++s) v += a.partial[s * plane + i];
+    if (a.bias != nullptr) v += load_as_f32(a.bias, n, a.bias_dtype);
+    if (a.c != nullptr) v = fmaf(a.beta, load_as_f32(a.c, static_cast<int64_t>(m) * a.ldc + n, a.out_dtype), v);
+    if (a.act == kActRelu) v = fmaxf(v, 0.0f);
+    if (a.act == kActGelu) v = gelu_tanh_f(v);
+    store_from_f32(a.d, static_cast<int64_t>(m) * a.ldd + n, a.out_dtype, v);
+  }
+}
+
+}  // namespace
+
+int split_k_factor(int64_t M, int64_t N, int64_t K, int64_t batch, bool fp8) {
+  if (batch != 1 || M > 128 || fp8) return 1;
+  const int64_t tiles = (N + 127) / 128;  // one row of 128 x 128 tiles
+  int64_t want = (5 * kAssumedSms / 2 + tiles - 1) / tiles;  // ~2.5 work units per SM
+  const int64_t cap = K / kMinChunk;
+  if (want > cap) want = cap;
+  // every chunk must be a whole number of pipeline slabs so that no chunk reads into the next
+  while (want > 1 && K % (want * kSlabElems16) != 0) --want;
+  return want < 2 ? 1 : static_cast<int>(want);
+}
+
+size_t split_k_workspace_bytes(int64_t M, int64_t N, int splits) {
+  return splits <= 1 ? 0 : static_cast<size_t>(splits) * M * N * sizeof(float);
+}
+
+int launch_split_k(const Problem& p, int splits, void* workspace, const DeviceInfo& dev, cudaStream_t stream) {
+  const int64_t chunk = p.K / splits;
+  Problem part = p;
+  part.K = chunk;
+  part.batch = splits;
+  part.a_batch_stride = p.a_mn_major ? chunk * p.lda : chunk;
+  part.b_batch_stride = p.b_mn_major ? chunk * p.ldb : chunk;
+  part.c = nullptr;
+  part.bias = nullptr;
+  part.beta = 0.0f;
+  part.act = kActNone;
+  part.d = workspace;
+  part.out_dtype = IXK_F32;
+  part.ldd = p.N;
+  part.d_batch_stride = p.M * p.N;
+  part.force_block_n = 128;
+  int rc = launch(part, dev, stream);
+  if (rc != IXK_OK) return rc;
+
+  ReduceArgs r{};
+  r.partial = static_cast<const float*>(workspace);
+  r.splits = splits;
+  r.M = static_cast<int>(p.M);
+  r.N = static_cast<int>(p.N);
+  r.bias = p.bias;
+  r.c = p.beta != 0.0f ? p.c : nullptr;
+  r.d = p.d;
+  r.ldc = p.ldc;
+  r.ldd = p.ldd;
+  r.out_dtype = p.out_dtype;
+  r.bias_dtype = p.bias_dtype;
+  r.act = p.act;
+  r.beta = p.beta;
+  const int64_t total = p.M * p.N;
+  const int threads = 256;
+  int64_t blocks = (total + threads - 1) / threads;
+  if (blocks > 4 * dev.sm_count) blocks = 4 * dev.sm_count;
+  splitk_reduce_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(r);
+  IXK_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return IXK_OK;
+}
+
+}  // namespace gemm
+}  // namespace ixk

@@ -25,11 +25,13 @@ import torch.distributed as dist
 class KernelOps:
     """The custom calls as the layers use them, bound to libixk.so."""
 
-    def __init__(self, pkg):
+    def __init__(self, pkg, gemm_workspace=None):
         self.pkg = pkg
+        self.gemm_workspace = gemm_workspace   # scratch for split-K of skinny (decode) GEMMs; may be None
 
     def gemm(self, x, w, *, bias=None, c=None, beta=0.0, epilogue="DEFAULT", out=None):
-        return self.pkg.gemm(x, w, bias=bias, c=c, beta=beta, epilogue=epilogue, out=out)
+        return self.pkg.gemm(x, w, bias=bias, c=c, beta=beta, epilogue=epilogue, out=out,
+                             workspace=self.gemm_workspace)
 
     def attention(self, q, k, v, out, *, scale, causal, workspace=None):
         """q/out [B,N,F,H] views, k/v [B,N,T,H] views."""

@@ -197,3 +197,33 @@ def test_empty_output_is_a_no_op(pkg, cuda):
     n0 = pkg.launch_count()
     out = pkg.gemm(x, w)
     assert out.shape == (0, 32) and pkg.launch_count() == n0
+
+
+@pytest.mark.parametrize("shape", [(64, 3072, 12288), (64, 4096, 3072), (64, 24576, 3072), (8, 1024, 256), (128, 2048, 1536)])
+@pytest.mark.parametrize("lb", ["row", "col"])
+def test_split_k_skinny(pkg, orc, cuda, shape, lb):
+    """Decode-shaped projections (M <= 128): with scratch the K range is split over CTAs and a
+    second kernel reduces the partials and applies the epilogue; results must match the un-split
+    path within accumulation-order noise, and the oracle within the usual tolerance."""
+    M, K, N = shape
+    g = torch.Generator().manual_seed(K + N)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(K, N, generator=g) * 0.03).bfloat16()
+    b = torch.randn(N, generator=g).bfloat16()
+    c = torch.randn(M, N, generator=g).bfloat16()
+    xd, wd, bd, cd = x.to(cuda), as_layout(w.to(cuda), lb), b.to(cuda), c.to(cuda)
+    need = pkg.gemm_workspace_bytes(xd, wd)
+    assert need > 0
+    ws = torch.empty(need, dtype=torch.uint8, device=cuda)
+    n0 = pkg.launch_count()
+    split = pkg.gemm(xd, wd, bias=bd, c=cd, beta=0.5, epilogue="BIAS_GELU", workspace=ws)
+    assert pkg.launch_count() == n0 + 2            # partial GEMMs + reduce
+    plain = pkg.gemm(xd, wd, bias=bd, c=cd, beta=0.5, epilogue="BIAS_GELU")
+    assert pkg.launch_count() == n0 + 3
+    want = orc.gemm_epilogue(f32(x) @ f32(w), f32(b), f32(c), 0.5, "BIAS_GELU", orc.BF16)
+    orc.check_close(f32(split), want, rtol=2e-2, atol=2e-2, what=f"split-K {shape}")
+    orc.check_close(f32(split), f32(plain), rtol=2e-2, atol=2e-2, what="split vs plain")
+    # too little scratch: silently runs un-split
+    n1 = pkg.launch_count()
+    small = pkg.gemm(xd, wd, workspace=ws[:64])
+    assert pkg.launch_count() == n1 + 1 and small.shape == (M, N)
