@@ -102,8 +102,10 @@ typedef struct ixk_gemm_desc {
  * (onednn_matmul_utils.cc:533-621) → hgemm_* kernels
  * (xetla/gemm/hgemm_impl.h:101-459) / dnnl::matmul (onednn_matmul_utils.cc:394-491).
  *
- *   D = act(A.B + bias[n]) + beta*C          fp32 accumulate, one rounding to D's type
+ *   D = act(A.B + bias[n] + beta*C)          fp32 accumulate, one rounding to D's type
  *
+ * (the residual is summed before the activation, as oneDNN's append_sum followed
+ * by the eltwise post-op does, onednn_matmul_utils.cc:434-449.)
  * act = identity | relu | gelu_tanh by `epilogue`.  bias is a length-N vector
  * of A's type, N being the column count AFTER a column-major output has been
  * rewritten as D^T = B^T.A^T (onednn_matmul_utils.cc:520-530, bias dims :363-365).
@@ -112,9 +114,12 @@ typedef struct ixk_gemm_desc {
  * (BF16,BF16,F32) (F16,F16,F32); others → IXK_UNIMPLEMENTED.
  * Requirements (else IXK_INVALID_ARGUMENT / IXK_UNIMPLEMENTED): pointers 16-byte
  * aligned, leading_dim_stride * sizeof(element) a multiple of 16 for A and B.
- * workspace is unused by the present kernels (ixk_gemm_workspace_bytes returns 0)
- * but kept in the signature because the reference hands its scratch allocator
- * down this path (sycl_onednn.h:37). */
+ * workspace is optional scratch (the reference hands its scratch allocator down
+ * this path, sycl_onednn.h:37).  ixk_gemm_workspace_bytes returns what a problem
+ * can use: non-zero only for skinny problems (M <= 128, one batch, a long K),
+ * which then run split along K with fp32 partials in the workspace and a reduce
+ * pass that applies the epilogue.  With workspace == NULL or fewer bytes the
+ * single-pass kernel runs; results agree within fp32 summation order. */
 int ixk_gemm(const ixk_gemm_desc* desc, const void* a, const void* b,
              const void* c, const void* bias, void* d, void* workspace,
              size_t workspace_bytes, void* cuda_stream);
