@@ -8,7 +8,7 @@
 //
 //   warps 0-3     softmax for query tile 0: one thread owns one row of S (a TMEM lane), so
 //   warps 4-7     softmax for query tile 1  row max / row sum need no cross-thread traffic
-//   warp 8        TMA producer: Q per work item, then K_0, V_0, K_1, V_1 ... through a shared-memory ring
+//   warp 8        TMA producer: Q_0, K_0, Q_1, V_0, K_1, V_1 ... (K/V through a shared-memory ring)
 //   warp 9        tcgen05.mma issuer (one thread, alternating between the tiles):
 //                                      S_t = Q_t.K_j^T  (A, B from shared memory, S in TMEM)
 //                                      O_t += P_t.V_j   (A = P from TMEM, B = V from shared memory)
@@ -23,11 +23,19 @@
 // so that P.V starts on the first 64 keys while the rest is still being exponentiated.  P overwrites
 // S in place in TMEM as packed 16-bit pairs.  The running maximum is only raised when it moved by more than 2^8
 // (exact: the same stale maximum scales P, the row sum and O), which keeps the O rescale off
-// the common path.  exp is evaluated as exp2 with head_scale*log2(e) folded in.
+// the common path.  exp is evaluated as exp2 with head_scale*log2(e) folded in.  bf16 P is cut
+// out of the fp32 bit pattern by a byte permute (a rounding conversion shares the quarter-rate
+// pipe with ex2); the mean truncation loss is compensated in the exponent and the row sum.
+// O leaves through a swizzled staging box per tile and TMA stores: stores issued from registers
+// (16 bytes per lane, a different line each) queue thousands of requests at every item boundary
+// and hold up the barrier traffic of every other warp.  Q has a full/empty pair per tile, each
+// K/V slot is handed back once per use behind the last tile's MMAs: a tcgen05.commit or a barrier
+// round trip costs the single issuing thread 50-120 cycles during which the tensor core drains.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <type_traits>
 
 #include "fmha_sm100.h"
 #include "ptx.cuh"
@@ -49,6 +57,8 @@ constexpr int kSoftmaxRegs = 216;  // per-thread register budgets after re-parti
 constexpr int kControlRegs = 64;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kTruncInflate = 1.0028179f;     // 1 + 2^-8 * (1 / (2 ln 2)): mean relative loss of bf16 truncation
+constexpr float kTruncBiasLog2 = 0.0040597f;    // log2(kTruncInflate)
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 enum : int { kSiteLoad = 201, kSiteMmaQ = 202, kSiteMmaKV = 203, kSiteMmaP = 204, kSiteSoftmaxS = 205, kSiteEpilogueO = 206,
@@ -64,7 +74,10 @@ struct Cfg {
   static constexpr int kKvSlots = (kHeadDim == 256) ? 2 : (kBias ? 3 : 4);
   static constexpr int kQBytes = kQTiles * kTileBytes;
   static constexpr int kBiasBytes = kBias ? kQTiles * kBiasTileBytes : 0;
-  static constexpr int kSmemBytes = kQBytes + kKvSlots * kTileBytes + kBiasBytes + 256 + 1024;
+  // O leaves through shared memory and TMA stores, one 64-column box per query tile at a time
+  // (no room is left for it beside the TMA-fed bias tiles: that variant stores from registers)
+  static constexpr int kStageBytes = kBias ? 0 : kQTiles * kChunkBytes;
+  static constexpr int kSmemBytes = kQBytes + kKvSlots * kTileBytes + kBiasBytes + kStageBytes + 320 + 1024;
   static_assert(kSmemBytes <= 232448, "shared memory budget");
   static constexpr int kTmemS = 0;                                // S_t at columns [128 t, 128 t + 128)
   static constexpr int kTmemO = 128 * kQTiles;                    // O_t at kTmemO + t * kHeadDim
@@ -82,6 +95,7 @@ struct KernelArgs {
   uint16_t* out;
   int64_t o_strides[3];
   int out_vec_ok;
+  int out_tma;  // O rows start on 16-byte boundaries: store through shared memory + TMA
   float* lse;
   int* status_word;
   int num_qblocks;  // query blocks of kBlockQ * kQTiles rows per (batch, head)
@@ -103,18 +117,38 @@ __device__ __forceinline__ float unpack_hi(uint32_t w, bool bf16) {
   return bf16 ? __uint_as_float(w & 0xffff0000u) : __half2float(__ushort_as_half(static_cast<uint16_t>(w >> 16)));
 }
 
-// Optional self-timing (compiled in only with -DIXK_FMHA_TRACE, for pipeline studies): CTA 0
-// stamps clock64() at the hand-over points of its first work item into a device array that
-// ixk_debug_fmha_trace() copies out.
+// Optional self-timing, compiled in only with -DIXK_FMHA_TRACE (pipeline studies; never part of
+// the shipped library).  CTA 0 stamps clock64() into a device array of [10 kinds][32 rows][8
+// events] that ixk_debug_fmha_trace() copies out:
+//   kinds 0-7  softmax warp w, row = 16 * (item - 1) + key block, for the CTA's 2nd and 3rd item
+//   kind  8    the MMA issuer, same rows
+//   kind  9    row = item: issuer loop-top (event 0; event 1 for the last CTA) and producer events
+//              4-7; rows 8 + key block of the 2nd item: issuer bookkeeping between two key blocks
+// The macros use the enclosing scope's `it` (item counter) and, for IXK_TRACE, `trace_on`.
 #ifdef IXK_FMHA_TRACE
-__device__ long long g_fmha_trace[9 * 32 * 8];
-#define IXK_TRACE(kind, j, ev)                                                              \
-  do {                                                                                       \
-    if (blockIdx.x == 0 && (j) < 32 && trace_on) g_fmha_trace[((kind)*32 + (j)) * 8 + (ev)] = clock64(); \
+__device__ long long g_fmha_trace[10 * 32 * 8];
+#define IXK_TRACE(kind, j, ev)                                                                \
+  do {                                                                                         \
+    if (blockIdx.x == 0 && (j) < 16 && trace_on)                                               \
+      g_fmha_trace[((kind)*32 + (it - 1) * 16 + (j)) * 8 + (ev)] = clock64();                  \
+  } while (0)
+#define IXK_HTRACE(jj, col)                                                                    \
+  do {                                                                                         \
+    if (blockIdx.x == 0 && it == 1 && (jj) < 16) g_fmha_trace[(9 * 32 + 8 + (jj)) * 8 + (col)] = clock64(); \
+  } while (0)
+#define IXK_PTRACE(col)                                                                        \
+  do {                                                                                         \
+    if (blockIdx.x == 0 && it < 8) g_fmha_trace[(9 * 32 + it) * 8 + (col)] = clock64();        \
   } while (0)
 #else
 #define IXK_TRACE(kind, j, ev) \
   do {                         \
+  } while (0)
+#define IXK_HTRACE(jj, col) \
+  do {                      \
+  } while (0)
+#define IXK_PTRACE(col) \
+  do {                  \
   } while (0)
 #endif
 
@@ -122,8 +156,9 @@ __device__ long long g_fmha_trace[9 * 32 * 8];
 // query tiles visits.
 struct Item {
   int q0, head, batch;
-  int nblk[2];
+  int nblk0, nblk1;  // key blocks of query tile 0 / 1 (scalars: a runtime index would put an array in local memory)
   int nblk_max;
+  __device__ __forceinline__ int nblk(int t) const { return t == 0 ? nblk0 : nblk1; }
 };
 
 template <int kQTiles>
@@ -138,17 +173,17 @@ __device__ __forceinline__ Item get_item(const KernelArgs& args, int w) {
   const int qb = args.causal ? (args.num_qblocks - 1 - rank) : rank;
   it.q0 = qb * (kBlockQ * kQTiles);
   const int kv_blocks_all = (args.T + kBlockKV - 1) / kBlockKV;
-  it.nblk[0] = it.nblk[1] = 0;
+  it.nblk0 = it.nblk1 = 0;
 #pragma unroll
   for (int t = 0; t < kQTiles; ++t) {
     const int row0 = it.q0 + t * kBlockQ;
     if (row0 < args.F) {
       int n = kv_blocks_all;
       if (args.causal) n = min(n, (row0 + kBlockQ - 1) / kBlockKV + 1);
-      it.nblk[t] = n;
+      if (t == 0) it.nblk0 = n; else it.nblk1 = n;
     }
   }
-  it.nblk_max = max(it.nblk[0], it.nblk[1]);
+  it.nblk_max = max(it.nblk0, it.nblk1);
   return it;
 }
 
@@ -196,7 +231,7 @@ template <int kHeadDim, int kQTiles, int kPolyOf4, bool kBias>
 __global__ void __launch_bounds__(kThreads, 1)
 fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_bias,
-                    const KernelArgs args) {
+                    const __grid_constant__ CUtensorMap tmap_o, const KernelArgs args) {
   using C = Cfg<kHeadDim, kQTiles, kBias>;
   constexpr int kSlots = C::kKvSlots;
 
@@ -206,10 +241,13 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t q_smem = smem_base;
   const uint32_t kv_smem = smem_base + C::kQBytes;
   const uint32_t bias_smem = kv_smem + kSlots * C::kTileBytes;  // kQTiles tiles when kBias
-  const uint32_t bar_base = bias_smem + C::kBiasBytes;
+  const uint32_t stage_smem = bias_smem + C::kBiasBytes;        // kQTiles boxes of 128 rows x 128 bytes
+  const uint32_t bar_base = stage_smem + C::kStageBytes;
   // barriers (8 bytes each)
-  const uint32_t q_full = bar_base;
-  const uint32_t q_empty = bar_base + 8u;
+  // Q has a full/empty pair per query tile: tile 0 issues its last S half a step before tile 1, and
+  // the next item's first S then needs only 32 KB of Q instead of 64 KB to have arrived.
+  auto q_full = [&](int t) { return bar_base + 8u * (t == 0 ? 0 : 22 + 2 * kSlots); };
+  auto q_empty = [&](int t) { return bar_base + 8u * (t == 0 ? 1 : 23 + 2 * kSlots); };
   auto kv_full = [&](int s) { return bar_base + 8u * (2 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (2 + kSlots + s); };
   auto s_full = [&](int t) { return bar_base + 8u * (2 + 2 * kSlots + t); };
@@ -218,7 +256,9 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   auto o_free = [&](int t) { return bar_base + 8u * (14 + 2 * kSlots + t); };
   auto bias_full = [&](int t) { return bar_base + 8u * (16 + 2 * kSlots + t); };
   auto bias_empty = [&](int t) { return bar_base + 8u * (18 + 2 * kSlots + t); };
-  uint8_t* tail = smem_gen + C::kQBytes + kSlots * C::kTileBytes + C::kBiasBytes + 8 * (20 + 2 * kSlots);
+  auto stage_sync = [&](int t) { return bar_base + 8u * (20 + 2 * kSlots + t); };
+  uint8_t* tail = smem_gen + (bar_base - smem_base) + 8 * (24 + 2 * kSlots);
+  static_assert(8 * (24 + 2 * kSlots) + 8 <= 320, "barrier area");
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
@@ -228,11 +268,13 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    ptx::mbar_init(q_full, 1);
-    ptx::mbar_init(q_empty, kQTiles);  // every issuer releases Q and each K/V slot
+    for (int t = 0; t < 2; ++t) {
+      ptx::mbar_init(q_full(t), 1);
+      ptx::mbar_init(q_empty(t), 1);
+    }
     for (int s = 0; s < kSlots; ++s) {
       ptx::mbar_init(kv_full(s), 1);
-      ptx::mbar_init(kv_empty(s), kQTiles);
+      ptx::mbar_init(kv_empty(s), 1);  // released once per use, behind the last tile's MMAs
     }
     for (int t = 0; t < 2; ++t) {
       ptx::mbar_init(s_full(t), 1);
@@ -241,12 +283,14 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       ptx::mbar_init(o_free(t), 128);
       ptx::mbar_init(bias_full(t), 1);
       ptx::mbar_init(bias_empty(t), 128);
+      ptx::mbar_init(stage_sync(t), 128);
     }
     ptx::fence_mbar_init();
     ptx::prefetch_tmap(&tmap_q);
     ptx::prefetch_tmap(&tmap_k);
     ptx::prefetch_tmap(&tmap_v);
     if (kBias) ptx::prefetch_tmap(&tmap_bias);
+    if (C::kStageBytes > 0) ptx::prefetch_tmap(&tmap_o);
   }
   if (warp == kMmaWarp) {
     ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
@@ -262,30 +306,46 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     ptx::setmaxnreg_dec<kControlRegs>();
     if (lane == 0) {
       uint32_t load_idx = 0;  // position in the CTA-wide K_0, V_0, K_1, V_1, ... sequence
-      [[maybe_unused]] uint32_t n_bias[2] = {0, 0};  // bias tiles loaded per query tile
+      [[maybe_unused]] uint32_t n_bias0 = 0, n_bias1 = 0;  // bias tiles loaded per query tile
       bool alive = true;
       uint32_t it = 0;
       for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
         const Item item = get_item<kQTiles>(args, w);
-        if (!ptx::mbar_wait(q_empty, (it & 1u) ^ 1u, ctl, kSiteLoadQ)) break;
-        int valid_tiles = 0;
-        for (int t = 0; t < kQTiles; ++t) valid_tiles += item.nblk[t] > 0 ? 1 : 0;
-        ptx::mbar_expect_tx(q_full, valid_tiles * C::kTileBytes);
-        for (int t = 0; t < kQTiles; ++t) {
-          if (item.nblk[t] == 0) continue;
+        IXK_PTRACE(7);
+        // Q of tile t, once the tile's last S of the previous item has been issued.  A tile with
+        // no rows in this item still completes its phase, so that parities follow the item count.
+        auto load_q = [&](int t) {
+          if (!ptx::mbar_wait(q_empty(t), (it & 1u) ^ 1u, ctl, kSiteLoadQ)) {
+            alive = false;
+            return;
+          }
+          if (item.nblk(t) == 0) {
+            ptx::mbar_arrive(q_full(t));
+            return;
+          }
+          ptx::mbar_expect_tx(q_full(t), C::kTileBytes);
 #pragma unroll
           for (int c = 0; c < C::kChunks; ++c)
-            ptx::tma_load_4d(q_smem + t * C::kTileBytes + c * kChunkBytes, &tmap_q, q_full, c * kChunkElems,
+            ptx::tma_load_4d(q_smem + t * C::kTileBytes + c * kChunkBytes, &tmap_q, q_full(t), c * kChunkElems,
                              item.q0 + t * kBlockQ, item.head, item.batch);
-        }
+        };
+        load_q(0);
+        if (!alive) break;
+        IXK_PTRACE(4);
         const int loads = 2 * item.nblk_max;
         for (int i = 0; i < loads; ++i, ++load_idx) {
+          if (kQTiles == 2 && i == 1) {  // order: Q_0, K_0, Q_1, V_0, K_1, ...
+            load_q(1);
+            if (!alive) break;
+            IXK_PTRACE(5);
+          }
           const int slot = load_idx % kSlots;
           const uint32_t use = load_idx / kSlots;
           if (!ptx::mbar_wait(kv_empty(slot), (use & 1u) ^ 1u, ctl, kSiteLoad)) {
             alive = false;
             break;
           }
+          if (i == 0) IXK_PTRACE(6);
           const CUtensorMap* map = (i & 1) ? &tmap_v : &tmap_k;
           ptx::mbar_expect_tx(kv_full(slot), C::kTileBytes);
 #pragma unroll
@@ -297,12 +357,12 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             // tile, handed back by the softmax warpgroup as soon as it has read it)
             const int j = i >> 1;
             for (int t = 0; t < kQTiles && alive; ++t) {
-              if (j >= item.nblk[t]) continue;
-              if (!ptx::mbar_wait(bias_empty(t), (n_bias[t] & 1u) ^ 1u, ctl, kSiteLoadBias)) {
+              if (j >= item.nblk(t)) continue;
+              if (!ptx::mbar_wait(bias_empty(t), ((t == 0 ? n_bias0 : n_bias1) & 1u) ^ 1u, ctl, kSiteLoadBias)) {
                 alive = false;
                 break;
               }
-              ++n_bias[t];
+              if (t == 0) ++n_bias0; else ++n_bias1;
               ptx::mbar_expect_tx(bias_full(t), kBiasTileBytes);
 #pragma unroll
               for (int c = 0; c < 2; ++c)
@@ -351,8 +411,8 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           mma_ts(d, a + ks * 8, vb + ((ks * 2048) >> 4), v_hi, idesc_o, (accumulate || k2 != 0) ? 1u : 0u);
         }
       };
-      // A K/V slot (and Q) is released once per tile: through tcgen05.commit when the tile's MMAs
-      // read it, by a plain arrive when the tile had no work on it.
+      // Q of a tile is released through tcgen05.commit when the tile's MMAs read it, by a plain
+      // arrive when the tile had no work on it.
       auto release = [&](uint32_t bar, bool used) {
         if (used) {
           ptx::umma_commit(bar);
@@ -362,7 +422,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       };
 
       uint32_t cons_idx = 0;                      // position in the K_0, V_0, K_1, ... sequence
-      uint32_t n_p[2] = {0, 0}, n_item[2] = {0, 0};  // per tile: P blocks consumed, items taken part in
+      uint32_t n_p0 = 0, n_p1 = 0, n_item0 = 0, n_item1 = 0;  // per tile: P blocks consumed, items taken part in
       uint32_t it = 0;
       bool alive = true;
       auto wait = [&](uint32_t bar, uint32_t parity, int site) {
@@ -371,19 +431,26 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       };
       for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
         const Item item = get_item<kQTiles>(args, w);
-        [[maybe_unused]] const bool trace_on = it == 1;
-        if (!wait(q_full, it & 1u, kSiteMmaQ)) break;
+        [[maybe_unused]] const bool trace_on = it == 1 || it == 2;
+#ifdef IXK_FMHA_TRACE
+        if (it < 8 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
+          g_fmha_trace[(9 * 32 + it) * 8 + (blockIdx.x == 0 ? 0 : 1)] = clock64();
+#endif
+        if (!wait(q_full(0), it & 1u, kSiteMmaQ)) break;
+        IXK_TRACE(8, 0, 3);
         {
           const int slot = cons_idx % kSlots;
           if (!wait(kv_full(slot), (cons_idx / kSlots) & 1u, kSiteMmaKV)) break;
           ptx::tc_fence_after_sync();
-          for (int t = 0; t < kQTiles; ++t) {
-            if (item.nblk[t] > 0) {
+          IXK_TRACE(8, 0, 7);
+          for (int t = 0; t < kQTiles && alive; ++t) {
+            if (t == 1 && !wait(q_full(1), it & 1u, kSiteMmaQ)) break;
+            if (item.nblk(t) > 0) {
               issue_s(t, slot);
               ptx::umma_commit(s_full(t));
             }
-            release(kv_empty(slot), item.nblk[t] > 0);
-            if (item.nblk_max == 1) release(q_empty, item.nblk[t] > 0);
+            if (t == kQTiles - 1) ptx::umma_commit(kv_empty(slot));
+            if (item.nblk_max == 1) release(q_empty(t), item.nblk(t) > 0);
           }
           ++cons_idx;
         }
@@ -392,18 +459,23 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           const int v_slot = cons_idx % kSlots;
           const uint32_t k_idx = cons_idx + 1;  // K_{j+1}, present when `more`
           const int k_slot = k_idx % kSlots;
-          // Every tile waits for the data even when it skips the block, so that its plain
-          // arrive cannot land in the slot's previous release phase.
+          // V_j and K_{j+1} are both needed in this step; asking for them here, where the issuer
+          // would otherwise idle until P arrives, keeps the round trips off the MMA sequence.
+          if (j > 0) IXK_HTRACE(j - 1, 3);
           if (!wait(kv_full(v_slot), (cons_idx / kSlots) & 1u, kSiteMmaKV)) break;
-          bool k_ready = false;
+          if (j > 0) IXK_HTRACE(j - 1, 4);
+          if (more && !wait(kv_full(k_slot), (k_idx / kSlots) & 1u, kSiteMmaKV)) break;
+          if (j > 0) IXK_HTRACE(j - 1, 5);
+          ptx::tc_fence_after_sync();
+          if (j > 0) IXK_TRACE(8, j, 7);
           for (int t = 0; t < kQTiles && alive; ++t) {
-            const bool active = j < item.nblk[t];
-            const bool next_s = (j + 1) < item.nblk[t];
+            const bool active = j < item.nblk(t);
+            const bool next_s = (j + 1) < item.nblk(t);
             if (active) {
               // O_t of the previous item must have been read out before it is overwritten
-              if (j == 0 && !wait(o_free(t), (n_item[t] & 1u) ^ 1u, kSiteMmaO)) break;
+              if (j == 0 && !wait(o_free(t), ((t == 0 ? n_item0 : n_item1) & 1u) ^ 1u, kSiteMmaO)) break;
               for (int part = 0; part < kParts; ++part) {
-                if (!wait(p_part(t, part), n_p[t] & 1u, kSiteMmaP)) break;
+                if (!wait(p_part(t, part), (t == 0 ? n_p0 : n_p1) & 1u, kSiteMmaP)) break;
                 ptx::tc_fence_after_sync();
                 IXK_TRACE(8, j, t * 4 + (part == 0 ? 0 : 1));
 #pragma unroll
@@ -413,27 +485,28 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 }
               }
               if (!alive) break;
-              ++n_p[t];
+              if (t == 0) ++n_p0; else ++n_p1;
+              if (j > 0 && t == 0) IXK_TRACE(8, j, 3);
             }
-            release(kv_empty(v_slot), active);
-            if (more) {
-              if (!k_ready) {  // K_{j+1} is first needed here
-                if (!wait(kv_full(k_slot), (k_idx / kSlots) & 1u, kSiteMmaKV)) break;
-                ptx::tc_fence_after_sync();
-                k_ready = true;
-              }
-              if (next_s) {
-                issue_s(t, k_slot);
-                ptx::umma_commit(s_full(t));
-                IXK_TRACE(8, j, t * 4 + 2);
-              }
-              release(kv_empty(k_slot), next_s);
+            if (more && next_s) {
+              issue_s(t, k_slot);
+              ptx::umma_commit(s_full(t));
+              IXK_TRACE(8, j, t * 4 + 2);
+            }
+            // Both slots go back behind the last tile's MMAs (a commit covers everything this
+            // thread has issued so far, the other tile's work included).
+            if (t == kQTiles - 1) {
+              IXK_HTRACE(j, 0);
+              ptx::umma_commit(kv_empty(v_slot));
+              IXK_HTRACE(j, 1);
+              if (more) ptx::umma_commit(kv_empty(k_slot));
+              IXK_HTRACE(j, 2);
             }
             if (active && !next_s) {
               ptx::umma_commit(o_final(t));
-              ++n_item[t];
+              if (t == 0) ++n_item0; else ++n_item1;
             }
-            if (j == item.nblk_max - 2) release(q_empty, next_s);  // the item's last S has been issued
+            if (j == item.nblk_max - 2) release(q_empty(t), next_s);  // the item's last S has been issued
           }
           cons_idx += more ? 2 : 1;
         }
@@ -454,13 +527,14 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const uint32_t o_addr = tmem_base + lane_addr + C::kTmemO + t * kHeadDim;
       uint32_t n_s = 0;  // S tiles consumed
       uint32_t n_o = 0;  // items finished
+      [[maybe_unused]] uint32_t n_sync = 0;  // rendezvous of this tile's four warps around the staging box
       [[maybe_unused]] uint32_t n_bias = 0;  // bias tiles consumed
       bool alive = true;
       uint32_t it = 0;
       for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
         const Item item = get_item<kQTiles>(args, w);
-        [[maybe_unused]] const bool trace_on = it == 1 && lane == 0;
-        const int my_blocks = item.nblk[t];
+        [[maybe_unused]] const bool trace_on = (it == 1 || it == 2) && lane == 0;
+        const int my_blocks = item.nblk(t);
         if (my_blocks == 0) continue;
         const int q0 = item.q0, head = item.head, batch = item.batch;
         const int f = q0 + t * kBlockQ + row_in_tile;
@@ -471,6 +545,9 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                      static_cast<int64_t>(f) * args.bias_strides[2];
         float m_run = -INFINITY;
         float l_run = 0.0f;
+        // The staging box must be free again before this item's epilogue: its owner checks here,
+        // and its first P arrival below orders the check before every thread's o_final.
+        if (C::kStageBytes > 0 && row_in_tile == 0) ptx::bulk_wait_group_read<0>();
         for (int j = 0; j < my_blocks; ++j) {
           if (!ptx::mbar_wait(s_full(t), n_s & 1u, ctl, kSiteSoftmaxS)) {
             alive = false;
@@ -607,12 +684,21 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           IXK_TRACE(warp, j, 2);
           const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
           const uint64_t mult2 = ptx::f32x2(mult, mult);
-          const uint64_t negm2 = ptx::f32x2(-m_use, -m_use);
+          // bf16 P is made by truncating the fp32 bit pattern (one byte-permute per pair) instead of
+          // a rounding conversion: conversions share the quarter-rate pipe with ex2, and at one per
+          // pair they cost half as much again as the exponentials.  Truncation loses 0.28 % on
+          // average (half an ulp over a log-uniform mantissa), so the exponent carries that much
+          // extra (kTruncBias) and the row sum is deflated by the same factor in the epilogue.
+          const bool trunc = bf16;
+          const float bias_log2 = trunc ? kTruncBiasLog2 : 0.0f;
+          const uint64_t negm2 = ptx::f32x2(bias_log2 - m_use, bias_log2 - m_use);
           uint64_t sum_a = ptx::f32x2(0.0f, 0.0f), sum_b = ptx::f32x2(0.0f, 0.0f);
           // P (16-bit pairs) overwrites the first 64 columns of this tile's S: the 32 scores of
           // chunk c become 16 packed columns at [16 c, 16 c + 16), already read by this thread.
           // Of every four pairs, kPolyOf4 take their 2^x from the FMA pipe, the rest from the
           // special-function unit, so that neither pipe alone bounds the softmax.
+          auto exp_block = [&](auto trunc_tag) {
+          constexpr bool kTrunc = decltype(trunc_tag)::value;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t pk[16];
@@ -630,16 +716,24 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 p1 = ptx::ex2_approx(x1);
                 sum_a = ptx::add2(sum_a, ptx::f32x2(p0, p1));
               }
-              pk[i >> 1] = pack2(p0, p1, bf16);
+              pk[i >> 1] = kTrunc ? __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632) : pack2(p0, p1, false);
             }
             ptx::tmem_st_32x16(s_addr + c * 16, pk);
             if ((c + 1) % (4 / kParts) == 0) {
               // hand over this part of P
+              if (j + 2 < my_blocks) IXK_TRACE(warp, j, c == 1 ? 3 : 5);
               ptx::tmem_st_wait();
+              if (j + 2 < my_blocks && c == 3) IXK_TRACE(warp, j, 7);
               ptx::tc_fence_before_sync();
               ptx::mbar_arrive(p_part(t, c / (4 / kParts)));
               IXK_TRACE(warp, j, 3 + c);
             }
+          }
+          };
+          if (trunc) {
+            exp_block(std::true_type{});
+          } else {
+            exp_block(std::false_type{});
           }
           float s0, s1;
           ptx::f32x2_split(ptx::add2(sum_a, sum_b), s0, s1);
@@ -653,10 +747,75 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
         ++n_o;
         ptx::tc_fence_after_sync();
-        const float inv_l = 1.0f / l_run;
+        IXK_TRACE(warp, my_blocks - 1, 5);
+        const float inv_l = (bf16 ? kTruncInflate : 1.0f) / l_run;  // the row sum carries the truncation bias
         uint16_t* orow = args.out + batch * args.o_strides[0] + head * args.o_strides[1] +
                          static_cast<int64_t>(f) * args.o_strides[2];
         constexpr int kOChunks = kHeadDim / 32;
+        if (C::kStageBytes > 0 && args.out_tma) {
+          // Rows go to a 128-byte-swizzled staging box (thread = row, so each st.shared.v4 of a
+          // warp covers every bank once per eight rows) and leave as one TMA store per 64 columns:
+          // from registers a warp's 16-byte stores would land in 32 different lines each, and
+          // that many requests hold up every other warp's shared-memory and barrier traffic.
+          const uint32_t stage = stage_smem + t * kChunkBytes;
+          const uint32_t my_row = stage + row_in_tile * 128;
+          const bool elected = row_in_tile == 0;
+          auto rendezvous = [&]() {
+            ptx::mbar_arrive(stage_sync(t));
+            if (!ptx::mbar_wait(stage_sync(t), n_sync & 1u, ctl, kSiteEpilogueO)) alive = false;
+            ++n_sync;
+          };
+          // 128 columns at a time live in registers; the TMEM copy of O_t is handed back as soon
+          // as its last column has been read, well before the stores are on their way.
+          constexpr int kHalves = kHeadDim > 128 ? kHeadDim / 128 : 1;
+          constexpr int kPassesPerHalf = (kHeadDim / 64) / kHalves;
+#pragma unroll 1
+          for (int h = 0; h < kHalves && alive; ++h) {
+            uint32_t o[2 * kPassesPerHalf][32];
+#pragma unroll
+            for (int c = 0; c < 2 * kPassesPerHalf; ++c) ptx::tmem_ld_32x32(o_addr + h * 128 + c * 32, o[c]);
+            ptx::tmem_ld_wait();
+            if (h == kHalves - 1) {
+              ptx::tc_fence_before_sync();
+              ptx::mbar_arrive(o_free(t));  // the next item's P.V may overwrite O_t
+            }
+            IXK_TRACE(warp, my_blocks - 1, 3);
+#pragma unroll
+            for (int c = 0; c < kPassesPerHalf; ++c) {
+              uint32_t wv[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                wv[i] = pack2(__uint_as_float(o[2 * c + (i >> 4)][2 * (i & 15)]) * inv_l,
+                              __uint_as_float(o[2 * c + (i >> 4)][2 * (i & 15) + 1]) * inv_l, bf16);
+              if (h + c > 0) {
+                // the box still holds the previous 64 columns until their store has read them
+                // (at the item's first pass that was settled before this item's first P hand-over)
+                if (elected) ptx::bulk_wait_group_read<0>();
+                rendezvous();
+                if (!alive) break;
+                IXK_TRACE(warp, my_blocks - 2, 5);
+              }
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                const uint32_t addr = my_row + static_cast<uint32_t>((g ^ (row_in_tile & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(wv[4 * g]),
+                             "r"(wv[4 * g + 1]), "r"(wv[4 * g + 2]), "r"(wv[4 * g + 3])
+                             : "memory");
+              }
+              ptx::fence_proxy_async_smem();
+              IXK_TRACE(warp, my_blocks - 2, c == 0 ? 1 : 2);
+              rendezvous();
+              if (!alive) break;
+              IXK_TRACE(warp, my_blocks - 2, c == 0 ? 3 : 7);
+              const int col0 = h * 128 + c * 64;
+              if (elected && col0 < args.H) {
+                ptx::tma_store_4d(&tmap_o, stage, col0, q0 + t * kBlockQ, head, batch);
+                ptx::bulk_commit_group();
+              }
+            }
+          }
+          if (!alive) break;
+        } else {
 #pragma unroll 1
         for (int c = 0; c < kOChunks; ++c) {
           uint32_t o[32];
@@ -687,14 +846,18 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             }
           }
         }
+        }
+        IXK_TRACE(warp, my_blocks - 1, 7);
         if (args.lse != nullptr && row_ok) {
           const int64_t idx = (static_cast<int64_t>(batch) * args.N + head) * args.F + f;
-          args.lse[idx] = (m_run + log2f(l_run)) * kLn2;
+          args.lse[idx] = (m_run + log2f(l_run) - (bf16 ? kTruncBiasLog2 : 0.0f)) * kLn2;
         }
       }
     }
   }
 
+  // the staging boxes must outlive the TMA stores that read them
+  if (C::kStageBytes > 0 && warp < 4 * kQTiles && (threadIdx.x & 127) == 0) ptx::bulk_wait_group<0>();
   if (*abort_flag != 0) __nanosleep(2000000);
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -736,6 +899,11 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   if ((rc = make_map(&tq, p.q, p.q_strides, p.F)) != IXK_OK) return rc;
   if ((rc = make_map(&tk, p.k, p.k_strides, p.T)) != IXK_OK) return rc;
   if ((rc = make_map(&tv, p.v, p.v_strides, p.T)) != IXK_OK) return rc;
+  CUtensorMap to = tq;  // placeholder unless O qualifies for TMA stores
+  bool out_tma = C::kStageBytes > 0 && (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0;
+  for (int i = 0; i < 3; ++i) out_tma = out_tma && p.o_strides[i] % 8 == 0;
+  out_tma = out_tma && p.o_strides[2] >= p.H;
+  if (out_tma && (rc = make_map(&to, p.out, p.o_strides, p.F)) != IXK_OK) return rc;
   tbias = tq;  // placeholder, never dereferenced unless kBias
   if (kBias) {
     // bias [B|1, N|1, F, T]: a broadcast dimension becomes extent 1 (coordinate always 0)
@@ -781,6 +949,7 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   }
   a.bias_vec_ok = bias_vec ? 1 : 0;
   a.out_vec_ok = out_vec ? 1 : 0;
+  a.out_tma = out_tma ? 1 : 0;
 
   auto* fn = &fmha_prefill_kernel<kHeadDim, kQTiles, kPolyOf4, kBias>;
   static thread_local int configured_device = -1;
@@ -793,8 +962,11 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   const int64_t items = static_cast<int64_t>(a.num_qblocks) * p.N * p.B;
   if (items > 0x7fffffff) return fail(IXK_UNIMPLEMENTED, "too many (batch, head, query block) work items");
   a.num_items = static_cast<int>(items);
-  const int grid = a.num_items < dev.sm_count ? a.num_items : dev.sm_count;
-  fn<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tbias, a);
+  int grid = a.num_items < dev.sm_count ? a.num_items : dev.sm_count;
+#ifdef IXK_FMHA_TRACE
+  if (const char* e = std::getenv("IXK_FMHA_GRID")) grid = std::min(grid, std::max(1, std::atoi(e)));
+#endif
+  fn<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tbias, to, a);
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
   return IXK_OK;
