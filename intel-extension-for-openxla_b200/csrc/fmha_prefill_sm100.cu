@@ -158,7 +158,15 @@ struct Item {
   int q0, head, batch;
   int nblk0, nblk1;  // key blocks of query tile 0 / 1 (scalars: a runtime index would put an array in local memory)
   int nblk_max;
+  int reversed;  // key blocks are walked from the diagonal down to block 0 (causal)
   __device__ __forceinline__ int nblk(int t) const { return t == 0 ? nblk0 : nblk1; }
+  // The item takes nblk_max steps; tile t takes part in nblk(t) consecutive ones: the first
+  // nblk(t) in forward order, the last nblk(t) in reversed order (every tile ends on block 0).
+  __device__ __forceinline__ int first(int t) const { return reversed ? nblk_max - nblk(t) : 0; }
+  __device__ __forceinline__ bool active(int t, int step) const {
+    return step >= first(t) && step < first(t) + nblk(t);
+  }
+  __device__ __forceinline__ int key_block(int step) const { return reversed ? nblk_max - 1 - step : step; }
 };
 
 template <int kQTiles>
@@ -184,6 +192,11 @@ __device__ __forceinline__ Item get_item(const KernelArgs& args, int w) {
     }
   }
   it.nblk_max = max(it.nblk0, it.nblk1);
+  // Under a causal mask the second tile sees one key block more than the first.  Walking the
+  // blocks backwards puts the step that only one tile takes part in at the START of the item,
+  // where the other tile is still busy with the previous item's epilogue and its Q has not
+  // arrived yet, instead of at the end, where it would leave half of the tensor core idle.
+  it.reversed = args.causal ? 1 : 0;
   return it;
 }
 
@@ -329,13 +342,15 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             ptx::tma_load_4d(q_smem + t * C::kTileBytes + c * kChunkBytes, &tmap_q, q_full(t), c * kChunkElems,
                              item.q0 + t * kBlockQ, item.head, item.batch);
         };
-        load_q(0);
+        // the tile that starts the item gets its Q first (tile 1 when the blocks run backwards)
+        const int first_tile = (kQTiles == 2 && item.reversed) ? 1 : 0;
+        load_q(first_tile);
         if (!alive) break;
         IXK_PTRACE(4);
         const int loads = 2 * item.nblk_max;
         for (int i = 0; i < loads; ++i, ++load_idx) {
           if (kQTiles == 2 && i == 1) {  // order: Q_0, K_0, Q_1, V_0, K_1, ...
-            load_q(1);
+            load_q(1 - first_tile);
             if (!alive) break;
             IXK_PTRACE(5);
           }
@@ -351,13 +366,13 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
           for (int c = 0; c < C::kChunks; ++c)
             ptx::tma_load_4d(kv_smem + slot * C::kTileBytes + c * kChunkBytes, map, kv_full(slot), c * kChunkElems,
-                             (i >> 1) * kBlockKV, item.head, item.batch);
+                             item.key_block(i >> 1) * kBlockKV, item.head, item.batch);
           if (kBias && (i & 1) == 0) {
             // right behind K_j: the bias tile of key block j for each query tile (one buffer per
             // tile, handed back by the softmax warpgroup as soon as it has read it)
             const int j = i >> 1;
             for (int t = 0; t < kQTiles && alive; ++t) {
-              if (j >= item.nblk(t)) continue;
+              if (!item.active(t, j)) continue;
               if (!ptx::mbar_wait(bias_empty(t), ((t == 0 ? n_bias0 : n_bias1) & 1u) ^ 1u, ctl, kSiteLoadBias)) {
                 alive = false;
                 break;
@@ -367,7 +382,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
               for (int c = 0; c < 2; ++c)
                 ptx::tma_load_4d(bias_smem + t * kBiasTileBytes + c * kChunkBytes, &tmap_bias, bias_full(t),
-                                 j * kBlockKV + c * kChunkElems, item.q0 + t * kBlockQ,
+                                 item.key_block(j) * kBlockKV + c * kChunkElems, item.q0 + t * kBlockQ,
                                  args.bias_strides[1] == 0 ? 0 : item.head, args.bias_strides[0] == 0 ? 0 : item.batch);
             }
             if (!alive) break;
@@ -390,7 +405,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const uint64_t mnmajor = ptx::umma_smem_desc(0, kChunkBytes, 1024);
       const uint32_t k_lo = static_cast<uint32_t>(kmajor), k_hi = static_cast<uint32_t>(kmajor >> 32);
       const uint32_t v_lo = static_cast<uint32_t>(mnmajor), v_hi = static_cast<uint32_t>(mnmajor >> 32);
-      auto issue_s = [&](int t, int slot) {
+      auto issue_s = [&](int t, uint32_t slot) {
         const uint32_t qa = k_lo + ((q_smem + t * C::kTileBytes) >> 4);
         const uint32_t kb = k_lo + ((kv_smem + slot * C::kTileBytes) >> 4);
         const uint32_t d = tmem_base + C::kTmemS + t * 128;
@@ -401,7 +416,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
       };
       // quarter q covers keys [32 q, 32 q + 32) of the block = P columns [16 q, 16 q + 16)
-      auto issue_pv = [&](int t, int slot, int quarter, bool accumulate) {
+      auto issue_pv = [&](int t, uint32_t slot, int quarter, bool accumulate) {
         const uint32_t vb = v_lo + ((kv_smem + slot * C::kTileBytes) >> 4);
         const uint32_t d = tmem_base + C::kTmemO + t * kHeadDim;
         const uint32_t a = tmem_base + C::kTmemS + t * 128;
@@ -421,94 +436,123 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
       };
 
-      uint32_t cons_idx = 0;                      // position in the K_0, V_0, K_1, ... sequence
-      uint32_t n_p0 = 0, n_p1 = 0, n_item0 = 0, n_item1 = 0;  // per tile: P blocks consumed, items taken part in
+      // Everything this thread does between two MMAs leaves the tensor core idle once its short
+      // queue has drained, so the loop carries its state incrementally (ring slot and parity bits,
+      // no divisions) and the per-tile code is instantiated with the tile as a constant.
+      uint32_t slot = 0, slot_par = 0;  // ring slot of the next K/V tile to consume, parity of that use
+      auto advance = [&]() {
+        if (++slot == static_cast<uint32_t>(kSlots)) {
+          slot = 0;
+          slot_par ^= 1u;
+        }
+      };
+      uint32_t p_par0 = 0, p_par1 = 0;    // parity of the next P block of each tile
+      uint32_t of_par0 = 1, of_par1 = 1;  // parity on which o_free reports the previous item's O read out
+      uint32_t q_par = 0;                 // parity of this item's q_full phases
       uint32_t it = 0;
       bool alive = true;
       auto wait = [&](uint32_t bar, uint32_t parity, int site) {
         if (!ptx::mbar_wait(bar, parity, ctl, site)) alive = false;
         return alive;
       };
-      for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
+      for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it), q_par ^= 1u) {
         const Item item = get_item<kQTiles>(args, w);
         [[maybe_unused]] const bool trace_on = it == 1 || it == 2;
 #ifdef IXK_FMHA_TRACE
         if (it < 8 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
           g_fmha_trace[(9 * 32 + it) * 8 + (blockIdx.x == 0 ? 0 : 1)] = clock64();
 #endif
-        if (!wait(q_full(0), it & 1u, kSiteMmaQ)) break;
-        IXK_TRACE(8, 0, 3);
+        const int nblk_max = item.nblk_max;
+        const int first0 = item.first(0), end0 = first0 + item.nblk0;
+        const int first1 = item.first(1), end1 = first1 + item.nblk1;
+        // One tile's share of step j: O_t += P_j.V_j, then S_t = Q_t.K_{j+1} for its next step.
+        auto tile_turn = [&](auto tile_tag, int j, bool more, uint32_t v_slot, uint32_t k_slot) {
+          constexpr int t = decltype(tile_tag)::value;
+          const int first = t == 0 ? first0 : first1;
+          const int end = t == 0 ? end0 : end1;
+          const bool active = j >= first && j < end;
+          const bool next_s = j + 1 >= first && j + 1 < end;
+          uint32_t& p_par = t == 0 ? p_par0 : p_par1;
+          uint32_t& of_par = t == 0 ? of_par0 : of_par1;
+          if (active) {
+            // O_t of the previous item must have been read out before it is overwritten
+            if (j == first && !wait(o_free(t), of_par, kSiteMmaO)) return;
+            for (int part = 0; part < kParts; ++part) {
+              if (!wait(p_part(t, part), p_par, kSiteMmaP)) return;
+              ptx::tc_fence_after_sync();
+              IXK_TRACE(8, j, t * 4 + (part == 0 ? 0 : 1));
+#pragma unroll
+              for (int q4 = 0; q4 < 4 / kParts; ++q4) {
+                const int quarter = part * (4 / kParts) + q4;
+                issue_pv(t, v_slot, quarter, j > first || quarter > 0);
+              }
+            }
+            p_par ^= 1u;
+            if (j > 0 && t == 0) IXK_TRACE(8, j, 3);
+          }
+          if (next_s) {
+            if (!active) {  // the tile joins at the next step: its Q is first needed here
+              if (!wait(q_full(t), q_par, kSiteMmaQ)) return;
+              ptx::tc_fence_after_sync();
+            }
+            issue_s(t, k_slot);
+            ptx::umma_commit(s_full(t));
+            IXK_TRACE(8, j, t * 4 + 2);
+          }
+          // Both slots go back behind the last tile's MMAs (a commit covers everything this
+          // thread has issued so far, the other tile's work included).
+          if (t == kQTiles - 1) {
+            IXK_HTRACE(j, 0);
+            ptx::umma_commit(kv_empty(v_slot));
+            IXK_HTRACE(j, 1);
+            if (more) ptx::umma_commit(kv_empty(k_slot));
+            IXK_HTRACE(j, 2);
+          }
+          if (active && !next_s) {
+            ptx::umma_commit(o_final(t));
+            of_par ^= 1u;
+          }
+          if (j == nblk_max - 2) release(q_empty(t), next_s);  // the item's last S has been issued
+        };
+        auto first_s = [&](auto tile_tag, uint32_t k_slot) {
+          constexpr int t = decltype(tile_tag)::value;
+          if ((t == 0 ? first0 : first1) == 0 && item.nblk(t) > 0) {  // a tile's Q is awaited where its first S is issued
+            if (!wait(q_full(t), q_par, kSiteMmaQ)) return;
+            ptx::tc_fence_after_sync();
+            IXK_TRACE(8, 0, 3);
+            issue_s(t, k_slot);
+            ptx::umma_commit(s_full(t));
+          }
+          if (t == kQTiles - 1) ptx::umma_commit(kv_empty(k_slot));
+          if (nblk_max == 1) release(q_empty(t), item.nblk(t) > 0);
+        };
         {
-          const int slot = cons_idx % kSlots;
-          if (!wait(kv_full(slot), (cons_idx / kSlots) & 1u, kSiteMmaKV)) break;
+          if (!wait(kv_full(slot), slot_par, kSiteMmaKV)) break;
           ptx::tc_fence_after_sync();
           IXK_TRACE(8, 0, 7);
-          for (int t = 0; t < kQTiles && alive; ++t) {
-            if (t == 1 && !wait(q_full(1), it & 1u, kSiteMmaQ)) break;
-            if (item.nblk(t) > 0) {
-              issue_s(t, slot);
-              ptx::umma_commit(s_full(t));
-            }
-            if (t == kQTiles - 1) ptx::umma_commit(kv_empty(slot));
-            if (item.nblk_max == 1) release(q_empty(t), item.nblk(t) > 0);
-          }
-          ++cons_idx;
+          first_s(std::integral_constant<int, 0>{}, slot);
+          if (kQTiles == 2 && alive) first_s(std::integral_constant<int, kQTiles - 1>{}, slot);
+          advance();
         }
-        for (int j = 0; j < item.nblk_max && alive; ++j) {
-          const bool more = (j + 1) < item.nblk_max;
-          const int v_slot = cons_idx % kSlots;
-          const uint32_t k_idx = cons_idx + 1;  // K_{j+1}, present when `more`
-          const int k_slot = k_idx % kSlots;
+        for (int j = 0; j < nblk_max && alive; ++j) {
+          const bool more = (j + 1) < nblk_max;
           // V_j and K_{j+1} are both needed in this step; asking for them here, where the issuer
           // would otherwise idle until P arrives, keeps the round trips off the MMA sequence.
+          const uint32_t v_slot = slot;
           if (j > 0) IXK_HTRACE(j - 1, 3);
-          if (!wait(kv_full(v_slot), (cons_idx / kSlots) & 1u, kSiteMmaKV)) break;
+          if (!wait(kv_full(v_slot), slot_par, kSiteMmaKV)) break;
+          advance();
+          const uint32_t k_slot = slot;  // K_{j+1}, present when `more`
           if (j > 0) IXK_HTRACE(j - 1, 4);
-          if (more && !wait(kv_full(k_slot), (k_idx / kSlots) & 1u, kSiteMmaKV)) break;
+          if (more) {
+            if (!wait(kv_full(k_slot), slot_par, kSiteMmaKV)) break;
+            advance();
+          }
           if (j > 0) IXK_HTRACE(j - 1, 5);
           ptx::tc_fence_after_sync();
           if (j > 0) IXK_TRACE(8, j, 7);
-          for (int t = 0; t < kQTiles && alive; ++t) {
-            const bool active = j < item.nblk(t);
-            const bool next_s = (j + 1) < item.nblk(t);
-            if (active) {
-              // O_t of the previous item must have been read out before it is overwritten
-              if (j == 0 && !wait(o_free(t), ((t == 0 ? n_item0 : n_item1) & 1u) ^ 1u, kSiteMmaO)) break;
-              for (int part = 0; part < kParts; ++part) {
-                if (!wait(p_part(t, part), (t == 0 ? n_p0 : n_p1) & 1u, kSiteMmaP)) break;
-                ptx::tc_fence_after_sync();
-                IXK_TRACE(8, j, t * 4 + (part == 0 ? 0 : 1));
-#pragma unroll
-                for (int q4 = 0; q4 < 4 / kParts; ++q4) {
-                  const int quarter = part * (4 / kParts) + q4;
-                  issue_pv(t, v_slot, quarter, j > 0 || quarter > 0);
-                }
-              }
-              if (!alive) break;
-              if (t == 0) ++n_p0; else ++n_p1;
-              if (j > 0 && t == 0) IXK_TRACE(8, j, 3);
-            }
-            if (more && next_s) {
-              issue_s(t, k_slot);
-              ptx::umma_commit(s_full(t));
-              IXK_TRACE(8, j, t * 4 + 2);
-            }
-            // Both slots go back behind the last tile's MMAs (a commit covers everything this
-            // thread has issued so far, the other tile's work included).
-            if (t == kQTiles - 1) {
-              IXK_HTRACE(j, 0);
-              ptx::umma_commit(kv_empty(v_slot));
-              IXK_HTRACE(j, 1);
-              if (more) ptx::umma_commit(kv_empty(k_slot));
-              IXK_HTRACE(j, 2);
-            }
-            if (active && !next_s) {
-              ptx::umma_commit(o_final(t));
-              if (t == 0) ++n_item0; else ++n_item1;
-            }
-            if (j == item.nblk_max - 2) release(q_empty(t), next_s);  // the item's last S has been issued
-          }
-          cons_idx += more ? 2 : 1;
+          tile_turn(std::integral_constant<int, 0>{}, j, more, v_slot, k_slot);
+          if (kQTiles == 2 && alive) tile_turn(std::integral_constant<int, kQTiles - 1>{}, j, more, v_slot, k_slot);
         }
       }
     }
@@ -561,7 +605,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32(s_addr + c * 32, r[c]);
           ptx::tmem_ld_wait();
           IXK_TRACE(warp, j, 1);
-          const int kv0 = j * kBlockKV;
+          const int kv0 = (item.reversed ? my_blocks - 1 - j : j) * kBlockKV;
           // Scores enter the exponential as x = r * mult - m.  Fast path: r is the raw Q.K^T and
           // mult = head_scale * log2(e) (> 0, so the row maximum can be taken on r).  With a bias
           // or a non-positive scale, r is first rewritten as the full log2-domain score and mult = 1.
