@@ -212,16 +212,23 @@ __device__ __forceinline__ int item_of(uint32_t round) {
 // tcgen05.mma with the shared-memory descriptors passed as (lo, hi) halves: the high half is a
 // per-operand constant and the low half is a base plus a compile-time offset, which keeps the
 // single issuing thread at a handful of instructions per MMA.
+//
+// The issuing warp runs its whole loop with all 32 lanes (uniform control flow) and elects one lane
+// per instruction: the descriptor arithmetic then stays in the uniform datapath, and an MMA costs
+// 10-20 issue cycles where the same code under `if (lane == 0)` takes about 50, which is most of
+// the 64 cycles the MMA runs, so that the tensor core's queue never fills and every barrier round
+// trip between two MMAs shows up as idle time.
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                        uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t"
-      ".reg .pred p;\n\t"
+      ".reg .pred p, e;\n\t"
       ".reg .b64 da, db;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
       "setp.ne.b32 p, %6, 0;\n\t"
       "mov.b64 da, {%1, %2};\n\t"
       "mov.b64 db, {%3, %4};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
       "}\n" ::"r"(d_tmem),
       "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
@@ -230,13 +237,25 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_
                                        uint32_t accumulate) {
   asm volatile(
       "{\n\t"
-      ".reg .pred p;\n\t"
+      ".reg .pred p, e;\n\t"
       ".reg .b64 db;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
       "setp.ne.b32 p, %5, 0;\n\t"
       "mov.b64 db, {%2, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
       "}\n" ::"r"(d_tmem),
       "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// tcgen05.commit by one elected lane of a converged warp.
+__device__ __forceinline__ void commit_elect(uint32_t bar) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}\n" ::"r"(bar)
       : "memory");
 }
 
@@ -391,9 +410,9 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
     }
   } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ MMA issuer (all 32 lanes)
     ptx::setmaxnreg_dec<kControlRegs>();
-    if (lane == 0) {
+    {
       const uint32_t fmt = args.is_bf16 ? 1u : 0u;
       // S = Q.K^T : M=128, N=128 keys, both operands K-major (head dim contiguous)
       const uint32_t idesc_s = ptx::umma_idesc(fmt, fmt, 0, 0, kBlockQ, kBlockKV);
@@ -430,8 +449,8 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       // arrive when the tile had no work on it.
       auto release = [&](uint32_t bar, bool used) {
         if (used) {
-          ptx::umma_commit(bar);
-        } else {
+          commit_elect(bar);
+        } else if (lane == 0) {
           ptx::mbar_arrive(bar);
         }
       };
@@ -457,9 +476,9 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       };
       for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it), q_par ^= 1u) {
         const Item item = get_item<kQTiles>(args, w);
-        [[maybe_unused]] const bool trace_on = it == 1 || it == 2;
+        [[maybe_unused]] const bool trace_on = (it == 1 || it == 2) && lane == 0;
 #ifdef IXK_FMHA_TRACE
-        if (it < 8 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
+        if (it < 8 && lane == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
           g_fmha_trace[(9 * 32 + it) * 8 + (blockIdx.x == 0 ? 0 : 1)] = clock64();
 #endif
         const int nblk_max = item.nblk_max;
@@ -496,20 +515,20 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
               ptx::tc_fence_after_sync();
             }
             issue_s(t, k_slot);
-            ptx::umma_commit(s_full(t));
+            commit_elect(s_full(t));
             IXK_TRACE(8, j, t * 4 + 2);
           }
           // Both slots go back behind the last tile's MMAs (a commit covers everything this
           // thread has issued so far, the other tile's work included).
           if (t == kQTiles - 1) {
             IXK_HTRACE(j, 0);
-            ptx::umma_commit(kv_empty(v_slot));
+            commit_elect(kv_empty(v_slot));
             IXK_HTRACE(j, 1);
-            if (more) ptx::umma_commit(kv_empty(k_slot));
+            if (more) commit_elect(kv_empty(k_slot));
             IXK_HTRACE(j, 2);
           }
           if (active && !next_s) {
-            ptx::umma_commit(o_final(t));
+            commit_elect(o_final(t));
             of_par ^= 1u;
           }
           if (j == nblk_max - 2) release(q_empty(t), next_s);  // the item's last S has been issued
@@ -521,9 +540,9 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             ptx::tc_fence_after_sync();
             IXK_TRACE(8, 0, 3);
             issue_s(t, k_slot);
-            ptx::umma_commit(s_full(t));
+            commit_elect(s_full(t));
           }
-          if (t == kQTiles - 1) ptx::umma_commit(kv_empty(k_slot));
+          if (t == kQTiles - 1) commit_elect(kv_empty(k_slot));
           if (nblk_max == 1) release(q_empty(t), item.nblk(t) > 0);
         };
         {
