@@ -248,17 +248,6 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_
       : "memory");
 }
 
-// tcgen05.commit by one elected lane of a converged warp.
-__device__ __forceinline__ void commit_elect(uint32_t bar) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred e;\n\t"
-      "elect.sync _|e, 0xffffffff;\n\t"
-      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
-      "}\n" ::"r"(bar)
-      : "memory");
-}
-
 template <int kHeadDim, int kQTiles, int kPolyOf4, bool kBias>
 __global__ void __launch_bounds__(kThreads, 1)
 fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -449,7 +438,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       // arrive when the tile had no work on it.
       auto release = [&](uint32_t bar, bool used) {
         if (used) {
-          commit_elect(bar);
+          ptx::umma_commit_elect(bar);
         } else if (lane == 0) {
           ptx::mbar_arrive(bar);
         }
@@ -515,20 +504,20 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
               ptx::tc_fence_after_sync();
             }
             issue_s(t, k_slot);
-            commit_elect(s_full(t));
+            ptx::umma_commit_elect(s_full(t));
             IXK_TRACE(8, j, t * 4 + 2);
           }
           // Both slots go back behind the last tile's MMAs (a commit covers everything this
           // thread has issued so far, the other tile's work included).
           if (t == kQTiles - 1) {
             IXK_HTRACE(j, 0);
-            commit_elect(kv_empty(v_slot));
+            ptx::umma_commit_elect(kv_empty(v_slot));
             IXK_HTRACE(j, 1);
-            if (more) commit_elect(kv_empty(k_slot));
+            if (more) ptx::umma_commit_elect(kv_empty(k_slot));
             IXK_HTRACE(j, 2);
           }
           if (active && !next_s) {
-            commit_elect(o_final(t));
+            ptx::umma_commit_elect(o_final(t));
             of_par ^= 1u;
           }
           if (j == nblk_max - 2) release(q_empty(t), next_s);  // the item's last S has been issued
@@ -540,9 +529,9 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             ptx::tc_fence_after_sync();
             IXK_TRACE(8, 0, 3);
             issue_s(t, k_slot);
-            commit_elect(s_full(t));
+            ptx::umma_commit_elect(s_full(t));
           }
-          if (t == kQTiles - 1) commit_elect(kv_empty(k_slot));
+          if (t == kQTiles - 1) ptx::umma_commit_elect(kv_empty(k_slot));
           if (nblk_max == 1) release(q_empty(t), item.nblk(t) > 0);
         };
         {

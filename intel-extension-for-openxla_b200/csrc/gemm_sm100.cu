@@ -221,7 +221,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // (all 32 lanes walk the loop; an elected lane issues the copies)
+    {
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
@@ -238,8 +239,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const uint32_t a_dst = smem_base + stage * C::kStageBytes;
           const uint32_t b_dst = a_dst + kATileBytes;
           const uint32_t bar = full_bar(stage);
-          ptx::mbar_expect_tx(bar, C::kStageBytes);
           const int k0 = kb * kSlabElems;
+          if (ptx::elect_one()) {
+          ptx::mbar_expect_tx(bar, C::kStageBytes);
           if (args.a_mn_major) {
             // box = [kSlabElems k-rows][128 bytes of M]; one box per 128-byte column block
 #pragma unroll
@@ -257,6 +259,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           } else {
             ptx::tma_load_3d(b_dst, &tmap_b, bar, k0, n0, bz);
           }
+          }
+          __syncwarp();
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -266,7 +270,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // (all 32 lanes walk the loop; an elected lane issues each MMA and commit)
+    {
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
@@ -295,16 +300,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int ks = 0; ks < kSlabElems / kUmmaK; ++ks) {
             const uint64_t da = ptx::umma_smem_desc(a_src + ks * a_kstep, a_lbo, 1024);
             const uint64_t db = ptx::umma_smem_desc(b_src + ks * b_kstep, b_lbo, 1024);
-            ptx::umma_ss<kFp8>(d_tmem, da, db, args.idesc, (kb | ks) != 0 ? 1u : 0u);
+            ptx::umma_ss_elect<kFp8>(d_tmem, da, db, args.idesc, (kb | ks) != 0 ? 1u : 0u);
           }
-          ptx::umma_commit(empty_bar(stage));
+          ptx::umma_commit_elect(empty_bar(stage));
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!alive) break;
-        ptx::umma_commit(acc_full_bar(buf));
+        ptx::umma_commit_elect(acc_full_bar(buf));
         buf ^= 1;
         if (buf == 0) acc_phase ^= 1u;
       }
