@@ -196,7 +196,9 @@ __device__ __forceinline__ Item get_item(const KernelArgs& args, int w) {
   // blocks backwards puts the step that only one tile takes part in at the START of the item,
   // where the other tile is still busy with the previous item's epilogue and its Q has not
   // arrived yet, instead of at the end, where it would leave half of the tensor core idle.
-  it.reversed = args.causal ? 1 : 0;
+  // (With one tile per item nothing is gained, and the forward walk keeps the CTAs that share a
+  // head on the same key blocks at the same time, which L2 rewards.)
+  it.reversed = (args.causal && kQTiles == 2) ? 1 : 0;
   return it;
 }
 
@@ -474,7 +476,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const int first0 = item.first(0), end0 = first0 + item.nblk0;
         const int first1 = item.first(1), end1 = first1 + item.nblk1;
         // One tile's share of step j: O_t += P_j.V_j, then S_t = Q_t.K_{j+1} for its next step.
-        auto tile_turn = [&](auto tile_tag, int j, bool more, uint32_t v_slot, uint32_t k_slot) {
+        auto tile_turn = [&](auto tile_tag, int j, bool more, uint32_t v_slot, uint32_t k_slot, uint32_t k_par) {
           constexpr int t = decltype(tile_tag)::value;
           const int first = t == 0 ? first0 : first1;
           const int end = t == 0 ? end0 : end1;
@@ -501,6 +503,10 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (next_s) {
             if (!active) {  // the tile joins at the next step: its Q is first needed here
               if (!wait(q_full(t), q_par, kSiteMmaQ)) return;
+              ptx::tc_fence_after_sync();
+            }
+            if (kSlots == 2 && t == 0) {
+              if (!wait(kv_full(k_slot), k_par, kSiteMmaKV)) return;
               ptx::tc_fence_after_sync();
             }
             issue_s(t, k_slot);
@@ -551,16 +557,19 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (!wait(kv_full(v_slot), slot_par, kSiteMmaKV)) break;
           advance();
           const uint32_t k_slot = slot;  // K_{j+1}, present when `more`
+          const uint32_t k_par = slot_par;
           if (j > 0) IXK_HTRACE(j - 1, 4);
           if (more) {
-            if (!wait(kv_full(k_slot), slot_par, kSiteMmaKV)) break;
+            // (with a two-slot ring K_{j+1} was only requested when K_j's S had been issued: there
+            // the wait stays behind P.V_j, where the load has had time to land)
+            if (kSlots > 2 && !wait(kv_full(k_slot), k_par, kSiteMmaKV)) break;
             advance();
           }
           if (j > 0) IXK_HTRACE(j - 1, 5);
           ptx::tc_fence_after_sync();
           if (j > 0) IXK_TRACE(8, j, 7);
-          tile_turn(std::integral_constant<int, 0>{}, j, more, v_slot, k_slot);
-          if (kQTiles == 2 && alive) tile_turn(std::integral_constant<int, kQTiles - 1>{}, j, more, v_slot, k_slot);
+          tile_turn(std::integral_constant<int, 0>{}, j, more, v_slot, k_slot, k_par);
+          if (kQTiles == 2 && alive) tile_turn(std::integral_constant<int, kQTiles - 1>{}, j, more, v_slot, k_slot, k_par);
         }
       }
     }
