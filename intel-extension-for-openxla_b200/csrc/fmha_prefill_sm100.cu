@@ -19,8 +19,8 @@
 // first, and every barrier keeps counting across items, so the loads and the first S of the next
 // item are issued while the current item's last softmax and its epilogue still run.
 // A work item carries kQTiles tiles of 128 query rows; with two tiles the tensor core works on one
-// tile's S / P.V while the other tile's softmax runs.  P is handed to the MMA issuer in two halves
-// so that P.V starts on the first 64 keys while the rest is still being exponentiated.  P overwrites
+// tile's S / P.V while the other tile's softmax runs.  P is handed to the MMA issuer in four quarters
+// so that P.V starts on the first 32 keys while the rest is still being exponentiated.  P overwrites
 // S in place in TMEM as packed 16-bit pairs.  The running maximum is only raised when it moved by more than 2^8
 // (exact: the same stale maximum scales P, the row sum and O), which keeps the O rescale off
 // the common path.  exp is evaluated as exp2 with head_scale*log2(e) folded in.  bf16 P is cut
@@ -52,7 +52,7 @@ constexpr int kChunkBytes = kBlockKV * 128;           // one 128-row x 128-byte 
 constexpr int kThreads = 384;  // warpgroups: softmax tile 0, softmax tile 1, {producer, MMA issuer, 2 idle}
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
-constexpr int kParts = 2;  // pieces in which a block of P is handed to the MMA issuer (1, 2 or 4)
+constexpr int kParts = 4;  // pieces in which a block of P is handed to the MMA issuer (1, 2 or 4)
 constexpr int kSoftmaxRegs = 216;  // per-thread register budgets after re-partitioning
 constexpr int kControlRegs = 64;
 constexpr float kLog2e = 1.4426950408889634f;

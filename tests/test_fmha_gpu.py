@@ -186,6 +186,29 @@ def test_full_size_matches_oracle_on_a_slice(pkg, orc, cuda):
         orc.check_close(f32(o[b:b + 1, n:n + 1]), want, rtol=2e-2, atol=2e-2, what=f"C2 causal b{b} n{n}")
 
 
+@pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
+def test_full_size_every_row_against_fp32_attention(pkg, cuda, causal):
+    """Configuration 2 shapes, every (batch, head, row): the persistent kernel deals 1024 work items
+    to 148 CTAs, and a scheduling or buffer-reuse fault shows up in some items only, so the whole
+    output is compared, one batch at a time, with plain fp32 attention on the same device (a
+    cross-check beside the oracle slices above; same tolerance)."""
+    B, N, S, H = 8, 16, 2048, 128
+    g = torch.Generator(device="cuda").manual_seed(59)
+    q = torch.randn(B, N, S, H, generator=g, device=cuda).bfloat16()
+    k = torch.randn(B, N, S, H, generator=g, device=cuda).bfloat16()
+    v = torch.randn(B, N, S, H, generator=g, device=cuda).bfloat16()
+    o, _ = run(pkg, q, k, v, causal=causal)
+    mask = torch.ones(S, S, dtype=torch.bool, device=cuda).tril() if causal else None
+    for b in range(B):
+        s = (q[b].float() @ k[b].float().transpose(-1, -2)) * H ** -0.5
+        if mask is not None:
+            s = s.masked_fill(~mask, float("-inf"))
+        want = torch.softmax(s, dim=-1) @ v[b].float()
+        got = o[b].float()
+        bad = (got - want).abs() > 2e-2 + 2e-2 * want.abs()
+        assert not bool(bad.any()), f"batch {b}: {int(bad.sum())} elements off, max {float((got - want).abs().max()):.4f}"
+
+
 def test_repeatable(pkg, cuda):
     g = torch.Generator(device="cuda").manual_seed(53)
     q = torch.randn(2, 4, 512, 128, generator=g, device=cuda).bfloat16()
