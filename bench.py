@@ -40,8 +40,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised
 # under profiles/ (None until a capture exists for that kernel).
 NCU_TRAFFIC_BYTES = {
-    "fmha_causal": 566.5e6,      # profiles/fmha_prefill_causal_B8_N16_S2048_H128.md
-    "fmha_bias": 1.132e9,        # profiles/fmha_prefill_bias_B8_N16_S2048_H128.md
+    "fmha_causal": 476.2e6,      # profiles/fmha_prefill_causal_B8_N16_S2048_H128.md
+    "fmha_bias": 1.110e9,        # profiles/fmha_prefill_bias_B8_N16_S2048_H128.md
     "gemm_bias_gelu": 1.39e9,     # profiles/gemm_bias_gelu_M8192_K4096_N16384_bf16.md
     "decode_attn": 4.30e9,        # profiles/fmha_decode_B64_N16_T4096_H256.md
 }
