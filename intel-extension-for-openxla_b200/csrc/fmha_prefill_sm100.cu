@@ -12,8 +12,10 @@
 //   warp 9        tcgen05.mma issuer (one thread, alternating between the tiles):
 //                                      S_t = Q_t.K_j^T  (A, B from shared memory, S in TMEM)
 //                                      O_t += P_t.V_j   (A = P from TMEM, B = V from shared memory)
-// The two softmax warpgroups take 216 registers per thread (a whole row of S lives in registers),
-// the control warpgroup gives its share up (setmaxnreg).
+//   warps 12-15   epilogue: O / row sum out of TMEM, one rounding, stores (both tiles); the softmax
+//                 warps hand over 1 / row sum and go straight on to the next work item
+// The two softmax warpgroups take 184 registers per thread (a whole row of S lives in registers),
+// the control and epilogue warpgroups give their share up (setmaxnreg).
 //
 // CTAs are persistent: each walks a static list of (batch, head, query block) work items, heaviest
 // first, and every barrier keeps counting across items, so the loads and the first S of the next
@@ -49,12 +51,15 @@ constexpr int kBlockQ = 128;   // query rows per tile (= TMEM lanes)
 constexpr int kBlockKV = 128;  // keys per block
 constexpr int kChunkElems = 64;                       // 16-bit elements per 128-byte swizzle row
 constexpr int kChunkBytes = kBlockKV * 128;           // one 128-row x 128-byte box
-constexpr int kThreads = 384;  // warpgroups: softmax tile 0, softmax tile 1, {producer, MMA issuer, 2 idle}
+constexpr int kThreads = 512;  // warpgroups: softmax tile 0, softmax tile 1, {producer, MMA issuer, 2 idle}, epilogue
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kParts = 4;  // pieces in which a block of P is handed to the MMA issuer (1, 2 or 4)
-constexpr int kSoftmaxRegs = 216;  // per-thread register budgets after re-partitioning
-constexpr int kControlRegs = 64;
+constexpr int kEpilogueWarp = 12;  // first warp of the epilogue warpgroup
+// per-thread register budgets after re-partitioning: 256 x 184 + 128 x 56 + 128 x 88 = 65536
+constexpr int kSoftmaxRegs = 184;
+constexpr int kControlRegs = 56;
+constexpr int kEpilogueRegs = 88;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kTruncInflate = 1.0028179f;     // 1 + 2^-8 * (1 / (2 ln 2)): mean relative loss of bf16 truncation
@@ -77,7 +82,7 @@ struct Cfg {
   // O leaves through shared memory and TMA stores, one 64-column box per query tile at a time
   // (no room is left for it beside the TMA-fed bias tiles: that variant stores from registers)
   static constexpr int kStageBytes = kBias ? 0 : kQTiles * kChunkBytes;
-  static constexpr int kSmemBytes = kQBytes + kKvSlots * kTileBytes + kBiasBytes + kStageBytes + 320 + 1024;
+  static constexpr int kSmemBytes = kQBytes + kKvSlots * kTileBytes + kBiasBytes + kStageBytes + 320 + 2 * kBlockQ * 4 + 1024;
   static_assert(kSmemBytes <= 232448, "shared memory budget");
   static constexpr int kTmemS = 0;                                // S_t at columns [128 t, 128 t + 128)
   static constexpr int kTmemO = 128 * kQTiles;                    // O_t at kTmemO + t * kHeadDim
@@ -280,8 +285,12 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   auto bias_full = [&](int t) { return bar_base + 8u * (16 + 2 * kSlots + t); };
   auto bias_empty = [&](int t) { return bar_base + 8u * (18 + 2 * kSlots + t); };
   auto stage_sync = [&](int t) { return bar_base + 8u * (20 + 2 * kSlots + t); };
-  uint8_t* tail = smem_gen + (bar_base - smem_base) + 8 * (24 + 2 * kSlots);
-  static_assert(8 * (24 + 2 * kSlots) + 8 <= 320, "barrier area");
+  auto stats_full = [&](int t) { return bar_base + 8u * (24 + 2 * kSlots + t); };
+  auto stats_empty = [&](int t) { return bar_base + 8u * (26 + 2 * kSlots + t); };
+  uint8_t* tail = smem_gen + (bar_base - smem_base) + 8 * (28 + 2 * kSlots);
+  static_assert(8 * (28 + 2 * kSlots) + 8 <= 320, "barrier area");
+  // 1 / row sum of every query row, from the softmax warps to the epilogue warps
+  float* inv_l_slot = reinterpret_cast<float*>(smem_gen + (bar_base - smem_base) + 320);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
@@ -307,6 +316,8 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       ptx::mbar_init(bias_full(t), 1);
       ptx::mbar_init(bias_empty(t), 128);
       ptx::mbar_init(stage_sync(t), 128);
+      ptx::mbar_init(stats_full(t), 128);
+      ptx::mbar_init(stats_empty(t), 128);
     }
     ptx::fence_mbar_init();
     ptx::prefetch_tmap(&tmap_q);
@@ -573,10 +584,128 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
       }
     }
+  } else if (warp >= kEpilogueWarp) {
+    // ------------------------------------------------------------------ epilogue: O / l out of TMEM
+    // Four warps (one per TMEM lane quarter) serve both query tiles.  The softmax warpgroups hand
+    // over 1 / row sum and go on with the next item; O_t is read 32 columns at a time once the
+    // tile's last P.V has landed, normalised, rounded once and stored.  With a staging box, rows
+    // go to shared memory 128-byte-swizzled (thread = row, so each st.shared.v4 of a warp covers
+    // every bank once per eight rows) and leave as one TMA store per 64 columns: from registers a
+    // warp's 16-byte stores land in 32 different lines each, and that many requests hold up every
+    // other warp's shared-memory and barrier traffic.
+    ptx::setmaxnreg_dec<kEpilogueRegs>();
+    const bool bf16 = args.is_bf16 != 0;
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const bool elected = warp == kEpilogueWarp && lane == 0;  // issues every TMA store
+    uint32_t n_fin0 = 0, n_fin1 = 0;    // items finished per tile
+    uint32_t n_sync0 = 0, n_sync1 = 0;  // rendezvous of the four warps around a tile's staging box
+    bool alive = true;
+    uint32_t it = 0;
+    for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
+      const Item item = get_item<kQTiles>(args, w);
+      for (int tt = 0; tt < kQTiles && alive; ++tt) {
+        const int t = item.reversed ? kQTiles - 1 - tt : tt;  // the tile that started first is served first
+        if (item.nblk(t) == 0) continue;
+        uint32_t& n_fin = t == 0 ? n_fin0 : n_fin1;
+        uint32_t& n_sync = t == 0 ? n_sync0 : n_sync1;
+        const uint32_t o_addr = tmem_base + lane_addr + C::kTmemO + t * kHeadDim;
+        const int row0 = item.q0 + t * kBlockQ;
+        const int f = row0 + row_in_tile;
+        const bool row_ok = f < args.F;
+        if (!ptx::mbar_wait(stats_full(t), n_fin & 1u, ctl, kSiteEpilogueO) ||
+            !ptx::mbar_wait(o_final(t), n_fin & 1u, ctl, kSiteEpilogueO)) {
+          alive = false;
+          break;
+        }
+        ++n_fin;
+        ptx::tc_fence_after_sync();
+        const float inv_l = inv_l_slot[t * kBlockQ + row_in_tile];
+        ptx::mbar_arrive(stats_empty(t));
+        // 32 columns of this thread's row, normalised and packed to 16-bit pairs
+        auto load_chunk = [&](int c, uint32_t (&wv)[16]) {
+          uint32_t o[32];
+          ptx::tmem_ld_32x32(o_addr + c * 32, o);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            wv[i] = pack2(__uint_as_float(o[2 * i]) * inv_l, __uint_as_float(o[2 * i + 1]) * inv_l, bf16);
+        };
+        constexpr int kOChunks = kHeadDim / 32;
+        if (C::kStageBytes > 0 && args.out_tma) {
+          const uint32_t stage = stage_smem + t * kChunkBytes;
+          const uint32_t my_row = stage + row_in_tile * 128;
+          auto rendezvous = [&]() {
+            ptx::mbar_arrive(stage_sync(t));
+            if (!ptx::mbar_wait(stage_sync(t), n_sync & 1u, ctl, kSiteEpilogueO)) alive = false;
+            ++n_sync;
+          };
+#pragma unroll 1
+          for (int pass = 0; pass < kHeadDim / 64 && alive; ++pass) {
+            uint32_t lo[16], hi[16];
+            load_chunk(2 * pass, lo);
+            load_chunk(2 * pass + 1, hi);
+            if (pass == kHeadDim / 64 - 1) {
+              ptx::tc_fence_before_sync();
+              ptx::mbar_arrive(o_free(t));  // O_t is in registers: the next item's P.V may overwrite it
+            }
+            // the box holds the previous 64 columns until their store has read them
+            if (elected) ptx::bulk_wait_group_read<0>();
+            rendezvous();
+            if (!alive) break;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const uint32_t addr = my_row + static_cast<uint32_t>((g ^ (row_in_tile & 7)) << 4);
+              const uint32_t* src = g < 4 ? &lo[4 * g] : &hi[4 * (g - 4)];
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(src[0]), "r"(src[1]), "r"(src[2]),
+                           "r"(src[3])
+                           : "memory");
+            }
+            ptx::fence_proxy_async_smem();
+            rendezvous();
+            if (!alive) break;
+            if (elected && pass * 64 < args.H) {
+              ptx::tma_store_4d(&tmap_o, stage, pass * 64, row0, item.head, item.batch);
+              ptx::bulk_commit_group();
+            }
+          }
+        } else {
+          uint16_t* orow = args.out + item.batch * args.o_strides[0] + item.head * args.o_strides[1] +
+                           static_cast<int64_t>(f) * args.o_strides[2];
+#pragma unroll 1
+          for (int c = 0; c < kOChunks; ++c) {
+            uint32_t wv[16];
+            load_chunk(c, wv);
+            if (c == kOChunks - 1) {
+              ptx::tc_fence_before_sync();
+              ptx::mbar_arrive(o_free(t));
+            }
+            if (row_ok && c * 32 < args.H) {
+              const int count = min(32, args.H - c * 32);
+              if (args.out_vec_ok && count == 32) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                  reinterpret_cast<uint4*>(orow + c * 32)[g] =
+                      make_uint4(wv[4 * g], wv[4 * g + 1], wv[4 * g + 2], wv[4 * g + 3]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  if (2 * i < count) orow[c * 32 + 2 * i] = static_cast<uint16_t>(wv[i] & 0xffffu);
+                  if (2 * i + 1 < count) orow[c * 32 + 2 * i + 1] = static_cast<uint16_t>(wv[i] >> 16);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+    // the staging boxes must outlive the TMA stores that read them
+    if (C::kStageBytes > 0 && elected) ptx::bulk_wait_group<0>();
   } else if (warp > kMmaWarp) {
     ptx::setmaxnreg_dec<kControlRegs>();  // idle warps of the control warpgroup
   } else {
-    // ------------------------------------------------------------------ softmax + epilogue
+    // ------------------------------------------------------------------ softmax
     ptx::setmaxnreg_inc<kSoftmaxRegs>();
     const int t = warp >> 2;  // query tile of this warpgroup (warps 0-3: tile 0, warps 4-7: tile 1)
     const int quarter = warp & 3;
@@ -588,7 +717,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const uint32_t o_addr = tmem_base + lane_addr + C::kTmemO + t * kHeadDim;
       uint32_t n_s = 0;  // S tiles consumed
       uint32_t n_o = 0;  // items finished
-      [[maybe_unused]] uint32_t n_sync = 0;  // rendezvous of this tile's four warps around the staging box
       [[maybe_unused]] uint32_t n_bias = 0;  // bias tiles consumed
       bool alive = true;
       uint32_t it = 0;
@@ -606,9 +734,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                      static_cast<int64_t>(f) * args.bias_strides[2];
         float m_run = -INFINITY;
         float l_run = 0.0f;
-        // The staging box must be free again before this item's epilogue: its owner checks here,
-        // and its first P arrival below orders the check before every thread's o_final.
-        if (C::kStageBytes > 0 && row_in_tile == 0) ptx::bulk_wait_group_read<0>();
         for (int j = 0; j < my_blocks; ++j) {
           if (!ptx::mbar_wait(s_full(t), n_s & 1u, ctl, kSiteSoftmaxS)) {
             alive = false;
@@ -801,114 +926,15 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           l_run = l_run * alpha + (s0 + s1);
         }
         if (!alive) break;
-        // ---- epilogue: O / l, one rounding, 16-byte stores
-        if (!ptx::mbar_wait(o_final(t), n_o & 1u, ctl, kSiteEpilogueO)) {
+        // ---- hand the row's normaliser to the epilogue warpgroup, which reads O out of TMEM once
+        // the last P.V has landed; this warp goes straight on to the next item.
+        if (!ptx::mbar_wait(stats_empty(t), (n_o & 1u) ^ 1u, ctl, kSiteEpilogueO)) {
           alive = false;
           break;
         }
         ++n_o;
-        ptx::tc_fence_after_sync();
-        IXK_TRACE(warp, my_blocks - 1, 5);
-        const float inv_l = (bf16 ? kTruncInflate : 1.0f) / l_run;  // the row sum carries the truncation bias
-        uint16_t* orow = args.out + batch * args.o_strides[0] + head * args.o_strides[1] +
-                         static_cast<int64_t>(f) * args.o_strides[2];
-        constexpr int kOChunks = kHeadDim / 32;
-        if (C::kStageBytes > 0 && args.out_tma) {
-          // Rows go to a 128-byte-swizzled staging box (thread = row, so each st.shared.v4 of a
-          // warp covers every bank once per eight rows) and leave as one TMA store per 64 columns:
-          // from registers a warp's 16-byte stores would land in 32 different lines each, and
-          // that many requests hold up every other warp's shared-memory and barrier traffic.
-          const uint32_t stage = stage_smem + t * kChunkBytes;
-          const uint32_t my_row = stage + row_in_tile * 128;
-          const bool elected = row_in_tile == 0;
-          auto rendezvous = [&]() {
-            ptx::mbar_arrive(stage_sync(t));
-            if (!ptx::mbar_wait(stage_sync(t), n_sync & 1u, ctl, kSiteEpilogueO)) alive = false;
-            ++n_sync;
-          };
-          // 128 columns at a time live in registers; the TMEM copy of O_t is handed back as soon
-          // as its last column has been read, well before the stores are on their way.
-          constexpr int kHalves = kHeadDim > 128 ? kHeadDim / 128 : 1;
-          constexpr int kPassesPerHalf = (kHeadDim / 64) / kHalves;
-#pragma unroll 1
-          for (int h = 0; h < kHalves && alive; ++h) {
-            uint32_t o[2 * kPassesPerHalf][32];
-#pragma unroll
-            for (int c = 0; c < 2 * kPassesPerHalf; ++c) ptx::tmem_ld_32x32(o_addr + h * 128 + c * 32, o[c]);
-            ptx::tmem_ld_wait();
-            if (h == kHalves - 1) {
-              ptx::tc_fence_before_sync();
-              ptx::mbar_arrive(o_free(t));  // the next item's P.V may overwrite O_t
-            }
-            IXK_TRACE(warp, my_blocks - 1, 3);
-#pragma unroll
-            for (int c = 0; c < kPassesPerHalf; ++c) {
-              uint32_t wv[32];
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                wv[i] = pack2(__uint_as_float(o[2 * c + (i >> 4)][2 * (i & 15)]) * inv_l,
-                              __uint_as_float(o[2 * c + (i >> 4)][2 * (i & 15) + 1]) * inv_l, bf16);
-              if (h + c > 0) {
-                // the box still holds the previous 64 columns until their store has read them
-                // (at the item's first pass that was settled before this item's first P hand-over)
-                if (elected) ptx::bulk_wait_group_read<0>();
-                rendezvous();
-                if (!alive) break;
-                IXK_TRACE(warp, my_blocks - 2, 5);
-              }
-#pragma unroll
-              for (int g = 0; g < 8; ++g) {
-                const uint32_t addr = my_row + static_cast<uint32_t>((g ^ (row_in_tile & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(wv[4 * g]),
-                             "r"(wv[4 * g + 1]), "r"(wv[4 * g + 2]), "r"(wv[4 * g + 3])
-                             : "memory");
-              }
-              ptx::fence_proxy_async_smem();
-              IXK_TRACE(warp, my_blocks - 2, c == 0 ? 1 : 2);
-              rendezvous();
-              if (!alive) break;
-              IXK_TRACE(warp, my_blocks - 2, c == 0 ? 3 : 7);
-              const int col0 = h * 128 + c * 64;
-              if (elected && col0 < args.H) {
-                ptx::tma_store_4d(&tmap_o, stage, col0, q0 + t * kBlockQ, head, batch);
-                ptx::bulk_commit_group();
-              }
-            }
-          }
-          if (!alive) break;
-        } else {
-#pragma unroll 1
-        for (int c = 0; c < kOChunks; ++c) {
-          uint32_t o[32];
-          ptx::tmem_ld_32x32(o_addr + c * 32, o);
-          ptx::tmem_ld_wait();
-          if (c == kOChunks - 1) {
-            // O_t is in registers: the next item's P.V may overwrite it
-            ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(o_free(t));
-          }
-          if (row_ok && c * 32 < args.H) {
-            uint32_t wv[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              wv[i] = pack2(__uint_as_float(o[2 * i]) * inv_l, __uint_as_float(o[2 * i + 1]) * inv_l, bf16);
-            const int count = min(32, args.H - c * 32);
-            if (args.out_vec_ok && count == 32) {
-#pragma unroll
-              for (int g = 0; g < 4; ++g)
-                reinterpret_cast<uint4*>(orow + c * 32)[g] =
-                    make_uint4(wv[4 * g], wv[4 * g + 1], wv[4 * g + 2], wv[4 * g + 3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                if (2 * i < count) orow[c * 32 + 2 * i] = static_cast<uint16_t>(wv[i] & 0xffffu);
-                if (2 * i + 1 < count) orow[c * 32 + 2 * i + 1] = static_cast<uint16_t>(wv[i] >> 16);
-              }
-            }
-          }
-        }
-        }
-        IXK_TRACE(warp, my_blocks - 1, 7);
+        inv_l_slot[t * kBlockQ + row_in_tile] = (bf16 ? kTruncInflate : 1.0f) / l_run;  // the row sum carries the truncation bias
+        ptx::mbar_arrive(stats_full(t));  // (release: the store above is visible to whoever sees the phase)
         if (args.lse != nullptr && row_ok) {
           const int64_t idx = (static_cast<int64_t>(batch) * args.N + head) * args.F + f;
           args.lse[idx] = (m_run + log2f(l_run) - (bf16 ? kTruncBiasLog2 : 0.0f)) * kLn2;
@@ -917,8 +943,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
   }
 
-  // the staging boxes must outlive the TMA stores that read them
-  if (C::kStageBytes > 0 && warp < 4 * kQTiles && (threadIdx.x & 127) == 0) ptx::bulk_wait_group<0>();
   if (*abort_flag != 0) __nanosleep(2000000);
   ptx::tc_fence_before_sync();
   __syncthreads();
