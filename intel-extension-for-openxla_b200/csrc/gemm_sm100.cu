@@ -38,7 +38,10 @@ struct Cfg {
   static constexpr int kStages = (192 * 1024) / kStageBytes;
   static constexpr int kTmemCols = 2 * kBlockN;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + align slack
+  // output staging: two boxes of 32 rows x 128 bytes per epilogue warp
+  static constexpr int kStagingBytes = 4 * 2 * 32 * 128;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;  // + align slack
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
 // Site codes written to the status word by a wait that gave up.
@@ -106,6 +109,23 @@ __device__ __forceinline__ void load_row16(const void* base, int64_t elem_off, i
   }
 }
 
+// 32 fp32 values -> 16 words of 16-bit pairs, rounded once.
+__device__ __forceinline__ void pack_row16(const float (&v)[32], int dtype, uint32_t* w) {
+  if (dtype == IXK_BF16) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+}
+
 __device__ __forceinline__ void store_row(void* base, int64_t elem_off, int dtype, int count,
                                           bool vec_ok, const float (&v)[32]) {
   if (dtype == IXK_F32) {
@@ -169,7 +189,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 template <int kBlockN, bool kFp8>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const KernelArgs args) {
+            const __grid_constant__ CUtensorMap tmap_d, const KernelArgs args) {
   using C = Cfg<kBlockN>;
   constexpr int kStages = C::kStages;
   constexpr int kElemBytes = kFp8 ? 1 : 2;
@@ -179,13 +199,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-  const uint32_t bar_base = smem_base + kStages * C::kStageBytes;
+  const uint32_t stage_smem = smem_base + kStages * C::kStageBytes;  // output staging boxes
+  const uint32_t bar_base = stage_smem + C::kStagingBytes;
   // barrier slots (8 bytes each): full[kStages], empty[kStages], acc_full[2], acc_empty[2]
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
-  uint8_t* tail = smem_gen + kStages * C::kStageBytes + 8 * (2 * kStages + 4);
+  uint8_t* tail = smem_gen + kStages * C::kStageBytes + C::kStagingBytes + 8 * (2 * kStages + 4);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
@@ -206,6 +227,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     ptx::fence_mbar_init();
     ptx::prefetch_tmap(&tmap_a);
     ptx::prefetch_tmap(&tmap_b);
+    if (args.d_tma) ptx::prefetch_tmap(&tmap_d);
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
@@ -323,6 +345,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const bool vec_d = args.d_vec_ok != 0;
     const bool vec_c = args.c_vec_ok != 0;
     const bool vec_bias = args.bias_vec_ok != 0;
+    uint32_t n_store = 0;  // TMA stores issued by this warp (alternating between its two boxes)
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int bz, bm, bn;
       tile_coords(t, args.tiles_m, args.tiles_n, bz, bm, bn);
@@ -332,15 +355,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const bool row_ok = m < args.M;
       const int64_t d_row = bz * args.d_batch_stride + static_cast<int64_t>(m) * args.ldd;
       const int64_t c_row = bz * args.c_batch_stride + static_cast<int64_t>(m) * args.ldc;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kBlockN; c0 += 32) {
-        const int n = bn * kBlockN + c0;
-        if (n >= args.N) break;  // warp-uniform
+      // 32 columns of this thread's row: accumulator -> scale, bias, residual, activation
+      auto chunk = [&](int c0, int n, int count, float (&v)[32]) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBlockN + c0, r);
         ptx::tmem_ld_wait();
-        const int count = min(32, args.N - n);
-        float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * args.acc_scale;
         if (args.bias != nullptr) {
@@ -362,13 +381,67 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
         }
-        if (row_ok) store_row(args.d, d_row + n, args.out_dtype, count, vec_d, v);
+      };
+      if (args.d_tma) {
+        // 16-bit output through shared memory: each warp writes its 32 rows x 64 columns into a
+        // 128-byte-swizzled box of its own (lane = row, conflict-free) and one lane hands the box
+        // to a TMA store; two boxes per warp, so a box is only rewritten after the store issued
+        // two passes earlier has read it.  Stored from registers, a warp's 16-byte stores land in
+        // 32 different lines each; those requests queue in front of the producer's and the
+        // issuer's barrier traffic and cost 8-11 % of the kernel.
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBlockN; c0 += 64) {
+          const int n = bn * kBlockN + c0;
+          if (n >= args.N) break;  // warp-uniform
+          uint32_t wv[32];
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int nh = n + 32 * half;
+            if (nh < args.N) {  // warp-uniform
+              float v[32];
+              chunk(c0 + 32 * half, nh, min(32, args.N - nh), v);
+              pack_row16(v, args.out_dtype, &wv[16 * half]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) wv[16 * half + i] = 0u;
+            }
+          }
+          const uint32_t box = stage_smem + static_cast<uint32_t>((quarter * 2 + (n_store & 1)) * 4096);
+          if (lane == 0) ptx::bulk_wait_group_read<1>();
+          __syncwarp();
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const uint32_t addr = box + static_cast<uint32_t>(lane * 128 + ((g ^ (lane & 7)) << 4));
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(wv[4 * g]), "r"(wv[4 * g + 1]),
+                         "r"(wv[4 * g + 2]), "r"(wv[4 * g + 3])
+                         : "memory");
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_3d(&tmap_d, box, n, bm * kBlockM + quarter * 32, bz);
+            ptx::bulk_commit_group();
+          }
+          ++n_store;
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBlockN; c0 += 32) {
+          const int n = bn * kBlockN + c0;
+          if (n >= args.N) break;  // warp-uniform
+          const int count = min(32, args.N - n);
+          float v[32];
+          chunk(c0, n, count, v);
+          if (row_ok) store_row(args.d, d_row + n, args.out_dtype, count, vec_d, v);
+        }
       }
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(acc_empty_bar(buf));
       buf ^= 1;
       if (buf == 0) acc_phase ^= 1u;
     }
+    // the staging boxes must outlive the stores that read them
+    if (args.d_tma && lane == 0) ptx::bulk_wait_group<0>();
   }
 
   // Teardown.  On the abort path give copies still in flight time to land before the
@@ -383,8 +456,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 }
 
 template <int kBlockN, bool kFp8>
-int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const KernelArgs& args, int grid,
-               cudaStream_t stream) {
+int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const KernelArgs& args,
+               int grid, cudaStream_t stream) {
   using C = Cfg<kBlockN>;
   auto* fn = &gemm_kernel<kBlockN, kFp8>;
   static thread_local int configured_device = -1;
@@ -394,7 +467,7 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const KernelArgs& a
     IXK_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     configured_device = dev;
   }
-  fn<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, args);
+  fn<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, td, args);
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
   return IXK_OK;
@@ -487,17 +560,35 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   k.c_vec_ok = k.c && aligned16(p.c) && (p.ldc * out_es) % 16 == 0 && (p.c_batch_stride * out_es) % 16 == 0;
   k.bias_vec_ok = p.bias && aligned16(p.bias);
   (void)bias_es;
+  // A 16-bit D whose rows start on 16-byte boundaries leaves through shared memory and TMA stores.
+  CUtensorMap td = ta;  // placeholder unless D qualifies
+  k.d_tma = (p.out_dtype != IXK_F32 && k.d_vec_ok) ? 1 : 0;
+  if (k.d_tma) {
+    TmapSpec s{};
+    s.dtype = p.out_dtype == IXK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    s.rank = 3;
+    s.swizzle128 = true;
+    s.dims[0] = p.N;
+    s.dims[1] = p.M;
+    s.dims[2] = p.batch;
+    s.box[0] = 64;
+    s.box[1] = 32;
+    s.box[2] = 1;
+    s.strides_bytes[0] = static_cast<uint64_t>(p.ldd) * 2;
+    s.strides_bytes[1] = p.batch > 1 ? static_cast<uint64_t>(p.d_batch_stride) * 2 : s.strides_bytes[0] * s.dims[1];
+    if ((rc = encode_tmap(&td, p.d, s)) != IXK_OK) return rc;
+  }
 
   const int64_t tiles = static_cast<int64_t>(k.tiles_m) * k.tiles_n * k.batch;
   const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
   if (p.fp8) {
-    if (bn == 256) return launch_one<256, true>(ta, tb, k, grid, stream);
-    if (bn == 128) return launch_one<128, true>(ta, tb, k, grid, stream);
-    return launch_one<64, true>(ta, tb, k, grid, stream);
+    if (bn == 256) return launch_one<256, true>(ta, tb, td, k, grid, stream);
+    if (bn == 128) return launch_one<128, true>(ta, tb, td, k, grid, stream);
+    return launch_one<64, true>(ta, tb, td, k, grid, stream);
   }
-  if (bn == 256) return launch_one<256, false>(ta, tb, k, grid, stream);
-  if (bn == 128) return launch_one<128, false>(ta, tb, k, grid, stream);
-  return launch_one<64, false>(ta, tb, k, grid, stream);
+  if (bn == 256) return launch_one<256, false>(ta, tb, td, k, grid, stream);
+  if (bn == 128) return launch_one<128, false>(ta, tb, td, k, grid, stream);
+  return launch_one<64, false>(ta, tb, td, k, grid, stream);
 }
 
 }  // namespace gemm

@@ -46,6 +46,7 @@ struct KernelArgs {
   int out_dtype, bias_dtype, act;
   float acc_scale, beta;
   int d_vec_ok, c_vec_ok, bias_vec_ok;
+  int d_tma;  // 16-bit D with 16-byte-aligned rows: stored through shared memory + TMA
   int* status_word;
 };
 
