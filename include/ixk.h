@@ -91,7 +91,7 @@ typedef struct ixk_gemm_desc {
   ixk_matrix_layout output; /* D (and C, which XLA aliases with D when beta != 0): [M, N] */
   int64_t batch_size;
   float alpha;              /* must be 1, as in the reference (onednn_matmul_utils.cc:438) */
-  float beta;               /* D = epi(A.B + bias) + beta*C; any real value (the reference's
+  float beta;               /* D = act(A.B + bias + beta*C); any real value (the reference's
                                XeTLA path only takes 0 or 1, onednn_matmul_utils.cc:262-270) */
   int32_t epilogue;         /* ixk_epilogue */
   int32_t reserved;         /* must be 0 */
@@ -135,6 +135,20 @@ size_t ixk_gemm_workspace_bytes(const ixk_gemm_desc* desc);
 int ixk_gemm_fp8(const ixk_gemm_desc* desc, const void* a, const void* b,
                  const void* c, const void* bias, void* d, float inv_scale_a,
                  float inv_scale_b, void* workspace, size_t workspace_bytes,
+                 void* cuda_stream);
+
+/* Three projections of one input (the QKV-fusion pass).  Replaces
+ * XetlaQKVGemmKernel::run (xetla/gemm/gemm.h:111-171) → HGEMM_QKV_KERNEL /
+ * HGEMM_QKV_BIAS_KERNEL (xetla/gemm/hgemm_impl.h:461-608):
+ *   out_i = A . B_i (+ bias_i),  i = 0, 1, 2      fp32 accumulate, one rounding
+ * A row-major [m,k] with pitch lda; b holds the three row-major [k,n] weight
+ * slabs one behind the other (slab i at b + i*k*n, pitch ldb, as hgemm_impl.h:518);
+ * bias NULL or three length-n vectors (bias + i*n, :596-602); out0/1/2 row-major
+ * [m,n] with pitch ldc, anywhere in memory (evenly spaced outputs run as one launch).
+ * dtype ∈ {BF16, F16} for every operand.  Same alignment rules as ixk_gemm. */
+int ixk_gemm_qkv(int dtype, int64_t m, int64_t n, int64_t k, const void* a,
+                 int64_t lda, const void* b, int64_t ldb, const void* bias,
+                 void* out0, void* out1, void* out2, int64_t ldc,
                  void* cuda_stream);
 
 /* --------------------------------------------------------------- attention */

@@ -83,6 +83,8 @@ ABI_SYMBOLS = {
     "ixk_gemm_workspace_bytes": (_sz, [ctypes.POINTER(_GemmDesc)]),
     "ixk_gemm_fp8": (ctypes.c_int, [ctypes.POINTER(_GemmDesc), _vp, _vp, _vp, _vp, _vp, ctypes.c_float,
                                     ctypes.c_float, _vp, _sz, _vp]),
+    "ixk_gemm_qkv": (ctypes.c_int, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp, ctypes.c_int64,
+                                    _vp, ctypes.c_int64, _vp, _vp, _vp, _vp, ctypes.c_int64, _vp]),
     "ixk_fmha_fwd": (ctypes.c_int, [ctypes.POINTER(_FmhaDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "ixk_fmha_fwd_workspace_bytes": (_sz, [ctypes.POINTER(_FmhaDesc)]),
     "ixk_fmha_fwd_static_scratch": (ctypes.c_int, [ctypes.POINTER(_FmhaDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
@@ -275,6 +277,33 @@ def gemm_fp8(lhs_q: torch.Tensor, rhs_q: torch.Tensor, inv_scale_a: float, inv_s
     run_gemm_custom_call(lhs_q, rhs_q, None, out, bias, stream, attrs, epilogue,
                          inv_scale_a=inv_scale_a, inv_scale_b=inv_scale_b)
     return out
+
+
+def gemm_qkv(x: torch.Tensor, w_qkv: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+             outs=None, stream=None):
+    """Three projections of one input, as XetlaQKVGemmKernel (xetla/gemm/gemm.h:111-171) runs them:
+    x [m,k] row-major, w_qkv [3,k,n] (three row-major slabs one behind the other), bias [3,n] or
+    None -> (q, k, v), each [m,n].  `outs` may give the three output tensors (any placement; a
+    contiguous [3,m,n] buffer runs as one launch)."""
+    if x.dim() != 2 or w_qkv.dim() != 3 or w_qkv.shape[0] != 3 or w_qkv.shape[1] != x.shape[1]:
+        raise IxkError(IXK_INVALID_ARGUMENT, "x must be [m,k] and w_qkv [3,k,n]")
+    if x.stride(1) != 1 or not w_qkv.is_contiguous():
+        raise IxkError(IXK_INVALID_ARGUMENT, "x must be row-major and w_qkv contiguous")
+    m, k = x.shape
+    n = w_qkv.shape[2]
+    if outs is None:
+        buf = torch.empty(3, m, n, dtype=x.dtype, device=x.device)
+        outs = (buf[0], buf[1], buf[2])
+    for o in outs:
+        if o.shape != (m, n) or o.stride(1) != 1 or o.stride(0) != outs[0].stride(0) or o.dtype != x.dtype:
+            raise IxkError(IXK_INVALID_ARGUMENT, "outputs must be row-major [m,n] of the input type with one pitch")
+    if bias is not None and (bias.shape != (3, n) or not bias.is_contiguous() or bias.dtype != x.dtype):
+        raise IxkError(IXK_INVALID_ARGUMENT, "bias must be a contiguous [3,n] tensor of the input type")
+    lib = load_library()
+    _check(lib.ixk_gemm_qkv(_TORCH_TO_IXK[x.dtype], m, n, k, x.data_ptr(), x.stride(0), w_qkv.data_ptr(), n,
+                            bias.data_ptr() if bias is not None else None, outs[0].data_ptr(), outs[1].data_ptr(),
+                            outs[2].data_ptr(), outs[0].stride(0), _stream_ptr(stream)))
+    return tuple(outs)
 
 
 # ----------------------------------------------------------------------------- attention

@@ -187,6 +187,70 @@ int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, 
   return gemm::launch(p, dev, static_cast<cudaStream_t>(stream));
 }
 
+// Three projections of one input: out_i = A . B_i (+ bias_i), i = 0..2, with the three [K,N]
+// weight slabs stacked behind one another (XetlaQKVGemmKernel, gemm.h:111-171; kernels
+// hgemm_impl.h:461-608: grid dimension 0 picks slab `b + k*n*id`, output out0/1/2 and bias
+// `bias + n*id`).  Runs as ONE launch with the projection as the batch index when the three outputs
+// are evenly spaced, A being read through a batch-less tensor map; otherwise as three launches.
+int run_qkv(int dtype, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+            const void* bias, void* out0, void* out1, void* out2, int64_t ldc, void* stream) {
+  if (dtype != IXK_BF16 && dtype != IXK_F16)
+    return fail(IXK_UNIMPLEMENTED, "QKV GEMM takes BF16 or F16 (gemm.cc instantiates sycl::half and bf16 only)");
+  if (m < 0 || n < 0 || k < 0) return fail(IXK_INVALID_ARGUMENT, "negative dimension");
+  if (m == 0 || n == 0) return IXK_OK;
+  if (k == 0) return fail(IXK_UNIMPLEMENTED, "K == 0 is not supported");
+  if (a == nullptr || b == nullptr || out0 == nullptr || out1 == nullptr || out2 == nullptr)
+    return fail(IXK_INVALID_ARGUMENT, "a, b and the three outputs must be non-NULL");
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX)
+    return fail(IXK_UNIMPLEMENTED, "dimensions above 2^31-1 are not supported");
+  if (lda < k || ldb < n || ldc < n) return fail(IXK_INVALID_ARGUMENT, "leading dimension smaller than the row length");
+  if (!aligned16(a) || !aligned16(b)) return fail(IXK_INVALID_ARGUMENT, "a and b must be 16-byte aligned (TMA)");
+  if ((lda * 2) % 16 != 0 || (ldb * 2) % 16 != 0 || (k * n * 2) % 16 != 0)
+    return fail(IXK_UNIMPLEMENTED, "lda, ldb and the slab size times 2 bytes must be multiples of 16 bytes (TMA)");
+  for (void* o : {out0, out1, out2})
+    if ((reinterpret_cast<uintptr_t>(o) & 1u) != 0) return fail(IXK_INVALID_ARGUMENT, "output is not aligned to its element size");
+
+  gemm::Problem p;
+  p.M = m;
+  p.N = n;
+  p.K = k;
+  p.ab_dtype = dtype;
+  p.a_fmt = p.b_fmt = (dtype == IXK_BF16) ? 1u : 0u;
+  p.bias_dtype = dtype;
+  p.out_dtype = dtype;
+  p.a = a;
+  p.a_mn_major = false;  // A row-major [M,K] (the reference falls back otherwise, gemm.h:158)
+  p.lda = lda;
+  p.b_mn_major = true;   // slabs row-major [K,N]
+  p.ldb = ldb;
+  p.ldc = p.ldd = ldc;
+  DeviceInfo dev;
+  int rc;
+  if ((rc = get_device_info(&dev)) != IXK_OK) return rc;
+  const intptr_t step01 = static_cast<const char*>(out1) - static_cast<const char*>(out0);
+  const intptr_t step12 = static_cast<const char*>(out2) - static_cast<const char*>(out1);
+  if (step01 == step12 && step01 > 0 && step01 % 2 == 0 && step01 / 2 >= (m - 1) * ldc + n) {
+    p.batch = 3;
+    p.a_broadcast = true;
+    p.b = b;
+    p.b_batch_stride = k * n;
+    p.bias = bias;
+    p.bias_batch_stride = n;
+    p.d = out0;
+    p.d_batch_stride = step01 / 2;
+    return gemm::launch(p, dev, static_cast<cudaStream_t>(stream));
+  }
+  void* outs[3] = {out0, out1, out2};
+  for (int i = 0; i < 3; ++i) {
+    p.batch = 1;
+    p.b = static_cast<const uint16_t*>(b) + static_cast<int64_t>(i) * k * n;
+    p.bias = bias ? static_cast<const uint16_t*>(bias) + static_cast<int64_t>(i) * n : nullptr;
+    p.d = outs[i];
+    if ((rc = gemm::launch(p, dev, static_cast<cudaStream_t>(stream))) != IXK_OK) return rc;
+  }
+  return IXK_OK;
+}
+
 // Shape of the problem after the column-major-output rewrite, for the workspace query.
 size_t workspace_query(const ixk_gemm_desc* desc) {
   if (desc == nullptr) return 0;
@@ -216,6 +280,12 @@ int ixk_gemm_fp8(const ixk_gemm_desc* desc, const void* a, const void* b, const 
                  size_t workspace_bytes, void* cuda_stream) {
   return ixk::run(desc, a, b, c, bias, d, /*fp8_call=*/true, inv_scale_a, inv_scale_b, workspace, workspace_bytes,
                   cuda_stream);
+}
+
+int ixk_gemm_qkv(int dtype, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, const void* b,
+                 int64_t ldb, const void* bias, void* out0, void* out1, void* out2, int64_t ldc,
+                 void* cuda_stream) {
+  return ixk::run_qkv(dtype, m, n, k, a, lda, b, ldb, bias, out0, out1, out2, ldc, cuda_stream);
 }
 
 }  // extern "C"

@@ -253,6 +253,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         tile_coords(t, args.tiles_m, args.tiles_n, bz, bm, bn);
         const int m0 = bm * kBlockM;
         const int n0 = bn * kBlockN;
+        const int az = args.a_broadcast ? 0 : bz;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, ctl, kSiteProducer)) {
             alive = false;
@@ -269,9 +270,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < kBlockM / kSlabElems; ++i)
               ptx::tma_load_3d(a_dst + i * (kSlabElems * kSlabBytes), &tmap_a, bar,
-                               m0 + i * kSlabElems, k0, bz);
+                               m0 + i * kSlabElems, k0, az);
           } else {
-            ptx::tma_load_3d(a_dst, &tmap_a, bar, k0, m0, bz);
+            ptx::tma_load_3d(a_dst, &tmap_a, bar, k0, m0, az);
           }
           if (args.b_mn_major) {
 #pragma unroll
@@ -364,7 +365,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * args.acc_scale;
         if (args.bias != nullptr) {
           float b[32];
-          load_row16(args.bias, n, args.bias_dtype, count, vec_bias, b);
+          load_row16(args.bias, bz * args.bias_batch_stride + n, args.bias_dtype, count, vec_bias, b);
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] += b[i];
         }
@@ -500,7 +501,7 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
                                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   // A is [M,K]: K-major when K is contiguous.  B is [K,N]: MN-major when N is contiguous.
   auto make_map = [&](CUtensorMap* out, const void* base, bool mn_major, int64_t mn, int64_t ld,
-                      int64_t batch_stride, int block_mn) -> int {
+                      int64_t batch_stride, int block_mn, bool broadcast) -> int {
     TmapSpec s{};
     s.dtype = dt;
     s.rank = 3;
@@ -516,18 +517,18 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
       s.box[0] = slab_elems;
       s.box[1] = block_mn;
     }
-    s.dims[2] = p.batch;
+    s.dims[2] = broadcast ? 1 : p.batch;
     s.box[2] = 1;
     s.strides_bytes[0] = static_cast<uint64_t>(ld) * es;
     // A batch of one still needs a legal (16-byte multiple, non-zero) stride.
-    s.strides_bytes[1] = p.batch > 1 ? static_cast<uint64_t>(batch_stride) * es
-                                     : s.strides_bytes[0] * s.dims[1];
+    s.strides_bytes[1] = (p.batch > 1 && !broadcast) ? static_cast<uint64_t>(batch_stride) * es
+                                                     : s.strides_bytes[0] * s.dims[1];
     return encode_tmap(out, base, s);
   };
   CUtensorMap ta, tb;
-  int rc = make_map(&ta, p.a, p.a_mn_major, p.M, p.lda, p.a_batch_stride, kBlockM);
+  int rc = make_map(&ta, p.a, p.a_mn_major, p.M, p.lda, p.a_batch_stride, kBlockM, p.a_broadcast);
   if (rc != IXK_OK) return rc;
-  rc = make_map(&tb, p.b, p.b_mn_major, p.N, p.ldb, p.b_batch_stride, bn);
+  rc = make_map(&tb, p.b, p.b_mn_major, p.N, p.ldb, p.b_batch_stride, bn, false);
   if (rc != IXK_OK) return rc;
 
   KernelArgs k{};
@@ -558,7 +559,9 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
   k.d_vec_ok = aligned16(p.d) && (p.ldd * out_es) % 16 == 0 && (p.d_batch_stride * out_es) % 16 == 0;
   k.c_vec_ok = k.c && aligned16(p.c) && (p.ldc * out_es) % 16 == 0 && (p.c_batch_stride * out_es) % 16 == 0;
-  k.bias_vec_ok = p.bias && aligned16(p.bias);
+  k.bias_vec_ok = p.bias && aligned16(p.bias) && (p.bias_batch_stride * bias_es) % 16 == 0;
+  k.a_broadcast = p.a_broadcast ? 1 : 0;
+  k.bias_batch_stride = p.bias_batch_stride;
   (void)bias_es;
   // A 16-bit D whose rows start on 16-byte boundaries leaves through shared memory and TMA stores.
   CUtensorMap td = ta;  // placeholder unless D qualifies

@@ -21,6 +21,8 @@ struct Problem {
   const void* a = nullptr;
   const void* b = nullptr;
   int64_t lda = 0, ldb = 0, a_batch_stride = 0, b_batch_stride = 0;
+  bool a_broadcast = false;        // every batch reads the same A (three projections of one input)
+  int64_t bias_batch_stride = 0;   // elements between the bias vectors of consecutive batches
   const void* c = nullptr;
   const void* bias = nullptr;
   void* d = nullptr;
@@ -47,6 +49,8 @@ struct KernelArgs {
   float acc_scale, beta;
   int d_vec_ok, c_vec_ok, bias_vec_ok;
   int d_tma;  // 16-bit D with 16-byte-aligned rows: stored through shared memory + TMA
+  int a_broadcast;
+  int64_t bias_batch_stride;
   int* status_word;
 };
 

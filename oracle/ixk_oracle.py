@@ -212,6 +212,23 @@ def gemm_custom_call(attrs: dict, lhs, rhs, c, bias, epilogue: str, out_dtype: i
 
 # --------------------------------------------------------------------------- fused attention
 
+def gemm_qkv(a: np.ndarray, b3: np.ndarray, bias3=None, *, dtype: int = BF16):
+    """Three projections of one input, out_i = A . B_i (+ bias_i): what HGEMM_QKV_KERNEL /
+    HGEMM_QKV_BIAS_KERNEL compute (xla/service/gpu/xetla/gemm/hgemm_impl.h:461-608: grid
+    dimension 0 picks the weight slab b + k*n*id, the output out0/1/2 and the bias slab bias + n*id),
+    fp32 accumulation and one rounding to the 16-bit type.  a [m,k], b3 [3,k,n], bias3 [3,n] or
+    None, all already holding values representable in `dtype`; returns three float32 [m,n] arrays."""
+    a = np.asarray(a, dtype=np.float32)
+    b3 = np.asarray(b3, dtype=np.float32)
+    outs = []
+    for i in range(3):
+        acc = a.astype(np.float64) @ b3[i].astype(np.float64)
+        if bias3 is not None:
+            acc = acc + np.asarray(bias3, dtype=np.float32)[i][None, :].astype(np.float64)
+        outs.append(round_to(acc.astype(np.float32), dtype))
+    return tuple(outs)
+
+
 def fmha_forward(q, k, v, bias=None, *, head_scale: float, causal: bool = False, dtype: int = BF16,
                  round_p: bool = True):
     """fmha_forward_t (xla/service/gpu/xetla/sdp/fmha_forward.h:256-568), un-tiled.

@@ -136,6 +136,44 @@ def test_qkv_fusion_shape(pkg, orc, cuda):
     orc.check_close(f32(out), want, rtol=1e-3, atol=1e-3, what="qkv")
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("with_bias", [False, True], ids=["nobias", "bias"])
+@pytest.mark.parametrize("placement", ["stacked", "scattered"])
+@pytest.mark.parametrize("shape", [(4, 4096, 4096), (300, 520, 200)], ids=lambda s: "x".join(map(str, s)))
+def test_qkv_gemm_entry_point(pkg, orc, cuda, shape, placement, with_bias, dtype):
+    """ixk_gemm_qkv: three projections of one input (hgemm_impl.h:461-608), at the reference test's
+    shape (example/qkv_fusion/test_qkv_fusion.py:37-51) and at a ragged one; outputs either stacked
+    in one buffer (one launch, projection = batch index) or scattered (three launches)."""
+    m, k, n = shape
+    g = torch.Generator().manual_seed(29)
+    x = torch.randn(m, k, generator=g).to(dtype)
+    w = (torch.randn(3, k, n, generator=g) / (k ** 0.5)).to(dtype)
+    b = torch.randn(3, n, generator=g).to(dtype) if with_bias else None
+    if placement == "stacked":
+        outs = None
+    else:
+        outs = tuple(torch.full((m, n), float("nan"), dtype=dtype, device=cuda) for _ in range(3))
+        outs = (outs[2], outs[0], outs[1])     # no common spacing
+    got = pkg.gemm_qkv(x.to(cuda), w.to(cuda), bias=b.to(cuda) if with_bias else None, outs=outs)
+    odt = orc.BF16 if dtype == torch.bfloat16 else orc.F16
+    want = orc.gemm_qkv(f32(x), f32(w), f32(b) if with_bias else None, dtype=odt)
+    rtol, atol = TOL[dtype]
+    for i in range(3):
+        orc.check_close(f32(got[i]), want[i], rtol=rtol, atol=atol, what=f"qkv out{i}")
+
+
+def test_qkv_gemm_rejections(pkg, cuda):
+    x = torch.zeros(8, 64, dtype=torch.float32, device=cuda)
+    w = torch.zeros(3, 64, 64, dtype=torch.float32, device=cuda)
+    with pytest.raises((pkg.IxkError, KeyError)):
+        pkg.gemm_qkv(x, w)                       # fp32 operands: BF16 / F16 only
+    x = torch.zeros(8, 68, dtype=torch.bfloat16, device=cuda)   # pitch 136 bytes: not a multiple of 16
+    w = torch.zeros(3, 68, 64, dtype=torch.bfloat16, device=cuda)
+    with pytest.raises(pkg.IxkError) as e:
+        pkg.gemm_qkv(x, w)
+    assert e.value.status == pkg.IXK_UNIMPLEMENTED
+
+
 def test_block_n_variants_agree(pkg, orc, cuda, monkeypatch):
     M, K, N = 384, 320, 768
     g = torch.Generator().manual_seed(29)

@@ -179,3 +179,16 @@ def test_check_close_reports(orc):
     with pytest.raises(AssertionError):
         orc.check_close(np.array([np.nan]), np.array([0.0]), rtol=1.0, atol=1.0)
     assert orc.check_close(np.array([1.0]), np.array([1.05]), rtol=0.0, atol=0.1) == pytest.approx(0.05)
+
+
+def test_qkv_gemm_matches_three_separate_products(orc):
+    """The fused form must equal the three separate matmuls it replaces
+    (example/qkv_fusion/test_qkv_fusion.py:24-35 compares exactly those)."""
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(5, 96, generator=g).bfloat16()
+    w = (torch.randn(3, 96, 40, generator=g) / 10).bfloat16()
+    b = torch.randn(3, 40, generator=g).bfloat16()
+    got = orc.gemm_qkv(x.float().numpy(), w.float().numpy(), b.float().numpy(), dtype=orc.BF16)
+    for i in range(3):
+        want = (x.float() @ w[i].float() + b[i].float()).bfloat16().float().numpy()
+        assert np.max(np.abs(got[i] - want)) <= 2e-2 * max(1.0, float(np.max(np.abs(want))))
