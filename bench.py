@@ -128,6 +128,11 @@ class GemmWorkload:
     def run(self, pkg, d, out):
         pkg.gemm(d["x"], d["w"], bias=d["b"], epilogue="BIAS_GELU", out=out)
 
+    library_name = "cuBLAS bf16 matmul through torch.matmul (no bias, no GELU)"
+
+    def library_run(self, d, out):
+        torch.matmul(d["x"], d["w"], out=out)
+
     def cpu_units(self):
         return self.M // 128  # row blocks
 
@@ -165,6 +170,15 @@ class Fp8GemmWorkload:
 
     def run(self, pkg, d, out):
         pkg.gemm_fp8(d["a"], d["b"], self.inv[0], self.inv[1], out=out)
+
+    library_name = "cuBLASLt fp8 matmul through torch._scaled_mm (B repacked column-major beforehand)"
+
+    def library_run(self, d, out):
+        if "b_col" not in d:
+            d["b_col"] = d["b"].t().contiguous().t()   # cuBLASLt wants the fp8 B operand column-major
+            d["sa"] = torch.tensor(self.inv[0], device=out.device)
+            d["sb"] = torch.tensor(self.inv[1], device=out.device)
+        torch._scaled_mm(d["a"], d["b_col"], scale_a=d["sa"], scale_b=d["sb"], out_dtype=torch.bfloat16, out=out)
 
     def cpu_units(self):
         return self.M // 128
@@ -308,6 +322,28 @@ def time_device(pkg, wl, dev_in, out, steps, warmup, flush_buf):
     return [s.elapsed_time(e) for s, e in zip(starts, ends)]
 
 
+def time_library(wl, dev_in, out, steps, warmup, flush_buf):
+    """The vendor library's kernel for the same product, timed the same way (context for the
+    roofline fraction; not on the product path).  None when the library refuses the operands."""
+    try:
+        for _ in range(warmup):
+            wl.library_run(dev_in, out)
+            flush_l2(flush_buf)
+        torch.cuda.synchronize()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(steps):
+            starts[i].record()
+            wl.library_run(dev_in, out)
+            ends[i].record()
+            flush_l2(flush_buf)
+        torch.cuda.synchronize()
+        ms = float(np.mean([s.elapsed_time(e) for s, e in zip(starts, ends)]))
+        return {"name": wl.library_name, "value": wl.work / (ms * 1e-3) / wl.scale_div, "unit": wl.unit, "ms": ms}
+    except Exception as e:  # noqa: BLE001 - any refusal of the library is reported, not fatal
+        return {"name": wl.library_name, "unavailable": str(e).splitlines()[0][:200]}
+
+
 def time_e2e(pkg, wl, host_in, dev_in, out, host_out, steps, warmup):
     """Steps through the public API with host buffers: H2D inputs, kernel, D2H result."""
     def one():
@@ -408,6 +444,8 @@ def run_ours(args, rank, world):
                          "peak_source": peak_note},
             "clocks": clk.summary(), "gpu_launches": int(launches),
         }
+        if hasattr(wl, "library_run") and world == 1:
+            res["library"] = time_library(wl, dev_in, out, max(3, min(args.steps, 10)), 3, flush_buf)
         if full:
             host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
             e2e_ms = time_e2e(pkg, wl, host, dev_in, out, host_out, max(3, min(args.steps, 10)), args.warmup)
@@ -447,6 +485,8 @@ def run_ours(args, rank, world):
                 r, w = measure(name, full=False)
                 others.append({"workload": w.name, "value": r["value"], "unit": r["unit"], "ms_per_step": r["ms_per_step"],
                                "roofline": r["roofline"], "gpu_launches": r["gpu_launches"]})
+                if "library" in r:
+                    others[-1]["library"] = r["library"]
             except Exception as ex:  # a failing side workload must not hide the headline
                 others.append({"workload": name, "error": repr(ex)})
         line["others"] = others
