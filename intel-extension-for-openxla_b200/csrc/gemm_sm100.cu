@@ -19,6 +19,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "ptx.cuh"
 
 namespace ixk {
@@ -186,6 +188,104 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   bn = r / rows;
 }
 
+// One tile's epilogue for the calling warp (TMEM lanes [32 quarter, 32 quarter + 32) of the
+// accumulator at tmem_acc): scale, bias, residual, activation, one rounding, store.
+template <int kBlockN>
+__device__ __forceinline__ void epilogue_tile(const KernelArgs& args, const CUtensorMap* tmap_d_ptr, uint32_t tmem_acc,
+                                              uint32_t stage_smem, int bz, int bm, int bn, int quarter, int lane,
+                                              uint32_t& n_store) {
+  const CUtensorMap& tmap_d = *tmap_d_ptr;
+  if (bm * kBlockM >= args.M) return;  // a CTA pair's second half past the last row block
+  const int row_in_tile = quarter * 32 + lane;
+  const bool vec_d = args.d_vec_ok != 0;
+  const bool vec_c = args.c_vec_ok != 0;
+  const bool vec_bias = args.bias_vec_ok != 0;
+      const int m = bm * kBlockM + row_in_tile;
+    const bool row_ok = m < args.M;
+    const int64_t d_row = bz * args.d_batch_stride + static_cast<int64_t>(m) * args.ldd;
+    const int64_t c_row = bz * args.c_batch_stride + static_cast<int64_t>(m) * args.ldc;
+    // 32 columns of this thread's row: accumulator -> scale, bias, residual, activation
+    auto chunk = [&](int c0, int n, int count, float (&v)[32]) {
+      uint32_t r[32];
+      ptx::tmem_ld_32x32(tmem_acc + c0, r);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * args.acc_scale;
+      if (args.bias != nullptr) {
+        float b[32];
+        load_row16(args.bias, bz * args.bias_batch_stride + n, args.bias_dtype, count, vec_bias, b);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += b[i];
+      }
+      if (args.c != nullptr && row_ok) {
+        float cc[32];
+        load_row16(args.c, c_row + n, args.out_dtype, count, vec_c, cc);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = fmaf(args.beta, cc[i], v[i]);
+      }
+      if (args.act == kActRelu) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
+      } else if (args.act == kActGelu) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+      }
+    };
+    if (args.d_tma) {
+      // 16-bit output through shared memory: each warp writes its 32 rows x 64 columns into a
+      // 128-byte-swizzled box of its own (lane = row, conflict-free) and one lane hands the box
+      // to a TMA store; two boxes per warp, so a box is only rewritten after the store issued
+      // two passes earlier has read it.  Stored from registers, a warp's 16-byte stores land in
+      // 32 different lines each; those requests queue in front of the producer's and the
+      // issuer's barrier traffic and cost 8-11 % of the kernel.
+#pragma unroll 1
+      for (int c0 = 0; c0 < kBlockN; c0 += 64) {
+        const int n = bn * kBlockN + c0;
+        if (n >= args.N) break;  // warp-uniform
+        uint32_t wv[32];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int nh = n + 32 * half;
+          if (nh < args.N) {  // warp-uniform
+            float v[32];
+            chunk(c0 + 32 * half, nh, min(32, args.N - nh), v);
+            pack_row16(v, args.out_dtype, &wv[16 * half]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) wv[16 * half + i] = 0u;
+          }
+        }
+        const uint32_t box = stage_smem + static_cast<uint32_t>((quarter * 2 + (n_store & 1)) * 4096);
+        if (lane == 0) ptx::bulk_wait_group_read<1>();
+        __syncwarp();
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const uint32_t addr = box + static_cast<uint32_t>(lane * 128 + ((g ^ (lane & 7)) << 4));
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(wv[4 * g]), "r"(wv[4 * g + 1]),
+                       "r"(wv[4 * g + 2]), "r"(wv[4 * g + 3])
+                       : "memory");
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::tma_store_3d(&tmap_d, box, n, bm * kBlockM + quarter * 32, bz);
+          ptx::bulk_commit_group();
+        }
+        ++n_store;
+      }
+    } else {
+#pragma unroll 1
+      for (int c0 = 0; c0 < kBlockN; c0 += 32) {
+        const int n = bn * kBlockN + c0;
+        if (n >= args.N) break;  // warp-uniform
+        const int count = min(32, args.N - n);
+        float v[32];
+        chunk(c0, n, count, v);
+        if (row_ok) store_row(args.d, d_row + n, args.out_dtype, count, vec_d, v);
+      }
+    }
+}
+
 template <int kBlockN, bool kFp8>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -340,102 +440,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    const int row_in_tile = quarter * 32 + lane;
     int buf = 0;
     uint32_t acc_phase = 0;
-    const bool vec_d = args.d_vec_ok != 0;
-    const bool vec_c = args.c_vec_ok != 0;
-    const bool vec_bias = args.bias_vec_ok != 0;
     uint32_t n_store = 0;  // TMA stores issued by this warp (alternating between its two boxes)
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int bz, bm, bn;
       tile_coords(t, args.tiles_m, args.tiles_n, bz, bm, bn);
       if (!ptx::mbar_wait(acc_full_bar(buf), acc_phase, ctl, kSiteEpilogue)) break;
       ptx::tc_fence_after_sync();
-      const int m = bm * kBlockM + row_in_tile;
-      const bool row_ok = m < args.M;
-      const int64_t d_row = bz * args.d_batch_stride + static_cast<int64_t>(m) * args.ldd;
-      const int64_t c_row = bz * args.c_batch_stride + static_cast<int64_t>(m) * args.ldc;
-      // 32 columns of this thread's row: accumulator -> scale, bias, residual, activation
-      auto chunk = [&](int c0, int n, int count, float (&v)[32]) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBlockN + c0, r);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * args.acc_scale;
-        if (args.bias != nullptr) {
-          float b[32];
-          load_row16(args.bias, bz * args.bias_batch_stride + n, args.bias_dtype, count, vec_bias, b);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] += b[i];
-        }
-        if (args.c != nullptr && row_ok) {
-          float cc[32];
-          load_row16(args.c, c_row + n, args.out_dtype, count, vec_c, cc);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = fmaf(args.beta, cc[i], v[i]);
-        }
-        if (args.act == kActRelu) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
-        } else if (args.act == kActGelu) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
-        }
-      };
-      if (args.d_tma) {
-        // 16-bit output through shared memory: each warp writes its 32 rows x 64 columns into a
-        // 128-byte-swizzled box of its own (lane = row, conflict-free) and one lane hands the box
-        // to a TMA store; two boxes per warp, so a box is only rewritten after the store issued
-        // two passes earlier has read it.  Stored from registers, a warp's 16-byte stores land in
-        // 32 different lines each; those requests queue in front of the producer's and the
-        // issuer's barrier traffic and cost 8-11 % of the kernel.
-#pragma unroll 1
-        for (int c0 = 0; c0 < kBlockN; c0 += 64) {
-          const int n = bn * kBlockN + c0;
-          if (n >= args.N) break;  // warp-uniform
-          uint32_t wv[32];
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const int nh = n + 32 * half;
-            if (nh < args.N) {  // warp-uniform
-              float v[32];
-              chunk(c0 + 32 * half, nh, min(32, args.N - nh), v);
-              pack_row16(v, args.out_dtype, &wv[16 * half]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) wv[16 * half + i] = 0u;
-            }
-          }
-          const uint32_t box = stage_smem + static_cast<uint32_t>((quarter * 2 + (n_store & 1)) * 4096);
-          if (lane == 0) ptx::bulk_wait_group_read<1>();
-          __syncwarp();
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const uint32_t addr = box + static_cast<uint32_t>(lane * 128 + ((g ^ (lane & 7)) << 4));
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(wv[4 * g]), "r"(wv[4 * g + 1]),
-                         "r"(wv[4 * g + 2]), "r"(wv[4 * g + 3])
-                         : "memory");
-          }
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            ptx::tma_store_3d(&tmap_d, box, n, bm * kBlockM + quarter * 32, bz);
-            ptx::bulk_commit_group();
-          }
-          ++n_store;
-        }
-      } else {
-#pragma unroll 1
-        for (int c0 = 0; c0 < kBlockN; c0 += 32) {
-          const int n = bn * kBlockN + c0;
-          if (n >= args.N) break;  // warp-uniform
-          const int count = min(32, args.N - n);
-          float v[32];
-          chunk(c0, n, count, v);
-          if (row_ok) store_row(args.d, d_row + n, args.out_dtype, count, vec_d, v);
-        }
-      }
+      epilogue_tile<kBlockN>(args, &tmap_d, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBlockN, stage_smem,
+                             bz, bm, bn, quarter, lane, n_store);
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(acc_empty_bar(buf));
       buf ^= 1;
@@ -456,6 +470,220 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs works on a 256 x 256 tile (tcgen05 cta_group::2).  Each
+// CTA loads its own 128 rows of A and its own 128 columns of B per k-slab, 32 KB instead of the
+// 48 KB a lone CTA needs for 128 x 256, so the operand traffic out of L2 drops by a third; that
+// traffic (17 TB/s for all SMs) is what bounds the single-CTA kernel.  The even CTA's MMA warp
+// issues for both; its commits arrive on the barriers of both CTAs, and both CTAs' TMA copies are
+// counted on the even CTA's full barrier.  Everything else is per CTA as above.
+struct PairCfg {
+  static constexpr int kBlockN = 256;                       // tile columns (128 per CTA as B rows)
+  static constexpr int kStageBytes = 2 * kATileBytes;       // A 128 x 128 B + B half 128 x 128 B
+  static constexpr int kStages = (192 * 1024) / kStageBytes;  // 6
+  static constexpr int kTmemCols = 2 * kBlockN;
+  static constexpr int kStagingBytes = 4 * 2 * 32 * 128;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
+};
+enum : int { kSitePairFull = 111, kSitePairPeer = 112, kSitePairAcc = 113, kSitePairForward = 114 };
+
+template <bool kFp8>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_d, const KernelArgs args) {
+  using C = PairCfg;
+  constexpr int kStages = C::kStages;
+  constexpr int kBlockN = C::kBlockN;
+  constexpr int kHalfN = kBlockN / 2;
+  constexpr int kElemBytes = kFp8 ? 1 : 2;
+  constexpr int kSlabElems = kSlabBytes / kElemBytes;
+  constexpr int kUmmaK = 32 / kElemBytes;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const uint32_t stage_smem = smem_base + kStages * C::kStageBytes;
+  const uint32_t bar_base = stage_smem + C::kStagingBytes;
+  // barrier slots: full[kStages], empty[kStages], peer_full[kStages] (even CTA), acc_full[2], acc_empty[2] (even CTA)
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto peer_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (3 * kStages + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (3 * kStages + 2 + b); };
+  uint8_t* tail = smem_gen + kStages * C::kStageBytes + C::kStagingBytes + 8 * (3 * kStages + 4);
+  static_assert(8 * (3 * kStages + 4) + 8 <= C::kBarrierBytes, "barrier area");
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();  // 0: issues the MMAs, 1: its partner
+  ptx::AbortCtl ctl{abort_flag, args.status_word};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+      ptx::mbar_init(peer_full_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(acc_full_bar(b), 1);
+      ptx::mbar_init(acc_empty_bar(b), 256);  // the epilogue threads of both CTAs
+    }
+    ptx::fence_mbar_init();
+    ptx::prefetch_tmap(&tmap_a);
+    ptx::prefetch_tmap(&tmap_b);
+    if (args.d_tma) ptx::prefetch_tmap(&tmap_d);
+  }
+  __syncthreads();
+  ptx::cluster_sync_all();  // both CTAs' barriers exist before anyone arrives on them remotely
+  // tcgen05.alloc / dealloc with cta_group::2 are collective over the pair: one warp of EACH CTA
+  // executes them (with the even CTA alone the odd CTA's columns were never released, and the
+  // next launch's allocation on that SM did not return).
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::cluster_sync_all();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_kb = (args.K + kSlabElems - 1) / kSlabElems;
+  const int tiles_m2 = (args.tiles_m + 1) / 2;  // pair tiles along M
+  const int num_tiles = tiles_m2 * args.tiles_n * args.batch;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (each CTA: its A rows, its B columns)
+    int stage = 0;
+    uint32_t phase = 0;
+    bool alive = true;
+    for (int t = pair_id; t < num_tiles && alive; t += num_pairs) {
+      int bz, bm2, bn;
+      tile_coords(t, tiles_m2, args.tiles_n, bz, bm2, bn);
+      const int m0 = (bm2 * 2 + static_cast<int>(rank)) * kBlockM;
+      const int n0 = bn * kBlockN + static_cast<int>(rank) * kHalfN;
+      const int az = args.a_broadcast ? 0 : bz;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, ctl, kSiteProducer)) {
+          alive = false;
+          break;
+        }
+        const uint32_t a_dst = smem_base + stage * C::kStageBytes;
+        const uint32_t b_dst = a_dst + kATileBytes;
+        // both CTAs' copies are counted on the EVEN CTA's barrier, which its issuer waits on
+        const uint32_t bar = ptx::map_to_cta(full_bar(stage), 0);
+        const int k0 = kb * kSlabElems;
+        if (ptx::elect_one()) {
+          if (rank == 0) ptx::mbar_expect_tx(full_bar(stage), 2 * C::kStageBytes);
+          if (args.a_mn_major) {
+#pragma unroll
+            for (int i = 0; i < kBlockM / kSlabElems; ++i)
+              ptx::tma_load_3d_pair(a_dst + i * (kSlabElems * kSlabBytes), &tmap_a, bar, m0 + i * kSlabElems, k0, az);
+          } else {
+            ptx::tma_load_3d_pair(a_dst, &tmap_a, bar, k0, m0, az);
+          }
+          if (args.b_mn_major) {
+#pragma unroll
+            for (int i = 0; i < kHalfN / kSlabElems; ++i)
+              ptx::tma_load_3d_pair(b_dst + i * (kSlabElems * kSlabBytes), &tmap_b, bar, n0 + i * kSlabElems, k0, bz);
+          } else {
+            ptx::tma_load_3d_pair(b_dst, &tmap_b, bar, k0, n0, bz);
+          }
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1 && rank == 1) {
+    // (the odd CTA's second warp only takes part in the TMEM allocation)
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ even CTA: MMA issuer for the pair
+    int stage = 0;
+    uint32_t phase = 0;
+    int buf = 0;
+    uint32_t acc_phase = 0;
+    bool alive = true;
+    const uint32_t a_lbo = args.a_mn_major ? kSlabElems * kSlabBytes : 16;
+    const uint32_t b_lbo = args.b_mn_major ? kSlabElems * kSlabBytes : 16;
+    const uint32_t a_kstep = args.a_mn_major ? kUmmaK * kSlabBytes : 32;
+    const uint32_t b_kstep = args.b_mn_major ? kUmmaK * kSlabBytes : 32;
+    for (int t = pair_id; t < num_tiles && alive; t += num_pairs) {
+      if (!ptx::mbar_wait(acc_empty_bar(buf), acc_phase ^ 1u, ctl, kSitePairAcc)) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + buf * kBlockN;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!ptx::mbar_wait(full_bar(stage), phase, ctl, kSitePairFull)) {
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t a_src = smem_base + stage * C::kStageBytes;
+        const uint32_t b_src = a_src + kATileBytes;
+#pragma unroll
+        for (int ks = 0; ks < kSlabElems / kUmmaK; ++ks) {
+          const uint64_t da = ptx::umma_smem_desc(a_src + ks * a_kstep, a_lbo, 1024);
+          const uint64_t db = ptx::umma_smem_desc(b_src + ks * b_kstep, b_lbo, 1024);
+          ptx::umma_ss_pair_elect<kFp8>(d_tmem, da, db, args.idesc, (kb | ks) != 0 ? 1u : 0u);
+        }
+        ptx::umma_commit_pair_elect(empty_bar(stage));  // both CTAs' producers may refill the slot
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (!alive) break;
+      ptx::umma_commit_pair_elect(acc_full_bar(buf));  // both CTAs' epilogue warps
+      buf ^= 1;
+      if (buf == 0) acc_phase ^= 1u;
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (each CTA: its 128 rows)
+    const int quarter = warp & 3;
+    int buf = 0;
+    uint32_t acc_phase = 0;
+    uint32_t n_store = 0;
+    for (int t = pair_id; t < num_tiles; t += num_pairs) {
+      int bz, bm2, bn;
+      tile_coords(t, tiles_m2, args.tiles_n, bz, bm2, bn);
+      if (!ptx::mbar_wait(acc_full_bar(buf), acc_phase, ctl, kSiteEpilogue)) break;
+      ptx::tc_fence_after_sync();
+      epilogue_tile<kBlockN>(args, &tmap_d, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBlockN,
+                             stage_smem, bz, bm2 * 2 + static_cast<int>(rank), bn, quarter, lane, n_store);
+      ptx::tc_fence_before_sync();
+      if (rank == 0) {
+        ptx::mbar_arrive(acc_empty_bar(buf));
+      } else {
+        ptx::mbar_arrive_cluster(acc_empty_bar(buf), 0);
+      }
+      buf ^= 1;
+      if (buf == 0) acc_phase ^= 1u;
+    }
+    if (args.d_tma && lane == 0) ptx::bulk_wait_group<0>();
+  }
+
+  // Teardown: neither CTA may leave while its partner can still read its shared memory or arrive
+  // on its barriers.
+  if (*abort_flag != 0) __nanosleep(2000000);
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc_pair(tmem_base, C::kTmemCols);
+  }
+  ptx::cluster_sync_all();
+}
+
 template <int kBlockN, bool kFp8>
 int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const KernelArgs& args,
                int grid, cudaStream_t stream) {
@@ -470,6 +698,34 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& 
   }
   fn<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, td, args);
   IXK_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return IXK_OK;
+}
+
+template <bool kFp8>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const KernelArgs& args,
+                int pairs, cudaStream_t stream) {
+  auto* fn = &gemm_pair_kernel<kFp8>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  IXK_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    IXK_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmemBytes));
+    configured_device = dev;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  IXK_CUDA_OK(cudaLaunchKernelEx(&cfg, fn, ta, tb, td, args));
   count_launch();
   return IXK_OK;
 }
@@ -495,6 +751,13 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   // An MN-major 8-bit B tile is loaded in 128-column boxes (one swizzle span), so it cannot be
   // narrower than 128 columns.
   if (p.fp8 && p.b_mn_major && bn < 128) bn = 128;
+
+  // Large problems run on CTA pairs (256 x 256 tiles): worth it once every pair of SMs has a tile.
+  const int64_t tiles_m_all = (p.M + kBlockM - 1) / kBlockM;
+  const int64_t pair_tiles = ((tiles_m_all + 1) / 2) * ((p.N + 255) / 256) * p.batch;
+  bool pair = bn == 256 && tiles_m_all >= 2 && pair_tiles >= dev.sm_count / 2;
+  if (const char* env = std::getenv("IXK_GEMM_PAIR")) pair = pair && std::atoi(env) != 0;
+  const int b_box_rows = pair ? 128 : bn;
 
   const CUtensorMapDataType dt = p.fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                        : (p.ab_dtype == IXK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -528,7 +791,7 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   CUtensorMap ta, tb;
   int rc = make_map(&ta, p.a, p.a_mn_major, p.M, p.lda, p.a_batch_stride, kBlockM, p.a_broadcast);
   if (rc != IXK_OK) return rc;
-  rc = make_map(&tb, p.b, p.b_mn_major, p.N, p.ldb, p.b_batch_stride, bn, false);
+  rc = make_map(&tb, p.b, p.b_mn_major, p.N, p.ldb, p.b_batch_stride, b_box_rows, false);
   if (rc != IXK_OK) return rc;
 
   KernelArgs k{};
@@ -540,7 +803,7 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   k.tiles_n = static_cast<int>((p.N + bn - 1) / bn);
   k.a_mn_major = p.a_mn_major;
   k.b_mn_major = p.b_mn_major;
-  k.idesc = ptx::umma_idesc(p.a_fmt, p.b_fmt, p.a_mn_major ? 1 : 0, p.b_mn_major ? 1 : 0, kBlockM, bn);
+  k.idesc = ptx::umma_idesc(p.a_fmt, p.b_fmt, p.a_mn_major ? 1 : 0, p.b_mn_major ? 1 : 0, pair ? 2 * kBlockM : kBlockM, bn);
   k.bias = p.bias;
   k.c = (p.beta != 0.0f) ? p.c : nullptr;
   k.d = p.d;
@@ -582,6 +845,10 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
     if ((rc = encode_tmap(&td, p.d, s)) != IXK_OK) return rc;
   }
 
+  if (pair) {
+    const int pairs = static_cast<int>(pair_tiles < dev.sm_count / 2 ? pair_tiles : dev.sm_count / 2);
+    return p.fp8 ? launch_pair<true>(ta, tb, td, k, pairs, stream) : launch_pair<false>(ta, tb, td, k, pairs, stream);
+  }
   const int64_t tiles = static_cast<int64_t>(k.tiles_m) * k.tiles_n * k.batch;
   const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
   if (p.fp8) {

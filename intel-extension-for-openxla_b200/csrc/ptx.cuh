@@ -304,6 +304,119 @@ __device__ __forceinline__ void umma_ss_elect(uint32_t d_tmem, uint64_t a_desc, 
   }
 }
 
+// ---------------------------------------------------------------- CTA pairs (cta_group::2)
+// A cluster of two CTAs shares one MMA tile: A comes from each CTA's own shared memory (its 128 rows
+// of a 256-row tile), B from both (CTA r supplies columns [r N/2, (r+1) N/2)), the accumulator lands
+// in each CTA's own TMEM.  One thread of the even CTA issues; tcgen05.alloc / dealloc with
+// cta_group::2 are collective: one warp of EACH CTA of the pair executes them.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t local_addr, uint32_t cta_rank) {
+  uint32_t remote, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta_rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+  return v;
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in BOTH CTAs once every MMA issued so far is done.
+__device__ __forceinline__ void umma_commit_pair_elect(uint32_t bar) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred e;\n\t"
+      ".reg .b16 mask;\n\t"
+      "mov.b16 mask, 3;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], mask;\n\t"
+      "}\n" ::"r"(bar)
+      : "memory");
+}
+template <bool kFp8>
+__device__ __forceinline__ void umma_ss_pair_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                   uint32_t idesc, uint32_t accumulate) {
+  if constexpr (kFp8) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// Address of `local_addr` (a shared-memory offset valid in every CTA) in CTA `cta_rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t cta_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta_rank));
+  return remote;
+}
+// Tile load into THIS CTA's shared memory whose completion is counted on a barrier that may live
+// in the other CTA of the pair (`bar_cluster` is a shared::cluster address).  No multicast.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster, int x, int y,
+                                                 int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(tmap), "r"(bar_cluster), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+// Bounded wait on a barrier that a thread of the OTHER CTA of the cluster arrives on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, const AbortCtl& ctl, int code) {
+  auto probe = [&]() {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+  };
+  if (probe()) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (probe()) return true;
+    if ((++spins & 0x3ffu) == 0) {
+      if (*ctl.cta_abort != 0) return false;
+      if (clock64() - t0 > kWaitCycleLimit) {
+        *ctl.cta_abort = 1;
+        atomicCAS(ctl.status_word, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
 // D[tmem] (+)= A[smem] . B[smem]; issued by ONE thread.
 template <bool kFp8>
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,

@@ -44,6 +44,21 @@ def test_scaled_gemm(pkg, orc, cuda, shape, b_dtype, lb):
     orc.check_close(f32(out), want, rtol=2e-2, atol=2e-2 * rms, what=f"fp8 {shape} {b_dtype} B {lb}")
 
 
+@pytest.mark.parametrize("b_dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
+@pytest.mark.parametrize("lb", ["row", "col"])
+def test_scaled_gemm_on_cta_pairs(pkg, orc, cuda, b_dtype, lb):
+    """A shape that runs on the CTA-pair kernel (odd row-block count, ragged N and K)."""
+    M, K, N = 1280 + 128, 400, 4608 + 48
+    g = torch.Generator().manual_seed(103)
+    aq, sa = pkg.quantize_fp8(torch.randn(M, K, generator=g), torch.float8_e4m3fn)
+    bq, sb = pkg.quantize_fp8(torch.randn(K, N, generator=g), b_dtype)
+    bd = bq.to(cuda) if lb == "row" else bq.to(cuda).t().contiguous().t()
+    out = pkg.gemm_fp8(aq.to(cuda), bd, 1.0 / sa, 1.0 / sb)
+    want = orc.fp8_scaled_gemm(aq.view(torch.uint8).numpy(), orc.F8E4M3, sa, bq.view(torch.uint8).numpy(), ODT[b_dtype], sb)
+    rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    orc.check_close(f32(out), want, rtol=2e-2, atol=2e-2 * rms, what=f"fp8 pair B {lb}")
+
+
 def test_e5m2_lhs_and_bias_epilogue(pkg, orc, cuda):
     M, K, N = 192, 256, 128
     g = torch.Generator().manual_seed(5)

@@ -136,6 +136,43 @@ def test_qkv_fusion_shape(pkg, orc, cuda):
     orc.check_close(f32(out), want, rtol=1e-3, atol=1e-3, what="qkv")
 
 
+@pytest.mark.parametrize("la", ["row", "col"])
+@pytest.mark.parametrize("lb", ["row", "col"])
+@pytest.mark.parametrize("dtype,out_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float16, torch.float16),
+                                             (torch.bfloat16, torch.float32)])
+def test_cta_pair_tiles(pkg, orc, cuda, monkeypatch, la, lb, dtype, out_dtype):
+    """Shapes large enough for the CTA-pair kernel (256 x 256 tiles on two SMs): an odd number of
+    row blocks (the last pair has an empty half), ragged N and K, every operand layout, bias +
+    GELU + residual; the single-CTA kernel must give the same numbers on the same inputs."""
+    M, K, N = 1152 + 40, 328, 4608 + 72
+    g = torch.Generator().manual_seed(97)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    w = (torch.randn(K, N, generator=g) * 0.1).to(dtype)
+    b = torch.randn(N, generator=g).to(dtype)
+    c = torch.randn(M, N, generator=g).to(out_dtype)
+    run = lambda: pkg.gemm(as_layout(x.to(cuda), la), as_layout(w.to(cuda), lb), bias=b.to(cuda), c=c.to(cuda), beta=0.5,
+                           epilogue="BIAS_GELU", out_dtype=out_dtype)
+    out = run()
+    odt = {torch.bfloat16: orc.BF16, torch.float16: orc.F16, torch.float32: orc.F32}[out_dtype]
+    want = orc.gemm_epilogue(f32(x) @ f32(w), f32(b), f32(c), 0.5, "BIAS_GELU", odt)
+    rtol, atol = TOL[out_dtype]
+    orc.check_close(f32(out), want, rtol=max(rtol, 4e-3), atol=max(atol, 4e-3), what=f"pair A {la} B {lb}")
+    monkeypatch.setenv("IXK_GEMM_PAIR", "0")
+    single = run()
+    assert torch.equal(out, single)   # same products in the same order: bit-identical
+
+
+def test_cta_pair_batched(pkg, orc, cuda):
+    B, M, K, N = 2, 768, 192, 3328
+    g = torch.Generator().manual_seed(101)
+    x = torch.randn(B, M, K, generator=g).bfloat16()
+    w = (torch.randn(B, K, N, generator=g) * 0.1).bfloat16()
+    out = pkg.gemm(x.to(cuda), w.to(cuda))
+    for i in range(B):
+        want = orc.gemm_epilogue(f32(x[i]) @ f32(w[i]), None, None, 0.0, "DEFAULT", orc.BF16)
+        orc.check_close(f32(out[i]), want, rtol=2e-2, atol=2e-2, what=f"pair batch {i}")
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
 @pytest.mark.parametrize("with_bias", [False, True], ids=["nobias", "bias"])
 @pytest.mark.parametrize("placement", ["stacked", "scattered"])
