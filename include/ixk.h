@@ -210,6 +210,39 @@ int ixk_fmha_fwd_static_scratch(const ixk_fmha_desc* desc, const void* q, const 
                                 const void* v, const void* bias, void* out, float* lse,
                                 void* cuda_stream);
 
+/* ------------------------------------------------- between the custom calls */
+/* The memory-bound steps a decoder layer runs between the calls above.  The
+ * reference has no custom call for them: XLA compiles them as loop fusions
+ * (the layers are example/gptj/jax_gptj.py and example/gemma/keras_nlp.patch:53-63).
+ * They are here so that a layer driven through this library is one pass over
+ * HBM per step instead of a chain of framework kernels.  dtype ∈ {BF16, F16};
+ * pointers 16-byte aligned; cols, rotary_dim and all strides multiples of 8
+ * elements (else IXK_INVALID_ARGUMENT). */
+typedef enum ixk_norm_kind { IXK_NORM_LAYER = 0, IXK_NORM_RMS = 1 } ixk_norm_kind;
+/* y[r,:] = (x[r,:] - mean) * rsqrt(var + eps)   (LAYER; biased variance)
+ * y[r,:] =  x[r,:] * rsqrt(mean(x^2) + eps)     (RMS)
+ * statistics in fp32, no learned gain or shift; ldx/ldy row pitches in elements;
+ * cols <= 8192 (else IXK_UNIMPLEMENTED).  x and y may be the same buffer. */
+int ixk_row_norm(int dtype, int kind, int64_t rows, int64_t cols, const void* x,
+                 int64_t ldx, void* y, int64_t ldy, float eps, void* cuda_stream);
+/* Rotary position embedding in place, GPT-J convention: elements (2i, 2i+1),
+ * 2i < rotary_dim, of every head rotate by the angle whose cosine / sine is
+ * cos_table / sin_table[position, i] (fp32 tables [seq_len, rotary_dim/2]).
+ * x addresses token t, head h at x + t*token_stride + h*head_stride; token t
+ * sits at position t % seq_len.  Giving heads = 2 * heads_local and x = the
+ * fused [tokens, 3, heads_local, head_dim] projection rotates q and k at once. */
+int ixk_rotary_interleaved(int dtype, void* x, int64_t tokens, int64_t seq_len,
+                           int64_t heads, int64_t rotary_dim, int64_t token_stride,
+                           int64_t head_stride, const float* cos_table,
+                           const float* sin_table, void* cuda_stream);
+/* out = x + partial                      (bias NULL)
+ * out = x + round(partial + bias[col])   (bias given; the inner sum is rounded
+ * to dtype before the residual add).  All [rows, cols] dense; out may alias x
+ * or partial. */
+int ixk_residual_add(int dtype, int64_t rows, int64_t cols, const void* x,
+                     const void* partial, const void* bias, void* out,
+                     void* cuda_stream);
+
 /* ------------------------------------------------------------ diagnostics */
 /* Every device-side wait in the tensor-core kernels is bounded; a wait that
  * gives up records a code in a per-device status word and the kernel drains and

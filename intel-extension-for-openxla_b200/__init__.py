@@ -86,6 +86,11 @@ ABI_SYMBOLS = {
     "ixk_gemm_qkv": (ctypes.c_int, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp, ctypes.c_int64,
                                     _vp, ctypes.c_int64, _vp, _vp, _vp, _vp, ctypes.c_int64, _vp]),
     "ixk_fmha_fwd": (ctypes.c_int, [ctypes.POINTER(_FmhaDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "ixk_row_norm": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, _vp, ctypes.c_int64,
+                                    _vp, ctypes.c_int64, ctypes.c_float, _vp]),
+    "ixk_rotary_interleaved": (ctypes.c_int, [ctypes.c_int, _vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                              ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp, _vp, _vp]),
+    "ixk_residual_add": (ctypes.c_int, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, _vp, _vp, _vp, _vp, _vp]),
     "ixk_fmha_fwd_workspace_bytes": (_sz, [ctypes.POINTER(_FmhaDesc)]),
     "ixk_fmha_fwd_static_scratch": (ctypes.c_int, [ctypes.POINTER(_FmhaDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ixk_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
@@ -304,6 +309,62 @@ def gemm_qkv(x: torch.Tensor, w_qkv: torch.Tensor, *, bias: Optional[torch.Tenso
                             bias.data_ptr() if bias is not None else None, outs[0].data_ptr(), outs[1].data_ptr(),
                             outs[2].data_ptr(), outs[0].stride(0), _stream_ptr(stream)))
     return tuple(outs)
+
+
+# ----------------------------------------------------------------------------- between the calls
+
+NORM_LAYER, NORM_RMS = 0, 1
+
+
+def row_norm(x: torch.Tensor, *, kind: int = NORM_LAYER, eps: float = 1e-5, out: Optional[torch.Tensor] = None,
+             stream=None) -> torch.Tensor:
+    """LayerNorm (unit gain, zero shift) or RMSNorm over the last dimension of a dense tensor."""
+    if not x.is_contiguous():
+        raise IxkError(IXK_INVALID_ARGUMENT, "row_norm wants a contiguous tensor")
+    out = torch.empty_like(x) if out is None else out
+    if out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous():
+        raise IxkError(IXK_INVALID_ARGUMENT, "out must match x")
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    _check(load_library().ixk_row_norm(_TORCH_TO_IXK[x.dtype], kind, rows, cols, x.data_ptr(), cols, out.data_ptr(),
+                                       cols, eps, _stream_ptr(stream)))
+    return out
+
+
+def rotary_interleaved_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_len: int, rotary_dim: int,
+                        stream=None) -> torch.Tensor:
+    """In place on x [tokens, heads, head_dim] (any token pitch, unit element stride): pairs (2i, 2i+1)
+    of the first rotary_dim elements of every head, token t at position t % seq_len; cos/sin fp32
+    [seq_len, rotary_dim/2]."""
+    if x.dim() != 3 or x.stride(2) != 1:
+        raise IxkError(IXK_INVALID_ARGUMENT, "x must be [tokens, heads, head_dim] with unit element stride")
+    if cos.dtype != torch.float32 or sin.dtype != torch.float32 or not cos.is_contiguous() or not sin.is_contiguous() \
+            or cos.shape != (seq_len, rotary_dim // 2) or sin.shape != cos.shape:
+        raise IxkError(IXK_INVALID_ARGUMENT, "cos/sin must be contiguous fp32 [seq_len, rotary_dim/2]")
+    if rotary_dim > x.shape[2]:
+        raise IxkError(IXK_INVALID_ARGUMENT, "rotary_dim exceeds head_dim")
+    _check(load_library().ixk_rotary_interleaved(_TORCH_TO_IXK[x.dtype], x.data_ptr(), x.shape[0], seq_len, x.shape[1],
+                                                 rotary_dim, x.stride(0), x.stride(1), cos.data_ptr(), sin.data_ptr(),
+                                                 _stream_ptr(stream)))
+    return x
+
+
+def residual_add(x: torch.Tensor, partial: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """x + partial, or x + round(partial + bias) with bias along the last dimension."""
+    if not x.is_contiguous() or not partial.is_contiguous() or partial.numel() != x.numel() or partial.dtype != x.dtype:
+        raise IxkError(IXK_INVALID_ARGUMENT, "x and partial must be dense tensors of one size and type")
+    cols = x.shape[-1]
+    if bias is not None and (bias.shape != (cols,) or bias.dtype != x.dtype or not bias.is_contiguous()):
+        raise IxkError(IXK_INVALID_ARGUMENT, "bias must be a dense [cols] vector of the input type")
+    out = torch.empty_like(x) if out is None else out
+    if out.numel() != x.numel() or out.dtype != x.dtype or not out.is_contiguous():
+        raise IxkError(IXK_INVALID_ARGUMENT, "out must match x")
+    rows = x.numel() // cols if cols else 0
+    _check(load_library().ixk_residual_add(_TORCH_TO_IXK[x.dtype], rows, cols, x.data_ptr(), partial.data_ptr(),
+                                           bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                                           _stream_ptr(stream)))
+    return out
 
 
 # ----------------------------------------------------------------------------- attention

@@ -1,0 +1,284 @@
+// The memory-bound steps between the custom calls of a decoder layer: row normalisation
+// (LayerNorm / RMSNorm without learned gain), interleaved-pair rotary embedding applied in place
+// to the q and k slices of a fused QKV projection, and the residual add that closes the block.
+// XLA emits these as loop fusions around the custom calls (they are not custom calls in the
+// reference); they live here so that a layer built from the library's GEMM and attention calls is
+// not dominated by many small framework kernels.  Each is one pass over its operands with 16-byte
+// accesses: the bound is HBM bandwidth, the cost is (bytes read + bytes written) / bandwidth.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "host_common.h"
+
+namespace ixk {
+namespace glue {
+
+namespace {
+
+constexpr int kNormThreads = 256;
+constexpr int kNormVecs = 4;          // 16-byte vectors a thread keeps in registers: cols <= 8192
+constexpr int kVecElems = 8;          // 16-bit elements per 16-byte vector
+
+template <bool kBf16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (kBf16) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  } else {
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  }
+}
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (kBf16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  } else {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
+template <bool kBf16>
+__device__ __forceinline__ float round_trip(float v) {   // value after a store in the 16-bit type
+  if constexpr (kBf16) return __bfloat162float(__float2bfloat16_rn(v));
+  else return __half2float(__float2half_rn(v));
+}
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();                    // scratch may still be read from the previous reduction
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = lane < kNormThreads / 32 ? scratch[lane] : 0.0f;
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return __shfl_sync(0xffffffffu, t, 0);
+}
+
+// One CTA per row; the row stays in registers between the statistics and the write.
+template <bool kBf16, bool kRms>
+__global__ void __launch_bounds__(kNormThreads) row_norm_kernel(const uint4* __restrict__ x, uint4* __restrict__ y,
+                                                                int cols, int64_t ldx_vec, int64_t ldy_vec, float eps) {
+  __shared__ float scratch[kNormThreads / 32];
+  const int nvec = cols / kVecElems;
+  const uint4* xr = x + static_cast<int64_t>(blockIdx.x) * ldx_vec;
+  uint4* yr = y + static_cast<int64_t>(blockIdx.x) * ldy_vec;
+  float v[kNormVecs][kVecElems];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kNormVecs; ++i) {
+    const int idx = threadIdx.x + i * kNormThreads;
+    if (idx < nvec) {
+      const uint4 w = xr[idx];
+      const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack2<kBf16>(words[j]);
+        v[i][2 * j] = f.x;
+        v[i][2 * j + 1] = f.y;
+        sum += kRms ? f.x * f.x + f.y * f.y : f.x + f.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kVecElems; ++j) v[i][j] = 0.0f;
+    }
+  }
+  const float inv_n = 1.0f / static_cast<float>(cols);
+  float mean = 0.0f, rstd;
+  if constexpr (kRms) {
+    rstd = rsqrtf(block_sum(sum, scratch) * inv_n + eps);
+  } else {
+    mean = block_sum(sum, scratch) * inv_n;
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kNormVecs; ++i) {
+      if (threadIdx.x + i * kNormThreads < nvec) {
+#pragma unroll
+        for (int j = 0; j < kVecElems; ++j) {
+          const float d = v[i][j] - mean;
+          sq = fmaf(d, d, sq);
+        }
+      }
+    }
+    rstd = rsqrtf(block_sum(sq, scratch) * inv_n + eps);
+  }
+#pragma unroll
+  for (int i = 0; i < kNormVecs; ++i) {
+    const int idx = threadIdx.x + i * kNormThreads;
+    if (idx < nvec) {
+      uint32_t words[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        words[j] = pack2<kBf16>((v[i][2 * j] - mean) * rstd, (v[i][2 * j + 1] - mean) * rstd);
+      yr[idx] = make_uint4(words[0], words[1], words[2], words[3]);
+    }
+  }
+}
+
+// One thread per 16-byte vector = four (even, odd) pairs of one head of one token.
+template <bool kBf16>
+__global__ void rotary_kernel(uint4* __restrict__ x, const float4* __restrict__ cos_t, const float4* __restrict__ sin_t,
+                              int64_t total_vecs, int vecs_per_head, int heads, int seq_len,
+                              int64_t token_stride_vec, int64_t head_stride_vec) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vecs;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int vec = static_cast<int>(i % vecs_per_head);
+    const int64_t th = i / vecs_per_head;
+    const int head = static_cast<int>(th % heads);
+    const int64_t token = th / heads;
+    const int pos = static_cast<int>(token % seq_len);
+    uint4* p = x + token * token_stride_vec + head * head_stride_vec + vec;
+    const uint4 w = *p;
+    const float4 c = cos_t[static_cast<int64_t>(pos) * vecs_per_head + vec];
+    const float4 s = sin_t[static_cast<int64_t>(pos) * vecs_per_head + vec];
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+    const float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+    uint32_t out[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack2<kBf16>(words[j]);
+      out[j] = pack2<kBf16>(f.x * cs[j] - f.y * sn[j], f.x * sn[j] + f.y * cs[j]);
+    }
+    *p = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
+// out = x + round(partial + bias): the sum with the bias is rounded to the storage type first,
+// like a framework that materialises (partial + bias) before the residual add.
+template <bool kBf16>
+__global__ void residual_add_kernel(const uint4* __restrict__ x, const uint4* __restrict__ partial,
+                                    const uint4* __restrict__ bias, uint4* __restrict__ out, int64_t total_vecs,
+                                    int vecs_per_row) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vecs;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 a = x[i], p = partial[i];
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, pw[4] = {p.x, p.y, p.z, p.w};
+    uint32_t bw[4] = {0, 0, 0, 0};
+    if (bias != nullptr) {
+      const uint4 b = bias[i % vecs_per_row];
+      bw[0] = b.x; bw[1] = b.y; bw[2] = b.z; bw[3] = b.w;
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 fa = unpack2<kBf16>(aw[j]), fp = unpack2<kBf16>(pw[j]), fb = unpack2<kBf16>(bw[j]);
+      const float t0 = bias != nullptr ? round_trip<kBf16>(fp.x + fb.x) : fp.x;
+      const float t1 = bias != nullptr ? round_trip<kBf16>(fp.y + fb.y) : fp.y;
+      o[j] = pack2<kBf16>(fa.x + t0, fa.y + t1);
+    }
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int elementwise_grid(int64_t total_vecs, int threads, int sm_count) {
+  const int64_t want = (total_vecs + threads - 1) / threads;
+  const int64_t cap = static_cast<int64_t>(sm_count) * 8;     // eight resident CTAs of 256 threads per SM
+  return static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
+}  // namespace
+}  // namespace glue
+}  // namespace ixk
+
+using namespace ixk;
+
+extern "C" {
+
+int ixk_row_norm(int dtype, int kind, int64_t rows, int64_t cols, const void* x, int64_t ldx, void* y, int64_t ldy,
+                 float eps, void* stream) {
+  clear_error();
+  if (dtype != IXK_BF16 && dtype != IXK_F16) return fail(IXK_UNIMPLEMENTED, "row_norm: dtype must be BF16 or F16");
+  if (kind != IXK_NORM_LAYER && kind != IXK_NORM_RMS) return fail(IXK_INVALID_ARGUMENT, "row_norm: unknown kind");
+  if (rows < 0 || cols <= 0 || (rows > 0 && (x == nullptr || y == nullptr)))
+    return fail(IXK_INVALID_ARGUMENT, "row_norm: null or negative argument");
+  if (cols % glue::kVecElems || ldx % glue::kVecElems || ldy % glue::kVecElems || ldx < cols || ldy < cols ||
+      !glue::aligned16(x) || !glue::aligned16(y))
+    return fail(IXK_INVALID_ARGUMENT, "row_norm: cols and row strides must be multiples of 8 elements, pointers 16-byte aligned");
+  if (cols > glue::kNormThreads * glue::kNormVecs * glue::kVecElems)
+    return fail(IXK_UNIMPLEMENTED, "row_norm: rows longer than 8192 elements");
+  if (rows > 0x7fffffff) return fail(IXK_UNIMPLEMENTED, "row_norm: more than 2^31-1 rows");
+  DeviceInfo info;
+  if (int st = get_device_info(&info)) return st;
+  if (rows == 0) return IXK_OK;
+  const dim3 grid(static_cast<unsigned>(rows));
+  auto s = static_cast<cudaStream_t>(stream);
+  const uint4* xv = static_cast<const uint4*>(x);
+  uint4* yv = static_cast<uint4*>(y);
+  const int64_t lx = ldx / glue::kVecElems, ly = ldy / glue::kVecElems;
+  const int c = static_cast<int>(cols);
+  if (dtype == IXK_BF16) {
+    if (kind == IXK_NORM_RMS) glue::row_norm_kernel<true, true><<<grid, glue::kNormThreads, 0, s>>>(xv, yv, c, lx, ly, eps);
+    else glue::row_norm_kernel<true, false><<<grid, glue::kNormThreads, 0, s>>>(xv, yv, c, lx, ly, eps);
+  } else {
+    if (kind == IXK_NORM_RMS) glue::row_norm_kernel<false, true><<<grid, glue::kNormThreads, 0, s>>>(xv, yv, c, lx, ly, eps);
+    else glue::row_norm_kernel<false, false><<<grid, glue::kNormThreads, 0, s>>>(xv, yv, c, lx, ly, eps);
+  }
+  IXK_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return IXK_OK;
+}
+
+int ixk_rotary_interleaved(int dtype, void* x, int64_t tokens, int64_t seq_len, int64_t heads, int64_t rotary_dim,
+                           int64_t token_stride, int64_t head_stride, const float* cos_table, const float* sin_table,
+                           void* stream) {
+  clear_error();
+  if (dtype != IXK_BF16 && dtype != IXK_F16) return fail(IXK_UNIMPLEMENTED, "rotary: dtype must be BF16 or F16");
+  if (tokens < 0 || seq_len <= 0 || heads <= 0 || rotary_dim <= 0 ||
+      (tokens > 0 && (x == nullptr || cos_table == nullptr || sin_table == nullptr)))
+    return fail(IXK_INVALID_ARGUMENT, "rotary: null or non-positive argument");
+  if (tokens % seq_len) return fail(IXK_INVALID_ARGUMENT, "rotary: tokens must be a multiple of seq_len");
+  if (rotary_dim % glue::kVecElems || token_stride % glue::kVecElems || head_stride % glue::kVecElems ||
+      head_stride < rotary_dim || !glue::aligned16(x) || !glue::aligned16(cos_table) || !glue::aligned16(sin_table))
+    return fail(IXK_INVALID_ARGUMENT, "rotary: rotary_dim and strides must be multiples of 8 elements, pointers 16-byte aligned");
+  DeviceInfo info;
+  if (int st = get_device_info(&info)) return st;
+  const int vph = static_cast<int>(rotary_dim / glue::kVecElems);
+  const int64_t total = tokens * heads * vph;
+  if (total == 0) return IXK_OK;
+  const int grid = glue::elementwise_grid(total, 256, info.sm_count);
+  auto s = static_cast<cudaStream_t>(stream);
+  auto* xv = static_cast<uint4*>(x);
+  auto* cv = reinterpret_cast<const float4*>(cos_table);
+  auto* sv = reinterpret_cast<const float4*>(sin_table);
+  if (dtype == IXK_BF16)
+    glue::rotary_kernel<true><<<grid, 256, 0, s>>>(xv, cv, sv, total, vph, static_cast<int>(heads), static_cast<int>(seq_len),
+                                                   token_stride / glue::kVecElems, head_stride / glue::kVecElems);
+  else
+    glue::rotary_kernel<false><<<grid, 256, 0, s>>>(xv, cv, sv, total, vph, static_cast<int>(heads), static_cast<int>(seq_len),
+                                                    token_stride / glue::kVecElems, head_stride / glue::kVecElems);
+  IXK_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return IXK_OK;
+}
+
+int ixk_residual_add(int dtype, int64_t rows, int64_t cols, const void* x, const void* partial, const void* bias,
+                     void* out, void* stream) {
+  clear_error();
+  if (dtype != IXK_BF16 && dtype != IXK_F16) return fail(IXK_UNIMPLEMENTED, "residual_add: dtype must be BF16 or F16");
+  if (rows < 0 || cols <= 0 || (rows > 0 && (x == nullptr || partial == nullptr || out == nullptr)))
+    return fail(IXK_INVALID_ARGUMENT, "residual_add: null or negative argument");
+  if (cols % glue::kVecElems || !glue::aligned16(x) || !glue::aligned16(partial) || !glue::aligned16(out) ||
+      (bias != nullptr && !glue::aligned16(bias)))
+    return fail(IXK_INVALID_ARGUMENT, "residual_add: cols must be a multiple of 8, pointers 16-byte aligned");
+  DeviceInfo info;
+  if (int st = get_device_info(&info)) return st;
+  const int64_t total = rows * (cols / glue::kVecElems);
+  if (total == 0) return IXK_OK;
+  const int grid = glue::elementwise_grid(total, 256, info.sm_count);
+  auto s = static_cast<cudaStream_t>(stream);
+  const int vpr = static_cast<int>(cols / glue::kVecElems);
+  if (dtype == IXK_BF16)
+    glue::residual_add_kernel<true><<<grid, 256, 0, s>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(partial),
+                                                         static_cast<const uint4*>(bias), static_cast<uint4*>(out), total, vpr);
+  else
+    glue::residual_add_kernel<false><<<grid, 256, 0, s>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(partial),
+                                                          static_cast<const uint4*>(bias), static_cast<uint4*>(out), total, vpr);
+  IXK_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return IXK_OK;
+}
+
+}  // extern "C"

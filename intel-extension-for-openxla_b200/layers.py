@@ -5,10 +5,11 @@ example/gemma/keras_nlp.patch:53-63), tensor-parallel the way the Gemma example 
 no exchange, attention by heads, the row-parallel projections (attention output, MLP down) ending
 in one all-reduce.
 
-The GEMMs and the attention go through libixk (`KernelOps`); layer norm, rotary embedding,
-residual adds and the GeGLU product are the glue XLA would emit as fusions and are plain torch.
-`ops` is injectable so that the sharding and reduction logic can be exercised on CPU ranks with
-a stand-in implementation of the two calls.
+The GEMMs and the attention go through libixk (`KernelOps`), and so do the steps between them
+that XLA would emit as fusions: row normalisation, rotary embedding and the residual adds are one
+pass over HBM each (csrc/glue_sm100.cu).  `ops` is injectable so that the sharding and reduction
+logic can be exercised on CPU ranks with a stand-in implementation of the two calls; an `ops`
+without the glue methods gets the plain torch versions defined below.
 """
 from __future__ import annotations
 
@@ -38,6 +39,27 @@ class KernelOps:
         self.pkg.fmha_forward_kernel(None, q, k, v, None, None, 0.0, out, None, scale, False, causal=causal,
                                      workspace=workspace)
         return out
+
+    def layer_norm(self, x, eps=1e-5):
+        return self.pkg.row_norm(x, kind=self.pkg.NORM_LAYER, eps=eps)
+
+    def rms_norm(self, x, eps=1e-6):
+        return self.pkg.row_norm(x, kind=self.pkg.NORM_RMS, eps=eps)
+
+    def rotary_qk_(self, qkv, cos, sin, rotary_dim):
+        """qkv [B, S, 3, heads_local, head_dim] dense: rotates the q and k slices in place (they are
+        2 * heads_local consecutive heads of every token)."""
+        B, S, _, hl, hd = qkv.shape
+        qk = qkv.view(B * S, 3 * hl, hd)[:, :2 * hl]
+        self.pkg.rotary_interleaved_(qk, cos, sin, S, rotary_dim)
+        return qkv
+
+    def residual_add(self, x, partial, bias=None, out=None):
+        return self.pkg.residual_add(x, partial, bias, out=out)
+
+
+def _glue(ops, name, fallback):
+    return getattr(ops, name, None) or fallback
 
 
 # ----------------------------------------------------------------------------- sharding
@@ -109,6 +131,17 @@ def apply_rotary_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rotary_
     return x
 
 
+def _rotary_qk_torch_(qkv, cos, sin, rotary_dim):
+    apply_rotary_(qkv[:, :, 0], cos, sin, rotary_dim)
+    apply_rotary_(qkv[:, :, 1], cos, sin, rotary_dim)
+    return qkv
+
+
+def _residual_add_torch(x, partial, bias=None, out=None):
+    t = partial if bias is None else (partial.float() + bias.float()).to(x.dtype)
+    return x + t.view(x.shape)
+
+
 # ----------------------------------------------------------------------------- GPT-J prefill layer
 
 @dataclass
@@ -145,11 +178,10 @@ def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None, ro
     capturable in a CUDA graph)."""
     B, S, hidden = x.shape
     hl, hd = w.heads_local, w.head_dim
-    h = layer_norm(x).view(B * S, hidden)
+    h = _glue(ops, "layer_norm", layer_norm)(x).view(B * S, hidden)
     qkv = ops.gemm(h, w.wqkv).view(B, S, 3, hl, hd)
     cos, sin = rope if rope is not None else rotary_tables(torch.arange(S, device=x.device), w.rotary_dim)
-    apply_rotary_(qkv[:, :, 0], cos, sin, w.rotary_dim)
-    apply_rotary_(qkv[:, :, 1], cos, sin, w.rotary_dim)
+    _glue(ops, "rotary_qk_", _rotary_qk_torch_)(qkv, cos, sin, w.rotary_dim)
     q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))        # [B, hl, S, hd] views, no copies
     ctx = torch.empty(B, S, hl, hd, dtype=x.dtype, device=x.device)
     ops.attention(q, k, v, ctx.permute(0, 2, 1, 3), scale=1.0 / math.sqrt(hd), causal=True)
@@ -157,7 +189,7 @@ def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None, ro
     up = ops.gemm(h, w.w1, bias=w.b1, epilogue="BIAS_GELU")
     partial = ops.gemm(up, w.w2, c=attn_partial, beta=1.0, out=attn_partial)   # in place: C aliases D
     partial = all_reduce_sum(partial, group)
-    return x + (partial.float() + w.b2.float()).to(x.dtype).view(B, S, hidden)
+    return _glue(ops, "residual_add", _residual_add_torch)(x, partial, w.b2)
 
 
 def gptj_layer_flops(B, S, hidden=4096, heads=16, head_dim=256, ffn=16384):
@@ -199,11 +231,12 @@ def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tens
     `rope` may carry the precomputed (cos, sin) row for `position` (no host work in the step)."""
     B, _, hidden = x.shape
     hl, hd = w.heads_local, w.head_dim
-    h = rms_norm(x).view(B, hidden)
+    norm = _glue(ops, "rms_norm", rms_norm)
+    add = _glue(ops, "residual_add", _residual_add_torch)
+    h = norm(x).view(B, hidden)
     qkv = ops.gemm(h, w.wqkv).view(B, 1, 3, hl, hd)
     cos, sin = rope if rope is not None else rotary_tables(torch.tensor([position], device=x.device), hd)
-    apply_rotary_(qkv[:, :, 0], cos, sin, hd)
-    apply_rotary_(qkv[:, :, 1], cos, sin, hd)
+    _glue(ops, "rotary_qk_", _rotary_qk_torch_)(qkv, cos, sin, hd)
     k_cache[:, position] = qkv[:, 0, 1]
     v_cache[:, position] = qkv[:, 0, 2]
     T = position + 1
@@ -212,12 +245,12 @@ def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tens
     ops.attention(q, k_cache[:, :T].permute(0, 2, 1, 3), v_cache[:, :T].permute(0, 2, 1, 3),
                   ctx.permute(0, 2, 1, 3), scale=1.0 / math.sqrt(hd), causal=False, workspace=workspace)
     attn = all_reduce_sum(ops.gemm(ctx.view(B, hl * hd), w.wo), group)
-    x1 = x + attn.view(B, 1, hidden)
-    h2 = rms_norm(x1).view(B, hidden)
+    x1 = add(x, attn)
+    h2 = norm(x1).view(B, hidden)
     gate = ops.gemm(h2, w.wgate, epilogue="GELU")
     up = ops.gemm(h2, w.wup)
     down = all_reduce_sum(ops.gemm(gate * up, w.wdown), group)
-    return x1 + down.view(B, 1, hidden)
+    return add(x1, down)
 
 
 def gemma_decode_bytes(B, T, hidden=3072, heads=16, head_dim=256, ffn=24576, elem=2):

@@ -1,0 +1,119 @@
+"""GPU parity of the memory-bound steps between the custom calls (row normalisation, interleaved
+rotary embedding, residual add) against the numpy layer oracle, through the C ABI.
+Tolerances: outputs are O(1) values rounded once to the 16-bit type; a result may differ from the
+oracle's by one rounding step where fp32 summation order differs, so 1 ulp of the type relative
+(2^-7 for bf16, 2^-10 for fp16) plus the same absolute."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ULP = {torch.bfloat16: 2.0 ** -7, torch.float16: 2.0 ** -10}
+
+
+def f32(t):
+    return t.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kind", ["layer", "rms"])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (3, 264), (37, 3072), (64, 4096), (5, 8192), (300, 520)])
+def test_row_norm(pkg, orc, cuda, dtype, kind, rows, cols):
+    from oracle import layers_oracle
+    g = torch.Generator().manual_seed(rows * 131 + cols)
+    x = (torch.randn(rows, cols, generator=g) * 1.7 + 0.3).to(dtype)
+    if kind == "layer":
+        got = pkg.row_norm(x.to(cuda), kind=pkg.NORM_LAYER, eps=1e-5)
+        xf = f32(x)
+        mu = xf.mean(-1, keepdims=True)
+        want = (xf - mu) / np.sqrt(((xf - mu) ** 2).mean(-1, keepdims=True) + 1e-5)
+    else:
+        got = pkg.row_norm(x.to(cuda), kind=pkg.NORM_RMS, eps=1e-6)
+        xf = f32(x)
+        want = xf / np.sqrt((xf * xf).mean(-1, keepdims=True) + 1e-6)
+    assert got.dtype == dtype and got.shape == x.shape
+    orc.check_close(f32(got), want, rtol=ULP[dtype], atol=ULP[dtype], what=f"row_norm {kind}")
+    if dtype == torch.bfloat16:      # the layer oracle's own statement, bf16 storage
+        ref = layers_oracle.layer_norm(xf) if kind == "layer" else layers_oracle.rms_norm(xf)
+        orc.check_close(f32(got), ref, rtol=ULP[dtype], atol=ULP[dtype], what=f"row_norm {kind} vs layer oracle")
+
+
+def test_row_norm_in_place_and_rejections(pkg, cuda):
+    x = torch.randn(16, 256).bfloat16().to(cuda)
+    want = pkg.row_norm(x)
+    pkg.row_norm(x, out=x)
+    assert torch.equal(x, want)
+    with pytest.raises(pkg.IxkError):
+        pkg.row_norm(torch.randn(4, 12).bfloat16().to(cuda))            # cols not a multiple of 8
+    with pytest.raises(pkg.IxkError):
+        pkg.row_norm(torch.randn(2, 8200).bfloat16().to(cuda))          # longer than 8192
+    with pytest.raises(pkg.IxkError):
+        pkg.row_norm(torch.randn(4, 16).to(cuda))                       # fp32 is not covered
+    empty = pkg.row_norm(torch.empty(0, 64, dtype=torch.bfloat16, device=cuda))
+    assert empty.shape == (0, 64)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,S,heads,hd,rot", [(2, 37, 2, 256, 64), (1, 1, 4, 256, 256), (3, 128, 3, 64, 64),
+                                              (5, 1, 2, 128, 32), (1, 700, 1, 256, 8)])
+def test_rotary_on_fused_qkv(pkg, orc, cuda, dtype, B, S, heads, hd, rot):
+    """q and k slices of a fused [B,S,3,heads,hd] projection rotate; v and the tail of every head stay."""
+    from oracle import layers_oracle
+    layers = __import__("importlib").import_module("ixk_b200.layers")
+    g = torch.Generator().manual_seed(B * 1000 + S)
+    qkv = torch.randn(B, S, 3, heads, hd, generator=g).to(dtype)
+    cos, sin = layers.rotary_tables(torch.arange(S), rot)
+    dev = qkv.to(cuda)
+    layers.KernelOps(pkg).rotary_qk_(dev, cos.to(cuda), sin.to(cuda), rot)
+    xf = f32(qkv)
+    assert torch.equal(dev[:, :, 2].cpu(), qkv[:, :, 2])
+    assert torch.equal(dev[..., rot:].cpu(), qkv[..., rot:])
+    for i in range(2):
+        want = layers_oracle.rotary(xf[:, :, i], np.arange(S), rot) if dtype == torch.bfloat16 else None
+        c, s = f32(cos)[:, None, :], f32(sin)[:, None, :]
+        x1, x2 = xf[:, :, i, :, 0:rot:2], xf[:, :, i, :, 1:rot:2]
+        exact = xf[:, :, i].copy()
+        exact[..., 0:rot:2] = x1 * c - x2 * s
+        exact[..., 1:rot:2] = x1 * s + x2 * c
+        orc.check_close(f32(dev[:, :, i]), exact, rtol=ULP[dtype], atol=ULP[dtype], what="rotary")
+        if want is not None:        # the oracle builds its own tables in numpy: table rounding adds an ulp
+            orc.check_close(f32(dev[:, :, i]), want, rtol=2 * ULP[dtype], atol=2 * ULP[dtype], what="rotary vs layer oracle")
+
+
+def test_rotary_rejections(pkg, cuda):
+    x = torch.randn(8, 2, 64).bfloat16().to(cuda)
+    cos = torch.ones(8, 16, device=cuda)
+    with pytest.raises(pkg.IxkError):
+        pkg.rotary_interleaved_(x, cos, cos, 8, 36)                      # table shape does not match rotary_dim
+    with pytest.raises(pkg.IxkError):
+        pkg.rotary_interleaved_(x, cos[:3].contiguous(), cos[:3].contiguous(), 3, 32)   # 8 tokens, seq_len 3
+    with pytest.raises(pkg.IxkError):
+        pkg.rotary_interleaved_(x, cos.double(), cos.double(), 8, 32)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("with_bias", [False, True])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (33, 3072), (640, 4096), (7, 520)])
+def test_residual_add(pkg, cuda, dtype, with_bias, rows, cols):
+    """Bit-exact: both roundings are defined (inner sum to the type, then the residual add)."""
+    g = torch.Generator().manual_seed(rows + cols)
+    x = torch.randn(rows, cols, generator=g).to(dtype)
+    p = torch.randn(rows, cols, generator=g).to(dtype)
+    b = torch.randn(cols, generator=g).to(dtype) if with_bias else None
+    got = pkg.residual_add(x.to(cuda), p.to(cuda), b.to(cuda) if with_bias else None)
+    inner = (p.float() + b.float()).to(dtype) if with_bias else p
+    want = (x.float() + inner.float()).to(dtype)
+    assert torch.equal(got.cpu(), want)
+
+
+def test_residual_add_aliasing_and_rejections(pkg, cuda):
+    x = torch.randn(40, 64).bfloat16().to(cuda)
+    p = torch.randn(40, 64).bfloat16().to(cuda)
+    want = pkg.residual_add(x, p)
+    pkg.residual_add(x, p, out=p)
+    assert torch.equal(p, want)
+    with pytest.raises(pkg.IxkError):
+        pkg.residual_add(x, p[:, :32].contiguous())
+    with pytest.raises(pkg.IxkError):
+        pkg.residual_add(x, p, torch.zeros(32, dtype=torch.bfloat16, device=cuda))
