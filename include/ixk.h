@@ -210,6 +210,33 @@ int ixk_fmha_fwd_static_scratch(const ixk_fmha_desc* desc, const void* q, const 
                                 const void* v, const void* bias, void* out, float* lse,
                                 void* cuda_stream);
 
+/* Attention backward.  Replaces fmha_backward_kernel_bf16 / _fp16
+ * (xla/service/gpu/xetla/sdp/sdp_backward.h:21-33, .cc:34-76), which the runner reaches from
+ * RunFusedMHABackward (xla/service/gpu/xetla_gpu_fused_mha_runner.cc:227-473).  With
+ *   P  = exp( head_scale * Q.K^T + bias - lse )        (masked as in the forward when causal)
+ *   D  = rowsum(dO * O),   dP = dO.V^T,   dS = P * (dP - D)
+ * it returns dV = P^T.dO, dK = head_scale * dS^T.Q, dQ = head_scale * dS.K
+ * (fmha_backward.h:182-222, :489-700, :836-850); P and dS are rounded to dtype as matmul
+ * operands, all sums are fp32, each gradient is rounded once.  No bias gradient (the reference
+ * has none).  `fwd` describes q, k, v, bias and the forward output `out` (o_strides) exactly as in
+ * the forward call; grad_out, dq, dk, dv are [B,N,F|T,H] views with their own strides (elements,
+ * innermost 1).  The reference's dp_sum and grad_query_accum scratch arguments are the workspace:
+ * ixk_fmha_bwd_workspace_bytes(desc) bytes, 16-byte aligned.  q, k, v, grad_out: 16-byte aligned
+ * with strides that are multiples of 8; dq, dk, dv likewise.  head_size <= 128 (256 is
+ * IXK_UNIMPLEMENTED: the reference's 64x128x256 policy has no counterpart yet). */
+typedef struct ixk_fmha_bwd_desc {
+  ixk_fmha_desc fwd;
+  int64_t do_strides[3]; /* B, N, F */
+  int64_t dq_strides[3]; /* B, N, F */
+  int64_t dk_strides[3]; /* B, N, T */
+  int64_t dv_strides[3]; /* B, N, T */
+} ixk_fmha_bwd_desc;
+int ixk_fmha_bwd(const ixk_fmha_bwd_desc* desc, const void* q, const void* k, const void* v,
+                 const void* out, const void* bias, const void* grad_out, const float* lse,
+                 void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes,
+                 void* cuda_stream);
+size_t ixk_fmha_bwd_workspace_bytes(const ixk_fmha_bwd_desc* desc);
+
 /* ------------------------------------------------- between the custom calls */
 /* The memory-bound steps a decoder layer runs between the calls above.  The
  * reference has no custom call for them: XLA compiles them as loop fusions

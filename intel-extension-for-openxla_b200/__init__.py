@@ -71,6 +71,11 @@ class _FmhaDesc(ctypes.Structure):
                 ("bias_strides", ctypes.c_int64 * 3)]
 
 
+class _FmhaBwdDesc(ctypes.Structure):
+    _fields_ = [("fwd", _FmhaDesc), ("do_strides", ctypes.c_int64 * 3), ("dq_strides", ctypes.c_int64 * 3),
+                ("dk_strides", ctypes.c_int64 * 3), ("dv_strides", ctypes.c_int64 * 3)]
+
+
 _LIB: Optional[ctypes.CDLL] = None
 
 # Every symbol include/ixk.h declares: name -> (restype, argtypes)
@@ -86,6 +91,9 @@ ABI_SYMBOLS = {
     "ixk_gemm_qkv": (ctypes.c_int, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp, ctypes.c_int64,
                                     _vp, ctypes.c_int64, _vp, _vp, _vp, _vp, ctypes.c_int64, _vp]),
     "ixk_fmha_fwd": (ctypes.c_int, [ctypes.POINTER(_FmhaDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "ixk_fmha_bwd": (ctypes.c_int, [ctypes.POINTER(_FmhaBwdDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                    _sz, _vp]),
+    "ixk_fmha_bwd_workspace_bytes": (_sz, [ctypes.POINTER(_FmhaBwdDesc)]),
     "ixk_row_norm": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, _vp, ctypes.c_int64,
                                     _vp, ctypes.c_int64, ctypes.c_float, _vp]),
     "ixk_rotary_interleaved": (ctypes.c_int, [ctypes.c_int, _vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
@@ -425,6 +433,52 @@ def fmha_forward_kernel(stream, query: torch.Tensor, key: torch.Tensor, value: t
     ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     st = lib.ixk_fmha_fwd(ctypes.byref(d), _ptr(query), _ptr(key), _ptr(value), _ptr(bias), _ptr(out),
                           _ptr(activation if is_training else None), _ptr(workspace), ws_bytes, _stream_ptr(stream))
+    _check(st)
+
+
+def _fmha_bwd_desc(query, key, value, out, bias, grad_out, grad_query, grad_key, grad_value, head_scale,
+                   causal) -> _FmhaBwdDesc:
+    d = _FmhaBwdDesc()
+    d.fwd = _fmha_desc(query, key, value, bias, out, head_scale, causal, 0.0)
+    for name, t, like in (("do", grad_out, query), ("dq", grad_query, query), ("dk", grad_key, key),
+                          ("dv", grad_value, value)):
+        if t.shape != like.shape or t.dtype != like.dtype:
+            raise IxkError(IXK_INVALID_ARGUMENT, f"{name}: shape and type must match the tensor it is the gradient of")
+        if t.stride(3) != 1 and t.shape[3] > 1:
+            raise IxkError(IXK_INVALID_ARGUMENT, f"{name}: head_size must be the contiguous dimension")
+        getattr(d, f"{name}_strides")[:] = [t.stride(0), t.stride(1), t.stride(2)]
+    return d
+
+
+def fmha_backward_workspace_bytes(query, key, value, out, bias, grad_out, grad_query, grad_key, grad_value,
+                                  head_scale, causal=False) -> int:
+    d = _fmha_bwd_desc(query, key, value, out, bias, grad_out, grad_query, grad_key, grad_value, head_scale, causal)
+    return int(load_library().ixk_fmha_bwd_workspace_bytes(ctypes.byref(d)))
+
+
+def fmha_backward_kernel(stream, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, out: torch.Tensor,
+                         bias: Optional[torch.Tensor], grad_out: torch.Tensor, activation: torch.Tensor,
+                         grad_query: torch.Tensor, grad_key: torch.Tensor, grad_value: torch.Tensor,
+                         head_scale: float, *, causal: bool = False,
+                         workspace: Optional[torch.Tensor] = None) -> None:
+    """fmha_backward_kernel_{bf16,fp16} (xla/service/gpu/xetla/sdp/sdp_backward.cc:34-76), the dtype
+    taken from `query`.  query/out/grad_out/grad_query are [B,N,F,H] views, key/value and their
+    gradients [B,N,T,H] views (any strides with H contiguous); `activation` is the forward's
+    log-sum-exp [B,N,F] fp32.  The reference's dp_sum and grad_query_accum scratch buffers are one
+    `workspace` here (allocated if not given)."""
+    _require_cuda(query, key, value, out, bias, grad_out, activation, grad_query, grad_key, grad_value)
+    if activation is None or activation.dtype != torch.float32 or not activation.is_contiguous() \
+            or activation.shape != query.shape[:3]:
+        raise IxkError(IXK_INVALID_ARGUMENT, "activation must be the forward's dense fp32 [B,N,F] log-sum-exp")
+    lib = load_library()
+    d = _fmha_bwd_desc(query, key, value, out, bias, grad_out, grad_query, grad_key, grad_value, head_scale, causal)
+    need = int(lib.ixk_fmha_bwd_workspace_bytes(ctypes.byref(d)))
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=query.device)
+    ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    st = lib.ixk_fmha_bwd(ctypes.byref(d), _ptr(query), _ptr(key), _ptr(value), _ptr(out), _ptr(bias), _ptr(grad_out),
+                          _ptr(activation), _ptr(grad_query), _ptr(grad_key), _ptr(grad_value), _ptr(workspace),
+                          ws_bytes, _stream_ptr(stream))
     _check(st)
 
 

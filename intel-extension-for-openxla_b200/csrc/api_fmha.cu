@@ -92,4 +92,49 @@ int ixk_fmha_fwd(const ixk_fmha_desc* desc, const void* q, const void* k, const 
   return ixk::fmha::launch_prefill(p, dev, stream);
 }
 
+size_t ixk_fmha_bwd_workspace_bytes(const ixk_fmha_bwd_desc* desc) {
+  if (desc == nullptr) return 0;
+  ixk::fmha::Problem p;
+  if (ixk::make_problem(&desc->fwd, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, &p, false) != IXK_OK) return 0;
+  return ixk::fmha::bwd_workspace_bytes(p);
+}
+
+int ixk_fmha_bwd(const ixk_fmha_bwd_desc* desc, const void* q, const void* k, const void* v, const void* out,
+                 const void* bias, const void* grad_out, const float* lse, void* dq, void* dk, void* dv,
+                 void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  ixk::clear_error();
+  if (desc == nullptr) return ixk::fail(IXK_INVALID_ARGUMENT, "desc is NULL");
+  ixk::fmha::BwdProblem bp;
+  int rc = ixk::make_problem(&desc->fwd, q, k, v, bias, const_cast<void*>(out), const_cast<float*>(lse), &bp.fwd, true);
+  if (rc != IXK_OK) return rc;
+  const ixk::fmha::Problem& p = bp.fwd;
+  if (p.B == 0 || p.N == 0 || (p.F == 0 && p.T == 0)) return IXK_OK;
+  if (p.F == 0 || p.T == 0)
+    return ixk::fail(IXK_UNIMPLEMENTED, "attention backward with an empty query or key axis");
+  if (grad_out == nullptr || lse == nullptr || dq == nullptr || dk == nullptr || dv == nullptr)
+    return ixk::fail(IXK_INVALID_ARGUMENT, "grad_out, lse, dq, dk and dv must be non-NULL");
+  auto aligned16 = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15u) == 0; };
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(grad_out) || !aligned16(dq) || !aligned16(dk) ||
+      !aligned16(dv))
+    return ixk::fail(IXK_INVALID_ARGUMENT, "q, k, v, grad_out, dq, dk and dv must be 16-byte aligned");
+  for (int i = 0; i < 3; ++i) {
+    bp.do_strides[i] = desc->do_strides[i];
+    bp.dq_strides[i] = desc->dq_strides[i];
+    bp.dk_strides[i] = desc->dk_strides[i];
+    bp.dv_strides[i] = desc->dv_strides[i];
+    if (bp.do_strides[i] < 0 || bp.dq_strides[i] < 0 || bp.dk_strides[i] < 0 || bp.dv_strides[i] < 0)
+      return ixk::fail(IXK_INVALID_ARGUMENT, "negative stride");
+    if (p.q_strides[i] % 8 != 0 || p.k_strides[i] % 8 != 0 || p.v_strides[i] % 8 != 0 || bp.do_strides[i] % 8 != 0 ||
+        bp.dq_strides[i] % 8 != 0 || bp.dk_strides[i] % 8 != 0 || bp.dv_strides[i] % 8 != 0)
+      return ixk::fail(IXK_UNIMPLEMENTED, "q/k/v/grad_out/dq/dk/dv strides must be multiples of 8 elements (16 bytes)");
+  }
+  bp.grad_out = grad_out;
+  bp.dq = dq;
+  bp.dk = dk;
+  bp.dv = dv;
+  ixk::DeviceInfo dev;
+  if ((rc = ixk::get_device_info(&dev)) != IXK_OK) return rc;
+  return ixk::fmha::launch_bwd(bp, dev, workspace, workspace_bytes, static_cast<cudaStream_t>(cuda_stream));
+}
+
 }  // extern "C"

@@ -1,0 +1,615 @@
+// Attention backward for sm_100a: dQ, dK, dV from Q, K, V, O, dO and the forward's row statistic.
+// Replaces fmha_backward_kernel_{bf16,fp16} (xla/service/gpu/xetla/sdp/sdp_backward.h) and follows
+// its three-kernel split (fmha_backward.h:854-918):
+//   1. bwd_prepare_kernel : D = rowsum(dO * O), -lse * log2(e) in padded rows, zero the fp32 dQ
+//                           accumulator                                   (fmha_backward.h:182-222)
+//   2. fmha_bwd_kernel    : one CTA per (batch, head, block of 128 keys) loops over the blocks of
+//                           128 queries that see those keys; dK and dV accumulate in tensor memory
+//                           for the whole loop, dQ contributions go to the fp32 accumulator with
+//                           vector reductions                              (fmha_backward.h:489-700)
+//   3. bwd_convert_kernel : dQ = head_scale * accumulator, rounded once    (fmha_backward.h:836-850)
+//
+// The main kernel works on TRANSPOSED score tiles, keys along the 128 TMEM lanes and queries along
+// the columns, so that P^T and dS^T are produced in the orientation the dV and dK products want:
+//   S^T  = K   . Q^T      (SS, both K-major)                 -> TMEM, fp32
+//   dP^T = V   . dO^T     (SS, both K-major)                 -> TMEM, fp32
+//   P^T  = exp2(S^T * scale*log2e + bias*log2e - lse*log2e)  -> TMEM, 16-bit, over S^T
+//   dS^T = P^T * (dP^T - D)                                  -> shared memory, 16-bit, swizzled
+//   dV  += P^T  . dO      (TS: A from TMEM, B = dO with the head dim contiguous)
+//   dK  += dS^T . Q       (SS: A K-major, B = Q with the head dim contiguous)
+//   dQ   = dS   . K       (SS: A = the same dS^T buffer read M-major, B = K head dim contiguous)
+// Tensor memory (512 columns) at head size 128: S^T/P^T 128, dP^T 128 (reused for dQ once dS^T is
+// out), dV 128, dK 128.  Warps 0-3 compute P^T and dS^T (one key row per thread), warps 4-7 move dQ
+// from TMEM to the accumulator (one query row per thread), warp 8 issues TMA loads, warp 9 issues
+// the MMAs with all lanes and an elected lane per instruction.  Every wait is bounded.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cmath>
+
+#include "fmha_sm100.h"
+#include "ptx.cuh"
+
+namespace ixk {
+namespace fmha {
+
+namespace {
+
+constexpr int kBlk = 128;                       // keys per CTA = queries per step = TMEM lanes
+constexpr int kChunkElems = 64;                 // 16-bit elements per 128-byte swizzle row
+constexpr int kChunkBytes = kBlk * 128;         // one 128-row x 128-byte box
+constexpr int kBwdThreads = 320;
+constexpr int kReduceWarp = 4;                  // first warp of the dQ warpgroup
+constexpr int kBwdProducerWarp = 8;
+constexpr int kBwdMmaWarp = 9;
+constexpr int kStages = 2;                      // Q / dO tiles in flight
+constexpr float kLog2e = 1.4426950408889634f;
+
+// wait sites reported in the device status word
+constexpr int kSiteBwdKv = 0x41, kSiteBwdQdoFull = 0x42, kSiteBwdQdoEmpty = 0x43, kSiteBwdSdp = 0x44,
+              kSiteBwdPds = 0x45, kSiteBwdDqFull = 0x46, kSiteBwdDqFree = 0x47, kSiteBwdFinal = 0x48,
+              kSiteBwdAlign = 0x49;
+
+template <int kHeadDim>
+struct BwdCfg {
+  static_assert(kHeadDim == 64 || kHeadDim == 128, "head size bucket");
+  static constexpr int kChunks = kHeadDim / kChunkElems;
+  static constexpr int kTileBytes = kChunks * kChunkBytes;          // a 128-row Q, dO, K or V tile
+  static constexpr int kDsBytes = 2 * kChunkBytes;                  // dS^T: 128 keys x 128 queries, 16-bit
+  static constexpr int kRowBytes = kBlk * 4;                        // 128 fp32 row values
+  static constexpr int kOffK = 0;
+  static constexpr int kOffV = kTileBytes;
+  static constexpr int kOffStage = 2 * kTileBytes;                  // per stage: Q tile, dO tile
+  static constexpr int kOffDs = kOffStage + kStages * 2 * kTileBytes;
+  static constexpr int kOffRows = kOffDs + kDsBytes;                // per stage: -lse*log2e row, D row
+  static constexpr int kOffBars = kOffRows + kStages * 2 * kRowBytes;
+  static constexpr int kSmemBytes = kOffBars + 256;
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
+  // tensor memory columns
+  static constexpr int kTmemS = 0;
+  static constexpr int kTmemDP = 128;
+  static constexpr int kTmemDV = 256;
+  static constexpr int kTmemDK = 256 + kHeadDim;
+  static constexpr int kTmemDQ = kHeadDim == 128 ? kTmemDP : 256 + 2 * kHeadDim;
+};
+
+struct BwdArgs {
+  int B, N, H, F, T;
+  int f_pad;                 // F rounded up to a multiple of 128: row pitch of the fp32 scratch arrays
+  int num_kblocks, num_qblocks;
+  int causal, is_bf16;
+  float scale_log2, head_scale;
+  const uint16_t* bias;
+  int64_t bias_strides[3];
+  const float* neg_lse2;     // [B*N, f_pad]  -lse * log2(e); -inf in the padding
+  const float* delta;        // [B*N, f_pad]  rowsum(dO * O); 0 in the padding
+  float* dq_acc;             // [B*N, f_pad, kHeadDim] fp32
+  uint16_t* dk;
+  uint16_t* dv;
+  int64_t dk_strides[3], dv_strides[3];
+  int* status_word;
+};
+
+struct PrepArgs {
+  int B, N, H, F, f_pad, head_pad, is_bf16;
+  const uint16_t* out;
+  const uint16_t* grad_out;
+  const float* lse;
+  int64_t o_strides[3], do_strides[3];
+  float* neg_lse2;
+  float* delta;
+  float* dq_acc;
+};
+
+__device__ __forceinline__ float to_f32(uint16_t h, int is_bf16) {
+  return is_bf16 ? __uint_as_float(static_cast<uint32_t>(h) << 16) : __half2float(__ushort_as_half(h));
+}
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {
+  if (is_bf16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// One warp per (batch, head, padded query row).
+__global__ void bwd_prepare_kernel(const PrepArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = static_cast<int64_t>(a.B) * a.N * a.f_pad;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+       row += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5)) {
+    const int f = static_cast<int>(row % a.f_pad);
+    const int64_t bn = row / a.f_pad;
+    const int n = static_cast<int>(bn % a.N), b = static_cast<int>(bn / a.N);
+    float* acc = a.dq_acc + row * a.head_pad;
+    for (int h = lane * 4; h < a.head_pad; h += 128) *reinterpret_cast<float4*>(acc + h) = make_float4(0.f, 0.f, 0.f, 0.f);
+    float sum = 0.0f;
+    if (f < a.F) {
+      const uint16_t* o = a.out + b * a.o_strides[0] + n * a.o_strides[1] + f * a.o_strides[2];
+      const uint16_t* g = a.grad_out + b * a.do_strides[0] + n * a.do_strides[1] + f * a.do_strides[2];
+      for (int h = lane; h < a.H; h += 32) sum = fmaf(to_f32(o[h], a.is_bf16), to_f32(g[h], a.is_bf16), sum);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane == 0) {
+      a.delta[row] = sum;
+      a.neg_lse2[row] = f < a.F ? -a.lse[bn * a.F + f] * kLog2e : -INFINITY;
+    }
+  }
+}
+
+struct ConvertArgs {
+  int B, N, H, F, f_pad, head_pad, is_bf16;
+  float head_scale;
+  const float* dq_acc;
+  uint16_t* dq;
+  int64_t dq_strides[3];
+};
+
+// One thread per pair of head elements.
+__global__ void bwd_convert_kernel(const ConvertArgs a) {
+  const int half_h = a.H / 2;
+  const int64_t total = static_cast<int64_t>(a.B) * a.N * a.F * half_h;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int hp = static_cast<int>(i % half_h);
+    const int64_t r = i / half_h;
+    const int f = static_cast<int>(r % a.F);
+    const int64_t bn = r / a.F;
+    const int n = static_cast<int>(bn % a.N), b = static_cast<int>(bn / a.N);
+    const float2 v = *reinterpret_cast<const float2*>(a.dq_acc + (bn * a.f_pad + f) * a.head_pad + 2 * hp);
+    uint16_t* dst = a.dq + b * a.dq_strides[0] + n * a.dq_strides[1] + f * a.dq_strides[2] + 2 * hp;
+    *reinterpret_cast<uint32_t*>(dst) = pack16(v.x * a.head_scale, v.y * a.head_scale, a.is_bf16);
+  }
+}
+
+__device__ __forceinline__ void bwd_mma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, e;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void bwd_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, e;\n\t"
+      ".reg .b64 db;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void red_add_v4(float* addr, float x, float y, float z, float w) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+
+template <int kHeadDim, bool kBias>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                const BwdArgs args) {
+  using C = BwdCfg<kHeadDim>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = ptx::smem_u32(smem_raw);
+  if ((smem_base & 1023u) != 0) {   // the swizzled tiles need 1024-byte alignment; never seen, but checked
+    if (threadIdx.x == 0) atomicCAS(args.status_word, 0, kSiteBwdAlign);
+    return;
+  }
+  const uint32_t k_smem = smem_base + C::kOffK;
+  const uint32_t v_smem = smem_base + C::kOffV;
+  const uint32_t ds_smem = smem_base + C::kOffDs;
+  auto stage_q = [&](uint32_t st) { return smem_base + C::kOffStage + st * 2 * C::kTileBytes; };
+  auto stage_do = [&](uint32_t st) { return stage_q(st) + C::kTileBytes; };
+  auto rows_off = [&](uint32_t st) { return static_cast<uint32_t>(C::kOffRows) + st * 2 * C::kRowBytes; };
+  const uint32_t bar_base = smem_base + C::kOffBars;
+  const uint32_t kv_full = bar_base;
+  auto qdo_full = [&](uint32_t st) { return bar_base + 8u * (1 + st); };
+  auto qdo_empty = [&](uint32_t st) { return bar_base + 8u * (3 + st); };
+  const uint32_t sdp_full = bar_base + 8u * 5, pds_ready = bar_base + 8u * 6, dq_full = bar_base + 8u * 7,
+                 dq_free = bar_base + 8u * 8, final_bar = bar_base + 8u * 9;
+  uint8_t* tail = smem_raw + C::kOffBars + 8 * 10;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  ptx::AbortCtl ctl{abort_flag, args.status_word};
+
+  // work item: heaviest key blocks first (under the causal mask block 0 is seen by every query block)
+  const int per_kb = args.N * args.B;
+  const int kb = blockIdx.x / per_kb;
+  const int bn = blockIdx.x % per_kb;
+  const int n = bn % args.N, b = bn / args.N;
+  const int i0 = args.causal ? kb : 0;
+  const int n_steps = args.num_qblocks > i0 ? args.num_qblocks - i0 : 0;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    ptx::mbar_init(kv_full, 1);
+    for (uint32_t st = 0; st < kStages; ++st) {
+      ptx::mbar_init(qdo_full(st), 1);
+      ptx::mbar_init(qdo_empty(st), 1);
+    }
+    ptx::mbar_init(sdp_full, 1);
+    ptx::mbar_init(pds_ready, 128);
+    ptx::mbar_init(dq_full, 1);
+    ptx::mbar_init(dq_free, 128);
+    ptx::mbar_init(final_bar, 1);
+    ptx::fence_mbar_init();
+    ptx::prefetch_tmap(&tmap_q);
+    ptx::prefetch_tmap(&tmap_k);
+    ptx::prefetch_tmap(&tmap_v);
+    ptx::prefetch_tmap(&tmap_do);
+  }
+  if (warp == kBwdMmaWarp) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == kBwdProducerWarp) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_steps > 0) {
+      ptx::mbar_expect_tx(kv_full, 2 * C::kTileBytes);
+      for (int c = 0; c < C::kChunks; ++c) {
+        ptx::tma_load_4d(k_smem + c * kChunkBytes, &tmap_k, kv_full, c * kChunkElems, kb * kBlk, n, b);
+        ptx::tma_load_4d(v_smem + c * kChunkBytes, &tmap_v, kv_full, c * kChunkElems, kb * kBlk, n, b);
+      }
+      for (int it = 0; it < n_steps; ++it) {
+        const uint32_t st = it & 1;
+        if (it >= kStages && !ptx::mbar_wait(qdo_empty(st), ((it >> 1) - 1) & 1, ctl, kSiteBwdQdoEmpty)) break;
+        const int q0 = (i0 + it) * kBlk;
+        ptx::mbar_expect_tx(qdo_full(st), 2 * C::kTileBytes + 2 * C::kRowBytes);
+        for (int c = 0; c < C::kChunks; ++c) {
+          ptx::tma_load_4d(stage_q(st) + c * kChunkBytes, &tmap_q, qdo_full(st), c * kChunkElems, q0, n, b);
+          ptx::tma_load_4d(stage_do(st) + c * kChunkBytes, &tmap_do, qdo_full(st), c * kChunkElems, q0, n, b);
+        }
+        const int64_t row0 = static_cast<int64_t>(bn) * args.f_pad + q0;
+        ptx::bulk_load_1d(smem_base + rows_off(st), args.neg_lse2 + row0, C::kRowBytes, qdo_full(st));
+        ptx::bulk_load_1d(smem_base + rows_off(st) + C::kRowBytes, args.delta + row0, C::kRowBytes, qdo_full(st));
+      }
+    }
+  } else if (warp == kBwdMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer (all 32 lanes)
+    if (n_steps > 0) {
+      const uint32_t fmt = args.is_bf16 ? 1u : 0u;
+      const uint32_t idesc_t = ptx::umma_idesc(fmt, fmt, 0, 0, kBlk, kBlk);         // S^T, dP^T
+      const uint32_t idesc_kv = ptx::umma_idesc(fmt, fmt, 0, 1, kBlk, kHeadDim);    // dV (A in TMEM), dK
+      const uint32_t idesc_dq = ptx::umma_idesc(fmt, fmt, 1, 1, kBlk, kHeadDim);    // A = dS^T read M-major
+      const uint64_t kmajor = ptx::umma_smem_desc(0, 16, 1024);
+      const uint64_t mnmajor = ptx::umma_smem_desc(0, kChunkBytes, 1024);
+      const uint32_t k_lo = static_cast<uint32_t>(kmajor), k_hi = static_cast<uint32_t>(kmajor >> 32);
+      const uint32_t m_lo = static_cast<uint32_t>(mnmajor), m_hi = static_cast<uint32_t>(mnmajor >> 32);
+      bool alive = ptx::mbar_wait(kv_full, 0, ctl, kSiteBwdKv);
+      for (int it = 0; it < n_steps && alive; ++it) {
+        const uint32_t st = it & 1;
+        if (!ptx::mbar_wait(qdo_full(st), (it >> 1) & 1, ctl, kSiteBwdQdoFull)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t q_addr = stage_q(st), do_addr = stage_do(st);
+#pragma unroll
+        for (int ks = 0; ks < kHeadDim / 16; ++ks) {
+          const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
+          bwd_mma_ss(tmem_base + C::kTmemS, k_lo + (k_smem >> 4) + off, k_hi, k_lo + (q_addr >> 4) + off, k_hi,
+                     idesc_t, ks != 0 ? 1u : 0u);
+        }
+        // dP^T shares its columns with the previous step's dQ at head size 128
+        if (it > 0 && !ptx::mbar_wait(dq_free, (it - 1) & 1, ctl, kSiteBwdDqFree)) break;
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < kHeadDim / 16; ++ks) {
+          const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
+          bwd_mma_ss(tmem_base + C::kTmemDP, k_lo + (v_smem >> 4) + off, k_hi, k_lo + (do_addr >> 4) + off, k_hi,
+                     idesc_t, ks != 0 ? 1u : 0u);
+        }
+        ptx::umma_commit_elect(sdp_full);
+        if (!ptx::mbar_wait(pds_ready, it & 1, ctl, kSiteBwdPds)) break;
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < kBlk / 16; ++ks)     // dV += P^T.dO over 16 queries at a time
+          bwd_mma_ts(tmem_base + C::kTmemDV, tmem_base + C::kTmemS + ks * 8, m_lo + (do_addr >> 4) + ((ks * 2048) >> 4),
+                     m_hi, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < kBlk / 16; ++ks) {   // dK += dS^T.Q
+          const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
+          bwd_mma_ss(tmem_base + C::kTmemDK, k_lo + (ds_smem >> 4) + off, k_hi, m_lo + (q_addr >> 4) + ((ks * 2048) >> 4),
+                     m_hi, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < kBlk / 16; ++ks)     // dQ = dS.K over 16 keys at a time
+          bwd_mma_ss(tmem_base + C::kTmemDQ, m_lo + (ds_smem >> 4) + ((ks * 2048) >> 4), m_hi,
+                     m_lo + (k_smem >> 4) + ((ks * 2048) >> 4), m_hi, idesc_dq, ks != 0 ? 1u : 0u);
+        ptx::umma_commit_elect(dq_full);
+        ptx::umma_commit_elect(qdo_empty(st));
+      }
+      ptx::umma_commit_elect(final_bar);
+    }
+  } else if (warp < kReduceWarp) {
+    // ------------------------------------------------------------------ P^T and dS^T (one key row per thread)
+    const int r = threadIdx.x;
+    const int key = kb * kBlk + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const bool key_ok = key < args.T;
+    bool alive = true;
+    for (int it = 0; it < n_steps && alive; ++it) {
+      const uint32_t st = it & 1;
+      if (!ptx::mbar_wait(qdo_full(st), (it >> 1) & 1, ctl, kSiteBwdQdoFull)) { alive = false; break; }
+      if (!ptx::mbar_wait(sdp_full, it & 1, ctl, kSiteBwdSdp)) { alive = false; break; }
+      ptx::tc_fence_after_sync();
+      const int q0 = (i0 + it) * kBlk;
+      const float* nl = reinterpret_cast<const float*>(smem_raw + rows_off(st));
+      const float* dl = nl + kBlk;
+      const bool diag = args.causal && (i0 + it) == kb;
+      [[maybe_unused]] const uint16_t* bias_row = nullptr;
+      if constexpr (kBias)
+        bias_row = args.bias + b * args.bias_strides[0] + n * args.bias_strides[1] + key;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32], dp[32];
+        ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemS + 32 * c, s);
+        ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDP + 32 * c, dp);
+        ptx::tmem_ld_wait();
+        uint32_t pw[16], dw[16];
+#pragma unroll
+        for (int j2 = 0; j2 < 16; ++j2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int j = 2 * j2 + e;
+            const int col = 32 * c + j;
+            float x = fmaf(__uint_as_float(s[j]), args.scale_log2, nl[col]);
+            if constexpr (kBias) {
+              const int q = q0 + col;
+              if (key_ok && q < args.F) x = fmaf(to_f32(bias_row[q * args.bias_strides[2]], args.is_bf16), kLog2e, x);
+            }
+            float p = ptx::ex2_approx(x);
+            if (!key_ok || (diag && key > q0 + col)) p = 0.0f;
+            pv[e] = p;
+            dv[e] = p * (__uint_as_float(dp[j]) - dl[col]);
+          }
+          pw[j2] = pack16(pv[0], pv[1], args.is_bf16);
+          dw[j2] = pack16(dv[0], dv[1], args.is_bf16);
+        }
+        ptx::tmem_st_32x16(tmem_base + lane_addr + C::kTmemS + 16 * c, pw);
+        const uint32_t row_addr = ds_smem + (c >> 1) * kChunkBytes + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint32_t grp = static_cast<uint32_t>((c & 1) * 4 + g) ^ static_cast<uint32_t>(r & 7);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (grp << 4)), "r"(dw[4 * g]),
+                       "r"(dw[4 * g + 1]), "r"(dw[4 * g + 2]), "r"(dw[4 * g + 3])
+                       : "memory");
+        }
+      }
+      ptx::tmem_st_wait();
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(pds_ready);
+    }
+    // epilogue: this thread's row of dV and dK
+    const bool have = n_steps > 0 && alive && ptx::mbar_wait(final_bar, 0, ctl, kSiteBwdFinal);
+    if (n_steps == 0 || have) {
+      ptx::tc_fence_after_sync();
+      uint16_t* dv_row = args.dv + b * args.dv_strides[0] + n * args.dv_strides[1] + static_cast<int64_t>(key) * args.dv_strides[2];
+      uint16_t* dk_row = args.dk + b * args.dk_strides[0] + n * args.dk_strides[1] + static_cast<int64_t>(key) * args.dk_strides[2];
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        uint16_t* dst = which == 0 ? dv_row : dk_row;
+        const uint32_t col0 = which == 0 ? C::kTmemDV : C::kTmemDK;
+        const float mul = which == 0 ? 1.0f : args.head_scale;
+#pragma unroll 1
+        for (int c = 0; c < kHeadDim / 32; ++c) {
+          uint32_t acc[32];
+          if (n_steps > 0) {
+            ptx::tmem_ld_32x32(tmem_base + lane_addr + col0 + 32 * c, acc);
+            ptx::tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j] = 0u;
+          }
+          if (key_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int h = 32 * c + 8 * g;
+              if (h < args.H) {
+                uint4 w;
+                w.x = pack16(__uint_as_float(acc[8 * g]) * mul, __uint_as_float(acc[8 * g + 1]) * mul, args.is_bf16);
+                w.y = pack16(__uint_as_float(acc[8 * g + 2]) * mul, __uint_as_float(acc[8 * g + 3]) * mul, args.is_bf16);
+                w.z = pack16(__uint_as_float(acc[8 * g + 4]) * mul, __uint_as_float(acc[8 * g + 5]) * mul, args.is_bf16);
+                w.w = pack16(__uint_as_float(acc[8 * g + 6]) * mul, __uint_as_float(acc[8 * g + 7]) * mul, args.is_bf16);
+                *reinterpret_cast<uint4*>(dst + h) = w;
+              }
+            }
+          }
+        }
+      }
+    }
+  } else if (warp < kBwdProducerWarp) {
+    // ------------------------------------------------------------------ dQ: TMEM -> fp32 accumulator
+    const int row = threadIdx.x - kReduceWarp * 32;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    for (int it = 0; it < n_steps; ++it) {
+      if (!ptx::mbar_wait(dq_full, it & 1, ctl, kSiteBwdDqFull)) break;
+      ptx::tc_fence_after_sync();
+      const int q0 = (i0 + it) * kBlk;
+      float* dst = args.dq_acc + (static_cast<int64_t>(bn) * args.f_pad + q0 + row) * kHeadDim;
+#pragma unroll 1
+      for (int c = 0; c < kHeadDim / 32; ++c) {
+        uint32_t acc[32];
+        ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDQ + 32 * c, acc);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          red_add_v4(dst + 32 * c + 4 * g, __uint_as_float(acc[4 * g]), __uint_as_float(acc[4 * g + 1]),
+                     __uint_as_float(acc[4 * g + 2]), __uint_as_float(acc[4 * g + 3]));
+      }
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(dq_free);
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kBwdMmaWarp) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int kHeadDim, bool kBias>
+int launch_bwd_cfg(const BwdProblem& bp, const DeviceInfo& dev, float* neg_lse2, float* delta, float* dq_acc,
+                   int f_pad, cudaStream_t stream) {
+  using C = BwdCfg<kHeadDim>;
+  const Problem& p = bp.fwd;
+  const CUtensorMapDataType dt = p.dtype == IXK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  auto make_map = [&](CUtensorMap* out, const void* base, const int64_t* strides, int rows) -> int {
+    TmapSpec s{};
+    s.dtype = dt;
+    s.rank = 4;
+    s.swizzle128 = true;
+    s.dims[0] = p.H;
+    s.dims[1] = rows;
+    s.dims[2] = p.N;
+    s.dims[3] = p.B;
+    auto stride_bytes = [&](int64_t st, uint64_t fallback) -> uint64_t {
+      return st > 0 ? static_cast<uint64_t>(st) * 2 : fallback;   // size-1 dimensions still need a legal stride
+    };
+    const uint64_t row_pitch = stride_bytes(strides[2], static_cast<uint64_t>(p.H) * 2);
+    s.strides_bytes[0] = row_pitch;
+    s.strides_bytes[1] = stride_bytes(strides[1], row_pitch * rows);
+    s.strides_bytes[2] = stride_bytes(strides[0], row_pitch * rows * p.N);
+    s.box[0] = kChunkElems;
+    s.box[1] = kBlk;
+    s.box[2] = 1;
+    s.box[3] = 1;
+    return encode_tmap(out, base, s);
+  };
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = make_map(&tq, p.q, p.q_strides, p.F)) != IXK_OK) return rc;
+  if ((rc = make_map(&tk, p.k, p.k_strides, p.T)) != IXK_OK) return rc;
+  if ((rc = make_map(&tv, p.v, p.v_strides, p.T)) != IXK_OK) return rc;
+  if ((rc = make_map(&tdo, bp.grad_out, bp.do_strides, p.F)) != IXK_OK) return rc;
+
+  BwdArgs a{};
+  a.B = p.B; a.N = p.N; a.H = p.H; a.F = p.F; a.T = p.T;
+  a.f_pad = f_pad;
+  a.num_kblocks = (p.T + kBlk - 1) / kBlk;
+  a.num_qblocks = (p.F + kBlk - 1) / kBlk;
+  a.causal = p.causal ? 1 : 0;
+  a.is_bf16 = p.dtype == IXK_BF16 ? 1 : 0;
+  a.scale_log2 = p.head_scale * kLog2e;
+  a.head_scale = p.head_scale;
+  a.bias = static_cast<const uint16_t*>(p.bias);
+  a.neg_lse2 = neg_lse2;
+  a.delta = delta;
+  a.dq_acc = dq_acc;
+  a.dk = static_cast<uint16_t*>(bp.dk);
+  a.dv = static_cast<uint16_t*>(bp.dv);
+  for (int i = 0; i < 3; ++i) {
+    a.bias_strides[i] = p.bias_strides[i];
+    a.dk_strides[i] = bp.dk_strides[i];
+    a.dv_strides[i] = bp.dv_strides[i];
+  }
+  a.status_word = dev.status_word;
+
+  auto* fn = &fmha_bwd_kernel<kHeadDim, kBias>;
+  static thread_local int configured_device = -1;
+  if (configured_device != dev.device) {
+    IXK_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    configured_device = dev.device;
+  }
+  const int64_t ctas = static_cast<int64_t>(a.num_kblocks) * p.N * p.B;
+  if (ctas > 0x7fffffff) return fail(IXK_UNIMPLEMENTED, "too many (batch, head, key block) work items");
+  fn<<<static_cast<unsigned>(ctas), kBwdThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, a);
+  IXK_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return IXK_OK;
+}
+
+int head_pad_of(int H) { return H <= 64 ? 64 : 128; }
+int f_pad_of(int F) { return (F + kBlk - 1) / kBlk * kBlk; }
+
+}  // namespace
+
+size_t bwd_workspace_bytes(const Problem& p) {
+  if (p.B == 0 || p.N == 0 || p.F == 0 || p.H > 128) return 0;
+  return static_cast<size_t>(p.B) * p.N * f_pad_of(p.F) * (head_pad_of(p.H) + 2) * sizeof(float);
+}
+
+int launch_bwd(const BwdProblem& bp, const DeviceInfo& dev, void* workspace, size_t workspace_bytes,
+               cudaStream_t stream) {
+  const Problem& p = bp.fwd;
+  if (p.H > 128)
+    return fail(IXK_UNIMPLEMENTED, "attention backward covers head_size <= 128 (dK and dV of a 256-wide head fill tensor memory)");
+  const size_t need = bwd_workspace_bytes(p);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(IXK_WORKSPACE_TOO_SMALL, "attention backward needs ixk_fmha_bwd_workspace_bytes(desc) bytes of workspace");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return fail(IXK_INVALID_ARGUMENT, "workspace must be 16-byte aligned");
+  const int f_pad = f_pad_of(p.F), head_pad = head_pad_of(p.H);
+  const int64_t rows = static_cast<int64_t>(p.B) * p.N * f_pad;
+  float* neg_lse2 = static_cast<float*>(workspace);
+  float* delta = neg_lse2 + rows;
+  float* dq_acc = delta + rows;
+
+  PrepArgs pa{};
+  pa.B = p.B; pa.N = p.N; pa.H = p.H; pa.F = p.F; pa.f_pad = f_pad; pa.head_pad = head_pad;
+  pa.is_bf16 = p.dtype == IXK_BF16 ? 1 : 0;
+  pa.out = static_cast<const uint16_t*>(p.out);
+  pa.grad_out = static_cast<const uint16_t*>(bp.grad_out);
+  pa.lse = p.lse;
+  for (int i = 0; i < 3; ++i) {
+    pa.o_strides[i] = p.o_strides[i];
+    pa.do_strides[i] = bp.do_strides[i];
+  }
+  pa.neg_lse2 = neg_lse2;
+  pa.delta = delta;
+  pa.dq_acc = dq_acc;
+  const int prep_grid = static_cast<int>(std::min<int64_t>((rows + 7) / 8, static_cast<int64_t>(dev.sm_count) * 8));
+  bwd_prepare_kernel<<<prep_grid, 256, 0, stream>>>(pa);
+  IXK_CUDA_OK(cudaGetLastError());
+  count_launch();
+
+  int rc;
+  const bool bias = p.bias != nullptr;
+  if (head_pad == 64) {
+    rc = bias ? launch_bwd_cfg<64, true>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream)
+              : launch_bwd_cfg<64, false>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream);
+  } else {
+    rc = bias ? launch_bwd_cfg<128, true>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream)
+              : launch_bwd_cfg<128, false>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream);
+  }
+  if (rc != IXK_OK) return rc;
+
+  ConvertArgs ca{};
+  ca.B = p.B; ca.N = p.N; ca.H = p.H; ca.F = p.F; ca.f_pad = f_pad; ca.head_pad = head_pad;
+  ca.is_bf16 = pa.is_bf16;
+  ca.head_scale = p.head_scale;
+  ca.dq_acc = dq_acc;
+  ca.dq = static_cast<uint16_t*>(bp.dq);
+  for (int i = 0; i < 3; ++i) ca.dq_strides[i] = bp.dq_strides[i];
+  const int64_t pairs = static_cast<int64_t>(p.B) * p.N * p.F * (p.H / 2);
+  const int conv_grid = static_cast<int>(std::min<int64_t>((pairs + 255) / 256, static_cast<int64_t>(dev.sm_count) * 8));
+  bwd_convert_kernel<<<conv_grid, 256, 0, stream>>>(ca);
+  IXK_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return IXK_OK;
+}
+}  // namespace fmha
+}  // namespace ixk

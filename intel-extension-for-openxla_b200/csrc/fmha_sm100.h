@@ -39,5 +39,23 @@ size_t decode_workspace_bytes(const Problem& p, int splits);
 int launch_decode(const Problem& p, const DeviceInfo& dev, void* workspace, size_t workspace_bytes,
                   cudaStream_t stream);
 
+// ---- tcgen05 backward kernels (fmha_bwd_sm100.cu)
+// `fwd` carries q, k, v, bias, the forward's output (`out`, read only) and row statistic (`lse`).
+struct BwdProblem {
+  Problem fwd;
+  const void* grad_out = nullptr;
+  void* dq = nullptr;
+  void* dk = nullptr;
+  void* dv = nullptr;
+  int64_t do_strides[3] = {0, 0, 0};
+  int64_t dq_strides[3] = {0, 0, 0};
+  int64_t dk_strides[3] = {0, 0, 0};
+  int64_t dv_strides[3] = {0, 0, 0};
+};
+// fp32 scratch: -lse*log2e and rowsum(dO*O) per padded query row, and the dQ accumulator.
+size_t bwd_workspace_bytes(const Problem& p);
+int launch_bwd(const BwdProblem& p, const DeviceInfo& dev, void* workspace, size_t workspace_bytes,
+               cudaStream_t stream);
+
 }  // namespace fmha
 }  // namespace ixk

@@ -269,6 +269,48 @@ def fmha_forward(q, k, v, bias=None, *, head_scale: float, causal: bool = False,
     return out, lse
 
 
+def fmha_backward(q, k, v, out, grad_out, lse, bias=None, *, head_scale: float, causal: bool = False,
+                  dtype: int = BF16, round_p: bool = True):
+    """fmha_backward_t (xla/service/gpu/xetla/sdp/fmha_backward.h), un-tiled.
+
+    q, out, grad_out [B,N,F,H]; k, v [B,N,T,H]; lse [B,N,F] as the forward returns it; bias
+    broadcastable to [B,N,F,T].  D = rowsum(dO * O) in fp32 (:182-222); P is recomputed from the
+    saved row statistic, P = exp(head_scale * Q.K^T + bias - lse) (:489-545), with the causal
+    mask of the forward; dP = dO.V^T, dS = P * (dP - D) (:556-584); P and dS are rounded to
+    `dtype` where the kernel stores them as matmul operands; dV = P^T.dO, dK = head_scale *
+    dS^T.Q (:671), dQ = head_scale * dS.K accumulated in fp32 and rounded once (:842).
+    Returns (dQ, dK, dV) float32 holding values rounded to `dtype`."""
+    q, k, v = (np.asarray(a, np.float32) for a in (q, k, v))
+    out, grad_out = np.asarray(out, np.float32), np.asarray(grad_out, np.float32)
+    lse = np.asarray(lse, np.float32)
+    B, N, F, H = q.shape
+    T = k.shape[2]
+    dq = np.empty_like(q)
+    dk = np.empty_like(k)
+    dv = np.empty_like(v)
+    if bias is not None:
+        bias = np.broadcast_to(np.asarray(bias, np.float32), (B, N, F, T))
+    mask = (np.arange(T)[None, :] > np.arange(F)[:, None]) if causal else None
+    scale = np.float32(head_scale)
+    for b in range(B):
+        for n in range(N):
+            delta = (grad_out[b, n] * out[b, n]).sum(axis=1, keepdims=True, dtype=np.float32)
+            s = (q[b, n] @ k[b, n].T) * scale
+            if bias is not None:
+                s = s + bias[b, n]
+            p = np.exp(s - lse[b, n][:, None]).astype(np.float32)
+            if mask is not None:
+                p = np.where(mask, np.float32(0), p)
+            dp = grad_out[b, n] @ v[b, n].T
+            ds = p * (dp - delta)
+            if round_p:
+                p, ds = round_to(p, dtype), round_to(ds, dtype)
+            dv[b, n] = round_to(p.T @ grad_out[b, n], dtype)
+            dk[b, n] = round_to((ds.T @ q[b, n]) * scale, dtype)
+            dq[b, n] = round_to((ds @ k[b, n]) * scale, dtype)
+    return dq, dk, dv
+
+
 # --------------------------------------------------------------------------- fp8 scaled GEMM
 
 def fp8_scaled_gemm(a_codes, a_dtype: int, a_scale: float, b_codes, b_dtype: int, b_scale: float,

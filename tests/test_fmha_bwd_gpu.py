@@ -1,0 +1,93 @@
+"""GPU parity of the attention backward (ixk_fmha_bwd) against the numpy oracle's statement of
+fmha_backward.h, through the C ABI.  The forward runs on the GPU first; its output and log-sum-exp
+rows are the inputs of both the kernel and the oracle, so that only the backward is compared.
+Tolerance: the bf16 bound of the forward tests (rtol 2e-2, atol 2e-2) element-wise, plus a relative
+Frobenius-norm bound of 1e-2 per gradient, which a structural error cannot meet."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def f32(t):
+    return t.float().cpu().numpy()
+
+
+def run_case(pkg, orc, cuda, *, B, N, F, T, H, causal=False, bias_shape=None, dtype=torch.bfloat16, seed=0,
+             seq_major=False):
+    g = torch.Generator().manual_seed(seed)
+
+    def make(S):
+        if seq_major:      # [B,S,N,H] storage handed over as a [B,N,S,H] view
+            return torch.randn(B, S, N, H, generator=g).to(dtype).to(cuda).permute(0, 2, 1, 3)
+        return torch.randn(B, N, S, H, generator=g).to(dtype).to(cuda)
+
+    q, k, v, do = make(F), make(T), make(T), make(F)
+    bias = None
+    if bias_shape is not None:
+        bias = (torch.randn(*bias_shape, F, T, generator=g) * 0.5).to(dtype).to(cuda)
+    scale = 1.0 / math.sqrt(H)
+    out = torch.empty_like(q)
+    lse = torch.empty(B, N, F, dtype=torch.float32, device=cuda)
+    pkg.fmha_forward_kernel(None, q, k, v, bias, None, 0.0, out, lse, scale, True, causal=causal)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    launches = pkg.launch_count()
+    pkg.fmha_backward_kernel(None, q, k, v, out, bias, do, lse, dq, dk, dv, scale, causal=causal)
+    torch.cuda.synchronize()
+    assert pkg.launch_count() - launches == 3
+    assert pkg.device_status() == 0
+    odt = orc.BF16 if dtype == torch.bfloat16 else orc.F16
+    wq, wk, wv = orc.fmha_backward(f32(q), f32(k), f32(v), f32(out), f32(do), f32(lse),
+                                   None if bias is None else f32(bias), head_scale=scale, causal=causal, dtype=odt)
+    for name, got, want in (("dv", dv, wv), ("dk", dk, wk), ("dq", dq, wq)):
+        got = f32(got)
+        assert np.isfinite(got).all(), name
+        rel = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
+        assert rel < 1e-2, f"{name}: relative error {rel:.3e}"
+        orc.check_close(got, want, rtol=2e-2, atol=2e-2, what=name)
+
+
+@pytest.mark.parametrize("H", [128, 64])
+@pytest.mark.parametrize("causal", [False, True])
+def test_one_block(pkg, orc, cuda, H, causal):
+    run_case(pkg, orc, cuda, B=1, N=1, F=128, T=128, H=H, causal=causal, seed=1)
+
+
+@pytest.mark.parametrize("F,T", [(256, 384), (384, 256), (200, 330), (130, 127), (640, 640)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_several_blocks_and_ragged_edges(pkg, orc, cuda, F, T, causal):
+    run_case(pkg, orc, cuda, B=2, N=3, F=F, T=T, H=128, causal=causal, seed=F + T)
+
+
+@pytest.mark.parametrize("H", [64, 32, 96, 128])
+def test_head_sizes(pkg, orc, cuda, H):
+    run_case(pkg, orc, cuda, B=1, N=2, F=300, T=260, H=H, causal=True, seed=H)
+
+
+@pytest.mark.parametrize("bias_shape", [(1, 1), (2, 1), (2, 2)])
+def test_additive_bias(pkg, orc, cuda, bias_shape):
+    run_case(pkg, orc, cuda, B=2, N=2, F=260, T=200, H=128, bias_shape=bias_shape, seed=7)
+
+
+def test_fp16_and_sequence_major_storage(pkg, orc, cuda):
+    run_case(pkg, orc, cuda, B=2, N=2, F=256, T=256, H=128, causal=True, dtype=torch.float16, seed=3)
+    run_case(pkg, orc, cuda, B=2, N=4, F=384, T=384, H=64, causal=True, seq_major=True, seed=4)
+
+
+def test_rejections(pkg, cuda):
+    q = torch.randn(1, 1, 128, 256, device=cuda).bfloat16()
+    lse = torch.zeros(1, 1, 128, device=cuda)
+    with pytest.raises(pkg.IxkError) as e:
+        pkg.fmha_backward_kernel(None, q, q, q, q, None, q, lse, torch.empty_like(q), torch.empty_like(q),
+                                 torch.empty_like(q), 1.0)
+    assert e.value.status == pkg.IXK_UNIMPLEMENTED
+    q = torch.randn(1, 1, 128, 64, device=cuda).bfloat16()
+    with pytest.raises(pkg.IxkError):      # gradient buffer of the wrong shape
+        pkg.fmha_backward_kernel(None, q, q, q, q, None, q, lse, torch.empty(1, 1, 64, 64, device=cuda).bfloat16(),
+                                 torch.empty_like(q), torch.empty_like(q), 1.0)
+    with pytest.raises(pkg.IxkError):      # log-sum-exp rows missing
+        pkg.fmha_backward_kernel(None, q, q, q, q, None, q, None, torch.empty_like(q), torch.empty_like(q),
+                                 torch.empty_like(q), 1.0)

@@ -192,3 +192,32 @@ def test_qkv_gemm_matches_three_separate_products(orc):
     for i in range(3):
         want = (x.float() @ w[i].float() + b[i].float()).bfloat16().float().numpy()
         assert np.max(np.abs(got[i] - want)) <= 2e-2 * max(1.0, float(np.max(np.abs(want))))
+
+
+def test_fmha_backward_matches_autograd(orc):
+    """The backward oracle (P recomputed from the saved log-sum-exp, dS = P * (dP - D)) against
+    torch autograd of plain fp32 attention, with the operand roundings switched off."""
+    import math
+    import torch
+    g = torch.Generator().manual_seed(5)
+    B, N, F, T, H = 2, 2, 70, 90, 32
+    for causal, with_bias in ((False, False), (True, False), (False, True)):
+        q = torch.randn(B, N, F, H, generator=g, requires_grad=True)
+        k = torch.randn(B, N, T, H, generator=g, requires_grad=True)
+        v = torch.randn(B, N, T, H, generator=g, requires_grad=True)
+        bias = torch.randn(B, 1, F, T, generator=g) if with_bias else None
+        do = torch.randn(B, N, F, H, generator=g)
+        scale = 1.0 / math.sqrt(H)
+        s = (q @ k.transpose(-1, -2)) * scale
+        if bias is not None:
+            s = s + bias
+        if causal:
+            s = s.masked_fill(torch.arange(T)[None, :] > torch.arange(F)[:, None], float("-inf"))
+        out = torch.softmax(s, dim=-1) @ v
+        out.backward(do)
+        lse = torch.logsumexp(s, dim=-1)
+        dq, dk, dv = orc.fmha_backward(q.detach().numpy(), k.detach().numpy(), v.detach().numpy(), out.detach().numpy(),
+                                       do.numpy(), lse.detach().numpy(), None if bias is None else bias.numpy(),
+                                       head_scale=scale, causal=causal, dtype=orc.F32, round_p=False)
+        for got, want in ((dq, q.grad), (dk, k.grad), (dv, v.grad)):
+            np.testing.assert_allclose(got, want.numpy(), rtol=2e-4, atol=2e-5)
