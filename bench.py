@@ -104,6 +104,56 @@ class FmhaWorkload:
         orc.fmha_forward(f(host["q"]), f(host["k"]), f(host["v"]), bias, head_scale=self.H ** -0.5, causal=self.causal)
 
 
+class FmhaBwdWorkload:
+    """Fused attention backward on configuration 2's shape: dQ, dK, dV from Q, K, V, O, dO and the
+    forward's log-sum-exp rows (the forward runs once, outside the timed steps).  Five matrix
+    products per tile against the forward's two: 2.5 x the forward's flops."""
+
+    def __init__(self, causal: bool, B=8, N=16, S=2048, H=128):
+        self.causal, self.B, self.N, self.S, self.H = causal, B, N, S, H
+        self.name = f"fmha_bwd_{'causal' if causal else 'full'}_B{B}_N{N}_S{S}_H{H}_bf16"
+        self.metric = "fused-MHA backward TFLOP/s per B200 (bf16, %s)" % ("causal" if causal else "non-causal")
+        self.unit = "TFLOP/s"
+        self.bound = "tensor"
+        self.dtype = "bf16"
+        self.kernel = "fmha_bwd_kernel"
+        self.work = 10.0 * B * N * H * S * ((S + 1) / 2 if causal else S)
+        self.scale_div = 1e12
+
+    def make(self, seed):
+        g = torch.Generator().manual_seed(seed)
+        shape = (self.B, self.N, self.S, self.H)
+        return {name: torch.randn(shape, generator=g).bfloat16() for name in ("q", "k", "v", "do")}
+
+    def alloc_out(self, dev):
+        return torch.empty(self.B, self.N, self.S, self.H, dtype=torch.bfloat16, device=dev)   # dQ
+
+    def run(self, pkg, d, out):
+        scale = self.H ** -0.5
+        if "_o" not in d:
+            d["_o"] = torch.empty_like(d["q"])
+            d["_lse"] = torch.empty(self.B, self.N, self.S, dtype=torch.float32, device=out.device)
+            pkg.fmha_forward_kernel(None, d["q"], d["k"], d["v"], None, None, 0.0, d["_o"], d["_lse"], scale, True,
+                                    causal=self.causal)
+            d["_dk"], d["_dv"] = torch.empty_like(d["k"]), torch.empty_like(d["v"])
+            need = pkg.fmha_backward_workspace_bytes(d["q"], d["k"], d["v"], d["_o"], None, d["do"], out, d["_dk"],
+                                                     d["_dv"], scale, self.causal)
+            d["_ws"] = torch.empty(need, dtype=torch.uint8, device=out.device)
+        pkg.fmha_backward_kernel(None, d["q"], d["k"], d["v"], d["_o"], None, d["do"], d["_lse"], out, d["_dk"],
+                                 d["_dv"], scale, causal=self.causal, workspace=d["_ws"])
+
+    def cpu_units(self):
+        return self.B * self.N
+
+    def cpu_run(self, orc, host, idx):
+        b, n = divmod(idx, self.N)
+        f = lambda t: t[b:b + 1, n:n + 1].float().numpy()
+        scale = self.H ** -0.5
+        o, lse = orc.fmha_forward(f(host["q"]), f(host["k"]), f(host["v"]), None, head_scale=scale, causal=self.causal)
+        orc.fmha_backward(f(host["q"]), f(host["k"]), f(host["v"]), o, f(host["do"]), lse, None, head_scale=scale,
+                          causal=self.causal)
+
+
 class GemmWorkload:
     """bf16 GEMM + bias + GELU(tanh) (configuration 1): X[8192x4096] ~ N(0,1), W[4096x16384] ~
     N(0,0.02), bias ~ N(0,0.02), fp32 accumulate, bf16 out."""
@@ -234,6 +284,8 @@ class DecodeWorkload:
 WORKLOADS = {
     "fmha_causal": lambda: FmhaWorkload(True),
     "fmha_bias": lambda: FmhaWorkload(False),
+    "fmha_bwd_causal": lambda: FmhaBwdWorkload(True),
+    "fmha_bwd_full": lambda: FmhaBwdWorkload(False),
     "gemm_bias_gelu": lambda: GemmWorkload(),
     "gemm_fp8": lambda: Fp8GemmWorkload(False),
     "gemm_fp8_e5m2": lambda: Fp8GemmWorkload(True),
@@ -241,7 +293,7 @@ WORKLOADS = {
 }
 LAYER_WORKLOADS = ("gptj_layer", "gemma_decode")   # tensor-parallel over --gpus N, strong scaling
 DEFAULT_WORKLOAD = "fmha_causal"
-OTHERS = ["fmha_bias", "gemm_bias_gelu", "gemm_fp8", "gemm_fp8_e5m2", "decode_attn"]
+OTHERS = ["fmha_bias", "fmha_bwd_causal", "gemm_bias_gelu", "gemm_fp8", "gemm_fp8_e5m2", "decode_attn"]
 
 
 # ------------------------------------------------------------------------------- clocks

@@ -39,10 +39,11 @@ namespace {
 constexpr int kBlk = 128;                       // keys per CTA = queries per step = TMEM lanes
 constexpr int kChunkElems = 64;                 // 16-bit elements per 128-byte swizzle row
 constexpr int kChunkBytes = kBlk * 128;         // one 128-row x 128-byte box
-constexpr int kBwdThreads = 320;
-constexpr int kReduceWarp = 4;                  // first warp of the dQ warpgroup
-constexpr int kBwdProducerWarp = 8;
-constexpr int kBwdMmaWarp = 9;
+constexpr int kBwdThreads = 448;
+constexpr int kComputeThreads = 256;            // two warpgroups, each takes half of a step's query columns
+constexpr int kReduceWarp = 8;                  // first warp of the dQ warpgroup
+constexpr int kBwdProducerWarp = 12;
+constexpr int kBwdMmaWarp = 13;
 constexpr int kStages = 2;                      // Q / dO tiles in flight
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -194,10 +195,6 @@ __device__ __forceinline__ void bwd_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uin
       "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void red_add_v4(float* addr, float x, float y, float z, float w) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
-}
-
 template <int kHeadDim, bool kBias>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -246,7 +243,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       ptx::mbar_init(qdo_empty(st), 1);
     }
     ptx::mbar_init(sdp_full, 1);
-    ptx::mbar_init(pds_ready, 128);
+    ptx::mbar_init(pds_ready, kComputeThreads);
     ptx::mbar_init(dq_full, 1);
     ptx::mbar_init(dq_free, 128);
     ptx::mbar_init(final_bar, 1);
@@ -293,7 +290,10 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const uint32_t fmt = args.is_bf16 ? 1u : 0u;
       const uint32_t idesc_t = ptx::umma_idesc(fmt, fmt, 0, 0, kBlk, kBlk);         // S^T, dP^T
       const uint32_t idesc_kv = ptx::umma_idesc(fmt, fmt, 0, 1, kBlk, kHeadDim);    // dV (A in TMEM), dK
-      const uint32_t idesc_dq = ptx::umma_idesc(fmt, fmt, 1, 1, kBlk, kHeadDim);    // A = dS^T read M-major
+      // dQ^T = K^T.dS^T: head dim along the lanes (M = 128; at head size 64 the upper 64 lanes
+      // multiply whatever follows the K tile in shared memory and are never read), queries along
+      // the columns, both operands read with their M / N dimension contiguous
+      const uint32_t idesc_dq = ptx::umma_idesc(fmt, fmt, 1, 1, kBlk, kBlk);
       const uint64_t kmajor = ptx::umma_smem_desc(0, 16, 1024);
       const uint64_t mnmajor = ptx::umma_smem_desc(0, kChunkBytes, 1024);
       const uint32_t k_lo = static_cast<uint32_t>(kmajor), k_hi = static_cast<uint32_t>(kmajor >> 32);
@@ -324,7 +324,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < kBlk / 16; ++ks)     // dV += P^T.dO over 16 queries at a time
-          bwd_mma_ts(tmem_base + C::kTmemDV, tmem_base + C::kTmemS + ks * 8, m_lo + (do_addr >> 4) + ((ks * 2048) >> 4),
+          bwd_mma_ts(tmem_base + C::kTmemDV, tmem_base + C::kTmemS + (ks >> 2) * 64 + (ks & 3) * 8, m_lo + (do_addr >> 4) + ((ks * 2048) >> 4),
                      m_hi, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
         for (int ks = 0; ks < kBlk / 16; ++ks) {   // dK += dS^T.Q
@@ -333,19 +333,21 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                      m_hi, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
         }
 #pragma unroll
-        for (int ks = 0; ks < kBlk / 16; ++ks)     // dQ = dS.K over 16 keys at a time
-          bwd_mma_ss(tmem_base + C::kTmemDQ, m_lo + (ds_smem >> 4) + ((ks * 2048) >> 4), m_hi,
-                     m_lo + (k_smem >> 4) + ((ks * 2048) >> 4), m_hi, idesc_dq, ks != 0 ? 1u : 0u);
+        for (int ks = 0; ks < kBlk / 16; ++ks)     // dQ^T = K^T.dS^T over 16 keys at a time
+          bwd_mma_ss(tmem_base + C::kTmemDQ, m_lo + (k_smem >> 4) + ((ks * 2048) >> 4), m_hi,
+                     m_lo + (ds_smem >> 4) + ((ks * 2048) >> 4), m_hi, idesc_dq, ks != 0 ? 1u : 0u);
         ptx::umma_commit_elect(dq_full);
         ptx::umma_commit_elect(qdo_empty(st));
       }
       ptx::umma_commit_elect(final_bar);
     }
   } else if (warp < kReduceWarp) {
-    // ------------------------------------------------------------------ P^T and dS^T (one key row per thread)
-    const int r = threadIdx.x;
+    // ------------------------------------------------------------------ P^T and dS^T (one key row per thread,
+    // warpgroup 0 on query columns 0-63 of the step, warpgroup 1 on 64-127)
+    const int r = threadIdx.x & 127;
+    const int half = threadIdx.x >> 7;
     const int key = kb * kBlk + r;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const bool key_ok = key < args.T;
     bool alive = true;
     for (int it = 0; it < n_steps && alive; ++it) {
@@ -361,7 +363,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if constexpr (kBias)
         bias_row = args.bias + b * args.bias_strides[0] + n * args.bias_strides[1] + key;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t s[32], dp[32];
         ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemS + 32 * c, s);
         ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDP + 32 * c, dp);
@@ -379,7 +381,11 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               const int q = q0 + col;
               if (key_ok && q < args.F) x = fmaf(to_f32(bias_row[q * args.bias_strides[2]], args.is_bf16), kLog2e, x);
             }
+#ifdef IXK_BWD_PROBE_NO_EXP
+            float p = x;
+#else
             float p = ptx::ex2_approx(x);
+#endif
             if (!key_ok || (diag && key > q0 + col)) p = 0.0f;
             pv[e] = p;
             dv[e] = p * (__uint_as_float(dp[j]) - dl[col]);
@@ -387,7 +393,9 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           pw[j2] = pack16(pv[0], pv[1], args.is_bf16);
           dw[j2] = pack16(dv[0], dv[1], args.is_bf16);
         }
-        ptx::tmem_st_32x16(tmem_base + lane_addr + C::kTmemS + 16 * c, pw);
+        // P^T goes over the S^T columns this warpgroup has already read: queries 0-63 at columns
+        // 0-31, queries 64-127 at columns 64-95
+        ptx::tmem_st_32x16(tmem_base + lane_addr + C::kTmemS + 64 * half + 16 * (c & 1), pw);
         const uint32_t row_addr = ds_smem + (c >> 1) * kChunkBytes + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -408,8 +416,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       ptx::tc_fence_after_sync();
       uint16_t* dv_row = args.dv + b * args.dv_strides[0] + n * args.dv_strides[1] + static_cast<int64_t>(key) * args.dv_strides[2];
       uint16_t* dk_row = args.dk + b * args.dk_strides[0] + n * args.dk_strides[1] + static_cast<int64_t>(key) * args.dk_strides[2];
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
+      {
+        const int which = half;      // warpgroup 0 stores dV, warpgroup 1 dK
         uint16_t* dst = which == 0 ? dv_row : dk_row;
         const uint32_t col0 = which == 0 ? C::kTmemDV : C::kTmemDK;
         const float mul = which == 0 ? 1.0f : args.head_scale;
@@ -441,26 +449,36 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
     }
   } else if (warp < kBwdProducerWarp) {
-    // ------------------------------------------------------------------ dQ: TMEM -> fp32 accumulator
-    const int row = threadIdx.x - kReduceWarp * 32;
+    // ------------------------------------------------------------------ dQ^T: TMEM -> fp32 accumulator
+    // One head-dim element per thread: the 32 lanes of a warp add to 32 consecutive floats of one
+    // query row of the accumulator, a full 128-byte line per instruction.
+    const int d = threadIdx.x - kReduceWarp * 32;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     for (int it = 0; it < n_steps; ++it) {
       if (!ptx::mbar_wait(dq_full, it & 1, ctl, kSiteBwdDqFull)) break;
       ptx::tc_fence_after_sync();
       const int q0 = (i0 + it) * kBlk;
-      float* dst = args.dq_acc + (static_cast<int64_t>(bn) * args.f_pad + q0 + row) * kHeadDim;
+      float* dst = args.dq_acc + (static_cast<int64_t>(bn) * args.f_pad + q0) * kHeadDim + d;
 #pragma unroll 1
-      for (int c = 0; c < kHeadDim / 32; ++c) {
-        uint32_t acc[32];
-        ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDQ + 32 * c, acc);
-        ptx::tmem_ld_wait();
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t acc[2][32];
+        if (d < kHeadDim) {
+          ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDQ + 64 * hf, acc[0]);
+          ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDQ + 64 * hf + 32, acc[1]);
+          ptx::tmem_ld_wait();
+        }
+        if (hf == 1) {   // the columns are free once they sit in registers; the adds follow
+          ptx::tc_fence_before_sync();
+          ptx::mbar_arrive(dq_free);
+        }
+#ifndef IXK_BWD_PROBE_NO_RED
+        if (d < kHeadDim) {
 #pragma unroll
-        for (int g = 0; g < 8; ++g)
-          red_add_v4(dst + 32 * c + 4 * g, __uint_as_float(acc[4 * g]), __uint_as_float(acc[4 * g + 1]),
-                     __uint_as_float(acc[4 * g + 2]), __uint_as_float(acc[4 * g + 3]));
+          for (int j = 0; j < 64; ++j)
+            atomicAdd(dst + static_cast<int64_t>(64 * hf + j) * kHeadDim, __uint_as_float(acc[j >> 5][j & 31]));
+        }
+#endif
       }
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(dq_free);
     }
   }
 
