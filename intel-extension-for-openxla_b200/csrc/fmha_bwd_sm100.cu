@@ -39,18 +39,21 @@ namespace {
 constexpr int kBlk = 128;                       // keys per CTA = queries per step = TMEM lanes
 constexpr int kChunkElems = 64;                 // 16-bit elements per 128-byte swizzle row
 constexpr int kChunkBytes = kBlk * 128;         // one 128-row x 128-byte box
-constexpr int kBwdThreads = 448;
+constexpr int kBwdThreads = 512;                // warps 14 and 15 only take part in the register re-partitioning
 constexpr int kComputeThreads = 256;            // two warpgroups, each takes half of a step's query columns
 constexpr int kReduceWarp = 8;                  // first warp of the dQ warpgroup
 constexpr int kBwdProducerWarp = 12;
 constexpr int kBwdMmaWarp = 13;
 constexpr int kStages = 2;                      // Q / dO tiles in flight
+// per-thread register budgets after re-partitioning: 384 x 152 + 128 x 56 = 65536
+constexpr int kWorkRegs = 152;
+constexpr int kCtrlRegs = 56;
 constexpr float kLog2e = 1.4426950408889634f;
 
 // wait sites reported in the device status word
-constexpr int kSiteBwdKv = 0x41, kSiteBwdQdoFull = 0x42, kSiteBwdQdoEmpty = 0x43, kSiteBwdSdp = 0x44,
-              kSiteBwdPds = 0x45, kSiteBwdDqFull = 0x46, kSiteBwdDqFree = 0x47, kSiteBwdFinal = 0x48,
-              kSiteBwdAlign = 0x49;
+constexpr int kSiteBwdKv = 0x41, kSiteBwdQdoFull = 0x42, kSiteBwdQdoEmpty = 0x43, kSiteBwdS = 0x44,
+              kSiteBwdP = 0x45, kSiteBwdDqFull = 0x46, kSiteBwdDqFree = 0x47, kSiteBwdFinal = 0x48,
+              kSiteBwdAlign = 0x49, kSiteBwdDp = 0x4a, kSiteBwdDs = 0x4b;
 
 template <int kHeadDim>
 struct BwdCfg {
@@ -217,9 +220,10 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t kv_full = bar_base;
   auto qdo_full = [&](uint32_t st) { return bar_base + 8u * (1 + st); };
   auto qdo_empty = [&](uint32_t st) { return bar_base + 8u * (3 + st); };
-  const uint32_t sdp_full = bar_base + 8u * 5, pds_ready = bar_base + 8u * 6, dq_full = bar_base + 8u * 7,
-                 dq_free = bar_base + 8u * 8, final_bar = bar_base + 8u * 9;
-  uint8_t* tail = smem_raw + C::kOffBars + 8 * 10;
+  const uint32_t s_full = bar_base + 8u * 5, p_ready = bar_base + 8u * 6, dq_full = bar_base + 8u * 7,
+                 dq_free = bar_base + 8u * 8, final_bar = bar_base + 8u * 9, dp_full = bar_base + 8u * 10,
+                 ds_ready = bar_base + 8u * 11;
+  uint8_t* tail = smem_raw + C::kOffBars + 8 * 12;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
@@ -242,8 +246,10 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       ptx::mbar_init(qdo_full(st), 1);
       ptx::mbar_init(qdo_empty(st), 1);
     }
-    ptx::mbar_init(sdp_full, 1);
-    ptx::mbar_init(pds_ready, kComputeThreads);
+    ptx::mbar_init(s_full, 1);
+    ptx::mbar_init(dp_full, 1);
+    ptx::mbar_init(p_ready, kComputeThreads);
+    ptx::mbar_init(ds_ready, kComputeThreads);
     ptx::mbar_init(dq_full, 1);
     ptx::mbar_init(dq_free, 128);
     ptx::mbar_init(final_bar, 1);
@@ -264,6 +270,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
   if (warp == kBwdProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
+    ptx::setmaxnreg_dec<kCtrlRegs>();
     if (lane == 0 && n_steps > 0) {
       ptx::mbar_expect_tx(kv_full, 2 * C::kTileBytes);
       for (int c = 0; c < C::kChunks; ++c) {
@@ -286,6 +293,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
   } else if (warp == kBwdMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer (all 32 lanes)
+    ptx::setmaxnreg_dec<kCtrlRegs>();
     if (n_steps > 0) {
       const uint32_t fmt = args.is_bf16 ? 1u : 0u;
       const uint32_t idesc_t = ptx::umma_idesc(fmt, fmt, 0, 0, kBlk, kBlk);         // S^T, dP^T
@@ -298,46 +306,68 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const uint64_t mnmajor = ptx::umma_smem_desc(0, kChunkBytes, 1024);
       const uint32_t k_lo = static_cast<uint32_t>(kmajor), k_hi = static_cast<uint32_t>(kmajor >> 32);
       const uint32_t m_lo = static_cast<uint32_t>(mnmajor), m_hi = static_cast<uint32_t>(mnmajor >> 32);
-      bool alive = ptx::mbar_wait(kv_full, 0, ctl, kSiteBwdKv);
-      for (int it = 0; it < n_steps && alive; ++it) {
-        const uint32_t st = it & 1;
-        if (!ptx::mbar_wait(qdo_full(st), (it >> 1) & 1, ctl, kSiteBwdQdoFull)) break;
-        ptx::tc_fence_after_sync();
-        const uint32_t q_addr = stage_q(st), do_addr = stage_do(st);
+      auto issue_s = [&](uint32_t q_addr) {        // S^T = K.Q^T
 #pragma unroll
         for (int ks = 0; ks < kHeadDim / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
           bwd_mma_ss(tmem_base + C::kTmemS, k_lo + (k_smem >> 4) + off, k_hi, k_lo + (q_addr >> 4) + off, k_hi,
                      idesc_t, ks != 0 ? 1u : 0u);
         }
-        // dP^T shares its columns with the previous step's dQ at head size 128
-        if (it > 0 && !ptx::mbar_wait(dq_free, (it - 1) & 1, ctl, kSiteBwdDqFree)) break;
-        ptx::tc_fence_after_sync();
+        ptx::umma_commit_elect(s_full);
+      };
+      auto issue_dp = [&](uint32_t do_addr) {      // dP^T = V.dO^T
 #pragma unroll
         for (int ks = 0; ks < kHeadDim / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
           bwd_mma_ss(tmem_base + C::kTmemDP, k_lo + (v_smem >> 4) + off, k_hi, k_lo + (do_addr >> 4) + off, k_hi,
                      idesc_t, ks != 0 ? 1u : 0u);
         }
-        ptx::umma_commit_elect(sdp_full);
-        if (!ptx::mbar_wait(pds_ready, it & 1, ctl, kSiteBwdPds)) break;
+        ptx::umma_commit_elect(dp_full);
+      };
+      // Order per step: dV(i), S^T(i+1), dQ^T(i), dK(i), dP^T(i+1).  S^T of the next step runs
+      // while the compute warps still turn dP^T into dS^T; dQ^T comes before dK so that it is
+      // drained from the columns it shares with dP^T while dK runs.
+      bool alive = ptx::mbar_wait(kv_full, 0, ctl, kSiteBwdKv) && ptx::mbar_wait(qdo_full(0), 0, ctl, kSiteBwdQdoFull);
+      if (alive) {
+        ptx::tc_fence_after_sync();
+        issue_s(stage_q(0));
+        issue_dp(stage_do(0));
+      }
+      for (int it = 0; it < n_steps && alive; ++it) {
+        const uint32_t st = it & 1;
+        const uint32_t q_addr = stage_q(st), do_addr = stage_do(st);
+        const bool more = it + 1 < n_steps;
+        if (!ptx::mbar_wait(p_ready, it & 1, ctl, kSiteBwdP)) break;
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < kBlk / 16; ++ks)     // dV += P^T.dO over 16 queries at a time
-          bwd_mma_ts(tmem_base + C::kTmemDV, tmem_base + C::kTmemS + (ks >> 2) * 64 + (ks & 3) * 8, m_lo + (do_addr >> 4) + ((ks * 2048) >> 4),
-                     m_hi, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
+          bwd_mma_ts(tmem_base + C::kTmemDV, tmem_base + C::kTmemS + (ks >> 2) * 64 + (ks & 3) * 8,
+                     m_lo + (do_addr >> 4) + ((ks * 2048) >> 4), m_hi, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
+        if (more) {
+          if (!ptx::mbar_wait(qdo_full(st ^ 1), ((it + 1) >> 1) & 1, ctl, kSiteBwdQdoFull)) break;
+          ptx::tc_fence_after_sync();
+          issue_s(stage_q(st ^ 1));
+        }
+        if (!ptx::mbar_wait(ds_ready, it & 1, ctl, kSiteBwdDs)) break;
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < kBlk / 16; ++ks)     // dQ^T = K^T.dS^T over 16 keys at a time
+          bwd_mma_ss(tmem_base + C::kTmemDQ, m_lo + (k_smem >> 4) + ((ks * 2048) >> 4), m_hi,
+                     m_lo + (ds_smem >> 4) + ((ks * 2048) >> 4), m_hi, idesc_dq, ks != 0 ? 1u : 0u);
+        ptx::umma_commit_elect(dq_full);
 #pragma unroll
         for (int ks = 0; ks < kBlk / 16; ++ks) {   // dK += dS^T.Q
           const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
           bwd_mma_ss(tmem_base + C::kTmemDK, k_lo + (ds_smem >> 4) + off, k_hi, m_lo + (q_addr >> 4) + ((ks * 2048) >> 4),
                      m_hi, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
         }
-#pragma unroll
-        for (int ks = 0; ks < kBlk / 16; ++ks)     // dQ^T = K^T.dS^T over 16 keys at a time
-          bwd_mma_ss(tmem_base + C::kTmemDQ, m_lo + (k_smem >> 4) + ((ks * 2048) >> 4), m_hi,
-                     m_lo + (ds_smem >> 4) + ((ks * 2048) >> 4), m_hi, idesc_dq, ks != 0 ? 1u : 0u);
-        ptx::umma_commit_elect(dq_full);
         ptx::umma_commit_elect(qdo_empty(st));
+        if (more) {
+          // dP^T shares its columns with dQ^T at head size 128
+          if (!ptx::mbar_wait(dq_free, it & 1, ctl, kSiteBwdDqFree)) break;
+          ptx::tc_fence_after_sync();
+          issue_dp(stage_do(st ^ 1));
+        }
       }
       ptx::umma_commit_elect(final_bar);
     }
@@ -349,66 +379,80 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int key = kb * kBlk + r;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const bool key_ok = key < args.T;
+    ptx::setmaxnreg_inc<kWorkRegs>();
     bool alive = true;
     for (int it = 0; it < n_steps && alive; ++it) {
       const uint32_t st = it & 1;
       if (!ptx::mbar_wait(qdo_full(st), (it >> 1) & 1, ctl, kSiteBwdQdoFull)) { alive = false; break; }
-      if (!ptx::mbar_wait(sdp_full, it & 1, ctl, kSiteBwdSdp)) { alive = false; break; }
+      if (!ptx::mbar_wait(s_full, it & 1, ctl, kSiteBwdS)) { alive = false; break; }
       ptx::tc_fence_after_sync();
       const int q0 = (i0 + it) * kBlk;
-      const float* nl = reinterpret_cast<const float*>(smem_raw + rows_off(st));
+      const float* nl = reinterpret_cast<const float*>(smem_raw + rows_off(st)) + 64 * half;
       const float* dl = nl + kBlk;
       const bool diag = args.causal && (i0 + it) == kb;
       [[maybe_unused]] const uint16_t* bias_row = nullptr;
       if constexpr (kBias)
         bias_row = args.bias + b * args.bias_strides[0] + n * args.bias_strides[1] + key;
-#pragma unroll 1
-      for (int c = 2 * half; c < 2 * half + 2; ++c) {
-        uint32_t s[32], dp[32];
-        ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemS + 32 * c, s);
-        ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDP + 32 * c, dp);
+      // phase A: P^T = exp2(S^T * scale*log2e + bias*log2e - lse*log2e) for this warpgroup's 64 queries
+      float p[64];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t s[32];
+        ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemS + 64 * half + 32 * c, s);
         ptx::tmem_ld_wait();
-        uint32_t pw[16], dw[16];
+        uint32_t pw[16];
 #pragma unroll
-        for (int j2 = 0; j2 < 16; ++j2) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int j = 2 * j2 + e;
-            const int col = 32 * c + j;
-            float x = fmaf(__uint_as_float(s[j]), args.scale_log2, nl[col]);
-            if constexpr (kBias) {
-              const int q = q0 + col;
-              if (key_ok && q < args.F) x = fmaf(to_f32(bias_row[q * args.bias_strides[2]], args.is_bf16), kLog2e, x);
-            }
-#ifdef IXK_BWD_PROBE_NO_EXP
-            float p = x;
-#else
-            float p = ptx::ex2_approx(x);
-#endif
-            if (!key_ok || (diag && key > q0 + col)) p = 0.0f;
-            pv[e] = p;
-            dv[e] = p * (__uint_as_float(dp[j]) - dl[col]);
+        for (int j = 0; j < 32; ++j) {
+          const int col = 32 * c + j;             // within the warpgroup's half
+          float x = fmaf(__uint_as_float(s[j]), args.scale_log2, nl[col]);
+          if constexpr (kBias) {
+            const int q = q0 + 64 * half + col;
+            if (key_ok && q < args.F) x = fmaf(to_f32(bias_row[q * args.bias_strides[2]], args.is_bf16), kLog2e, x);
           }
-          pw[j2] = pack16(pv[0], pv[1], args.is_bf16);
-          dw[j2] = pack16(dv[0], dv[1], args.is_bf16);
+#ifdef IXK_BWD_PROBE_NO_EXP
+          float pe = x;
+#else
+          float pe = ptx::ex2_approx(x);
+#endif
+          if (!key_ok || (diag && key > q0 + 64 * half + col)) pe = 0.0f;
+          p[col] = pe;
         }
+#pragma unroll
+        for (int j2 = 0; j2 < 16; ++j2) pw[j2] = pack16(p[32 * c + 2 * j2], p[32 * c + 2 * j2 + 1], args.is_bf16);
         // P^T goes over the S^T columns this warpgroup has already read: queries 0-63 at columns
         // 0-31, queries 64-127 at columns 64-95
-        ptx::tmem_st_32x16(tmem_base + lane_addr + C::kTmemS + 64 * half + 16 * (c & 1), pw);
-        const uint32_t row_addr = ds_smem + (c >> 1) * kChunkBytes + r * 128;
+        ptx::tmem_st_32x16(tmem_base + lane_addr + C::kTmemS + 64 * half + 16 * c, pw);
+      }
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(p_ready);
+      // phase B: dS^T = P^T * (dP^T - D)
+      if (!ptx::mbar_wait(dp_full, it & 1, ctl, kSiteBwdDp)) { alive = false; break; }
+      ptx::tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t dp[32];
+        ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDP + 64 * half + 32 * c, dp);
+        ptx::tmem_ld_wait();
+        uint32_t dw[16];
+#pragma unroll
+        for (int j2 = 0; j2 < 16; ++j2) {
+          const int col = 32 * c + 2 * j2;
+          dw[j2] = pack16(p[col] * (__uint_as_float(dp[2 * j2]) - dl[col]),
+                          p[col + 1] * (__uint_as_float(dp[2 * j2 + 1]) - dl[col + 1]), args.is_bf16);
+        }
+        const uint32_t row_addr = ds_smem + half * kChunkBytes + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const uint32_t grp = static_cast<uint32_t>((c & 1) * 4 + g) ^ static_cast<uint32_t>(r & 7);
+          const uint32_t grp = static_cast<uint32_t>(c * 4 + g) ^ static_cast<uint32_t>(r & 7);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (grp << 4)), "r"(dw[4 * g]),
                        "r"(dw[4 * g + 1]), "r"(dw[4 * g + 2]), "r"(dw[4 * g + 3])
                        : "memory");
         }
       }
-      ptx::tmem_st_wait();
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(pds_ready);
+      ptx::mbar_arrive(ds_ready);
     }
     // epilogue: this thread's row of dV and dK
     const bool have = n_steps > 0 && alive && ptx::mbar_wait(final_bar, 0, ctl, kSiteBwdFinal);
@@ -452,6 +496,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     // ------------------------------------------------------------------ dQ^T: TMEM -> fp32 accumulator
     // One head-dim element per thread: the 32 lanes of a warp add to 32 consecutive floats of one
     // query row of the accumulator, a full 128-byte line per instruction.
+    ptx::setmaxnreg_inc<kWorkRegs>();
     const int d = threadIdx.x - kReduceWarp * 32;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     for (int it = 0; it < n_steps; ++it) {
@@ -459,27 +504,25 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       ptx::tc_fence_after_sync();
       const int q0 = (i0 + it) * kBlk;
       float* dst = args.dq_acc + (static_cast<int64_t>(bn) * args.f_pad + q0) * kHeadDim + d;
-#pragma unroll 1
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t acc[2][32];
-        if (d < kHeadDim) {
-          ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDQ + 64 * hf, acc[0]);
-          ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDQ + 64 * hf + 32, acc[1]);
-          ptx::tmem_ld_wait();
-        }
-        if (hf == 1) {   // the columns are free once they sit in registers; the adds follow
-          ptx::tc_fence_before_sync();
-          ptx::mbar_arrive(dq_free);
-        }
-#ifndef IXK_BWD_PROBE_NO_RED
-        if (d < kHeadDim) {
+      uint32_t acc[4][32];
+      if (d < kHeadDim) {
 #pragma unroll
-          for (int j = 0; j < 64; ++j)
-            atomicAdd(dst + static_cast<int64_t>(64 * hf + j) * kHeadDim, __uint_as_float(acc[j >> 5][j & 31]));
-        }
-#endif
+        for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDQ + 32 * c, acc[c]);
+        ptx::tmem_ld_wait();
       }
+      // the columns are free once they sit in registers; the adds follow
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(dq_free);
+#ifndef IXK_BWD_PROBE_NO_RED
+      if (d < kHeadDim) {
+#pragma unroll
+        for (int j = 0; j < 128; ++j)
+          atomicAdd(dst + static_cast<int64_t>(j) * kHeadDim, __uint_as_float(acc[j >> 5][j & 31]));
+      }
+#endif
     }
+  } else {
+    ptx::setmaxnreg_dec<kCtrlRegs>();     // warps 14, 15: nothing else to do
   }
 
   ptx::tc_fence_before_sync();
