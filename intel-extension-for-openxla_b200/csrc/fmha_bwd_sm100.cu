@@ -39,12 +39,13 @@ namespace {
 constexpr int kBlk = 128;                       // keys per CTA = queries per step = TMEM lanes
 constexpr int kChunkElems = 64;                 // 16-bit elements per 128-byte swizzle row
 constexpr int kChunkBytes = kBlk * 128;         // one 128-row x 128-byte box
-constexpr int kBwdThreads = 512;                // warps 14 and 15 only take part in the register re-partitioning
+constexpr int kBwdThreads = 512;                // warp 15 only takes part in the register re-partitioning
 constexpr int kComputeThreads = 256;            // two warpgroups, each takes half of a step's query columns
 constexpr int kReduceWarp = 8;                  // first warp of the dQ warpgroup
 constexpr int kBwdProducerWarp = 12;
 constexpr int kBwdMmaWarp = 13;
-constexpr int kStages = 2;                      // Q / dO tiles in flight
+constexpr int kStages = 2;                      // Q tiles in flight
+constexpr int kDoWarp = 14;                     // loads the dO tiles
 // per-thread register budgets after re-partitioning: 384 x 152 + 128 x 56 = 65536
 constexpr int kWorkRegs = 152;
 constexpr int kCtrlRegs = 56;
@@ -64,9 +65,13 @@ struct BwdCfg {
   static constexpr int kRowBytes = kBlk * 4;                        // 128 fp32 row values
   static constexpr int kOffK = 0;
   static constexpr int kOffV = kTileBytes;
-  static constexpr int kOffStage = 2 * kTileBytes;                  // per stage: Q tile, dO tile
-  static constexpr int kOffDs = kOffStage + kStages * 2 * kTileBytes;
-  static constexpr int kOffRows = kOffDs + kDsBytes;                // per stage: -lse*log2e row, D row
+  static constexpr int kOffQ = 2 * kTileBytes;                      // kStages Q tiles
+  static constexpr int kOffDo = kOffQ + kStages * kTileBytes;       // one dO tile: it lives from dP^T to the next dV
+  static constexpr int kOffDs = kOffDo + kTileBytes;
+  static constexpr int kPieceRows = 32;                             // query rows per bulk reduction of dQ
+  static constexpr int kPieceBytes = kPieceRows * kHeadDim * 4;
+  static constexpr int kOffDqStage = kOffDs + kDsBytes;             // two pieces
+  static constexpr int kOffRows = kOffDqStage + 2 * kPieceBytes;    // per stage: -lse*log2e row, D row
   static constexpr int kOffBars = kOffRows + kStages * 2 * kRowBytes;
   static constexpr int kSmemBytes = kOffBars + 256;
   static_assert(kSmemBytes <= 232448, "shared memory budget");
@@ -213,17 +218,18 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t k_smem = smem_base + C::kOffK;
   const uint32_t v_smem = smem_base + C::kOffV;
   const uint32_t ds_smem = smem_base + C::kOffDs;
-  auto stage_q = [&](uint32_t st) { return smem_base + C::kOffStage + st * 2 * C::kTileBytes; };
-  auto stage_do = [&](uint32_t st) { return stage_q(st) + C::kTileBytes; };
+  auto stage_q = [&](uint32_t st) { return smem_base + C::kOffQ + st * C::kTileBytes; };
+  const uint32_t do_smem = smem_base + C::kOffDo;
+  const uint32_t dq_stage = smem_base + C::kOffDqStage;
   auto rows_off = [&](uint32_t st) { return static_cast<uint32_t>(C::kOffRows) + st * 2 * C::kRowBytes; };
   const uint32_t bar_base = smem_base + C::kOffBars;
   const uint32_t kv_full = bar_base;
-  auto qdo_full = [&](uint32_t st) { return bar_base + 8u * (1 + st); };
-  auto qdo_empty = [&](uint32_t st) { return bar_base + 8u * (3 + st); };
+  auto q_full = [&](uint32_t st) { return bar_base + 8u * (1 + st); };
+  auto q_empty = [&](uint32_t st) { return bar_base + 8u * (3 + st); };
   const uint32_t s_full = bar_base + 8u * 5, p_ready = bar_base + 8u * 6, dq_full = bar_base + 8u * 7,
                  dq_free = bar_base + 8u * 8, final_bar = bar_base + 8u * 9, dp_full = bar_base + 8u * 10,
-                 ds_ready = bar_base + 8u * 11;
-  uint8_t* tail = smem_raw + C::kOffBars + 8 * 12;
+                 ds_ready = bar_base + 8u * 11, do_full = bar_base + 8u * 12, do_empty = bar_base + 8u * 13;
+  uint8_t* tail = smem_raw + C::kOffBars + 8 * 14;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
@@ -231,10 +237,12 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int lane = threadIdx.x & 31;
   ptx::AbortCtl ctl{abort_flag, args.status_word};
 
-  // work item: heaviest key blocks first (under the causal mask block 0 is seen by every query block)
-  const int per_kb = args.N * args.B;
-  const int kb = blockIdx.x / per_kb;
-  const int bn = blockIdx.x % per_kb;
+  // work item: the key blocks of one (batch, head) are neighbours in launch order, so that its Q, dO
+  // and slice of the dQ accumulator (1 MB at 2048 queries) stay in L2 while they are shared;
+  // within a head the heaviest key block comes first (under the causal mask block 0 is seen by
+  // every query block)
+  const int kb = blockIdx.x % args.num_kblocks;
+  const int bn = blockIdx.x / args.num_kblocks;
   const int n = bn % args.N, b = bn / args.N;
   const int i0 = args.causal ? kb : 0;
   const int n_steps = args.num_qblocks > i0 ? args.num_qblocks - i0 : 0;
@@ -243,9 +251,11 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     *abort_flag = 0;
     ptx::mbar_init(kv_full, 1);
     for (uint32_t st = 0; st < kStages; ++st) {
-      ptx::mbar_init(qdo_full(st), 1);
-      ptx::mbar_init(qdo_empty(st), 1);
+      ptx::mbar_init(q_full(st), 1);
+      ptx::mbar_init(q_empty(st), 1);
     }
+    ptx::mbar_init(do_full, 1);
+    ptx::mbar_init(do_empty, 1);
     ptx::mbar_init(s_full, 1);
     ptx::mbar_init(dp_full, 1);
     ptx::mbar_init(p_ready, kComputeThreads);
@@ -279,16 +289,25 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       for (int it = 0; it < n_steps; ++it) {
         const uint32_t st = it & 1;
-        if (it >= kStages && !ptx::mbar_wait(qdo_empty(st), ((it >> 1) - 1) & 1, ctl, kSiteBwdQdoEmpty)) break;
+        if (it >= kStages && !ptx::mbar_wait(q_empty(st), ((it >> 1) - 1) & 1, ctl, kSiteBwdQdoEmpty)) break;
         const int q0 = (i0 + it) * kBlk;
-        ptx::mbar_expect_tx(qdo_full(st), 2 * C::kTileBytes + 2 * C::kRowBytes);
-        for (int c = 0; c < C::kChunks; ++c) {
-          ptx::tma_load_4d(stage_q(st) + c * kChunkBytes, &tmap_q, qdo_full(st), c * kChunkElems, q0, n, b);
-          ptx::tma_load_4d(stage_do(st) + c * kChunkBytes, &tmap_do, qdo_full(st), c * kChunkElems, q0, n, b);
-        }
+        ptx::mbar_expect_tx(q_full(st), C::kTileBytes + 2 * C::kRowBytes);
+        for (int c = 0; c < C::kChunks; ++c)
+          ptx::tma_load_4d(stage_q(st) + c * kChunkBytes, &tmap_q, q_full(st), c * kChunkElems, q0, n, b);
         const int64_t row0 = static_cast<int64_t>(bn) * args.f_pad + q0;
-        ptx::bulk_load_1d(smem_base + rows_off(st), args.neg_lse2 + row0, C::kRowBytes, qdo_full(st));
-        ptx::bulk_load_1d(smem_base + rows_off(st) + C::kRowBytes, args.delta + row0, C::kRowBytes, qdo_full(st));
+        ptx::bulk_load_1d(smem_base + rows_off(st), args.neg_lse2 + row0, C::kRowBytes, q_full(st));
+        ptx::bulk_load_1d(smem_base + rows_off(st) + C::kRowBytes, args.delta + row0, C::kRowBytes, q_full(st));
+      }
+    }
+  } else if (warp == kDoWarp) {
+    // ------------------------------------------------------------------ dO loads (one buffer)
+    ptx::setmaxnreg_dec<kCtrlRegs>();
+    if (lane == 0) {
+      for (int it = 0; it < n_steps; ++it) {
+        if (it >= 1 && !ptx::mbar_wait(do_empty, (it - 1) & 1, ctl, kSiteBwdQdoEmpty)) break;
+        ptx::mbar_expect_tx(do_full, C::kTileBytes);
+        for (int c = 0; c < C::kChunks; ++c)
+          ptx::tma_load_4d(do_smem + c * kChunkBytes, &tmap_do, do_full, c * kChunkElems, (i0 + it) * kBlk, n, b);
       }
     }
   } else if (warp == kBwdMmaWarp) {
@@ -327,15 +346,16 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // Order per step: dV(i), S^T(i+1), dQ^T(i), dK(i), dP^T(i+1).  S^T of the next step runs
       // while the compute warps still turn dP^T into dS^T; dQ^T comes before dK so that it is
       // drained from the columns it shares with dP^T while dK runs.
-      bool alive = ptx::mbar_wait(kv_full, 0, ctl, kSiteBwdKv) && ptx::mbar_wait(qdo_full(0), 0, ctl, kSiteBwdQdoFull);
+      bool alive = ptx::mbar_wait(kv_full, 0, ctl, kSiteBwdKv) && ptx::mbar_wait(q_full(0), 0, ctl, kSiteBwdQdoFull) &&
+                   ptx::mbar_wait(do_full, 0, ctl, kSiteBwdQdoFull);
       if (alive) {
         ptx::tc_fence_after_sync();
         issue_s(stage_q(0));
-        issue_dp(stage_do(0));
+        issue_dp(do_smem);
       }
       for (int it = 0; it < n_steps && alive; ++it) {
         const uint32_t st = it & 1;
-        const uint32_t q_addr = stage_q(st), do_addr = stage_do(st);
+        const uint32_t q_addr = stage_q(st), do_addr = do_smem;
         const bool more = it + 1 < n_steps;
         if (!ptx::mbar_wait(p_ready, it & 1, ctl, kSiteBwdP)) break;
         ptx::tc_fence_after_sync();
@@ -343,8 +363,9 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int ks = 0; ks < kBlk / 16; ++ks)     // dV += P^T.dO over 16 queries at a time
           bwd_mma_ts(tmem_base + C::kTmemDV, tmem_base + C::kTmemS + (ks >> 2) * 64 + (ks & 3) * 8,
                      m_lo + (do_addr >> 4) + ((ks * 2048) >> 4), m_hi, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
+        ptx::umma_commit_elect(do_empty);          // dO(i) has no reader after dV(i)
         if (more) {
-          if (!ptx::mbar_wait(qdo_full(st ^ 1), ((it + 1) >> 1) & 1, ctl, kSiteBwdQdoFull)) break;
+          if (!ptx::mbar_wait(q_full(st ^ 1), ((it + 1) >> 1) & 1, ctl, kSiteBwdQdoFull)) break;
           ptx::tc_fence_after_sync();
           issue_s(stage_q(st ^ 1));
         }
@@ -361,12 +382,13 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           bwd_mma_ss(tmem_base + C::kTmemDK, k_lo + (ds_smem >> 4) + off, k_hi, m_lo + (q_addr >> 4) + ((ks * 2048) >> 4),
                      m_hi, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
         }
-        ptx::umma_commit_elect(qdo_empty(st));
+        ptx::umma_commit_elect(q_empty(st));
         if (more) {
           // dP^T shares its columns with dQ^T at head size 128
           if (!ptx::mbar_wait(dq_free, it & 1, ctl, kSiteBwdDqFree)) break;
+          if (!ptx::mbar_wait(do_full, (it + 1) & 1, ctl, kSiteBwdQdoFull)) break;
           ptx::tc_fence_after_sync();
-          issue_dp(stage_do(st ^ 1));
+          issue_dp(do_smem);
         }
       }
       ptx::umma_commit_elect(final_bar);
@@ -383,7 +405,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     bool alive = true;
     for (int it = 0; it < n_steps && alive; ++it) {
       const uint32_t st = it & 1;
-      if (!ptx::mbar_wait(qdo_full(st), (it >> 1) & 1, ctl, kSiteBwdQdoFull)) { alive = false; break; }
+      if (!ptx::mbar_wait(q_full(st), (it >> 1) & 1, ctl, kSiteBwdQdoFull)) { alive = false; break; }
       if (!ptx::mbar_wait(s_full, it & 1, ctl, kSiteBwdS)) { alive = false; break; }
       ptx::tc_fence_after_sync();
       const int q0 = (i0 + it) * kBlk;
@@ -499,30 +521,48 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     ptx::setmaxnreg_inc<kWorkRegs>();
     const int d = threadIdx.x - kReduceWarp * 32;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    uint32_t piece = 0;      // running count of staged pieces: buffer = piece & 1
     for (int it = 0; it < n_steps; ++it) {
       if (!ptx::mbar_wait(dq_full, it & 1, ctl, kSiteBwdDqFull)) break;
       ptx::tc_fence_after_sync();
       const int q0 = (i0 + it) * kBlk;
-      float* dst = args.dq_acc + (static_cast<int64_t>(bn) * args.f_pad + q0) * kHeadDim + d;
+      float* dst = args.dq_acc + (static_cast<int64_t>(bn) * args.f_pad + q0) * kHeadDim;
       uint32_t acc[4][32];
       if (d < kHeadDim) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDQ + 32 * c, acc[c]);
         ptx::tmem_ld_wait();
       }
-      // the columns are free once they sit in registers; the adds follow
+      // the columns are free once they sit in registers
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(dq_free);
 #ifndef IXK_BWD_PROBE_NO_RED
-      if (d < kHeadDim) {
+      // Four pieces of 32 query rows: transpose through shared memory into the accumulator's
+      // [query][head dim] order (conflict-free: a warp writes 32 consecutive floats of one row),
+      // then one bulk reduction per piece adds the contiguous block to global memory.
 #pragma unroll
-        for (int j = 0; j < 128; ++j)
-          atomicAdd(dst + static_cast<int64_t>(j) * kHeadDim, __uint_as_float(acc[j >> 5][j & 31]));
+      for (int c = 0; c < 4; ++c, ++piece) {
+        const uint32_t buf = dq_stage + (piece & 1u) * C::kPieceBytes;
+        if (d < kHeadDim) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(buf + (j * kHeadDim + d) * 4), "r"(acc[c][j]) : "memory");
+        }
+        ptx::fence_proxy_async_smem();
+        // the previous piece's reduction has finished reading the other buffer before anyone
+        // passes this barrier, so that the next piece may overwrite it
+        if (threadIdx.x == kReduceWarp * 32) ptx::bulk_wait_group_read<0>();
+        ptx::named_barrier_sync(1, 128);
+        if (threadIdx.x == kReduceWarp * 32) {
+          ptx::bulk_reduce_add_f32(dst + c * C::kPieceRows * kHeadDim, buf, C::kPieceBytes);
+          ptx::bulk_commit_group();
+        }
       }
 #endif
     }
+    if (threadIdx.x == kReduceWarp * 32) ptx::bulk_wait_group<0>();   // all additions performed before the CTA exits
   } else {
-    ptx::setmaxnreg_dec<kCtrlRegs>();     // warps 14, 15: nothing else to do
+    ptx::setmaxnreg_dec<kCtrlRegs>();     // warp 15: nothing else to do
   }
 
   ptx::tc_fence_before_sync();

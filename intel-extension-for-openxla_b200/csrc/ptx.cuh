@@ -172,6 +172,14 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
+// Untiled bulk reduction shared -> global: global[i] += shared[i] over `bytes` of fp32 (both
+// addresses 16-byte aligned, size a multiple of 16 bytes), performed by the memory system.
+// Tracked by the issuing thread's bulk async-groups like a TMA store.
+__device__ __forceinline__ void bulk_reduce_add_f32(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst), "r"(src),
+               "r"(bytes)
+               : "memory");
+}
 // Tile store shared -> global (rows/columns outside the tensor are dropped).  The issuing thread
 // tracks completion through bulk async-groups.
 __device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src, int x, int y, int z, int w) {
