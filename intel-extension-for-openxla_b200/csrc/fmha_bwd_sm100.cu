@@ -5,8 +5,8 @@
 //                           accumulator                                   (fmha_backward.h:182-222)
 //   2. fmha_bwd_kernel    : one CTA per (batch, head, block of 128 keys) loops over the blocks of
 //                           128 queries that see those keys; dK and dV accumulate in tensor memory
-//                           for the whole loop, dQ contributions go to the fp32 accumulator with
-//                           vector reductions                              (fmha_backward.h:489-700)
+//                           for the whole loop, dQ contributions are added to the fp32 accumulator
+//                           by bulk reductions                             (fmha_backward.h:489-700)
 //   3. bwd_convert_kernel : dQ = head_scale * accumulator, rounded once    (fmha_backward.h:836-850)
 //
 // The main kernel works on TRANSPOSED score tiles, keys along the 128 TMEM lanes and queries along
@@ -17,11 +17,23 @@
 //   dS^T = P^T * (dP^T - D)                                  -> shared memory, 16-bit, swizzled
 //   dV  += P^T  . dO      (TS: A from TMEM, B = dO with the head dim contiguous)
 //   dK  += dS^T . Q       (SS: A K-major, B = Q with the head dim contiguous)
-//   dQ   = dS   . K       (SS: A = the same dS^T buffer read M-major, B = K head dim contiguous)
-// Tensor memory (512 columns) at head size 128: S^T/P^T 128, dP^T 128 (reused for dQ once dS^T is
-// out), dV 128, dK 128.  Warps 0-3 compute P^T and dS^T (one key row per thread), warps 4-7 move dQ
-// from TMEM to the accumulator (one query row per thread), warp 8 issues TMA loads, warp 9 issues
-// the MMAs with all lanes and an elected lane per instruction.  Every wait is bounded.
+//   dQ^T = K^T  . dS^T    (SS: A = the K tile read with the head dim as M, B = dS^T read with the
+//                          queries as N) -> TMEM with the head dim along the lanes
+// Tensor memory (512 columns) at head size 128: S^T/P^T 128, dP^T 128 (reused for dQ^T once dS^T
+// is out), dV 128, dK 128.  Shared memory (224 KB at head size 128): K, V, two Q tiles, one dO
+// tile, dS^T, two 16 KB staging pieces for dQ.
+// Warps 0-7 compute P^T and dS^T (one key row per thread, each warpgroup half of the step's
+// queries); warps 8-11 drain dQ^T into registers, transpose it through the staging pieces and hand
+// each piece (32 query rows, contiguous in the accumulator) to a bulk reduction; warp 12 loads K,
+// V, Q and the row statistics, warp 14 the dO tiles; warp 13 issues the MMAs with all lanes and an
+// elected lane per instruction, in the order dV(i), S^T(i+1), dQ^T(i), dK(i), dP^T(i+1), so that
+// the next scores are ready when the compute warps finish dS^T and dQ^T leaves the columns it
+// shares with dP^T while dK runs.  CTAs of one (batch, head) are neighbours in launch order: its
+// Q, dO and accumulator slice stay in L2.  Every wait is bounded.
+// What bounds it: the additions to the dQ accumulator.  Each step adds 64 KB; the memory system
+// sustained about 3 TB/s of fp32 reductions over the whole GPU whether they were issued as bulk
+// reductions, as per-lane vector reductions or as warp-coalesced scalar ones, which is about
+// 3600 cycles per step against 2560 cycles of MMA work.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -203,6 +215,13 @@ __device__ __forceinline__ void bwd_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uin
       "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+#ifdef IXK_BWD_TRACE
+__device__ long long g_bwd_trace[4096];
+#define BWD_TRACE(role, ev, it) do { if (blockIdx.x == 0 && (it) < 16) g_bwd_trace[((role) * 16 + (it)) * 8 + (ev)] = clock64(); } while (0)
+#else
+#define BWD_TRACE(role, ev, it) do {} while (0)
+#endif
+
 template <int kHeadDim, bool kBias>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -357,7 +376,9 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const uint32_t st = it & 1;
         const uint32_t q_addr = stage_q(st), do_addr = do_smem;
         const bool more = it + 1 < n_steps;
+        BWD_TRACE(0, 0, it);
         if (!ptx::mbar_wait(p_ready, it & 1, ctl, kSiteBwdP)) break;
+        BWD_TRACE(0, 1, it);
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < kBlk / 16; ++ks)     // dV += P^T.dO over 16 queries at a time
@@ -369,7 +390,9 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           ptx::tc_fence_after_sync();
           issue_s(stage_q(st ^ 1));
         }
+        BWD_TRACE(0, 2, it);
         if (!ptx::mbar_wait(ds_ready, it & 1, ctl, kSiteBwdDs)) break;
+        BWD_TRACE(0, 3, it);
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < kBlk / 16; ++ks)     // dQ^T = K^T.dS^T over 16 keys at a time
@@ -385,8 +408,11 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         ptx::umma_commit_elect(q_empty(st));
         if (more) {
           // dP^T shares its columns with dQ^T at head size 128
+          BWD_TRACE(0, 4, it);
           if (!ptx::mbar_wait(dq_free, it & 1, ctl, kSiteBwdDqFree)) break;
+          BWD_TRACE(0, 5, it);
           if (!ptx::mbar_wait(do_full, (it + 1) & 1, ctl, kSiteBwdQdoFull)) break;
+          BWD_TRACE(0, 6, it);
           ptx::tc_fence_after_sync();
           issue_dp(do_smem);
         }
@@ -406,7 +432,9 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     for (int it = 0; it < n_steps && alive; ++it) {
       const uint32_t st = it & 1;
       if (!ptx::mbar_wait(q_full(st), (it >> 1) & 1, ctl, kSiteBwdQdoFull)) { alive = false; break; }
+      if (threadIdx.x == 0) BWD_TRACE(1, 0, it);
       if (!ptx::mbar_wait(s_full, it & 1, ctl, kSiteBwdS)) { alive = false; break; }
+      if (threadIdx.x == 0) BWD_TRACE(1, 1, it);
       ptx::tc_fence_after_sync();
       const int q0 = (i0 + it) * kBlk;
       const float* nl = reinterpret_cast<const float*>(smem_raw + rows_off(st)) + 64 * half;
@@ -431,11 +459,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const int q = q0 + 64 * half + col;
             if (key_ok && q < args.F) x = fmaf(to_f32(bias_row[q * args.bias_strides[2]], args.is_bf16), kLog2e, x);
           }
-#ifdef IXK_BWD_PROBE_NO_EXP
-          float pe = x;
-#else
           float pe = ptx::ex2_approx(x);
-#endif
           if (!key_ok || (diag && key > q0 + 64 * half + col)) pe = 0.0f;
           p[col] = pe;
         }
@@ -448,8 +472,10 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       ptx::tmem_st_wait();
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(p_ready);
+      if (threadIdx.x == 0) BWD_TRACE(1, 2, it);
       // phase B: dS^T = P^T * (dP^T - D)
       if (!ptx::mbar_wait(dp_full, it & 1, ctl, kSiteBwdDp)) { alive = false; break; }
+      if (threadIdx.x == 0) BWD_TRACE(1, 3, it);
       ptx::tc_fence_after_sync();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -475,6 +501,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(ds_ready);
+      if (threadIdx.x == 0) BWD_TRACE(1, 4, it);
     }
     // epilogue: this thread's row of dV and dK
     const bool have = n_steps > 0 && alive && ptx::mbar_wait(final_bar, 0, ctl, kSiteBwdFinal);
@@ -523,7 +550,9 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t piece = 0;      // running count of staged pieces: buffer = piece & 1
     for (int it = 0; it < n_steps; ++it) {
+      if (d == 0) BWD_TRACE(2, 0, it);
       if (!ptx::mbar_wait(dq_full, it & 1, ctl, kSiteBwdDqFull)) break;
+      if (d == 0) BWD_TRACE(2, 1, it);
       ptx::tc_fence_after_sync();
       const int q0 = (i0 + it) * kBlk;
       float* dst = args.dq_acc + (static_cast<int64_t>(bn) * args.f_pad + q0) * kHeadDim;
@@ -536,7 +565,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // the columns are free once they sit in registers
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(dq_free);
-#ifndef IXK_BWD_PROBE_NO_RED
+      if (d == 0) BWD_TRACE(2, 2, it);
       // Four pieces of 32 query rows: transpose through shared memory into the accumulator's
       // [query][head dim] order (conflict-free: a warp writes 32 consecutive floats of one row),
       // then one bulk reduction per piece adds the contiguous block to global memory.
@@ -558,7 +587,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           ptx::bulk_commit_group();
         }
       }
-#endif
+      if (d == 0) BWD_TRACE(2, 3, it);
     }
     if (threadIdx.x == kReduceWarp * 32) ptx::bulk_wait_group<0>();   // all additions performed before the CTA exits
   } else {
@@ -714,3 +743,9 @@ int launch_bwd(const BwdProblem& bp, const DeviceInfo& dev, void* workspace, siz
 }
 }  // namespace fmha
 }  // namespace ixk
+
+#ifdef IXK_BWD_TRACE
+extern "C" int ixk_debug_bwd_trace(long long* host_out, int count) {
+  return cudaMemcpyFromSymbol(host_out, ixk::fmha::g_bwd_trace, sizeof(long long) * count) == cudaSuccess ? 0 : 1;
+}
+#endif

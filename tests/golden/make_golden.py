@@ -3,7 +3,8 @@ oracle/ixk_oracle.py): the CPU oracle is checked against these files, and so are
 kernels.  The reference itself cannot produce vectors here (its kernels need a SYCL
 toolchain and XeTLA / oneDNN), so these stand in for them.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py            # all files
+    python tests/golden/make_golden.py backward   # only fmha_bwd_bf16.npz
 """
 import os
 
@@ -15,6 +16,31 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def bits(t: torch.Tensor) -> np.ndarray:
     return t.contiguous().view(torch.uint16).numpy().copy()
+
+
+def backward():
+    """Attention gradients by autograd over plain fp32 attention: causal, and non-causal with a
+    head-broadcast additive bias; ragged sizes."""
+    torch.manual_seed(4321)
+    torch.set_num_threads(1)
+    B, Nh, F, T, H = 1, 2, 140, 150, 64
+    scale = H ** -0.5
+    q, k, v = (torch.randn(B, Nh, S, H).bfloat16() for S in (F, T, T))
+    do = torch.randn(B, Nh, F, H).bfloat16()
+    bias = (torch.randn(B, 1, F, T) * 0.5).bfloat16()
+    out = {"q": bits(q), "k": bits(k), "v": bits(v), "do": bits(do), "bias": bits(bias), "scale": np.float32(scale)}
+    for name in ("causal", "bias"):
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        s = torch.einsum("bnfh,bnth->bnft", qf, kf) * scale
+        if name == "causal":
+            s = s.masked_fill(~torch.ones(F, T, dtype=torch.bool).tril(), float("-inf"))
+        else:
+            s = s + bias.float()
+        o = torch.softmax(s, dim=-1) @ vf
+        o.backward(do.float())
+        out.update({f"o_{name}": o.detach().numpy(), f"lse_{name}": torch.logsumexp(s, dim=-1).detach().numpy(),
+                    f"dq_{name}": qf.grad.numpy(), f"dk_{name}": kf.grad.numpy(), f"dv_{name}": vf.grad.numpy()})
+    np.savez_compressed(os.path.join(HERE, "fmha_bwd_bf16.npz"), **out)
 
 
 def main():
@@ -85,4 +111,9 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    import sys
+    if sys.argv[1:] == ["backward"]:
+        backward()
+    else:
+        main()
+        backward()

@@ -91,3 +91,50 @@ def test_rejections(pkg, cuda):
     with pytest.raises(pkg.IxkError):      # log-sum-exp rows missing
         pkg.fmha_backward_kernel(None, q, q, q, q, None, q, None, torch.empty_like(q), torch.empty_like(q),
                                  torch.empty_like(q), 1.0)
+
+
+def test_golden_vectors(pkg, orc, cuda):
+    """Gradients made by autograd over fp32 attention on the CPU (tests/golden/make_golden.py)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "fmha_bwd_bf16.npz"))
+    t = lambda name: torch.from_numpy(g[name].view(np.int16)).view(torch.bfloat16).to(cuda)
+    q, k, v, do, bias = (t(n) for n in ("q", "k", "v", "do", "bias"))
+    scale = float(g["scale"])
+    for name in ("causal", "bias"):
+        b = bias if name == "bias" else None
+        out = torch.empty_like(q)
+        lse = torch.empty(q.shape[:3], dtype=torch.float32, device=cuda)
+        pkg.fmha_forward_kernel(None, q, k, v, b, None, 0.0, out, lse, scale, True, causal=name == "causal")
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        pkg.fmha_backward_kernel(None, q, k, v, out, b, do, lse, dq, dk, dv, scale, causal=name == "causal")
+        for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+            orc.check_close(f32(got), g[f"{key}_{name}"], rtol=2e-2, atol=2e-2, what=f"golden {key} {name}")
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_full_size_against_fp32_autograd(pkg, cuda, causal):
+    """The benchmark's shape (B8 N16 S2048 H128): a few (batch, head) slices of all three gradients
+    against autograd over fp32 attention on the same GPU; every element must also be finite."""
+    B, N, S, H = 8, 16, 2048, 128
+    g = torch.Generator(device="cuda").manual_seed(11)
+    mk = lambda: torch.randn(B, N, S, H, generator=g, device=cuda).bfloat16()
+    q, k, v, do = mk(), mk(), mk(), mk()
+    scale = H ** -0.5
+    out = torch.empty_like(q)
+    lse = torch.empty(B, N, S, dtype=torch.float32, device=cuda)
+    pkg.fmha_forward_kernel(None, q, k, v, None, None, 0.0, out, lse, scale, True, causal=causal)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    pkg.fmha_backward_kernel(None, q, k, v, out, None, do, lse, dq, dk, dv, scale, causal=causal)
+    assert pkg.device_status() == 0
+    for t in (dq, dk, dv):
+        assert torch.isfinite(t.float()).all()
+    mask = torch.ones(S, S, dtype=torch.bool, device=cuda).tril() if causal else None
+    for b, n in ((0, 0), (3, 7), (7, 15)):
+        qq, kk, vv = (t[b:b + 1, n:n + 1].float().requires_grad_() for t in (q, k, v))
+        ref = torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, attn_mask=mask, scale=scale)
+        ref.backward(do[b:b + 1, n:n + 1].float())
+        for name, got, want in (("dq", dq, qq.grad), ("dk", dk, kk.grad), ("dv", dv, vv.grad)):
+            got = got[b:b + 1, n:n + 1].float()
+            rel = ((got - want).norm() / want.norm()).item()
+            assert rel < 1e-2, f"{name}[{b},{n}]: relative error {rel:.3e}"
+            assert torch.allclose(got, want, rtol=2e-2, atol=2e-2), name

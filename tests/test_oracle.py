@@ -221,3 +221,16 @@ def test_fmha_backward_matches_autograd(orc):
                                        head_scale=scale, causal=causal, dtype=orc.F32, round_p=False)
         for got, want in ((dq, q.grad), (dk, k.grad), (dv, v.grad)):
             np.testing.assert_allclose(got, want.numpy(), rtol=2e-4, atol=2e-5)
+
+
+def test_fmha_backward_golden(orc):
+    """Backward oracle (bf16 operand rounding on) against autograd gradients of fp32 attention."""
+    g = np.load(os.path.join(GOLDEN, "fmha_bwd_bf16.npz"))
+    q, k, v, do = (orc.bf16_to_f32(g[n]) for n in ("q", "k", "v", "do"))
+    bias = orc.bf16_to_f32(g["bias"])
+    for name in ("causal", "bias"):
+        dq, dk, dv = orc.fmha_backward(q, k, v, g[f"o_{name}"], do, g[f"lse_{name}"],
+                                       bias if name == "bias" else None, head_scale=float(g["scale"]),
+                                       causal=name == "causal")
+        for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+            orc.check_close(got, g[f"{key}_{name}"], rtol=2e-2, atol=2e-2, what=f"golden {key} {name}")
