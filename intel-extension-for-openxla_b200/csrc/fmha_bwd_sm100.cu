@@ -21,10 +21,10 @@
 //                          queries as N) -> TMEM with the head dim along the lanes
 // Tensor memory (512 columns) at head size 128: S^T/P^T 128, dP^T 128 (reused for dQ^T once dS^T
 // is out), dV 128, dK 128.  Shared memory (224 KB at head size 128): K, V, two Q tiles, one dO
-// tile, dS^T, two 16 KB staging pieces for dQ.
+// tile, dS^T, four 8 KB staging pieces for dQ.
 // Warps 0-7 compute P^T and dS^T (one key row per thread, each warpgroup half of the step's
 // queries); warps 8-11 drain dQ^T into registers, transpose it through the staging pieces and hand
-// each piece (32 query rows, contiguous in the accumulator) to a bulk reduction; warp 12 loads K,
+// each piece (16 query rows, contiguous in the accumulator) to a bulk reduction; warp 12 loads K,
 // V, Q and the row statistics, warp 14 the dO tiles; warp 13 issues the MMAs with all lanes and an
 // elected lane per instruction, in the order dV(i), S^T(i+1), dQ^T(i), dK(i), dP^T(i+1), so that
 // the next scores are ready when the compute warps finish dS^T and dQ^T leaves the columns it
@@ -39,6 +39,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <type_traits>
 
 #include "fmha_sm100.h"
 #include "ptx.cuh"
@@ -80,10 +81,11 @@ struct BwdCfg {
   static constexpr int kOffQ = 2 * kTileBytes;                      // kStages Q tiles
   static constexpr int kOffDo = kOffQ + kStages * kTileBytes;       // one dO tile: it lives from dP^T to the next dV
   static constexpr int kOffDs = kOffDo + kTileBytes;
-  static constexpr int kPieceRows = 32;                             // query rows per bulk reduction of dQ
+  static constexpr int kPieceRows = 16;                              // query rows per bulk reduction of dQ
   static constexpr int kPieceBytes = kPieceRows * kHeadDim * 4;
-  static constexpr int kOffDqStage = kOffDs + kDsBytes;             // two pieces
-  static constexpr int kOffRows = kOffDqStage + 2 * kPieceBytes;    // per stage: -lse*log2e row, D row
+  static constexpr int kPieceBufs = 64 / kPieceRows;                // staging buffers: 64 query rows in all
+  static constexpr int kOffDqStage = kOffDs + kDsBytes;
+  static constexpr int kOffRows = kOffDqStage + kPieceBufs * kPieceBytes;   // per stage: -lse*log2e row, D row
   static constexpr int kOffBars = kOffRows + kStages * 2 * kRowBytes;
   static constexpr int kSmemBytes = kOffBars + 256;
   static_assert(kSmemBytes <= 232448, "shared memory budget");
@@ -222,7 +224,7 @@ __device__ long long g_bwd_trace[4096];
 #define BWD_TRACE(role, ev, it) do {} while (0)
 #endif
 
-template <int kHeadDim, bool kBias>
+template <int kHeadDim, bool kBias, bool kBf16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -333,7 +335,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     // ------------------------------------------------------------------ MMA issuer (all 32 lanes)
     ptx::setmaxnreg_dec<kCtrlRegs>();
     if (n_steps > 0) {
-      const uint32_t fmt = args.is_bf16 ? 1u : 0u;
+      const uint32_t fmt = kBf16 ? 1u : 0u;
       const uint32_t idesc_t = ptx::umma_idesc(fmt, fmt, 0, 0, kBlk, kBlk);         // S^T, dP^T
       const uint32_t idesc_kv = ptx::umma_idesc(fmt, fmt, 0, 1, kBlk, kHeadDim);    // dV (A in TMEM), dK
       // dQ^T = K^T.dS^T: head dim along the lanes (M = 128; at head size 64 the upper 64 lanes
@@ -443,33 +445,57 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       [[maybe_unused]] const uint16_t* bias_row = nullptr;
       if constexpr (kBias)
         bias_row = args.bias + b * args.bias_strides[0] + n * args.bias_strides[1] + key;
-      // phase A: P^T = exp2(S^T * scale*log2e + bias*log2e - lse*log2e) for this warpgroup's 64 queries
-      float p[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t s[32];
-        ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemS + 64 * half + 32 * c, s);
+      // phase A: P^T = exp2(S^T * scale*log2e + bias*log2e - lse*log2e) for this warpgroup's 64 queries.
+      // Only the diagonal block of a causal problem and a ragged last key block need the mask.
+      const bool need_mask = diag || (kb + 1) * kBlk > args.T;
+      const uint64_t scale2 = ptx::f32x2(args.scale_log2, args.scale_log2);
+      uint64_t p2[32];     // P as fp32 pairs (queries 2j, 2j+1 of this warpgroup's half)
+      auto phase_a = [&](auto masked) {
+        constexpr bool kMasked = decltype(masked)::value;
+        uint32_t s[2][32];
+        ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemS + 64 * half, s[0]);
+        ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemS + 64 * half + 32, s[1]);
         ptx::tmem_ld_wait();
-        uint32_t pw[16];
+        if (threadIdx.x == 0) BWD_TRACE(1, 5, it);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = 32 * c + j;             // within the warpgroup's half
-          float x = fmaf(__uint_as_float(s[j]), args.scale_log2, nl[col]);
-          if constexpr (kBias) {
-            const int q = q0 + 64 * half + col;
-            if (key_ok && q < args.F) x = fmaf(to_f32(bias_row[q * args.bias_strides[2]], args.is_bf16), kLog2e, x);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pw[16];
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 nl4 = *reinterpret_cast<const float4*>(nl + 32 * c + 4 * j4);
+            uint64_t x[2] = {ptx::fma2(ptx::f32x2(__uint_as_float(s[c][4 * j4]), __uint_as_float(s[c][4 * j4 + 1])), scale2,
+                                       ptx::f32x2(nl4.x, nl4.y)),
+                             ptx::fma2(ptx::f32x2(__uint_as_float(s[c][4 * j4 + 2]), __uint_as_float(s[c][4 * j4 + 3])), scale2,
+                                       ptx::f32x2(nl4.z, nl4.w))};
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              float x0, x1;
+              ptx::f32x2_split(x[e], x0, x1);
+              const int col = 32 * c + 4 * j4 + 2 * e;
+              if constexpr (kBias) {
+                const int q = q0 + 64 * half + col;
+                if (key_ok && q < args.F) x0 = fmaf(to_f32(bias_row[q * args.bias_strides[2]], kBf16), kLog2e, x0);
+                if (key_ok && q + 1 < args.F) x1 = fmaf(to_f32(bias_row[(q + 1) * args.bias_strides[2]], kBf16), kLog2e, x1);
+              }
+              float e0 = ptx::ex2_approx(x0), e1 = ptx::ex2_approx(x1);
+              if constexpr (kMasked) {
+                const int lim = diag ? key - (q0 + 64 * half + col) : 0;   // masked when key > query
+                e0 = (!key_ok || lim > 0) ? 0.0f : e0;
+                e1 = (!key_ok || lim > 1) ? 0.0f : e1;
+              }
+              p2[16 * c + 2 * j4 + e] = ptx::f32x2(e0, e1);
+              pw[2 * j4 + e] = pack16(e0, e1, kBf16);
+            }
           }
-          float pe = ptx::ex2_approx(x);
-          if (!key_ok || (diag && key > q0 + 64 * half + col)) pe = 0.0f;
-          p[col] = pe;
+          // P^T goes over the S^T columns this warpgroup has already read: queries 0-63 at columns
+          // 0-31, queries 64-127 at columns 64-95
+          ptx::tmem_st_32x16(tmem_base + lane_addr + C::kTmemS + 64 * half + 16 * c, pw);
         }
-#pragma unroll
-        for (int j2 = 0; j2 < 16; ++j2) pw[j2] = pack16(p[32 * c + 2 * j2], p[32 * c + 2 * j2 + 1], args.is_bf16);
-        // P^T goes over the S^T columns this warpgroup has already read: queries 0-63 at columns
-        // 0-31, queries 64-127 at columns 64-95
-        ptx::tmem_st_32x16(tmem_base + lane_addr + C::kTmemS + 64 * half + 16 * c, pw);
-      }
+      };
+      if (need_mask) phase_a(std::true_type{}); else phase_a(std::false_type{});
+      if (threadIdx.x == 0) BWD_TRACE(1, 6, it);
       ptx::tmem_st_wait();
+      if (threadIdx.x == 0) BWD_TRACE(1, 7, it);
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(p_ready);
       if (threadIdx.x == 0) BWD_TRACE(1, 2, it);
@@ -477,17 +503,27 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (!ptx::mbar_wait(dp_full, it & 1, ctl, kSiteBwdDp)) { alive = false; break; }
       if (threadIdx.x == 0) BWD_TRACE(1, 3, it);
       ptx::tc_fence_after_sync();
+      uint32_t dp[2][32];
+      ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDP + 64 * half, dp[0]);
+      ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDP + 64 * half + 32, dp[1]);
+      ptx::tmem_ld_wait();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t dp[32];
-        ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDP + 64 * half + 32 * c, dp);
-        ptx::tmem_ld_wait();
         uint32_t dw[16];
 #pragma unroll
-        for (int j2 = 0; j2 < 16; ++j2) {
-          const int col = 32 * c + 2 * j2;
-          dw[j2] = pack16(p[col] * (__uint_as_float(dp[2 * j2]) - dl[col]),
-                          p[col + 1] * (__uint_as_float(dp[2 * j2 + 1]) - dl[col + 1]), args.is_bf16);
+        for (int j4 = 0; j4 < 8; ++j4) {
+          const float4 dl4 = *reinterpret_cast<const float4*>(dl + 32 * c + 4 * j4);
+          const uint64_t d0 = ptx::mul2(p2[16 * c + 2 * j4],
+                                        ptx::sub2(ptx::f32x2(__uint_as_float(dp[c][4 * j4]), __uint_as_float(dp[c][4 * j4 + 1])),
+                                                  ptx::f32x2(dl4.x, dl4.y)));
+          const uint64_t d1 = ptx::mul2(p2[16 * c + 2 * j4 + 1],
+                                        ptx::sub2(ptx::f32x2(__uint_as_float(dp[c][4 * j4 + 2]), __uint_as_float(dp[c][4 * j4 + 3])),
+                                                  ptx::f32x2(dl4.z, dl4.w)));
+          float a0, a1, b0, b1;
+          ptx::f32x2_split(d0, a0, a1);
+          ptx::f32x2_split(d1, b0, b1);
+          dw[2 * j4] = pack16(a0, a1, kBf16);
+          dw[2 * j4 + 1] = pack16(b0, b1, kBf16);
         }
         const uint32_t row_addr = ds_smem + half * kChunkBytes + r * 128;
 #pragma unroll
@@ -530,10 +566,10 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               const int h = 32 * c + 8 * g;
               if (h < args.H) {
                 uint4 w;
-                w.x = pack16(__uint_as_float(acc[8 * g]) * mul, __uint_as_float(acc[8 * g + 1]) * mul, args.is_bf16);
-                w.y = pack16(__uint_as_float(acc[8 * g + 2]) * mul, __uint_as_float(acc[8 * g + 3]) * mul, args.is_bf16);
-                w.z = pack16(__uint_as_float(acc[8 * g + 4]) * mul, __uint_as_float(acc[8 * g + 5]) * mul, args.is_bf16);
-                w.w = pack16(__uint_as_float(acc[8 * g + 6]) * mul, __uint_as_float(acc[8 * g + 7]) * mul, args.is_bf16);
+                w.x = pack16(__uint_as_float(acc[8 * g]) * mul, __uint_as_float(acc[8 * g + 1]) * mul, kBf16);
+                w.y = pack16(__uint_as_float(acc[8 * g + 2]) * mul, __uint_as_float(acc[8 * g + 3]) * mul, kBf16);
+                w.z = pack16(__uint_as_float(acc[8 * g + 4]) * mul, __uint_as_float(acc[8 * g + 5]) * mul, kBf16);
+                w.w = pack16(__uint_as_float(acc[8 * g + 6]) * mul, __uint_as_float(acc[8 * g + 7]) * mul, kBf16);
                 *reinterpret_cast<uint4*>(dst + h) = w;
               }
             }
@@ -566,21 +602,23 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(dq_free);
       if (d == 0) BWD_TRACE(2, 2, it);
-      // Four pieces of 32 query rows: transpose through shared memory into the accumulator's
+      // Pieces of 16 query rows in four staging buffers: transpose through shared memory into the accumulator's
       // [query][head dim] order (conflict-free: a warp writes 32 consecutive floats of one row),
       // then one bulk reduction per piece adds the contiguous block to global memory.
 #pragma unroll
-      for (int c = 0; c < 4; ++c, ++piece) {
-        const uint32_t buf = dq_stage + (piece & 1u) * C::kPieceBytes;
+      for (int c = 0; c < kBlk / C::kPieceRows; ++c, ++piece) {
+        const uint32_t buf = dq_stage + (piece % C::kPieceBufs) * C::kPieceBytes;
         if (d < kHeadDim) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(buf + (j * kHeadDim + d) * 4), "r"(acc[c][j]) : "memory");
+          for (int j = 0; j < C::kPieceRows; ++j) {
+            const int row = c * C::kPieceRows + j;
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(buf + (j * kHeadDim + d) * 4), "r"(acc[row >> 5][row & 31]) : "memory");
+          }
         }
         ptx::fence_proxy_async_smem();
-        // the previous piece's reduction has finished reading the other buffer before anyone
-        // passes this barrier, so that the next piece may overwrite it
-        if (threadIdx.x == kReduceWarp * 32) ptx::bulk_wait_group_read<0>();
+        // the reduction that last read the NEXT piece's buffer has finished before anyone passes
+        // this barrier
+        if (threadIdx.x == kReduceWarp * 32) ptx::bulk_wait_group_read<C::kPieceBufs - 2>();
         ptx::named_barrier_sync(1, 128);
         if (threadIdx.x == kReduceWarp * 32) {
           ptx::bulk_reduce_add_f32(dst + c * C::kPieceRows * kHeadDim, buf, C::kPieceBytes);
@@ -602,7 +640,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   }
 }
 
-template <int kHeadDim, bool kBias>
+template <int kHeadDim, bool kBias, bool kBf16>
 int launch_bwd_cfg(const BwdProblem& bp, const DeviceInfo& dev, float* neg_lse2, float* delta, float* dq_acc,
                    int f_pad, cudaStream_t stream) {
   using C = BwdCfg<kHeadDim>;
@@ -659,7 +697,7 @@ int launch_bwd_cfg(const BwdProblem& bp, const DeviceInfo& dev, float* neg_lse2,
   }
   a.status_word = dev.status_word;
 
-  auto* fn = &fmha_bwd_kernel<kHeadDim, kBias>;
+  auto* fn = &fmha_bwd_kernel<kHeadDim, kBias, kBf16>;
   static thread_local int configured_device = -1;
   if (configured_device != dev.device) {
     IXK_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
@@ -671,6 +709,16 @@ int launch_bwd_cfg(const BwdProblem& bp, const DeviceInfo& dev, float* neg_lse2,
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
   return IXK_OK;
+}
+
+template <int kHeadDim>
+int launch_bwd_dtype(const BwdProblem& bp, const DeviceInfo& dev, float* neg_lse2, float* delta, float* dq_acc, int f_pad,
+                     cudaStream_t stream, bool bias) {
+  if (bp.fwd.dtype == IXK_BF16)
+    return bias ? launch_bwd_cfg<kHeadDim, true, true>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream)
+                : launch_bwd_cfg<kHeadDim, false, true>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream);
+  return bias ? launch_bwd_cfg<kHeadDim, true, false>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream)
+              : launch_bwd_cfg<kHeadDim, false, false>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream);
 }
 
 int head_pad_of(int H) { return H <= 64 ? 64 : 128; }
@@ -719,11 +767,9 @@ int launch_bwd(const BwdProblem& bp, const DeviceInfo& dev, void* workspace, siz
   int rc;
   const bool bias = p.bias != nullptr;
   if (head_pad == 64) {
-    rc = bias ? launch_bwd_cfg<64, true>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream)
-              : launch_bwd_cfg<64, false>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream);
+    rc = launch_bwd_dtype<64>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream, bias);
   } else {
-    rc = bias ? launch_bwd_cfg<128, true>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream)
-              : launch_bwd_cfg<128, false>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream);
+    rc = launch_bwd_dtype<128>(bp, dev, neg_lse2, delta, dq_acc, f_pad, stream, bias);
   }
   if (rc != IXK_OK) return rc;
 
