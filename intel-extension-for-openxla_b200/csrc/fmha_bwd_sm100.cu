@@ -30,6 +30,10 @@
 // the next scores are ready when the compute warps finish dS^T and dQ^T leaves the columns it
 // shares with dP^T while dK runs.  CTAs of one (batch, head) are neighbours in launch order: its
 // Q, dO and accumulator slice stay in L2.  Every wait is bounded.
+// Tried and dropped: two CTAs of a cluster on neighbouring key blocks that exchange halves of their
+// dQ^T partials through distributed shared memory before one bulk reduction each (half the L2
+// traffic).  Correct, but 1.13 ms against 0.85 ms: 64 remote 4-byte stores per thread took 2500
+// cycles per step, the local add 1070 and the 32 KB reduction still 2370.
 // What bounds it: the additions to the dQ accumulator.  Each step adds 64 KB; the memory system
 // sustained about 3 TB/s of fp32 reductions over the whole GPU whether they were issued as bulk
 // reductions, as per-lane vector reductions or as warp-coalesced scalar ones, which is about
@@ -342,6 +346,10 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // multiply whatever follows the K tile in shared memory and are never read), queries along
       // the columns, both operands read with their M / N dimension contiguous
       const uint32_t idesc_dq = ptx::umma_idesc(fmt, fmt, 1, 1, kBlk, kBlk);
+      // descriptor address field: 16-byte units of the offset inside this CTA's window (were the
+      // kernel launched in a cluster, the shared addresses of every CTA but the first would carry
+      // the rank in their upper bits: measured 0x01000400 for the second CTA of a pair)
+      auto da = [](uint32_t addr) { return (addr & 0x3ffffu) >> 4; };
       const uint64_t kmajor = ptx::umma_smem_desc(0, 16, 1024);
       const uint64_t mnmajor = ptx::umma_smem_desc(0, kChunkBytes, 1024);
       const uint32_t k_lo = static_cast<uint32_t>(kmajor), k_hi = static_cast<uint32_t>(kmajor >> 32);
@@ -350,7 +358,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
         for (int ks = 0; ks < kHeadDim / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
-          bwd_mma_ss(tmem_base + C::kTmemS, k_lo + (k_smem >> 4) + off, k_hi, k_lo + (q_addr >> 4) + off, k_hi,
+          bwd_mma_ss(tmem_base + C::kTmemS, k_lo + da(k_smem) + off, k_hi, k_lo + da(q_addr) + off, k_hi,
                      idesc_t, ks != 0 ? 1u : 0u);
         }
         ptx::umma_commit_elect(s_full);
@@ -359,7 +367,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
         for (int ks = 0; ks < kHeadDim / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
-          bwd_mma_ss(tmem_base + C::kTmemDP, k_lo + (v_smem >> 4) + off, k_hi, k_lo + (do_addr >> 4) + off, k_hi,
+          bwd_mma_ss(tmem_base + C::kTmemDP, k_lo + da(v_smem) + off, k_hi, k_lo + da(do_addr) + off, k_hi,
                      idesc_t, ks != 0 ? 1u : 0u);
         }
         ptx::umma_commit_elect(dp_full);
@@ -385,7 +393,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
         for (int ks = 0; ks < kBlk / 16; ++ks)     // dV += P^T.dO over 16 queries at a time
           bwd_mma_ts(tmem_base + C::kTmemDV, tmem_base + C::kTmemS + (ks >> 2) * 64 + (ks & 3) * 8,
-                     m_lo + (do_addr >> 4) + ((ks * 2048) >> 4), m_hi, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
+                     m_lo + da(do_addr) + ((ks * 2048) >> 4), m_hi, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
         ptx::umma_commit_elect(do_empty);          // dO(i) has no reader after dV(i)
         if (more) {
           if (!ptx::mbar_wait(q_full(st ^ 1), ((it + 1) >> 1) & 1, ctl, kSiteBwdQdoFull)) break;
@@ -398,13 +406,13 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < kBlk / 16; ++ks)     // dQ^T = K^T.dS^T over 16 keys at a time
-          bwd_mma_ss(tmem_base + C::kTmemDQ, m_lo + (k_smem >> 4) + ((ks * 2048) >> 4), m_hi,
-                     m_lo + (ds_smem >> 4) + ((ks * 2048) >> 4), m_hi, idesc_dq, ks != 0 ? 1u : 0u);
+          bwd_mma_ss(tmem_base + C::kTmemDQ, m_lo + da(k_smem) + ((ks * 2048) >> 4), m_hi,
+                     m_lo + da(ds_smem) + ((ks * 2048) >> 4), m_hi, idesc_dq, ks != 0 ? 1u : 0u);
         ptx::umma_commit_elect(dq_full);
 #pragma unroll
         for (int ks = 0; ks < kBlk / 16; ++ks) {   // dK += dS^T.Q
           const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
-          bwd_mma_ss(tmem_base + C::kTmemDK, k_lo + (ds_smem >> 4) + off, k_hi, m_lo + (q_addr >> 4) + ((ks * 2048) >> 4),
+          bwd_mma_ss(tmem_base + C::kTmemDK, k_lo + da(ds_smem) + off, k_hi, m_lo + da(q_addr) + ((ks * 2048) >> 4),
                      m_hi, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
         }
         ptx::umma_commit_elect(q_empty(st));
