@@ -221,8 +221,8 @@ int ixk_fmha_fwd_static_scratch(const ixk_fmha_desc* desc, const void* q, const 
  * has none).  `fwd` describes q, k, v, bias and the forward output `out` (o_strides) exactly as in
  * the forward call; grad_out, dq, dk, dv are [B,N,F|T,H] views with their own strides (elements,
  * innermost 1).  The reference's dp_sum and grad_query_accum scratch arguments are the workspace:
- * ixk_fmha_bwd_workspace_bytes(desc) bytes, 16-byte aligned.  q, k, v, grad_out: 16-byte aligned
- * with strides that are multiples of 8; dq, dk, dv likewise.  head_size <= 128 (256 is
+ * ixk_fmha_bwd_workspace_bytes(desc) bytes, 16-byte aligned.  q, k, v, out, grad_out: 16-byte
+ * aligned with strides that are multiples of 8; dq, dk, dv likewise.  head_size <= 128 (256 is
  * IXK_UNIMPLEMENTED: the reference's 64x128x256 policy has no counterpart yet). */
 typedef struct ixk_fmha_bwd_desc {
   ixk_fmha_desc fwd;

@@ -114,9 +114,9 @@ int ixk_fmha_bwd(const ixk_fmha_bwd_desc* desc, const void* q, const void* k, co
   if (grad_out == nullptr || lse == nullptr || dq == nullptr || dk == nullptr || dv == nullptr)
     return ixk::fail(IXK_INVALID_ARGUMENT, "grad_out, lse, dq, dk and dv must be non-NULL");
   auto aligned16 = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15u) == 0; };
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(grad_out) || !aligned16(dq) || !aligned16(dk) ||
-      !aligned16(dv))
-    return ixk::fail(IXK_INVALID_ARGUMENT, "q, k, v, grad_out, dq, dk and dv must be 16-byte aligned");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(grad_out) || !aligned16(dq) ||
+      !aligned16(dk) || !aligned16(dv))
+    return ixk::fail(IXK_INVALID_ARGUMENT, "q, k, v, out, grad_out, dq, dk and dv must be 16-byte aligned");
   for (int i = 0; i < 3; ++i) {
     bp.do_strides[i] = desc->do_strides[i];
     bp.dq_strides[i] = desc->dq_strides[i];
@@ -124,9 +124,10 @@ int ixk_fmha_bwd(const ixk_fmha_bwd_desc* desc, const void* q, const void* k, co
     bp.dv_strides[i] = desc->dv_strides[i];
     if (bp.do_strides[i] < 0 || bp.dq_strides[i] < 0 || bp.dk_strides[i] < 0 || bp.dv_strides[i] < 0)
       return ixk::fail(IXK_INVALID_ARGUMENT, "negative stride");
-    if (p.q_strides[i] % 8 != 0 || p.k_strides[i] % 8 != 0 || p.v_strides[i] % 8 != 0 || bp.do_strides[i] % 8 != 0 ||
+    if (p.q_strides[i] % 8 != 0 || p.k_strides[i] % 8 != 0 || p.v_strides[i] % 8 != 0 || p.o_strides[i] % 8 != 0 ||
+        bp.do_strides[i] % 8 != 0 ||
         bp.dq_strides[i] % 8 != 0 || bp.dk_strides[i] % 8 != 0 || bp.dv_strides[i] % 8 != 0)
-      return ixk::fail(IXK_UNIMPLEMENTED, "q/k/v/grad_out/dq/dk/dv strides must be multiples of 8 elements (16 bytes)");
+      return ixk::fail(IXK_UNIMPLEMENTED, "q/k/v/out/grad_out/dq/dk/dv strides must be multiples of 8 elements (16 bytes)");
   }
   bp.grad_out = grad_out;
   bp.dq = dq;

@@ -141,7 +141,13 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// One warp per (batch, head, padded query row).
+__device__ __forceinline__ float2 unpack16(uint32_t w, int is_bf16) {
+  if (is_bf16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+
+// One warp per (batch, head, padded query row); a lane takes 8 head elements (16 bytes) of O and
+// dO and one float4 per 128 floats of the accumulator row.
 __global__ void bwd_prepare_kernel(const PrepArgs a) {
   const int lane = threadIdx.x & 31;
   const int64_t rows = static_cast<int64_t>(a.B) * a.N * a.f_pad;
@@ -156,7 +162,16 @@ __global__ void bwd_prepare_kernel(const PrepArgs a) {
     if (f < a.F) {
       const uint16_t* o = a.out + b * a.o_strides[0] + n * a.o_strides[1] + f * a.o_strides[2];
       const uint16_t* g = a.grad_out + b * a.do_strides[0] + n * a.do_strides[1] + f * a.do_strides[2];
-      for (int h = lane; h < a.H; h += 32) sum = fmaf(to_f32(o[h], a.is_bf16), to_f32(g[h], a.is_bf16), sum);
+      for (int h = lane * 8; h < a.H; h += 256) {
+        const uint4 ow = *reinterpret_cast<const uint4*>(o + h), gw = *reinterpret_cast<const uint4*>(g + h);
+        const uint32_t ov[4] = {ow.x, ow.y, ow.z, ow.w}, gv[4] = {gw.x, gw.y, gw.z, gw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 x = unpack16(ov[j], a.is_bf16), y = unpack16(gv[j], a.is_bf16);
+          sum = fmaf(x.x, y.x, sum);
+          sum = fmaf(x.y, y.y, sum);
+        }
+      }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
@@ -175,20 +190,25 @@ struct ConvertArgs {
   int64_t dq_strides[3];
 };
 
-// One thread per pair of head elements.
+// One thread per 8 head elements: two float4 in, 16 bytes out.
 __global__ void bwd_convert_kernel(const ConvertArgs a) {
-  const int half_h = a.H / 2;
-  const int64_t total = static_cast<int64_t>(a.B) * a.N * a.F * half_h;
+  const int groups = a.H / 8;
+  const int64_t total = static_cast<int64_t>(a.B) * a.N * a.F * groups;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int hp = static_cast<int>(i % half_h);
-    const int64_t r = i / half_h;
+    const int hg = static_cast<int>(i % groups);
+    const int64_t r = i / groups;
     const int f = static_cast<int>(r % a.F);
     const int64_t bn = r / a.F;
     const int n = static_cast<int>(bn % a.N), b = static_cast<int>(bn / a.N);
-    const float2 v = *reinterpret_cast<const float2*>(a.dq_acc + (bn * a.f_pad + f) * a.head_pad + 2 * hp);
-    uint16_t* dst = a.dq + b * a.dq_strides[0] + n * a.dq_strides[1] + f * a.dq_strides[2] + 2 * hp;
-    *reinterpret_cast<uint32_t*>(dst) = pack16(v.x * a.head_scale, v.y * a.head_scale, a.is_bf16);
+    const float4* src = reinterpret_cast<const float4*>(a.dq_acc + (bn * a.f_pad + f) * a.head_pad + 8 * hg);
+    const float4 lo = src[0], hi = src[1];
+    uint4 w;
+    w.x = pack16(lo.x * a.head_scale, lo.y * a.head_scale, a.is_bf16);
+    w.y = pack16(lo.z * a.head_scale, lo.w * a.head_scale, a.is_bf16);
+    w.z = pack16(hi.x * a.head_scale, hi.y * a.head_scale, a.is_bf16);
+    w.w = pack16(hi.z * a.head_scale, hi.w * a.head_scale, a.is_bf16);
+    *reinterpret_cast<uint4*>(a.dq + b * a.dq_strides[0] + n * a.dq_strides[1] + f * a.dq_strides[2] + 8 * hg) = w;
   }
 }
 
@@ -788,7 +808,7 @@ int launch_bwd(const BwdProblem& bp, const DeviceInfo& dev, void* workspace, siz
   ca.dq_acc = dq_acc;
   ca.dq = static_cast<uint16_t*>(bp.dq);
   for (int i = 0; i < 3; ++i) ca.dq_strides[i] = bp.dq_strides[i];
-  const int64_t pairs = static_cast<int64_t>(p.B) * p.N * p.F * (p.H / 2);
+  const int64_t pairs = static_cast<int64_t>(p.B) * p.N * p.F * (p.H / 8);
   const int conv_grid = static_cast<int>(std::min<int64_t>((pairs + 255) / 256, static_cast<int64_t>(dev.sm_count) * 8));
   bwd_convert_kernel<<<conv_grid, 256, 0, stream>>>(ca);
   IXK_CUDA_OK(cudaGetLastError());
