@@ -146,38 +146,54 @@ __device__ __forceinline__ float2 unpack16(uint32_t w, int is_bf16) {
   return __half22float2(*reinterpret_cast<const __half2*>(&w));
 }
 
-// One warp per (batch, head, padded query row); a lane takes 8 head elements (16 bytes) of O and
-// dO and one float4 per 128 floats of the accumulator row.
+// One warp per (batch, head, padded query row), four rows in flight per warp; a lane takes 8 head
+// elements (16 bytes) of O and dO and one float4 per 128 floats of the accumulator row.
 __global__ void bwd_prepare_kernel(const PrepArgs a) {
+  constexpr int kRows = 4;
   const int lane = threadIdx.x & 31;
   const int64_t rows = static_cast<int64_t>(a.B) * a.N * a.f_pad;
-  for (int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
-       row += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5)) {
-    const int f = static_cast<int>(row % a.f_pad);
-    const int64_t bn = row / a.f_pad;
-    const int n = static_cast<int>(bn % a.N), b = static_cast<int>(bn / a.N);
-    float* acc = a.dq_acc + row * a.head_pad;
-    for (int h = lane * 4; h < a.head_pad; h += 128) *reinterpret_cast<float4*>(acc + h) = make_float4(0.f, 0.f, 0.f, 0.f);
-    float sum = 0.0f;
-    if (f < a.F) {
-      const uint16_t* o = a.out + b * a.o_strides[0] + n * a.o_strides[1] + f * a.o_strides[2];
-      const uint16_t* g = a.grad_out + b * a.do_strides[0] + n * a.do_strides[1] + f * a.do_strides[2];
-      for (int h = lane * 8; h < a.H; h += 256) {
-        const uint4 ow = *reinterpret_cast<const uint4*>(o + h), gw = *reinterpret_cast<const uint4*>(g + h);
-        const uint32_t ov[4] = {ow.x, ow.y, ow.z, ow.w}, gv[4] = {gw.x, gw.y, gw.z, gw.w};
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row0 < rows;
+       row0 += warps * kRows) {
+    uint4 ow[kRows], gw[kRows];
+    bool live[kRows];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 x = unpack16(ov[j], a.is_bf16), y = unpack16(gv[j], a.is_bf16);
-          sum = fmaf(x.x, y.x, sum);
-          sum = fmaf(x.y, y.y, sum);
+    for (int r = 0; r < kRows; ++r) {
+      const int64_t row = row0 + r * warps;
+      ow[r] = gw[r] = make_uint4(0u, 0u, 0u, 0u);
+      live[r] = false;
+      if (row < rows) {
+        const int f = static_cast<int>(row % a.f_pad);
+        const int64_t bn = row / a.f_pad;
+        const int n = static_cast<int>(bn % a.N), b = static_cast<int>(bn / a.N);
+        live[r] = f < a.F;
+        if (live[r] && lane * 8 < a.H) {      // head sizes up to 256 fit one 16-byte load per lane
+          ow[r] = *reinterpret_cast<const uint4*>(a.out + b * a.o_strides[0] + n * a.o_strides[1] + f * a.o_strides[2] + lane * 8);
+          gw[r] = *reinterpret_cast<const uint4*>(a.grad_out + b * a.do_strides[0] + n * a.do_strides[1] +
+                                                  f * a.do_strides[2] + lane * 8);
         }
+        float* acc = a.dq_acc + row * a.head_pad;
+        for (int h = lane * 4; h < a.head_pad; h += 128) *reinterpret_cast<float4*>(acc + h) = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-    if (lane == 0) {
-      a.delta[row] = sum;
-      a.neg_lse2[row] = f < a.F ? -a.lse[bn * a.F + f] * kLog2e : -INFINITY;
+    for (int r = 0; r < kRows; ++r) {
+      const int64_t row = row0 + r * warps;
+      if (row >= rows) break;
+      const uint32_t ov[4] = {ow[r].x, ow[r].y, ow[r].z, ow[r].w}, gv[4] = {gw[r].x, gw[r].y, gw[r].z, gw[r].w};
+      float sum = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x = unpack16(ov[j], a.is_bf16), y = unpack16(gv[j], a.is_bf16);
+        sum = fmaf(x.x, y.x, sum);
+        sum = fmaf(x.y, y.y, sum);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+      if (lane == 0) {
+        a.delta[row] = sum;
+        a.neg_lse2[row] = live[r] ? -a.lse[(row / a.f_pad) * a.F + row % a.f_pad] * kLog2e : -INFINITY;
+      }
     }
   }
 }
