@@ -40,6 +40,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised
 # under profiles/ (None until a capture exists for that kernel).
 NCU_TRAFFIC_BYTES = {
+    "fmha_bwd_full": 626.8e6,    # profiles/fmha_bwd_full_B8_N16_S2048_H128.md (main kernel)
     "fmha_causal": 476.2e6,      # profiles/fmha_prefill_causal_B8_N16_S2048_H128.md
     "fmha_bias": 1.110e9,        # profiles/fmha_prefill_bias_B8_N16_S2048_H128.md
     "gemm_bias_gelu": 0.909e9,    # profiles/gemm_bias_gelu_M8192_K4096_N16384_bf16.md
