@@ -76,6 +76,16 @@ def test_workspace_queries_need_no_gpu(pkg):
     d.num_queries = 2048  # prefill keeps everything on chip
     assert lib.ixk_fmha_fwd_workspace_bytes(ctypes.byref(d)) == 0
     assert lib.ixk_gemm_workspace_bytes(None) == 0
+    # backward: -lse*log2e, rowsum(dO*O) and the fp32 dQ accumulator over rows padded to 128 queries
+    bd = pkg._FmhaBwdDesc()
+    bd.fwd.dtype, bd.fwd.num_batches, bd.fwd.num_heads, bd.fwd.head_size = 0, 2, 3, 96
+    bd.fwd.num_queries, bd.fwd.num_keys = 200, 77
+    assert lib.ixk_fmha_bwd_workspace_bytes(ctypes.byref(bd)) == 2 * 3 * 256 * (128 + 2) * 4
+    bd.fwd.head_size = 64
+    assert lib.ixk_fmha_bwd_workspace_bytes(ctypes.byref(bd)) == 2 * 3 * 256 * (64 + 2) * 4
+    bd.fwd.head_size = 256       # not covered by the backward kernels
+    assert lib.ixk_fmha_bwd_workspace_bytes(ctypes.byref(bd)) == 0
+    assert lib.ixk_fmha_bwd_workspace_bytes(None) == 0
 
 
 def test_argument_errors_come_back_as_codes_not_aborts(pkg):
@@ -99,6 +109,16 @@ def test_argument_errors_come_back_as_codes_not_aborts(pkg):
     assert lib.ixk_fmha_fwd(ctypes.byref(f), None, None, None, None, None, None, None, 0, None) == pkg.IXK_UNIMPLEMENTED
     f.head_size, f.dtype = 64, 2  # F32
     assert lib.ixk_fmha_fwd(ctypes.byref(f), None, None, None, None, None, None, None, 0, None) == pkg.IXK_UNIMPLEMENTED
+    assert lib.ixk_fmha_bwd(None, None, None, None, None, None, None, None, None, None, None, None, 0, None) \
+        == pkg.IXK_INVALID_ARGUMENT
+    bd = pkg._FmhaBwdDesc()
+    bd.fwd.dtype, bd.fwd.dropout_prob = 0, 0.5
+    assert lib.ixk_fmha_bwd(ctypes.byref(bd), None, None, None, None, None, None, None, None, None, None, None, 0,
+                            None) == pkg.IXK_UNIMPLEMENTED
+    assert lib.ixk_row_norm(2, 0, 4, 16, None, 16, None, 16, 1e-5, None) == pkg.IXK_UNIMPLEMENTED      # fp32
+    assert lib.ixk_row_norm(0, 7, 4, 16, None, 16, None, 16, 1e-5, None) == pkg.IXK_INVALID_ARGUMENT  # kind
+    assert lib.ixk_residual_add(0, 4, 12, None, None, None, None, None) == pkg.IXK_INVALID_ARGUMENT   # null, cols % 8
+    assert lib.ixk_rotary_interleaved(0, None, 8, 3, 2, 32, 64, 64, None, None, None) == pkg.IXK_INVALID_ARGUMENT
 
 
 def test_missing_library_fails_loudly(pkg, monkeypatch):
