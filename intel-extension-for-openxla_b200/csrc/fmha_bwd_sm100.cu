@@ -301,9 +301,23 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   // work item: the key blocks of one (batch, head) are neighbours in launch order, so that its Q, dO
   // and slice of the dQ accumulator (1 MB at 2048 queries) stay in L2 while they are shared;
   // within a head the heaviest key block comes first (under the causal mask block 0 is seen by
-  // every query block)
-  const int kb = blockIdx.x % args.num_kblocks;
-  const int bn = blockIdx.x / args.num_kblocks;
+  // every query block).  A causal launch runs in two passes over the heads, the heavy half of the
+  // key blocks first and the light half after it, so that the last CTAs to start are short ones.
+  int kb, bn;
+  {
+    const int heads = args.B * args.N;
+    const int first = args.causal ? (args.num_kblocks + 1) / 2 : args.num_kblocks;   // key blocks in pass 0
+    const int pass0 = heads * first;
+    if (static_cast<int>(blockIdx.x) < pass0) {
+      kb = blockIdx.x % first;
+      bn = blockIdx.x / first;
+    } else {
+      const int rest = args.num_kblocks - first;
+      const int idx = blockIdx.x - pass0;
+      kb = first + idx % rest;
+      bn = idx / rest;
+    }
+  }
   const int n = bn % args.N, b = bn / args.N;
   const int i0 = args.causal ? kb : 0;
   const int n_steps = args.num_qblocks > i0 ? args.num_qblocks - i0 : 0;
