@@ -110,10 +110,12 @@ class FmhaBwdWorkload:
     forward's log-sum-exp rows (the forward runs once, outside the timed steps).  Five matrix
     products per tile against the forward's two: 2.5 x the forward's flops."""
 
-    def __init__(self, causal: bool, B=8, N=16, S=2048, H=128):
-        self.causal, self.B, self.N, self.S, self.H = causal, B, N, S, H
-        self.name = f"fmha_bwd_{'causal' if causal else 'full'}_B{B}_N{N}_S{S}_H{H}_bf16"
-        self.metric = "fused-MHA backward TFLOP/s per B200 (bf16, %s)" % ("causal" if causal else "non-causal")
+    def __init__(self, causal: bool, bias: bool = False, B=8, N=16, S=2048, H=128):
+        self.causal, self.bias, self.B, self.N, self.S, self.H = causal, bias, B, N, S, H
+        kind = "causal" if causal else ("bias" if bias else "full")
+        self.name = f"fmha_bwd_{kind}_B{B}_N{N}_S{S}_H{H}_bf16"
+        self.metric = "fused-MHA backward TFLOP/s per B200 (bf16, %s)" % (
+            "causal" if causal else ("additive bias" if bias else "non-causal"))
         self.unit = "TFLOP/s"
         self.bound = "tensor"
         self.dtype = "bf16"
@@ -124,7 +126,10 @@ class FmhaBwdWorkload:
     def make(self, seed):
         g = torch.Generator().manual_seed(seed)
         shape = (self.B, self.N, self.S, self.H)
-        return {name: torch.randn(shape, generator=g).bfloat16() for name in ("q", "k", "v", "do")}
+        t = {name: torch.randn(shape, generator=g).bfloat16() for name in ("q", "k", "v", "do")}
+        if self.bias:
+            t["bias"] = torch.randn(self.B, 1, self.S, self.S, generator=g).bfloat16()
+        return t
 
     def alloc_out(self, dev):
         return torch.empty(self.B, self.N, self.S, self.H, dtype=torch.bfloat16, device=dev)   # dQ
@@ -134,13 +139,13 @@ class FmhaBwdWorkload:
         if "_o" not in d:
             d["_o"] = torch.empty_like(d["q"])
             d["_lse"] = torch.empty(self.B, self.N, self.S, dtype=torch.float32, device=out.device)
-            pkg.fmha_forward_kernel(None, d["q"], d["k"], d["v"], None, None, 0.0, d["_o"], d["_lse"], scale, True,
-                                    causal=self.causal)
+            pkg.fmha_forward_kernel(None, d["q"], d["k"], d["v"], d.get("bias"), None, 0.0, d["_o"], d["_lse"], scale,
+                                    True, causal=self.causal)
             d["_dk"], d["_dv"] = torch.empty_like(d["k"]), torch.empty_like(d["v"])
-            need = pkg.fmha_backward_workspace_bytes(d["q"], d["k"], d["v"], d["_o"], None, d["do"], out, d["_dk"],
+            need = pkg.fmha_backward_workspace_bytes(d["q"], d["k"], d["v"], d["_o"], d.get("bias"), d["do"], out, d["_dk"],
                                                      d["_dv"], scale, self.causal)
             d["_ws"] = torch.empty(need, dtype=torch.uint8, device=out.device)
-        pkg.fmha_backward_kernel(None, d["q"], d["k"], d["v"], d["_o"], None, d["do"], d["_lse"], out, d["_dk"],
+        pkg.fmha_backward_kernel(None, d["q"], d["k"], d["v"], d["_o"], d.get("bias"), d["do"], d["_lse"], out, d["_dk"],
                                  d["_dv"], scale, causal=self.causal, workspace=d["_ws"])
 
     def cpu_units(self):
@@ -150,8 +155,9 @@ class FmhaBwdWorkload:
         b, n = divmod(idx, self.N)
         f = lambda t: t[b:b + 1, n:n + 1].float().numpy()
         scale = self.H ** -0.5
-        o, lse = orc.fmha_forward(f(host["q"]), f(host["k"]), f(host["v"]), None, head_scale=scale, causal=self.causal)
-        orc.fmha_backward(f(host["q"]), f(host["k"]), f(host["v"]), o, f(host["do"]), lse, None, head_scale=scale,
+        bias = host["bias"][b:b + 1].float().numpy() if self.bias else None
+        o, lse = orc.fmha_forward(f(host["q"]), f(host["k"]), f(host["v"]), bias, head_scale=scale, causal=self.causal)
+        orc.fmha_backward(f(host["q"]), f(host["k"]), f(host["v"]), o, f(host["do"]), lse, bias, head_scale=scale,
                           causal=self.causal)
 
 
@@ -287,6 +293,7 @@ WORKLOADS = {
     "fmha_bias": lambda: FmhaWorkload(False),
     "fmha_bwd_causal": lambda: FmhaBwdWorkload(True),
     "fmha_bwd_full": lambda: FmhaBwdWorkload(False),
+    "fmha_bwd_bias": lambda: FmhaBwdWorkload(False, bias=True),
     "gemm_bias_gelu": lambda: GemmWorkload(),
     "gemm_fp8": lambda: Fp8GemmWorkload(False),
     "gemm_fp8_e5m2": lambda: Fp8GemmWorkload(True),

@@ -500,12 +500,14 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const float* nl = reinterpret_cast<const float*>(smem_raw + rows_off(st)) + 64 * half;
       const float* dl = nl + kBlk;
       const bool diag = args.causal && (i0 + it) == kb;
-      [[maybe_unused]] const uint16_t* bias_row = nullptr;
+      // bias column of this key (clamped to the last valid key: the mask zeroes what lies beyond)
+      [[maybe_unused]] const uint16_t* bias_col = nullptr;
       if constexpr (kBias)
-        bias_row = args.bias + b * args.bias_strides[0] + n * args.bias_strides[1] + key;
+        bias_col = args.bias + b * args.bias_strides[0] + n * args.bias_strides[1] + (key_ok ? key : args.T - 1);
       // phase A: P^T = exp2(S^T * scale*log2e + bias*log2e - lse*log2e) for this warpgroup's 64 queries.
       // Only the diagonal block of a causal problem and a ragged last key block need the mask.
-      const bool need_mask = diag || (kb + 1) * kBlk > args.T;
+      // (with a bias, a ragged last query block takes the same path: it clamps the bias row index)
+      const bool need_mask = diag || (kb + 1) * kBlk > args.T || (kBias && q0 + kBlk > args.F);
       const uint64_t scale2 = ptx::f32x2(args.scale_log2, args.scale_log2);
       uint64_t p2[32];     // P as fp32 pairs (queries 2j, 2j+1 of this warpgroup's half)
       auto phase_a = [&](auto masked) {
@@ -513,11 +515,26 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         uint32_t s[2][32];
         ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemS + 64 * half, s[0]);
         ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemS + 64 * half + 32, s[1]);
+        // bias values of this thread's key for 32 queries: no branch per element (row indices past
+        // the last query are clamped; those columns come out as zero through -inf in the lse row)
+        [[maybe_unused]] uint16_t bv[32];
+        [[maybe_unused]] auto load_bias = [&](int c) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            int q = q0 + 64 * half + 32 * c + j;
+            if constexpr (kMasked) q = min(q, args.F - 1);
+            bv[j] = bias_col[static_cast<int64_t>(q) * args.bias_strides[2]];
+          }
+        };
+        if constexpr (kBias) load_bias(0);
         ptx::tmem_ld_wait();
         if (threadIdx.x == 0) BWD_TRACE(1, 5, it);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t pw[16];
+          if constexpr (kBias) {
+            if (c == 1) load_bias(1);
+          }
 #pragma unroll
           for (int j4 = 0; j4 < 8; ++j4) {
             const float4 nl4 = *reinterpret_cast<const float4*>(nl + 32 * c + 4 * j4);
@@ -531,9 +548,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               ptx::f32x2_split(x[e], x0, x1);
               const int col = 32 * c + 4 * j4 + 2 * e;
               if constexpr (kBias) {
-                const int q = q0 + 64 * half + col;
-                if (key_ok && q < args.F) x0 = fmaf(to_f32(bias_row[q * args.bias_strides[2]], kBf16), kLog2e, x0);
-                if (key_ok && q + 1 < args.F) x1 = fmaf(to_f32(bias_row[(q + 1) * args.bias_strides[2]], kBf16), kLog2e, x1);
+                x0 = fmaf(to_f32(bv[4 * j4 + 2 * e], kBf16), kLog2e, x0);
+                x1 = fmaf(to_f32(bv[4 * j4 + 2 * e + 1], kBf16), kLog2e, x1);
               }
               float e0 = ptx::ex2_approx(x0), e1 = ptx::ex2_approx(x1);
               if constexpr (kMasked) {
