@@ -94,6 +94,7 @@ struct KernelArgs {
   int causal;
   int is_bf16;
   float scale_log2;  // head_scale * log2(e)
+  float head_scale;
   const uint16_t* bias;
   int64_t bias_strides[3];
   int bias_vec_ok;
@@ -749,16 +750,22 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           IXK_TRACE(warp, j, 1);
           const int kv0 = (item.reversed ? my_blocks - 1 - j : j) * kBlockKV;
           // Scores enter the exponential as x = r * mult - m.  Fast path: r is the raw Q.K^T and
-          // mult = head_scale * log2(e) (> 0, so the row maximum can be taken on r).  With a bias
-          // or a non-positive scale, r is first rewritten as the full log2-domain score and mult = 1.
+          // mult = head_scale * log2(e) (> 0, so the row maximum can be taken on r).  With a
+          // non-positive scale, r is first rewritten as the full log2-domain score and mult = 1.
           float mult = args.scale_log2;
-          if (args.bias != nullptr || !(args.scale_log2 > 0.0f)) {
+          if (args.bias == nullptr && !(args.scale_log2 > 0.0f)) {
             mult = 1.0f;
   #pragma unroll
             for (int c = 0; c < 4; ++c) {
   #pragma unroll
               for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__uint_as_float(r[c][i]) * args.scale_log2);
             }
+          }
+          if (args.bias != nullptr) {
+            // With a bias, r becomes the natural-log score head_scale * r + bias in one fused
+            // multiply-add per element and mult = log2(e) (> 0 whatever the sign of the scale).
+            mult = kLog2e;
+            const float hs = args.head_scale;
             if (kBias) {
               // The bias tile was brought in by TMA as two 128-byte-swizzled boxes of 64 keys; this
               // thread reads its own row, 16 bytes at a time (8 consecutive rows touch 8 different
@@ -780,8 +787,8 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {
                     const int i = g * 8 + e * 2;
-                    r[c][i] = __float_as_uint(fmaf(unpack_lo(ww[e], bf16), kLog2e, __uint_as_float(r[c][i])));
-                    r[c][i + 1] = __float_as_uint(fmaf(unpack_hi(ww[e], bf16), kLog2e, __uint_as_float(r[c][i + 1])));
+                    r[c][i] = __float_as_uint(fmaf(__uint_as_float(r[c][i]), hs, unpack_lo(ww[e], bf16)));
+                    r[c][i + 1] = __float_as_uint(fmaf(__uint_as_float(r[c][i + 1]), hs, unpack_hi(ww[e], bf16)));
                   }
                 }
               }
@@ -810,12 +817,16 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   #pragma unroll
                   for (int i = 0; i < 32; ++i) {
                     const int col = c * 32 + i;
-                    if (col < count) {
-                      const uint32_t w = __ldg(bp + col);
-                      r[c][i] = __float_as_uint(fmaf(unpack_lo(w, bf16), kLog2e, __uint_as_float(r[c][i])));
-                    }
+                    const float bias_v = col < count ? unpack_lo(__ldg(bp + col), bf16) : 0.0f;
+                    r[c][i] = __float_as_uint(fmaf(__uint_as_float(r[c][i]), hs, bias_v));
                   }
                 }
+              }
+            } else {
+  #pragma unroll
+              for (int c = 0; c < 4; ++c) {
+  #pragma unroll
+                for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__uint_as_float(r[c][i]) * hs);
               }
             }
           }
@@ -1020,6 +1031,7 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   a.causal = p.causal ? 1 : 0;
   a.is_bf16 = p.dtype == IXK_BF16 ? 1 : 0;
   a.scale_log2 = p.head_scale * kLog2e;
+  a.head_scale = p.head_scale;
   a.bias = static_cast<const uint16_t*>(p.bias);
   a.out = static_cast<uint16_t*>(p.out);
   a.lse = p.lse;
