@@ -45,8 +45,11 @@ def run_case(pkg, orc, cuda, *, B, N, F, T, H, causal=False, bias_shape=None, dt
     for name, got, want in (("dv", dv, wv), ("dk", dk, wk), ("dq", dq, wq)):
         got = f32(got)
         assert np.isfinite(got).all(), name
-        rel = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
-        assert rel < 1e-2, f"{name}: relative error {rel:.3e}"
+        # (a gradient that is zero up to rounding, e.g. dQ and dK of a single key, has no meaningful
+        # relative error: the element-wise bound below still applies)
+        if np.linalg.norm(want) > 1e-3 * math.sqrt(want.size):
+            rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+            assert rel < 1e-2, f"{name}: relative error {rel:.3e}"
         orc.check_close(got, want, rtol=2e-2, atol=2e-2, what=name)
 
 
@@ -56,7 +59,7 @@ def test_one_block(pkg, orc, cuda, H, causal):
     run_case(pkg, orc, cuda, B=1, N=1, F=128, T=128, H=H, causal=causal, seed=1)
 
 
-@pytest.mark.parametrize("F,T", [(256, 384), (384, 256), (200, 330), (130, 127), (640, 640)])
+@pytest.mark.parametrize("F,T", [(256, 384), (384, 256), (200, 330), (130, 127), (640, 640), (5, 300), (300, 5), (1, 1)])
 @pytest.mark.parametrize("causal", [False, True])
 def test_several_blocks_and_ragged_edges(pkg, orc, cuda, F, T, causal):
     run_case(pkg, orc, cuda, B=2, N=3, F=F, T=T, H=128, causal=causal, seed=F + T)
