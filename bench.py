@@ -640,7 +640,7 @@ def run_layer(args, rank, world):
         x_host = torch.randn(B, S, 4096, generator=g).bfloat16().pin_memory()
         x = x_host.to(dev)
         rope = layers.rotary_tables(torch.arange(S, device=dev), 64)
-        step = lambda: layers.gptj_layer_prefill(x, w, ops, rope=rope)
+        step = lambda reduce=None: layers.gptj_layer_prefill(x, w, ops, rope=rope, reduce=reduce)
         work, div, unit, bound = layers.gptj_layer_flops(B, S), 1e12, "TFLOP/s", "tensor"
         metric = "GPT-J-6B-shaped decoder layer prefill TFLOP/s (bf16, tensor-parallel)"
         name = f"gptj_layer_prefill_B{B}_S{S}_hidden4096_heads16x256_mlp16384_tp{world}"
@@ -659,7 +659,8 @@ def run_layer(args, rank, world):
         v_cache = torch.randn(B, T, hl, 256, generator=gk, device=dev).bfloat16()
         ws = torch.empty(8 << 20, dtype=torch.uint8, device=dev)
         rope = layers.rotary_tables(torch.tensor([T - 1], device=dev), 256)
-        step = lambda: layers.gemma_decode_step(x, w, k_cache, v_cache, T - 1, ops, workspace=ws, rope=rope)
+        step = lambda reduce=None: layers.gemma_decode_step(x, w, k_cache, v_cache, T - 1, ops, workspace=ws, rope=rope,
+                                                            reduce=reduce)
         work, div, unit, bound = layers.gemma_decode_bytes(B, T), 1e9, "GB/s", "hbm"
         metric = "Gemma-7B-shaped decode step GB/s of algorithmic bytes (bf16, tensor-parallel)"
         name = f"gemma_decode_B{B}_T{T}_hidden3072_heads16x256_mlp24576_tp{world}"
@@ -697,6 +698,48 @@ def run_layer(args, rank, world):
         for _ in range(2):
             step()
         torch.cuda.synchronize()
+    # N > 1, opt-in (--graph-segments): the pieces of the step between the all-reduces are captured
+    # as separate CUDA graphs and the all-reduces stay eager NCCL calls between the replays, so
+    # that the host issues a handful of calls per step instead of ~40.
+    segmented = world > 1 and args.graph_segments and not args.no_graph
+    if segmented:
+        import torch.distributed as dist
+        n_before = pkg.launch_count()
+        cap_stream = torch.cuda.Stream()
+        cap_stream.wait_stream(torch.cuda.current_stream())
+        pool = torch.cuda.graph_pool_handle()
+        plan = []
+        with torch.cuda.stream(cap_stream):
+            cur = torch.cuda.CUDAGraph()
+            cur.capture_begin(pool=pool, capture_error_mode="thread_local")
+
+            def cut(t, group=None):
+                nonlocal cur
+                cur.capture_end()
+                plan.append(cur)
+                plan.append(t)
+                dist.all_reduce(t)
+                cur = torch.cuda.CUDAGraph()
+                cur.capture_begin(pool=pool, capture_error_mode="thread_local")
+                return t
+
+            y = step(cut)
+            cur.capture_end()
+            plan.append(cur)
+        torch.cuda.current_stream().wait_stream(cap_stream)
+        launches_per_step = pkg.launch_count() - n_before
+
+        def step():
+            for item in plan:
+                if isinstance(item, torch.cuda.CUDAGraph):
+                    item.replay()
+                else:
+                    dist.all_reduce(item)
+            return y
+        for _ in range(2):
+            step()
+        barrier()
+        use_graph = True
     n0 = pkg.launch_count()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -738,7 +781,8 @@ def run_layer(args, rank, world):
         "data": "synthetic (random-init weights ~N(0,0.02), activations ~N(0,1), seeded)",
         "config": {"workload": name, "parallelism": f"tp{world} by heads / MLP columns, all-reduce after row-parallel GEMMs",
                    "l2": "L2 flushed (512 MB read+write) between timed steps",
-                   "launch": "CUDA graph replay" if use_graph else "eager"},
+                   "launch": ("CUDA graphs between eager all-reduces" if segmented else "CUDA graph replay") if use_graph
+                   else "eager"},
         "clocks": clk.summary(),
         "e2e": {"value": work / (e2e_ms * 1e-3) / div, "unit": unit, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(x_host.numel() * 2), "d2h_bytes_per_step": int(y_host.numel() * 2)},
@@ -806,6 +850,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + list(LAYER_WORKLOADS))
     ap.add_argument("--no-others", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-graph", action="store_true", help="layer workloads: launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--graph-segments", action="store_true",
+                    help="layer workloads at N > 1: replay CUDA graphs of the pieces between the (eager) all-reduces")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-timed steps only (no e2e, no CPU baseline): the command profiled under ncu")
     args = ap.parse_args()

@@ -170,12 +170,13 @@ class GptJLayerWeights:
             heads_local=num_heads // world, head_dim=head_dim, rotary_dim=rotary_dim)
 
 
-def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None, rope=None) -> torch.Tensor:
+def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None, rope=None, reduce=None) -> torch.Tensor:
     """GPT-J block, prefill: y = x + Attn(LN(x)) + MLP(LN(x)), x [B, S, hidden] replicated on every
     rank.  The attention-output and MLP-down partial sums are added locally (the second GEMM takes
     the first as its C operand with beta = 1), so the block needs ONE all-reduce.  `rope` may carry
     precomputed (cos, sin) tables for positions 0..S-1, which keeps the step free of host work (and
-    capturable in a CUDA graph)."""
+    capturable in a CUDA graph).  `reduce(t, group)` replaces the all-reduce call (a caller that
+    records the step in pieces around the exchange passes its own)."""
     B, S, hidden = x.shape
     hl, hd = w.heads_local, w.head_dim
     h = _glue(ops, "layer_norm", layer_norm)(x).view(B * S, hidden)
@@ -188,7 +189,7 @@ def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None, ro
     attn_partial = ops.gemm(ctx.view(B * S, hl * hd), w.wo)
     up = ops.gemm(h, w.w1, bias=w.b1, epilogue="BIAS_GELU")
     partial = ops.gemm(up, w.w2, c=attn_partial, beta=1.0, out=attn_partial)   # in place: C aliases D
-    partial = all_reduce_sum(partial, group)
+    partial = (reduce or all_reduce_sum)(partial, group)
     return _glue(ops, "residual_add", _residual_add_torch)(x, partial, w.b2)
 
 
@@ -224,7 +225,7 @@ class GemmaLayerWeights:
 
 
 def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                      position: int, ops, group=None, workspace=None, rope=None) -> torch.Tensor:
+                      position: int, ops, group=None, workspace=None, rope=None, reduce=None) -> torch.Tensor:
     """One new token per sequence: x [B, 1, hidden]; k_cache / v_cache [B, T, heads_local, head_dim]
     (this rank's heads) are updated in place at `position` and attended over [0, position].
     Two all-reduces: after the attention output projection and after the MLP down projection.
@@ -244,12 +245,13 @@ def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tens
     ctx = torch.empty(B, 1, hl, hd, dtype=x.dtype, device=x.device)
     ops.attention(q, k_cache[:, :T].permute(0, 2, 1, 3), v_cache[:, :T].permute(0, 2, 1, 3),
                   ctx.permute(0, 2, 1, 3), scale=1.0 / math.sqrt(hd), causal=False, workspace=workspace)
-    attn = all_reduce_sum(ops.gemm(ctx.view(B, hl * hd), w.wo), group)
+    reduce = reduce or all_reduce_sum
+    attn = reduce(ops.gemm(ctx.view(B, hl * hd), w.wo), group)
     x1 = add(x, attn)
     h2 = norm(x1).view(B, hidden)
     gate = ops.gemm(h2, w.wgate, epilogue="GELU")
     up = ops.gemm(h2, w.wup)
-    down = all_reduce_sum(ops.gemm(gate * up, w.wdown), group)
+    down = reduce(ops.gemm(gate * up, w.wdown), group)
     return add(x1, down)
 
 
