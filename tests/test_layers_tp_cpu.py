@@ -75,6 +75,11 @@ def _worker(rank, world, port, result_queue):
         w = layers.GptJLayerWeights.shard(full, heads, hd, rot, rank, world)
         assert w.wqkv.shape == (hidden, 3 * heads * hd // world) and w.wo.shape == (heads * hd // world, hidden)
         y = layers.gptj_layer_prefill(x, w, ops)
+        # the exchange call is pluggable (a caller that records the step in pieces passes its own)
+        calls = []
+        y_hook = layers.gptj_layer_prefill(x, w, ops, reduce=lambda t, group=None: (calls.append(tuple(t.shape)),
+                                                                                    layers.all_reduce_sum(t, group))[1])
+        assert calls == [(B * S, hidden)] and torch.equal(y, y_hook)
         want = layers_oracle.gptj_layer_prefill(f(x), {k: f(v) for k, v in full.items()}, heads, hd, rot)
         err_gptj = float(np.abs(f(y) - want).max())
 
@@ -88,6 +93,11 @@ def _worker(rank, world, port, result_queue):
         w = layers.GemmaLayerWeights.shard(full, heads, hd, rank, world)
         k_loc, v_loc = kc[:, :, h0:h1].contiguous(), vc[:, :, h0:h1].contiguous()
         y = layers.gemma_decode_step(x, w, k_loc, v_loc, T - 1, ops)
+        calls = []
+        y_hook = layers.gemma_decode_step(x, w, k_loc.clone(), v_loc.clone(), T - 1, ops,
+                                          reduce=lambda t, group=None: (calls.append(tuple(t.shape)),
+                                                                        layers.all_reduce_sum(t, group))[1])
+        assert len(calls) == 2 and torch.equal(y, y_hook)
         want = layers_oracle.gemma_decode_step(f(x), {k: f(v) for k, v in full.items()}, f(kc), f(vc), T - 1, heads, hd)
         err_gemma = float(np.abs(f(y) - want).max())
         cache_written = bool((k_loc[:, T - 1] != kc[:, T - 1, h0:h1]).any())
