@@ -728,6 +728,7 @@ def run_layer(args, rank, world):
             plan.append(cur)
         torch.cuda.current_stream().wait_stream(cap_stream)
         launches_per_step = pkg.launch_count() - n_before
+        y_eager = step().clone()      # the same step launched eagerly, to check the replay against
 
         def step():
             for item in plan:
@@ -739,6 +740,8 @@ def run_layer(args, rank, world):
         for _ in range(2):
             step()
         barrier()
+        if not torch.equal(step(), y_eager):
+            raise RuntimeError("segmented graph replay and eager launch of the layer step disagree")
         use_graph = True
     n0 = pkg.launch_count()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
