@@ -374,10 +374,13 @@ def time_device(pkg, wl, dev_in, out, steps, warmup, flush_buf):
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
     for i in range(steps):
+        # the flush goes first: every timed step, the first included, starts from a flushed L2, and
+        # the host has the flush's run time to enqueue the step behind it (an idle GPU would add
+        # the host's launch latency to the first event pair)
+        flush_l2(flush_buf)
         starts[i].record()
         wl.run(pkg, dev_in, out)
         ends[i].record()
-        flush_l2(flush_buf)
     torch.cuda.synchronize()
     return [s.elapsed_time(e) for s, e in zip(starts, ends)]
 
@@ -393,10 +396,10 @@ def time_library(wl, dev_in, out, steps, warmup, flush_buf):
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         for i in range(steps):
+            flush_l2(flush_buf)
             starts[i].record()
             wl.library_run(dev_in, out)
             ends[i].record()
-            flush_l2(flush_buf)
         torch.cuda.synchronize()
         ms = float(np.mean([s.elapsed_time(e) for s, e in zip(starts, ends)]))
         return {"name": wl.library_name, "value": wl.work / (ms * 1e-3) / wl.scale_div, "unit": wl.unit, "ms": ms}
@@ -748,10 +751,10 @@ def run_layer(args, rank, world):
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     with ClockSampler(local) as clk:
         for i in range(args.steps):
+            flush_l2(flush_buf)      # first, so that the host enqueues the step while the flush runs
             starts[i].record()
             y = step()
             ends[i].record()
-            flush_l2(flush_buf)
         torch.cuda.synchronize()
     launches = pkg.launch_count() - n0
     if launches_per_step is not None:
