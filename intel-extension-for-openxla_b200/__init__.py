@@ -382,6 +382,14 @@ def _fmha_desc(query, key, value, bias, out, head_scale, causal, dropout_prob) -
         raise IxkError(IXK_INVALID_ARGUMENT, "q, k, v, out must be 4-D [B,N,S,H] views")
     B, N, F, H = query.shape
     T = key.shape[2]
+    # The descriptor carries one B, N and H for all four tensors: a K of [B,1,T,H] has to be
+    # handed over as an expanded (stride-0) view, not as a smaller tensor that would be read
+    # as if it had N heads.
+    if tuple(key.shape) != (B, N, T, H) or value.shape != key.shape or out.shape != query.shape:
+        raise IxkError(IXK_INVALID_ARGUMENT, "k and v must be [B,N,T,H] and out [B,N,F,H] with q's B, N and H "
+                       "(share K/V between heads with .expand(), which gives stride 0)")
+    if not (key.dtype == value.dtype == out.dtype == query.dtype) or (bias is not None and bias.dtype != query.dtype):
+        raise IxkError(IXK_INVALID_ARGUMENT, "q, k, v, bias and out must have one element type")
     d = _FmhaDesc()
     d.dtype = _TORCH_TO_IXK[query.dtype]
     d.causal = 1 if causal else 0

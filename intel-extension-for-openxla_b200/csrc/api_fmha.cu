@@ -46,6 +46,23 @@ int make_problem(const ixk_fmha_desc* d, const void* q, const void* k, const voi
         d->bias_strides[i] < 0)
       return fail(IXK_INVALID_ARGUMENT, "negative stride");
   }
+  // Stride 0 on a dimension with more than one entry means "one tensor for all of them".  That is
+  // a broadcast READ for K and V over heads and batches (multi-query attention) and for the bias
+  // (ixk.h); anywhere else it would alias rows of a tensor that is read row by row, or make the
+  // writes of different (batch, head, row) triples land on one address.  (The workspace queries
+  // pass descriptors whose strides may be unset: they are not checked there.)
+  if (need_pointers) {
+    const int64_t ext_q[3] = {p->B, p->N, p->F};
+    const int64_t ext_k[3] = {p->B, p->N, p->T};
+    for (int i = 0; i < 3; ++i) {
+      if (ext_q[i] > 1 && d->o_strides[i] == 0)
+        return fail(IXK_INVALID_ARGUMENT, "out: stride 0 on a dimension with more than one entry (rows would overwrite each other)");
+      if (ext_q[i] > 1 && d->q_strides[i] == 0)
+        return fail(IXK_UNIMPLEMENTED, "q: stride 0 (broadcast) is only supported for k, v and bias");
+    }
+    if (ext_k[2] > 1 && (d->k_strides[2] == 0 || d->v_strides[2] == 0))
+      return fail(IXK_UNIMPLEMENTED, "k/v: stride 0 on the key dimension");
+  }
   if (need_pointers) {
     if (p->B == 0 || p->N == 0 || p->F == 0) return IXK_OK;
     if (q == nullptr || k == nullptr || v == nullptr || out == nullptr)
@@ -124,6 +141,17 @@ int ixk_fmha_bwd(const ixk_fmha_bwd_desc* desc, const void* q, const void* k, co
     bp.dv_strides[i] = desc->dv_strides[i];
     if (bp.do_strides[i] < 0 || bp.dq_strides[i] < 0 || bp.dk_strides[i] < 0 || bp.dv_strides[i] < 0)
       return ixk::fail(IXK_INVALID_ARGUMENT, "negative stride");
+    {
+      // The gradients are written once per (batch, head, row): no zero strides.  K and V shared
+      // between heads (stride 0) would need dK / dV summed over those heads, which this kernel
+      // does not do.
+      const int64_t ext_q = i == 0 ? p.B : (i == 1 ? p.N : p.F);
+      const int64_t ext_k = i == 2 ? p.T : ext_q;
+      if ((ext_q > 1 && bp.dq_strides[i] == 0) || (ext_k > 1 && (bp.dk_strides[i] == 0 || bp.dv_strides[i] == 0)))
+        return ixk::fail(IXK_INVALID_ARGUMENT, "dq/dk/dv: stride 0 on a dimension with more than one entry");
+      if ((ext_q > 1 && bp.do_strides[i] == 0) || (ext_k > 1 && (p.k_strides[i] == 0 || p.v_strides[i] == 0)))
+        return ixk::fail(IXK_UNIMPLEMENTED, "attention backward with a broadcast (stride 0) k, v or grad_out");
+    }
     if (p.q_strides[i] % 8 != 0 || p.k_strides[i] % 8 != 0 || p.v_strides[i] % 8 != 0 || p.o_strides[i] % 8 != 0 ||
         bp.do_strides[i] % 8 != 0 ||
         bp.dq_strides[i] % 8 != 0 || bp.dk_strides[i] % 8 != 0 || bp.dv_strides[i] % 8 != 0)

@@ -106,6 +106,9 @@ struct KernelArgs {
   int* status_word;
   int num_qblocks;  // query blocks of kBlockQ * kQTiles rows per (batch, head)
   int num_items;    // num_qblocks * N * B
+  // 0 where K / V is one tensor broadcast over heads / batches (stride 0: multi-query attention),
+  // 1 otherwise: multiplies the head / batch coordinate of the K and V loads
+  int k_head_mul, k_batch_mul, v_head_mul, v_batch_mul;
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
@@ -384,11 +387,13 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           }
           if (i == 0) IXK_PTRACE(6);
           const CUtensorMap* map = (i & 1) ? &tmap_v : &tmap_k;
+          const int kv_head = item.head * ((i & 1) ? args.v_head_mul : args.k_head_mul);
+          const int kv_batch = item.batch * ((i & 1) ? args.v_batch_mul : args.k_batch_mul);
           ptx::mbar_expect_tx(kv_full(slot), C::kTileBytes);
 #pragma unroll
           for (int c = 0; c < C::kChunks; ++c)
             ptx::tma_load_4d(kv_smem + slot * C::kTileBytes + c * kChunkBytes, map, kv_full(slot), c * kChunkElems,
-                             item.key_block(i >> 1) * kBlockKV, item.head, item.batch);
+                             item.key_block(i >> 1) * kBlockKV, kv_head, kv_batch);
           if (kBias && (i & 1) == 0) {
             // right behind K_j: the bias tile of key block j for each query tile (one buffer per
             // tile, handed back by the softmax warpgroup as soon as it has read it)
@@ -967,6 +972,9 @@ template <int kHeadDim, int kQTiles, int kPolyOf4, bool kBias>
 int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   using C = Cfg<kHeadDim, kQTiles, kBias>;
   const CUtensorMapDataType dt = p.dtype == IXK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  // A head / batch dimension with stride 0 (one K or V shared by all heads or batches) is encoded
+  // with extent 1 and the kernel addresses it with coordinate 0; the host entry point has already
+  // refused stride 0 wherever that is not a broadcast read (q, out, rows).
   auto make_map = [&](CUtensorMap* out, const void* base, const int64_t* strides, int rows) -> int {
     TmapSpec s{};
     s.dtype = dt;
@@ -974,9 +982,9 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
     s.swizzle128 = true;
     s.dims[0] = p.H;
     s.dims[1] = rows;
-    s.dims[2] = p.N;
-    s.dims[3] = p.B;
-    // Size-1 dimensions still need a legal stride; any 16-byte multiple will do.
+    s.dims[2] = strides[1] == 0 ? 1 : p.N;
+    s.dims[3] = strides[0] == 0 ? 1 : p.B;
+    // Extent-1 dimensions still need a legal stride; any 16-byte multiple will do.
     auto stride_bytes = [&](int64_t st, uint64_t fallback) -> uint64_t {
       return st > 0 ? static_cast<uint64_t>(st) * 2 : fallback;
     };
@@ -1036,6 +1044,10 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   a.out = static_cast<uint16_t*>(p.out);
   a.lse = p.lse;
   a.status_word = dev.status_word;
+  a.k_head_mul = p.k_strides[1] == 0 ? 0 : 1;
+  a.k_batch_mul = p.k_strides[0] == 0 ? 0 : 1;
+  a.v_head_mul = p.v_strides[1] == 0 ? 0 : 1;
+  a.v_batch_mul = p.v_strides[0] == 0 ? 0 : 1;
   bool bias_vec = p.bias != nullptr && (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;
   bool out_vec = (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0;
   for (int i = 0; i < 3; ++i) {

@@ -121,6 +121,63 @@ def test_argument_errors_come_back_as_codes_not_aborts(pkg):
     assert lib.ixk_rotary_interleaved(0, None, 8, 3, 2, 32, 64, 64, None, None, None) == pkg.IXK_INVALID_ARGUMENT
 
 
+def test_zero_strides_are_a_broadcast_only_where_that_is_a_read(pkg):
+    """Stride 0 on a dimension with several entries: accepted for k / v over heads and batches
+    (one K/V for all heads) and for the bias; refused for q, for the key rows and for everything
+    that is written.  All on the host, before any pointer is looked at."""
+    lib = pkg.load_library()
+
+    def desc(**over):
+        f = pkg._FmhaDesc()
+        f.dtype, f.num_batches, f.num_heads, f.head_size, f.num_queries, f.num_keys = 0, 2, 4, 64, 128, 256
+        f.head_scale = 0.125
+        f.q_strides[:] = [4 * 128 * 64, 128 * 64, 64]
+        f.o_strides[:] = [4 * 128 * 64, 128 * 64, 64]
+        f.k_strides[:] = [4 * 256 * 64, 256 * 64, 64]
+        f.v_strides[:] = [4 * 256 * 64, 256 * 64, 64]
+        for name, val in over.items():
+            getattr(f, name)[:] = val
+        return f
+
+    def fwd(f):
+        return lib.ixk_fmha_fwd(ctypes.byref(f), None, None, None, None, None, None, None, 0, None)
+
+    # with legal strides the call gets as far as the NULL pointers
+    assert fwd(desc()) == pkg.IXK_INVALID_ARGUMENT and b"non-NULL" in lib.ixk_last_error()
+    assert fwd(desc(k_strides=[0, 0, 64], v_strides=[256 * 64, 0, 64])) == pkg.IXK_INVALID_ARGUMENT
+    assert b"non-NULL" in lib.ixk_last_error()                       # K/V shared between heads: accepted
+    assert fwd(desc(q_strides=[4 * 128 * 64, 0, 64])) == pkg.IXK_UNIMPLEMENTED
+    assert fwd(desc(k_strides=[4 * 256 * 64, 256 * 64, 0])) == pkg.IXK_UNIMPLEMENTED
+    assert fwd(desc(o_strides=[4 * 128 * 64, 0, 64])) == pkg.IXK_INVALID_ARGUMENT
+    assert b"overwrite" in lib.ixk_last_error()
+
+    bd = pkg._FmhaBwdDesc()
+    bd.fwd = desc(k_strides=[4 * 256 * 64, 0, 64])
+    for name, t in (("do", 128), ("dq", 128), ("dk", 256), ("dv", 256)):
+        getattr(bd, name + "_strides")[:] = [4 * t * 64, t * 64, 64]
+    one = ctypes.c_void_p(256)   # never dereferenced: the stride check comes first
+    args = [one] * 10
+    assert lib.ixk_fmha_bwd(ctypes.byref(bd), *args, None, 0, None) == pkg.IXK_UNIMPLEMENTED   # dK would need a sum over heads
+    bd.fwd = desc()
+    bd.dk_strides[:] = [4 * 256 * 64, 0, 64]
+    assert lib.ixk_fmha_bwd(ctypes.byref(bd), *args, None, 0, None) == pkg.IXK_INVALID_ARGUMENT
+
+
+def test_python_descriptor_checks_that_shapes_agree(pkg):
+    import torch
+    q = torch.zeros(2, 4, 16, 64, dtype=torch.bfloat16)
+    k1 = torch.zeros(2, 1, 32, 64, dtype=torch.bfloat16)
+    with pytest.raises(pkg.IxkError, match="expand"):
+        pkg._fmha_desc(q, k1, k1, None, q, 1.0, False, 0.0)           # one K head handed over as a smaller tensor
+    ke = k1.expand(2, 4, 32, 64)
+    d = pkg._fmha_desc(q, ke, ke, None, q, 1.0, False, 0.0)
+    assert list(d.k_strides) == [32 * 64, 0, 64]
+    with pytest.raises(pkg.IxkError):
+        pkg._fmha_desc(q, ke, ke, None, q[:, :2], 1.0, False, 0.0)    # out with fewer heads
+    with pytest.raises(pkg.IxkError, match="element type"):
+        pkg._fmha_desc(q, ke.half(), ke, None, q, 1.0, False, 0.0)
+
+
 def test_missing_library_fails_loudly(pkg, monkeypatch):
     """No silent fallback: without libixk.so the package raises."""
     monkeypatch.setattr(pkg, "_LIB", None)

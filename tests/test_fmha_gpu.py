@@ -186,6 +186,44 @@ def test_full_size_matches_oracle_on_a_slice(pkg, orc, cuda):
         orc.check_close(f32(o[b:b + 1, n:n + 1]), want, rtol=2e-2, atol=2e-2, what=f"C2 causal b{b} n{n}")
 
 
+def test_full_size_bias_matches_oracle_on_slices(pkg, orc, cuda):
+    """Configuration 2's second variant on its own inputs: non-causal, additive bias [B,1,S,S] ~ N(0,1)
+    shared by the 16 heads, Q, K, V ~ N(0,1), at full size; the oracle checks two (batch, head)
+    pairs in full, output and log-sum-exp rows (a random V, so the P.V product is what is compared)."""
+    B, N, S, H = 8, 16, 2048, 128
+    g = torch.Generator().manual_seed(61)
+    q = torch.randn(B, N, S, H, generator=g).bfloat16()
+    k = torch.randn(B, N, S, H, generator=g).bfloat16()
+    v = torch.randn(B, N, S, H, generator=g).bfloat16()
+    bias = torch.randn(B, 1, S, S, generator=g).bfloat16()
+    o, lse = run(pkg, q.to(cuda), k.to(cuda), v.to(cuda), bias=bias.to(cuda), lse=True)
+    for (b, n) in ((0, 3), (7, 15)):
+        sl = lambda t: f32(t[b:b + 1, n:n + 1])
+        want, want_lse = orc.fmha_forward(sl(q), sl(k), sl(v), f32(bias[b:b + 1]), head_scale=H ** -0.5)
+        orc.check_close(f32(o[b:b + 1, n:n + 1]), want, rtol=2e-2, atol=2e-2, what=f"C2 bias b{b} n{n}")
+        orc.check_close(f32(lse[b:b + 1, n:n + 1]), want_lse, rtol=2e-3, atol=2e-3, what=f"C2 bias lse b{b} n{n}")
+
+
+@pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
+@pytest.mark.parametrize("H", [64, 128, 256])
+def test_keys_and_values_shared_between_heads(pkg, orc, cuda, H, causal):
+    """Multi-query attention through stride-0 views: one K / V per batch (or one for everything)
+    expanded over the heads.  The prefill kernel must read the shared tensor, not walk past it."""
+    B, N, F, T = 2, 4, 200, 333
+    g = torch.Generator().manual_seed(67 + H)
+    q = torch.randn(B, N, F, H, generator=g).bfloat16()
+    k1 = torch.randn(B, 1, T, H, generator=g).bfloat16()
+    v1 = torch.randn(1, 1, T, H, generator=g).bfloat16()
+    # the shared tensors sit at the END of a larger allocation: reading them with dense strides
+    # would leave the allocation
+    kd = torch.cat([torch.zeros(7, 1, T, H, dtype=torch.bfloat16), k1]).to(cuda)[7:]
+    vd = torch.cat([torch.zeros(7, 1, T, H, dtype=torch.bfloat16), v1]).to(cuda)[7:]
+    o, _ = run(pkg, q.to(cuda), kd.expand(B, N, T, H), vd.expand(B, N, T, H), causal=causal)
+    want, _ = orc.fmha_forward(f32(q), f32(k1.expand(B, N, T, H)), f32(v1.expand(B, N, T, H)), None,
+                               head_scale=H ** -0.5, causal=causal)
+    orc.check_close(f32(o), want, rtol=2e-2, atol=2e-2, what="shared K/V prefill")
+
+
 @pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
 def test_full_size_every_row_against_fp32_attention(pkg, cuda, causal):
     """Configuration 2 shapes, every (batch, head, row): the persistent kernel deals 1024 work items

@@ -89,6 +89,23 @@ def test_exact_integers_at_full_size(pkg, cuda):
     assert torch.equal(o1[rows], a[rows].float() @ b1)
 
 
+@pytest.mark.parametrize("b_dtype", [torch.float8_e4m3fn, torch.float8_e5m2], ids=["e4m3", "e5m2"])
+def test_full_size_on_the_configuration_inputs(pkg, orc, cuda, b_dtype):
+    """Configuration 3 on its own inputs: A[16384,8192], B[8192,8192] ~ N(0,1) in fp32, quantised per
+    tensor with scale = max_finite / amax (A e4m3, B e4m3 or e5m2), bf16 out.  The oracle recomputes
+    two 128-row strips (first and last) over all 8192 columns from the dequantised operands."""
+    M, K, N = 16384, 8192, 8192
+    g = torch.Generator().manual_seed(73)
+    aq, sa = pkg.quantize_fp8(torch.randn(M, K, generator=g), torch.float8_e4m3fn)
+    bq, sb = pkg.quantize_fp8(torch.randn(K, N, generator=g), b_dtype)
+    out = pkg.gemm_fp8(aq.to(cuda), bq.to(cuda), 1.0 / sa, 1.0 / sb)
+    a_codes, b_codes = aq.view(torch.uint8).numpy(), bq.view(torch.uint8).numpy()
+    for r0 in (0, M - 128):
+        want = orc.fp8_scaled_gemm(a_codes[r0:r0 + 128], orc.F8E4M3, sa, b_codes, ODT[b_dtype], sb)
+        rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+        orc.check_close(f32(out[r0:r0 + 128]), want, rtol=2e-2, atol=2e-2 * rms, what=f"C3 rows {r0}..{r0 + 127}")
+
+
 def test_bf16_operands_rejected_by_fp8_entry(pkg, cuda):
     x = torch.zeros(128, 128, dtype=torch.bfloat16, device=cuda)
     with pytest.raises(pkg.IxkError) as e:

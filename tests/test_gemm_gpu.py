@@ -255,6 +255,22 @@ def test_linearity_at_full_size(pkg, cuda):
     assert torch.equal(o1[rows], want)
 
 
+def test_full_size_on_the_configuration_inputs(pkg, orc, cuda):
+    """Configuration 1 on its own inputs and epilogue: X[8192,4096] ~ N(0,1), W[4096,16384] ~ N(0,0.02),
+    bias ~ N(0,0.02), BIAS_GELU, bf16 out.  The oracle recomputes three 128-row blocks (first, one
+    from the middle of a tile band, last) over all 16384 columns."""
+    M, K, N = 8192, 4096, 16384
+    g = torch.Generator().manual_seed(71)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(K, N, generator=g) * 0.02).bfloat16()
+    b = (torch.randn(N, generator=g) * 0.02).bfloat16()
+    out = pkg.gemm(x.to(cuda), w.to(cuda), bias=b.to(cuda), epilogue="BIAS_GELU")
+    w32, b32 = f32(w), f32(b)
+    for r0 in (0, 4480, M - 128):
+        want = orc.gemm_epilogue(f32(x[r0:r0 + 128]) @ w32, b32, None, 0.0, "BIAS_GELU", orc.BF16)
+        orc.check_close(f32(out[r0:r0 + 128]), want, rtol=2e-2, atol=2e-2, what=f"C1 rows {r0}..{r0 + 127}")
+
+
 def test_unaligned_pitch_is_rejected(pkg, cuda):
     x = torch.zeros(16, 20, dtype=torch.bfloat16, device=cuda)   # pitch 40 bytes
     w = torch.zeros(20, 16, dtype=torch.bfloat16, device=cuda)
