@@ -14,9 +14,14 @@ attention forward, causal, B=8 N=16 S=2048 H=128 bf16.  Rank 0 prints ONE JSON l
              measured peak in MEASURED_PEAKS.json
   cpu_baseline  the CPU oracle timed on this machine's cores on a bounded sample (reported only)
 
-With --gpus N > 1 (launched by torch.distributed.run) every rank runs the same workload on its own
-batch (the path has no cross-GPU exchange: independent batches/heads), and `value` is the sum of
-the work over all ranks divided by the slowest rank's time.  `--impl reference` times the CPU
+With --gpus N > 1 (launched by torch.distributed.run) every rank runs the headline workload on its
+own batch (the custom calls have no cross-GPU exchange: independent batches/heads), and `value` is
+the sum of the work over all ranks divided by the slowest rank's time.  The same line carries,
+under `others`, every other benchmark configuration: at N = 1 the single-GPU ones (each with its
+own e2e and cpu_baseline), and at every N the two decoder-layer configurations run
+tensor-parallel over the N GPUs (strong scaling; the exchange after the row-parallel projections
+is libixk's NVLink all-reduce, or NCCL where the exchange buffers cannot be shared), each checked
+once against the un-sharded layer on the same inputs.  `--impl reference` times the CPU
 restatement of the reference's algorithm (oracle/) on the host cores with the same JSON schema.
 """
 from __future__ import annotations
@@ -37,14 +42,14 @@ import __graft_entry__ as entry
 ROOT = os.path.dirname(os.path.abspath(__file__))
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised
-# under profiles/ (None until a capture exists for that kernel).
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each workload's dominant kernel, from
+# one ncu capture of that kernel at this size (absent: no capture of that kernel exists).
 NCU_TRAFFIC_BYTES = {
-    "fmha_bwd_full": 626.8e6,    # profiles/fmha_bwd_full_B8_N16_S2048_H128.md (main kernel)
-    "fmha_causal": 476.2e6,      # profiles/fmha_prefill_causal_B8_N16_S2048_H128.md
-    "fmha_bias": 1.110e9,        # profiles/fmha_prefill_bias_B8_N16_S2048_H128.md
-    "gemm_bias_gelu": 0.909e9,    # profiles/gemm_bias_gelu_M8192_K4096_N16384_bf16.md
-    "decode_attn": 4.30e9,        # profiles/fmha_decode_B64_N16_T4096_H256.md
+    "fmha_bwd_full": 626.8e6,
+    "fmha_causal": 493.8e6,
+    "fmha_bias": 1.110e9,
+    "gemm_bias_gelu": 0.909e9,
+    "decode_attn": 4.30e9,
 }
 
 
@@ -68,7 +73,7 @@ class FmhaWorkload:
     def __init__(self, causal: bool, B=8, N=16, S=2048, H=128):
         self.causal, self.B, self.N, self.S, self.H = causal, B, N, S, H
         self.name = f"fmha_fwd_{'causal' if causal else 'bias'}_B{B}_N{N}_S{S}_H{H}_bf16"
-        self.metric = "fused-MHA forward TFLOP/s per B200 (bf16, %s)" % ("causal" if causal else "additive bias")
+        self.metric = "fused-MHA forward TFLOP/s, whole job (bf16, %s)" % ("causal" if causal else "additive bias")
         self.unit = "TFLOP/s"
         self.bound = "tensor"
         self.dtype = "bf16"
@@ -114,7 +119,7 @@ class FmhaBwdWorkload:
         self.causal, self.bias, self.B, self.N, self.S, self.H = causal, bias, B, N, S, H
         kind = "causal" if causal else ("bias" if bias else "full")
         self.name = f"fmha_bwd_{kind}_B{B}_N{N}_S{S}_H{H}_bf16"
-        self.metric = "fused-MHA backward TFLOP/s per B200 (bf16, %s)" % (
+        self.metric = "fused-MHA backward TFLOP/s, whole job (bf16, %s)" % (
             "causal" if causal else ("additive bias" if bias else "non-causal"))
         self.unit = "TFLOP/s"
         self.bound = "tensor"
@@ -168,7 +173,7 @@ class GemmWorkload:
     def __init__(self, M=8192, K=4096, N=16384):
         self.M, self.K, self.N = M, K, N
         self.name = f"gemm_bias_gelu_M{M}_K{K}_N{N}_bf16"
-        self.metric = "bf16 GEMM+bias+GELU TFLOP/s per B200"
+        self.metric = "bf16 GEMM+bias+GELU TFLOP/s, whole job"
         self.unit, self.bound, self.dtype, self.kernel = "TFLOP/s", "tensor", "bf16", "gemm_pair_kernel"
         self.work = 2.0 * M * N * K
         self.scale_div = 1e12
@@ -208,7 +213,7 @@ class Fp8GemmWorkload:
     def __init__(self, b_e5m2=False, M=16384, K=8192, N=8192):
         self.M, self.K, self.N, self.b_e5m2 = M, K, N, b_e5m2
         self.name = f"gemm_fp8_e4m3x{'e5m2' if b_e5m2 else 'e4m3'}_M{M}_K{K}_N{N}"
-        self.metric = "fp8 scaled GEMM TFLOP/s per B200"
+        self.metric = "fp8 scaled GEMM TFLOP/s, whole job"
         self.unit, self.bound, self.dtype, self.kernel = "TFLOP/s", "tensor", "fp8", "gemm_pair_kernel"
         self.work = 2.0 * M * N * K
         self.scale_div = 1e12
@@ -255,7 +260,7 @@ class DecodeWorkload:
     def __init__(self, B=64, N=16, T=4096, H=256):
         self.B, self.N, self.T, self.H = B, N, T, H
         self.name = f"fmha_decode_B{B}_N{N}_T{T}_H{H}_bf16"
-        self.metric = "decode attention GB/s per B200 (bf16 KV cache)"
+        self.metric = "decode attention GB/s, whole job (bf16 KV cache)"
         self.unit, self.bound, self.dtype, self.kernel = "GB/s", "hbm", "bf16", "fmha_decode_kernel"
         self.work = 2.0 * B * N * T * H * 2 + 2.0 * B * N * H * 2
         self.scale_div = 1e9
@@ -454,6 +459,77 @@ def cpu_baseline(wl, orc, host, budget_s=15.0, threads=None):
             "sample": f"{n} of {total_units} independent units of {wl.name} ({dt:.1f} s)"}, dt
 
 
+def headline_config(wl):
+    """`config` of the JSON line; the same dictionary in both arms."""
+    return {"workload": wl.name, "per_gpu": "one full batch per GPU, no cross-GPU exchange",
+            "l2": "L2 flushed (512 MB read+write) between timed steps; inputs also exceed L2"}
+
+
+def probe_xla_cpu():
+    """BASELINE.json names "the same HLO on JAX's XLA CPU backend" as the reference semantics.  This
+    looks for it on the machine the bench runs on and says what it found."""
+    try:
+        import jax  # noqa: F401
+        return "jax %s is importable here" % getattr(jax, "__version__", "?")
+    except Exception as e:  # noqa: BLE001
+        return "XLA CPU: unavailable on this box (%s)" % (str(e).splitlines()[0][:120] if str(e) else type(e).__name__)
+
+
+def xla_cpu_sample(wl, host):
+    """If jax is present, time the headline attention on its CPU backend on one (batch, head) unit;
+    returns a dict or None.  Any failure is reported, never fatal."""
+    try:
+        import jax
+        import jax.numpy as jnp
+    except Exception:  # noqa: BLE001
+        return None
+    try:
+        if not isinstance(wl, FmhaWorkload):
+            return {"note": "jax present; XLA-CPU timing is implemented for the attention workloads only"}
+        cpu = jax.devices("cpu")[0]
+        f = lambda t: jax.device_put(jnp.asarray(t[:1, :1].float().numpy()).transpose(0, 2, 1, 3), cpu)   # [B,S,N,H]
+        q, k, v = f(host["q"]), f(host["k"]), f(host["v"])
+        bias = None if wl.causal else jax.device_put(jnp.asarray(host["bias"][:1].float().numpy()), cpu)
+        fn = jax.jit(lambda q, k, v: jax.nn.dot_product_attention(q, k, v, bias=bias, scale=wl.H ** -0.5,
+                                                                  is_causal=wl.causal), device=cpu)
+        fn(q, k, v).block_until_ready()
+        best = 1e30
+        for _ in range(3):
+            t0 = time.perf_counter()
+            fn(q, k, v).block_until_ready()
+            best = min(best, time.perf_counter() - t0)
+        unit_work = wl.work / (wl.B * wl.N)
+        return {"value": unit_work / best / wl.scale_div, "unit": wl.unit, "kind": "xla-cpu",
+                "sample": "1 of %d (batch, head) units, best of 3" % (wl.B * wl.N), "cores": os.cpu_count()}
+    except Exception as e:  # noqa: BLE001
+        return {"error": str(e).splitlines()[0][:200]}
+
+
+def measure_fp8_peak(dev, flush_buf):
+    """Dense fp8 throughput of the vendor library on this GPU, measured the way the bf16 figure in
+    MEASURED_PEAKS.json was (8192^3 product, best of 10): cuBLASLt e4m3 x e4m3 through
+    torch._scaled_mm.  None if the library refuses."""
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t().contiguous().t()
+        one = torch.tensor(1.0, device=dev)
+        for _ in range(3):
+            torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        best = 1e30
+        for _ in range(10):
+            flush_l2(flush_buf)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            e.record()
+            torch.cuda.synchronize()
+            best = min(best, s.elapsed_time(e))
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:  # noqa: BLE001
+        return None
+
+
 def run_ours(args, rank, world):
     pkg = entry.load_package()
     pkg.load_library()
@@ -466,8 +542,10 @@ def run_ours(args, rank, world):
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
     flush_buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=dev)
+    want_others = not args.no_others and args.workload not in LAYER_WORKLOADS
+    fp8_peak = measure_fp8_peak(dev, flush_buf) if (world == 1 and want_others) or "fp8" in args.workload else None
 
-    def measure(name, full):
+    def measure(name, full, cpu_budget):
         wl = WORKLOADS[name]()
         host = {k: t.pin_memory() for k, t in wl.make(seed=1000 * rank + 17).items()}
         dev_in = {k: t.to(dev, non_blocking=True) for k, t in host.items()}
@@ -494,9 +572,16 @@ def run_ours(args, rank, world):
         value = wl.work * world / (ms_per_step * 1e-3) / wl.scale_div
         kernel_ms = float(np.mean(ms))  # one dominant kernel per step
         achieved = wl.work / (kernel_ms * 1e-3) / wl.scale_div
-        if wl.bound == "tensor":
-            peak = peaks["bf16_tflops"] * (2.0 if wl.dtype == "fp8" else 1.0)
-            peak_note = ("2 x " if wl.dtype == "fp8" else "") + f"{peaks['source']} bf16 burst peak"
+        extra = {}
+        if wl.bound == "tensor" and wl.dtype == "fp8":
+            assumed = 2.0 * peaks["bf16_tflops"]
+            if fp8_peak is not None:
+                peak, peak_note = fp8_peak, "cuBLASLt e4m3 8192^3 burst measured in this run (no fp8 figure in MEASURED_PEAKS.json)"
+            else:
+                peak, peak_note = assumed, f"2 x {peaks['source']} bf16 burst peak (assumed)"
+            extra = {"frac_of_2x_bf16_peak": achieved / assumed}
+        elif wl.bound == "tensor":
+            peak, peak_note = peaks["bf16_tflops"], f"{peaks['source']} bf16 burst peak"
         else:
             peak, peak_note = peaks["hbm_gbs"], f"{peaks['source']} HBM copy bandwidth"
         res = {
@@ -504,54 +589,75 @@ def run_ours(args, rank, world):
             "min_ms": float(min(ms)), "workload": wl.name, "device_status": status,
             "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": wl.unit,
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(name), "kernel": wl.kernel,
-                         "peak_source": peak_note},
+                         "peak_source": peak_note, **extra},
             "clocks": clk.summary(), "gpu_launches": int(launches),
         }
         if hasattr(wl, "library_run") and world == 1:
             res["library"] = time_library(wl, dev_in, out, max(3, min(args.steps, 10)), 3, flush_buf)
         if full:
             host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-            e2e_ms = time_e2e(pkg, wl, host, dev_in, out, host_out, max(3, min(args.steps, 10)), args.warmup)
+            host_in = {k: v for k, v in host.items()}
+            e2e_ms = time_e2e(pkg, wl, host_in, dev_in, out, host_out, max(3, min(args.steps, 10)), args.warmup)
             if world > 1:
                 import torch.distributed as dist
                 t = torch.tensor([e2e_ms], device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 e2e_ms = float(t.item())
-            h2d = sum(t.numel() * t.element_size() for t in host.values())
+            h2d = sum(t.numel() * t.element_size() for t in host_in.values())
             d2h = host_out.numel() * host_out.element_size()
             res["e2e"] = {"value": wl.work * world / (e2e_ms * 1e-3) / wl.scale_div, "unit": wl.unit,
                           "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms}
             if rank == 0 and world == 1:
-                cb, _ = cpu_baseline(wl, orc, {k: v for k, v in host.items()}, budget_s=15.0)
+                cb, _ = cpu_baseline(wl, orc, {k: v for k, v in host.items()}, budget_s=cpu_budget)
                 res["cpu_baseline"] = cb
-        del dev_in, out, host
+        del dev_in, out
         torch.cuda.empty_cache()
-        return res, wl
+        return res, wl, host
 
-    main, wl = measure(args.workload, full=not args.kernel_only)
-    line = {
-        "metric": main["metric"], "value": main["value"], "unit": main["unit"], "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["ms_per_step"],
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
-        "data": "synthetic (seeded N(0,1) tensors of the configuration's shapes)",
-        "config": {"workload": wl.name, "per_gpu": "one full batch per GPU, no cross-GPU exchange",
-                   "l2": "L2 flushed (512 MB read+write) between timed steps; inputs also exceed L2"},
-        "clocks": main["clocks"], "e2e": main.get("e2e"), "gpu_launches": main["gpu_launches"],
-        "roofline": main["roofline"], "device_status": main["device_status"],
-    }
-    if "cpu_baseline" in main:
-        line["cpu_baseline"] = main["cpu_baseline"]
-    if not args.no_others and world == 1:
+    if args.workload in LAYER_WORKLOADS:
+        line = run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=not args.kernel_only)
+    else:
+        main, wl, host = measure(args.workload, full=not args.kernel_only, cpu_budget=12.0)
+        line = {
+            "metric": main["metric"], "value": main["value"], "unit": main["unit"], "n_gpus": world,
+            "per_gpu_value": main["value"] / world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+            "data": "synthetic (seeded N(0,1) tensors of the configuration's shapes)",
+            "config": headline_config(wl),
+            "clocks": main["clocks"], "e2e": main.get("e2e"), "gpu_launches": main["gpu_launches"],
+            "roofline": main["roofline"], "device_status": main["device_status"],
+        }
+        if "cpu_baseline" in main:
+            line["cpu_baseline"] = main["cpu_baseline"]
+            line["cpu_baseline"]["xla_cpu"] = probe_xla_cpu()
+            sample = xla_cpu_sample(wl, host)
+            if sample is not None:
+                line["cpu_baseline"]["xla_cpu_sample"] = sample
+        del host
+    if want_others:
         others = []
-        for name in OTHERS:
+        keys = ("value", "unit", "ms_per_step", "roofline", "gpu_launches", "e2e", "cpu_baseline", "library", "clocks")
+        if world == 1:
+            for name in OTHERS:
+                if name == args.workload:
+                    continue
+                try:
+                    r, w, _ = measure(name, full=not args.kernel_only, cpu_budget=6.0)
+                    others.append({"workload": w.name, "metric": w.metric, **{k: r[k] for k in keys if k in r}})
+                except Exception as ex:  # a failing side workload must not hide the headline
+                    others.append({"workload": name, "error": repr(ex)})
+        for lname in LAYER_WORKLOADS:
             try:
-                r, w = measure(name, full=False)
-                others.append({"workload": w.name, "value": r["value"], "unit": r["unit"], "ms_per_step": r["ms_per_step"],
-                               "roofline": r["roofline"], "gpu_launches": r["gpu_launches"]})
-                if "library" in r:
-                    others[-1]["library"] = r["library"]
-            except Exception as ex:  # a failing side workload must not hide the headline
-                others.append({"workload": name, "error": repr(ex)})
+                largs = argparse.Namespace(**{**vars(args), "workload": lname})
+                r = run_layer(largs, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=not args.kernel_only)
+                others.append({"workload": r["config"]["workload"], "metric": r["metric"], "n_gpus": world,
+                               "scaling": r["scaling"], "config": r["config"], "tp_check": r.get("tp_check"),
+                               **{k: r[k] for k in keys if k in r}})
+            except Exception as ex:  # noqa: BLE001
+                if world > 1:
+                    raise      # a rank that leaves a collective workload alone would strand the others
+                others.append({"workload": lname, "error": repr(ex)})
         line["others"] = others
     if world > 1:
         import torch.distributed as dist
@@ -567,13 +673,14 @@ def run_reference(args, rank, world):
     be built or run here, so `kind` is "port".  Rank 0 alone runs."""
     if rank != 0:
         return
+    if args.workload in LAYER_WORKLOADS:
+        print(json.dumps(layer_reference(args, full_line=True)))
+        return
     orc = entry.load_oracle()
     wl = WORKLOADS[args.workload]()
     host = wl.make(seed=17)
     threads = os.cpu_count() or 1
     # size the per-step sample so that steps+warmup passes stay within ~2 minutes
-    probe, dt = cpu_baseline(wl, orc, host, budget_s=2.0, threads=threads)
-    per_unit_rate = probe["value"]
     budget = max(1.0, 100.0 / (args.steps + args.warmup))
     times, sample = [], None
     for i in range(args.warmup + args.steps):
@@ -586,10 +693,12 @@ def run_reference(args, rank, world):
     line = {
         "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
         "data": "synthetic (seeded N(0,1) tensors of the configuration's shapes)",
-        "config": {"workload": wl.name, "note": "each step is a bounded sample of the workload"},
-        "cpu_baseline": {"value": value, "unit": wl.unit, "cores": threads, "kind": "port", "sample": sample},
+        "config": headline_config(wl),
+        "note": "each step is a bounded sample of the workload; arithmetic in fp32 on bf16-rounded inputs",
+        "cpu_baseline": {"value": value, "unit": wl.unit, "cores": threads, "kind": "port", "sample": sample,
+                         "xla_cpu": probe_xla_cpu()},
         "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -609,71 +718,103 @@ def _layer_weights(name, seed=7):
             "wdown": r(24576, 3072)}   # Gemma-7B shape: hidden 3072, 16 heads x 256, GeGLU 24576
 
 
-def run_layer(args, rank, world):
+LAYER_METRIC = {
+    "gptj_layer": "GPT-J-6B-shaped decoder layer prefill TFLOP/s (bf16, tensor-parallel, whole job)",
+    "gemma_decode": "Gemma-7B-shaped decode step GB/s of algorithmic bytes (bf16, tensor-parallel, whole job)",
+}
+
+
+def layer_config(name, world):
+    if name == "gptj_layer":
+        wname = f"gptj_layer_prefill_B4_S2048_hidden4096_heads16x256_mlp16384_tp{world}"
+    else:
+        wname = f"gemma_decode_B64_T4096_hidden3072_heads16x256_mlp24576_tp{world}"
+    return {"workload": wname, "parallelism": f"tp{world} by heads / MLP columns, all-reduce after row-parallel GEMMs",
+            "l2": "L2 flushed (512 MB read+write) between timed steps"}
+
+
+def run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=True):
     """Configurations 4 and 5: one decoder layer, tensor-parallel over `world` GPUs by heads / MLP
-    columns, NCCL all-reduce after the row-parallel projections.  Total work is fixed (strong scaling).
+    columns, one exchange after the row-parallel projections.  Total work is fixed (strong scaling).
       gptj_layer    prefill, batch 4 x seq 2048, reported in TFLOP/s of the layer's GEMM+attention FLOPs
       gemma_decode  one token for 64 sequences against a 4096-entry KV cache, reported in GB/s of the
-                    algorithmic bytes (K, V and every weight once)"""
+                    algorithmic bytes (K, V and every weight once)
+    Returns the JSON line as a dictionary (every rank; rank 0's is the one printed)."""
     import importlib
-    pkg = entry.load_package()
-    pkg.load_library()
+    import torch.distributed as dist
     layers = importlib.import_module(entry.PKG_NAME + ".layers")
-    if args.impl == "reference":
-        if rank == 0:
-            run_layer_reference(args, layers)
-        return
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
-    peaks = load_peaks()
+    comm_mod = importlib.import_module(entry.PKG_NAME + ".comm")
     ops = layers.KernelOps(pkg, gemm_workspace=torch.empty(32 << 20, dtype=torch.uint8, device=dev))
     full = _layer_weights(args.workload)
     g = torch.Generator().manual_seed(11)
-    flush_buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=dev)
-    if args.workload == "gptj_layer":
-        B, S = 4, 2048
-        w = layers.GptJLayerWeights.shard(full, 16, 256, 64, rank, world)
+    ident = lambda t, group=None: t
+    tol_abs, tol_rel = 6e-2, 2e-2      # the layer tests' bound: bf16 activations of O(1) through a block
+
+    def to_dev(w):
         for k, v in vars(w).items():
             if torch.is_tensor(v):
                 setattr(w, k, v.to(dev))
+        return w
+
+    # ---- exchange: libixk's NVLink all-reduce where the buffers can be shared, else NCCL
+    comm, comm_note = None, None
+    if world > 1 and not args.nccl:
+        nbytes = 4 * 2048 * 4096 * 2 if args.workload == "gptj_layer" else 1 << 20
+        try:
+            comm = comm_mod.Communicator(pkg, rank, world, nbytes)
+        except Exception as ex:  # noqa: BLE001 - e.g. CUDA IPC not permitted between the ranks' containers
+            comm_note = "libixk exchange buffers could not be shared (%s): NCCL all-reduce" % str(ex).splitlines()[0][:160]
+        ok = torch.tensor([1 if comm is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0 and comm is not None:
+            comm.close()
+            comm, comm_note = None, "a peer could not share its exchange buffer: NCCL all-reduce"
+
+    tp_check = None
+    if args.workload == "gptj_layer":
+        B, S = 4, 2048
+        w = to_dev(layers.GptJLayerWeights.shard(full, 16, 256, 64, rank, world))
         x_host = torch.randn(B, S, 4096, generator=g).bfloat16().pin_memory()
         x = x_host.to(dev)
         rope = layers.rotary_tables(torch.arange(S, device=dev), 64)
-        step = lambda reduce=None: layers.gptj_layer_prefill(x, w, ops, rope=rope, reduce=reduce)
+        step = lambda reduce=None: layers.gptj_layer_prefill(x, w, ops, rope=rope, reduce=reduce, comm=comm)
         work, div, unit, bound = layers.gptj_layer_flops(B, S), 1e12, "TFLOP/s", "tensor"
-        metric = "GPT-J-6B-shaped decoder layer prefill TFLOP/s (bf16, tensor-parallel)"
-        name = f"gptj_layer_prefill_B{B}_S{S}_hidden4096_heads16x256_mlp16384_tp{world}"
         peak = peaks["bf16_tflops"] * world
+        if world > 1:   # once, outside the timed region: the sharded step against the un-sharded layer, same inputs
+            w_full = to_dev(layers.GptJLayerWeights.shard(full, 16, 256, 64, 0, 1))
+            y_ref = layers.gptj_layer_prefill(x, w_full, ops, rope=rope, reduce=ident).float()
+            del w_full
     else:
         B, T = 64, 4096
-        w = layers.GemmaLayerWeights.shard(full, 16, 256, rank, world)
-        for k, v in vars(w).items():
-            if torch.is_tensor(v):
-                setattr(w, k, v.to(dev))
+        w = to_dev(layers.GemmaLayerWeights.shard(full, 16, 256, rank, world))
         hl = 16 // world
         x_host = torch.randn(B, 1, 3072, generator=g).bfloat16().pin_memory()
         x = x_host.to(dev)
-        gk = torch.Generator(device=dev).manual_seed(13 + rank)
-        k_cache = torch.randn(B, T, hl, 256, generator=gk, device=dev).bfloat16()
-        v_cache = torch.randn(B, T, hl, 256, generator=gk, device=dev).bfloat16()
+        # the full cache from one seed on every rank (same device generator, same values); a rank keeps its heads
+        gk = torch.Generator(device=dev).manual_seed(13)
+        k_full = torch.randn(B, T, 16, 256, generator=gk, device=dev, dtype=torch.bfloat16)
+        v_full = torch.randn(B, T, 16, 256, generator=gk, device=dev, dtype=torch.bfloat16)
+        h0 = rank * hl
+        k_cache = k_full[:, :, h0:h0 + hl].contiguous() if world > 1 else k_full
+        v_cache = v_full[:, :, h0:h0 + hl].contiguous() if world > 1 else v_full
         ws = torch.empty(8 << 20, dtype=torch.uint8, device=dev)
         rope = layers.rotary_tables(torch.tensor([T - 1], device=dev), 256)
         step = lambda reduce=None: layers.gemma_decode_step(x, w, k_cache, v_cache, T - 1, ops, workspace=ws, rope=rope,
-                                                            reduce=reduce)
+                                                            reduce=reduce, comm=comm)
         work, div, unit, bound = layers.gemma_decode_bytes(B, T), 1e9, "GB/s", "hbm"
-        metric = "Gemma-7B-shaped decode step GB/s of algorithmic bytes (bf16, tensor-parallel)"
-        name = f"gemma_decode_B{B}_T{T}_hidden3072_heads16x256_mlp24576_tp{world}"
         peak = peaks["hbm_gbs"] * world
+        if world > 1:
+            w_full = to_dev(layers.GemmaLayerWeights.shard(full, 16, 256, 0, 1))
+            y_ref = layers.gemma_decode_step(x, w_full, k_full, v_full, T - 1, ops, workspace=ws, rope=rope,
+                                             reduce=ident).float()
+            del w_full
+        del k_full, v_full
     del full
+    torch.cuda.empty_cache()
 
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
-            import torch.distributed as dist
             dist.barrier()
             torch.cuda.synchronize()
 
@@ -681,37 +822,45 @@ def run_layer(args, rank, world):
         y = step()
         flush_l2(flush_buf)
     barrier()
-    # A layer step is a fixed sequence of ~10 library kernels and ~30 small glue kernels: on one GPU
-    # it is captured once into a CUDA graph and replayed, which removes the launch gaps (the decode
-    # step is launch-bound otherwise).  Multi-GPU runs launch eagerly (NCCL inside the step).
+    if world > 1:
+        err = (y.float() - y_ref).abs()
+        bad = int((err > tol_abs + tol_rel * y_ref.abs()).sum().item())
+        tp_check = {"against": "the un-sharded layer on this GPU, same weights and inputs", "max_abs_err": float(err.max().item()),
+                    "tolerance": f"{tol_abs} + {tol_rel} * |ref|", "elements_outside": bad, "ok": bad == 0}
+        del y_ref, err
+        flag = torch.tensor([bad], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        if int(flag.item()) != 0:
+            raise RuntimeError(f"tensor-parallel {args.workload} disagrees with the un-sharded layer: {tp_check}")
+    # A layer step is a fixed sequence of ~10-15 library kernels: it is captured once into a CUDA
+    # graph and replayed, which removes the launch gaps (the decode step is launch-bound otherwise).
+    # With libixk's all-reduce the exchange is an ordinary kernel inside that graph.  With NCCL the
+    # pieces of the step between the all-reduces are captured as separate graphs and the
+    # all-reduces stay eager calls between the replays (NCCL is never captured here).
     launches_per_step = None
-    use_graph = world == 1 and not args.no_graph
-    if use_graph:
+    launch_mode = "eager"
+    whole_graph = not args.no_graph and (world == 1 or comm is not None)
+    segmented = not args.no_graph and world > 1 and comm is None
+    if whole_graph:
         n_before = pkg.launch_count()
         cap_stream = torch.cuda.Stream()
         cap_stream.wait_stream(torch.cuda.current_stream())
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(cap_stream):
-            with torch.cuda.graph(graph, stream=cap_stream):
+            with torch.cuda.graph(graph, stream=cap_stream, capture_error_mode="thread_local"):
                 y = step()
         torch.cuda.current_stream().wait_stream(cap_stream)
         launches_per_step = pkg.launch_count() - n_before
-        eager_step = step
-        step = lambda: (graph.replay(), y)[1]
-        for _ in range(2):
-            step()
-        torch.cuda.synchronize()
-    # N > 1, opt-in (--graph-segments): the pieces of the step between the all-reduces are captured
-    # as separate CUDA graphs and the all-reduces stay eager NCCL calls between the replays, so
-    # that the host issues a handful of calls per step instead of ~40.
-    segmented = world > 1 and args.graph_segments and not args.no_graph
-    if segmented:
-        import torch.distributed as dist
+        y_graph = y
+        step = lambda: (graph.replay(), y_graph)[1]
+        launch_mode = "CUDA graph replay of the whole step" + (" (libixk NVLink all-reduce inside)" if comm is not None else "")
+    elif segmented:
         n_before = pkg.launch_count()
         cap_stream = torch.cuda.Stream()
         cap_stream.wait_stream(torch.cuda.current_stream())
         pool = torch.cuda.graph_pool_handle()
         plan = []
+        eager = step
         with torch.cuda.stream(cap_stream):
             cur = torch.cuda.CUDAGraph()
             cur.capture_begin(pool=pool, capture_error_mode="thread_local")
@@ -726,12 +875,11 @@ def run_layer(args, rank, world):
                 cur.capture_begin(pool=pool, capture_error_mode="thread_local")
                 return t
 
-            y = step(cut)
+            y_seg = eager(cut)
             cur.capture_end()
             plan.append(cur)
         torch.cuda.current_stream().wait_stream(cap_stream)
         launches_per_step = pkg.launch_count() - n_before
-        y_eager = step().clone()      # the same step launched eagerly, to check the replay against
 
         def step():
             for item in plan:
@@ -739,13 +887,13 @@ def run_layer(args, rank, world):
                     item.replay()
                 else:
                     dist.all_reduce(item)
-            return y
+            return y_seg
+        launch_mode = "CUDA graphs of the pieces between eager NCCL all-reduces"
+    if whole_graph or segmented:
+        y_before = y.clone() if not whole_graph else None
         for _ in range(2):
-            step()
+            y = step()
         barrier()
-        if not torch.equal(step(), y_eager):
-            raise RuntimeError("segmented graph replay and eager launch of the layer step disagree")
-        use_graph = True
     n0 = pkg.launch_count()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -774,42 +922,47 @@ def run_layer(args, rank, world):
     torch.cuda.synchronize()
     e2e_ms = s_ev.elapsed_time(e_ev) / e2e_steps
     if world > 1:
-        import torch.distributed as dist
         t = torch.tensor([total_ms, e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms, e2e_ms = float(t[0].item()), float(t[1].item())
     status = pkg.device_status()
     ms_per_step = total_ms / args.steps
     value = work / (ms_per_step * 1e-3) / div
+    config = layer_config(args.workload, world)
+    config["launch"] = launch_mode
+    config["exchange"] = ("none (one GPU)" if world == 1 else
+                          "libixk NVLink all-reduce (peer loads/stores, device-side flags)" if comm is not None else
+                          (comm_note or "NCCL all-reduce"))
     line = {
-        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": LAYER_METRIC[args.workload], "value": value, "unit": unit, "n_gpus": world, "per_gpu_value": value / world,
+        "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (random-init weights ~N(0,0.02), activations ~N(0,1), seeded)",
-        "config": {"workload": name, "parallelism": f"tp{world} by heads / MLP columns, all-reduce after row-parallel GEMMs",
-                   "l2": "L2 flushed (512 MB read+write) between timed steps",
-                   "launch": ("CUDA graphs between eager all-reduces" if segmented else "CUDA graph replay") if use_graph
-                   else "eager"},
-        "clocks": clk.summary(),
+        "config": config, "clocks": clk.summary(),
         "e2e": {"value": work / (e2e_ms * 1e-3) / div, "unit": unit, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(x_host.numel() * 2), "d2h_bytes_per_step": int(y_host.numel() * 2)},
         "gpu_launches": int(launches),
         "roofline": {"bound": bound, "achieved": value, "peak": peak, "unit": unit, "frac": value / peak, "traffic": None,
-                     "kernel": "whole layer step (libixk GEMM + attention kernels, torch glue, NCCL)",
+                     "kernel": "whole layer step (libixk GEMM, attention, glue and exchange kernels)",
                      "peak_source": f"{world} x {peaks['source']} single-GPU peak"},
         "device_status": status,
     }
-    if world > 1:
-        import torch.distributed as dist
-        dist.barrier()
-        dist.destroy_process_group()
-    if rank == 0:
-        print(json.dumps(line))
+    if tp_check is not None:
+        line["tp_check"] = tp_check
+    if with_cpu and rank == 0 and world == 1:
+        ref = layer_reference(args, full_line=False)
+        line["cpu_baseline"] = ref
+    if comm is not None:
+        comm.close()
+    return line
 
 
-def run_layer_reference(args, layers):
-    """Reference arm of the layer configurations: the un-sharded numpy layer oracle on the host
-    cores, on a bounded sample (one sequence of the batch)."""
+def layer_reference(args, full_line):
+    """CPU arm of the layer configurations: the un-sharded numpy layer oracle on the host cores, on
+    a bounded sample of the batch.  Returns the cpu_baseline object, or the whole reference-arm line."""
+    import importlib
     from oracle import layers_oracle
+    layers = importlib.import_module(entry.PKG_NAME + ".layers")
     full = {k: v.float().numpy() for k, v in _layer_weights(args.workload).items()}
     g = torch.Generator().manual_seed(11)
     times = []
@@ -818,7 +971,6 @@ def run_layer_reference(args, layers):
         x = torch.randn(B, S, 4096, generator=g).bfloat16().float().numpy()[:1]
         work, div, unit, frac = layers.gptj_layer_flops(1, S), 1e12, "TFLOP/s", "1 of 4 sequences"
         fn = lambda: layers_oracle.gptj_layer_prefill(x, full, 16, 256, 64)
-        metric = "GPT-J-6B-shaped decoder layer prefill TFLOP/s (bf16, tensor-parallel)"
     else:
         B, T = 64, 4096
         nb = 8
@@ -827,24 +979,29 @@ def run_layer_reference(args, layers):
         vc = np.random.default_rng(1).standard_normal((nb, T, 16, 256), dtype=np.float32)
         work, div, unit, frac = layers.gemma_decode_bytes(nb, T), 1e9, "GB/s", f"{nb} of 64 sequences (weights read once per sample)"
         fn = lambda: layers_oracle.gemma_decode_step(x, full, kc, vc, T - 1, 16, 256)
-        metric = "Gemma-7B-shaped decode step GB/s of algorithmic bytes (bf16, tensor-parallel)"
-    for i in range(args.warmup + args.steps):
+    passes = (args.warmup + args.steps) if full_line else 2
+    warm = args.warmup if full_line else 1
+    for i in range(passes):
         t0 = time.perf_counter()
         fn()
-        if i >= args.warmup:
+        if i >= warm:
             times.append(time.perf_counter() - t0)
         if sum(times) > 120:
             break
     dt = float(np.mean(times))
     value = work / dt / div
     cores = os.cpu_count() or 1
-    print(json.dumps({
-        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": int(os.environ.get("WORLD_SIZE", 1)),
+    cb = {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": frac + " (%.1f s per pass)" % dt}
+    if not full_line:
+        return cb
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    return {
+        "impl": "reference", "metric": LAYER_METRIC[args.workload], "value": value, "unit": unit, "n_gpus": world,
         "steps": len(times), "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic (random-init weights ~N(0,0.02), activations ~N(0,1), seeded)",
-        "config": {"workload": args.workload, "note": "each step is a bounded sample of the workload: " + frac},
-        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": frac},
-        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random-init weights ~N(0,0.02), activations ~N(0,1), seeded)",
+        "config": layer_config(args.workload, world), "note": "each step is a bounded sample of the workload: " + frac,
+        "cpu_baseline": {**cb, "xla_cpu": probe_xla_cpu()},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
 
 
 def main():
@@ -856,17 +1013,15 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + list(LAYER_WORKLOADS))
     ap.add_argument("--no-others", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-graph", action="store_true", help="layer workloads: launch eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--graph-segments", action="store_true",
-                    help="layer workloads at N > 1: replay CUDA graphs of the pieces between the (eager) all-reduces")
+    ap.add_argument("--nccl", action="store_true",
+                    help="layer workloads at N > 1: exchange through NCCL instead of libixk's NVLink all-reduce")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-timed steps only (no e2e, no CPU baseline): the command profiled under ncu")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.workload in LAYER_WORKLOADS:
-        run_layer(args, rank, world)
-    elif args.impl == "reference":
+    if args.impl == "reference":
         run_reference(args, rank, world)
     else:
         if world != args.gpus and world == 1 and args.gpus > 1:

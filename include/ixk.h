@@ -9,6 +9,9 @@
  * Every function below replaces one of those, with plain pointers and sizes
  * only.  All buffers are caller-owned device memory; nothing is retained past
  * the call; kernels are enqueued on the caller's stream and never synchronised.
+ * No call allocates device memory except ixk_comm_create (a set-up call).
+ * The first call of any entry point on a device looks up and clears the device's status word
+ * (a host-side query and a 4-byte memset on the default stream): make it outside stream capture.
  * No entry point except the *_workspace_bytes queries is valid without a
  * B200-class GPU: there is no CPU fallback.
  */
@@ -270,11 +273,78 @@ int ixk_residual_add(int dtype, int64_t rows, int64_t cols, const void* x,
                      const void* partial, const void* bias, void* out,
                      void* cuda_stream);
 
+/* ------------------------------------------------------ all-reduce over NVLink */
+/* The exchange step of a tensor-parallel layer: the partial sums of a row-parallel projection,
+ * one per GPU, summed into every GPU.  Replaces sycl_allreduce (xla/service/gpu/ccl_ops.h:40-46,
+ * ccl_ops.cc:604-789) and its kernel allreduce_dpcpp (ccl_ops.cc:98-246): ranks read each other's
+ * buffers directly (NVLink peer loads and stores), 16-bit floats are combined in fp32
+ * (ccl_ops.cc:674-676).  The reference's participants are threads of one process that meet on the
+ * host; here a rank is a process (or a thread) per GPU and the ranks meet on the device, through
+ * flags in each other's memory, so a call costs no host synchronisation and a captured step
+ * replays as a CUDA graph.
+ *
+ * Set-up (the only calls of this library that allocate device memory): every rank creates a
+ * communicator, which allocates `buffer_bytes` of exchange buffer (plus 8 KB of flags) on the
+ * current device and returns an IPC handle; the host passes all handles to every rank (in rank
+ * order) and each rank connects.  Ranks that share a process skip IPC and connect with the peers'
+ * ixk_comm_base() pointers (peer access between the devices must be enabled by the host).
+ * After connecting, and again before destroying, the host must make the ranks meet (any host
+ * barrier): a peer may not touch a buffer that is not there yet, or any more.
+ *
+ * Use: a rank's contribution is whatever lies at byte offset `in_offset` of ITS OWN exchange buffer
+ * (ixk_comm_buffer(); the producing kernel writes there directly) — the same offset and count on
+ * every rank.  `out` is this rank's result.  If `out` is the contribution itself (in place), or
+ * lies elsewhere inside the exchange buffer (again the same offset on every rank) and the message
+ * is at least 1 MiB, each rank reduces one slice and writes it to all ranks (2 x the message over
+ * NVLink); otherwise each rank reads all contributions in full (one exchange, for latency-bound
+ * messages) and `out` must not overlap the contribution.  Ranks are combined in rank order, so every
+ * rank ends up with the same bits.  Calls on one communicator must be issued in the same order on
+ * every rank and must not overlap on the GPU.  A rank whose peers do not arrive within the wait
+ * limit (about a second unless changed) gives up: the kernel returns, ixk_device_status reports
+ * IXK_DEVICE_TIMEOUT with site 301 (before reading) or 302 (before leaving), and the communicator
+ * must be destroyed. */
+typedef struct ixk_comm ixk_comm;
+#define IXK_COMM_HANDLE_BYTES 64
+#define IXK_COMM_MAX_RANKS 8
+/* ReductionKind of the reference call (ccl_ops.cc:656-779). */
+typedef enum ixk_reduce_kind {
+  IXK_REDUCE_SUM = 0, IXK_REDUCE_PRODUCT = 1, IXK_REDUCE_MIN = 2, IXK_REDUCE_MAX = 3
+} ixk_reduce_kind;
+int ixk_comm_create(int rank, int world, size_t buffer_bytes, ixk_comm** comm,
+                    void* handle_out /* IXK_COMM_HANDLE_BYTES, may be NULL */);
+int ixk_comm_connect_ipc(ixk_comm* comm, const void* handles /* world x IXK_COMM_HANDLE_BYTES */);
+int ixk_comm_connect_pointers(ixk_comm* comm, void* const* peer_bases /* world x ixk_comm_base() */);
+void* ixk_comm_base(ixk_comm* comm);
+void* ixk_comm_buffer(ixk_comm* comm);
+size_t ixk_comm_buffer_bytes(ixk_comm* comm);
+int ixk_comm_set_wait_limit(ixk_comm* comm, long long cycles);
+int ixk_comm_destroy(ixk_comm* comm);
+/* dtype in {BF16, F16, F32}; kind: ixk_reduce_kind; count in elements. */
+int ixk_all_reduce(ixk_comm* comm, int dtype, int kind, size_t in_offset, void* out,
+                   size_t count, void* cuda_stream);
+/* All-reduce fused with the residual add that follows a row-parallel projection:
+ *   out = x + round(sum over ranks [+ bias[col]])      [rows, cols] dense
+ * the same bits as ixk_all_reduce followed by ixk_residual_add.  out may alias x, but not the
+ * contribution. */
+int ixk_all_reduce_residual(ixk_comm* comm, int dtype, size_t in_offset, const void* x,
+                            const void* bias, void* out, int64_t rows, int64_t cols,
+                            void* cuda_stream);
+/* [begin, end) in elements of the slice rank `rank` reduces in the two-shot scheme: whole 16-byte
+ * vectors split evenly, the last rank takes the remainder (ccl_ops.cc:103-114).  Host arithmetic. */
+int ixk_all_reduce_slice(int dtype, size_t count, int rank, int world, size_t* begin, size_t* end);
+
 /* ------------------------------------------------------------ diagnostics */
 /* Every device-side wait in the tensor-core kernels is bounded; a wait that
  * gives up records a code in a per-device status word and the kernel drains and
  * returns.  Reads and clears that word (synchronises the device).  0 = clean. */
 int ixk_device_status(int* status_word);
+/* Exercises that mechanism on purpose: launches one small CTA whose first warp waits, with a
+ * budget of `limit_cycles` (at most 1e8, i.e. well under 0.1 s), for a barrier phase that nothing
+ * completes, and whose second warp depends on the first.  The kernel returns by itself; afterwards
+ * ixk_device_status reports IXK_DEVICE_TIMEOUT with site code 901 and clears the word, and the
+ * device is as usable as before.  cycles_out_device (device memory, may be NULL) receives the
+ * cycles the CTA spent.  No counterpart in the reference, whose kernels have no device-side waits. */
+int ixk_selftest_bounded_wait(long long limit_cycles, long long* cycles_out_device, void* cuda_stream);
 /* Number of kernels this library has launched from this process (all threads). */
 uint64_t ixk_launch_count(void);
 

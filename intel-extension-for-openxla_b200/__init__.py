@@ -101,6 +101,19 @@ ABI_SYMBOLS = {
     "ixk_residual_add": (ctypes.c_int, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, _vp, _vp, _vp, _vp, _vp]),
     "ixk_fmha_fwd_workspace_bytes": (_sz, [ctypes.POINTER(_FmhaDesc)]),
     "ixk_fmha_fwd_static_scratch": (ctypes.c_int, [ctypes.POINTER(_FmhaDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "ixk_comm_create": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, ctypes.POINTER(_vp), _vp]),
+    "ixk_comm_connect_ipc": (ctypes.c_int, [_vp, _vp]),
+    "ixk_comm_connect_pointers": (ctypes.c_int, [_vp, ctypes.POINTER(_vp)]),
+    "ixk_comm_base": (_vp, [_vp]),
+    "ixk_comm_buffer": (_vp, [_vp]),
+    "ixk_comm_buffer_bytes": (_sz, [_vp]),
+    "ixk_comm_set_wait_limit": (ctypes.c_int, [_vp, ctypes.c_longlong]),
+    "ixk_comm_destroy": (ctypes.c_int, [_vp]),
+    "ixk_all_reduce": (ctypes.c_int, [_vp, ctypes.c_int, ctypes.c_int, _sz, _vp, _sz, _vp]),
+    "ixk_all_reduce_residual": (ctypes.c_int, [_vp, ctypes.c_int, _sz, _vp, _vp, _vp, ctypes.c_int64, ctypes.c_int64, _vp]),
+    "ixk_all_reduce_slice": (ctypes.c_int, [ctypes.c_int, _sz, ctypes.c_int, ctypes.c_int, ctypes.POINTER(_sz),
+                                            ctypes.POINTER(_sz)]),
+    "ixk_selftest_bounded_wait": (ctypes.c_int, [ctypes.c_longlong, _vp, _vp]),
     "ixk_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
     "ixk_launch_count": (ctypes.c_uint64, []),
 }

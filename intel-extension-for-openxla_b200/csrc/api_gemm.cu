@@ -194,6 +194,7 @@ int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, 
 // are evenly spaced, A being read through a batch-less tensor map; otherwise as three launches.
 int run_qkv(int dtype, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
             const void* bias, void* out0, void* out1, void* out2, int64_t ldc, void* stream) {
+  clear_error();
   if (dtype != IXK_BF16 && dtype != IXK_F16)
     return fail(IXK_UNIMPLEMENTED, "QKV GEMM takes BF16 or F16 (gemm.cc instantiates sycl::half and bf16 only)");
   if (m < 0 || n < 0 || k < 0) return fail(IXK_INVALID_ARGUMENT, "negative dimension");

@@ -58,7 +58,7 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 // One CTA per row; the row stays in registers between the statistics and the write.
 template <bool kBf16, bool kRms>
-__global__ void __launch_bounds__(kNormThreads) row_norm_kernel(const uint4* __restrict__ x, uint4* __restrict__ y,
+__global__ void __launch_bounds__(kNormThreads) row_norm_kernel(const uint4* x, uint4* y,  // may be one buffer: no __restrict__
                                                                 int cols, int64_t ldx_vec, int64_t ldy_vec, float eps) {
   __shared__ float scratch[kNormThreads / 32];
   const int nvec = cols / kVecElems;
@@ -147,8 +147,8 @@ __global__ void rotary_kernel(uint4* __restrict__ x, const float4* __restrict__ 
 // out = x + round(partial + bias): the sum with the bias is rounded to the storage type first,
 // like a framework that materialises (partial + bias) before the residual add.
 template <bool kBf16>
-__global__ void residual_add_kernel(const uint4* __restrict__ x, const uint4* __restrict__ partial,
-                                    const uint4* __restrict__ bias, uint4* __restrict__ out, int64_t total_vecs,
+__global__ void residual_add_kernel(const uint4* x, const uint4* partial,  // out may alias either: no __restrict__
+                                    const uint4* __restrict__ bias, uint4* out, int64_t total_vecs,
                                     int vecs_per_row) {
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vecs;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {

@@ -93,9 +93,10 @@ struct AbortCtl {
   int* status_word;         // in global memory; first failure code wins
 };
 
-// Bounded wait.  `code` identifies the waiting site in the status word.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtl& ctl,
-                                          int code) {
+// Bounded wait.  `code` identifies the waiting site in the status word; `limit` is the cycle
+// budget (the kernels use kWaitCycleLimit; the self-test passes a short one).
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, const AbortCtl& ctl,
+                                                int code, long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
@@ -103,13 +104,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ffu) == 0) {
       if (*ctl.cta_abort != 0) return false;
-      if (clock64() - t0 > kWaitCycleLimit) {
+      if (clock64() - t0 > limit) {
         *ctl.cta_abort = 1;
         atomicCAS(ctl.status_word, 0, code);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtl& ctl,
+                                          int code) {
+  return mbar_wait_limit(bar, parity, ctl, code, kWaitCycleLimit);
 }
 
 // Register re-partitioning between warpgroups (all four warps of a warpgroup execute it).

@@ -170,13 +170,17 @@ class GptJLayerWeights:
             heads_local=num_heads // world, head_dim=head_dim, rotary_dim=rotary_dim)
 
 
-def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None, rope=None, reduce=None) -> torch.Tensor:
+def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None, rope=None, reduce=None,
+                       comm=None) -> torch.Tensor:
     """GPT-J block, prefill: y = x + Attn(LN(x)) + MLP(LN(x)), x [B, S, hidden] replicated on every
     rank.  The attention-output and MLP-down partial sums are added locally (the second GEMM takes
     the first as its C operand with beta = 1), so the block needs ONE all-reduce.  `rope` may carry
     precomputed (cos, sin) tables for positions 0..S-1, which keeps the step free of host work (and
     capturable in a CUDA graph).  `reduce(t, group)` replaces the all-reduce call (a caller that
-    records the step in pieces around the exchange passes its own)."""
+    records the step in pieces around the exchange passes its own).  With `comm` (a
+    comm.Communicator) the partial sum is produced straight into the NVLink exchange buffer and
+    reduced there by libixk's own all-reduce kernel: no NCCL call, so the whole step is one stream of
+    kernel launches that a CUDA graph can hold."""
     B, S, hidden = x.shape
     hl, hd = w.heads_local, w.head_dim
     h = _glue(ops, "layer_norm", layer_norm)(x).view(B * S, hidden)
@@ -186,10 +190,14 @@ def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None, ro
     q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))        # [B, hl, S, hd] views, no copies
     ctx = torch.empty(B, S, hl, hd, dtype=x.dtype, device=x.device)
     ops.attention(q, k, v, ctx.permute(0, 2, 1, 3), scale=1.0 / math.sqrt(hd), causal=True)
-    attn_partial = ops.gemm(ctx.view(B * S, hl * hd), w.wo)
+    slot = comm.view(0, (B * S, hidden), x.dtype) if comm is not None else None
+    attn_partial = ops.gemm(ctx.view(B * S, hl * hd), w.wo, out=slot)
     up = ops.gemm(h, w.w1, bias=w.b1, epilogue="BIAS_GELU")
     partial = ops.gemm(up, w.w2, c=attn_partial, beta=1.0, out=attn_partial)   # in place: C aliases D
-    partial = (reduce or all_reduce_sum)(partial, group)
+    if comm is not None:
+        partial = comm.all_reduce(partial)              # in place in the exchange buffer
+    else:
+        partial = (reduce or all_reduce_sum)(partial, group)
     return _glue(ops, "residual_add", _residual_add_torch)(x, partial, w.b2)
 
 
@@ -225,11 +233,15 @@ class GemmaLayerWeights:
 
 
 def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                      position: int, ops, group=None, workspace=None, rope=None, reduce=None) -> torch.Tensor:
+                      position: int, ops, group=None, workspace=None, rope=None, reduce=None, comm=None) -> torch.Tensor:
     """One new token per sequence: x [B, 1, hidden]; k_cache / v_cache [B, T, heads_local, head_dim]
     (this rank's heads) are updated in place at `position` and attended over [0, position].
     Two all-reduces: after the attention output projection and after the MLP down projection.
-    `rope` may carry the precomputed (cos, sin) row for `position` (no host work in the step)."""
+    `rope` may carry the precomputed (cos, sin) row for `position` (no host work in the step).
+    With `comm` (a comm.Communicator) each row-parallel projection writes its partial into the
+    NVLink exchange buffer and one libixk kernel does the exchange and the residual add that
+    follows it (the two partials use different offsets, so the second exchange never waits for
+    readers of the first)."""
     B, _, hidden = x.shape
     hl, hd = w.heads_local, w.head_dim
     norm = _glue(ops, "rms_norm", rms_norm)
@@ -246,13 +258,19 @@ def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tens
     ops.attention(q, k_cache[:, :T].permute(0, 2, 1, 3), v_cache[:, :T].permute(0, 2, 1, 3),
                   ctx.permute(0, 2, 1, 3), scale=1.0 / math.sqrt(hd), causal=False, workspace=workspace)
     reduce = reduce or all_reduce_sum
-    attn = reduce(ops.gemm(ctx.view(B, hl * hd), w.wo), group)
-    x1 = add(x, attn)
+    if comm is not None:
+        nbytes = (B * hidden * x.element_size() + 255) // 256 * 256
+        part = ops.gemm(ctx.view(B, hl * hd), w.wo, out=comm.view(0, (B, hidden), x.dtype))
+        x1 = comm.all_reduce_residual(part, x)
+    else:
+        x1 = add(x, reduce(ops.gemm(ctx.view(B, hl * hd), w.wo), group))
     h2 = norm(x1).view(B, hidden)
     gate = ops.gemm(h2, w.wgate, epilogue="GELU")
     up = ops.gemm(h2, w.wup)
-    down = reduce(ops.gemm(gate * up, w.wdown), group)
-    return add(x1, down)
+    if comm is not None:
+        part = ops.gemm(gate * up, w.wdown, out=comm.view(nbytes, (B, hidden), x.dtype))
+        return comm.all_reduce_residual(part, x1)
+    return add(x1, reduce(ops.gemm(gate * up, w.wdown), group))
 
 
 def gemma_decode_bytes(B, T, hidden=3072, heads=16, head_dim=256, ffn=24576, elem=2):

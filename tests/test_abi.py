@@ -178,6 +178,30 @@ def test_python_descriptor_checks_that_shapes_agree(pkg):
         pkg._fmha_desc(q, ke.half(), ke, None, q, 1.0, False, 0.0)
 
 
+def test_all_reduce_slices_and_set_up_errors(pkg):
+    """The two-shot all-reduce splits whole 16-byte vectors evenly and gives the remainder to the
+    last rank (ccl_ops.cc:103-114); creating a communicator needs a device."""
+    lib = pkg.load_library()
+    b, e = ctypes.c_size_t(), ctypes.c_size_t()
+    count = 8 * 1001 + 5                       # 1001 vectors of 8 bf16 and 5 loose elements
+    covered = []
+    for r in range(4):
+        assert lib.ixk_all_reduce_slice(pkg.IXK_BF16, count, r, 4, ctypes.byref(b), ctypes.byref(e)) == pkg.IXK_OK
+        covered.append((b.value, e.value))
+    assert covered == [(0, 2000), (2000, 4000), (4000, 6000), (6000, count)]
+    assert lib.ixk_all_reduce_slice(pkg.IXK_F32, 10, 0, 1, ctypes.byref(b), ctypes.byref(e)) == pkg.IXK_OK
+    assert (b.value, e.value) == (0, 10)
+    assert lib.ixk_all_reduce_slice(pkg.IXK_F32, 10, 3, 2, ctypes.byref(b), ctypes.byref(e)) == pkg.IXK_INVALID_ARGUMENT
+    import torch
+    if not torch.cuda.is_available():
+        h = ctypes.c_void_p()
+        assert lib.ixk_comm_create(0, 2, 1 << 20, ctypes.byref(h), None) == pkg.IXK_NO_DEVICE
+        assert h.value is None
+        assert lib.ixk_selftest_bounded_wait(1000, None, None) == pkg.IXK_NO_DEVICE
+    assert lib.ixk_all_reduce(None, 0, 0, 0, None, 16, None) == pkg.IXK_INVALID_ARGUMENT
+    assert lib.ixk_comm_destroy(None) == pkg.IXK_OK
+
+
 def test_missing_library_fails_loudly(pkg, monkeypatch):
     """No silent fallback: without libixk.so the package raises."""
     monkeypatch.setattr(pkg, "_LIB", None)

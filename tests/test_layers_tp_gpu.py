@@ -1,6 +1,9 @@
-"""GPU, two ranks over NCCL (skipped on a single-GPU machine): the tensor-parallel layer drivers
-with the real kernels — TP=2 must agree with the un-sharded numpy layer oracle, and the
-all-reduce must leave both ranks with the same bits."""
+"""GPU, two ranks, one process per GPU (skipped on a single-GPU machine): the tensor-parallel layer
+drivers with the real kernels.  TP=2 must agree with the un-sharded numpy layer oracle and leave
+both ranks with the same bits, with the exchange done by NCCL and by libixk's own NVLink
+all-reduce (exchange buffers shared through CUDA IPC); the two must agree bit for bit at two
+ranks (a sum of two 16-bit values is exact in fp32 and rounded once either way).  The all-reduce
+itself is checked against ncclAllReduce on integer data, one-shot and two-shot."""
 import os
 import socket
 import sys
@@ -48,13 +51,82 @@ def _worker(rank, world, port, q):
         gathered = [torch.empty_like(y) for _ in range(world)]
         dist.all_gather(gathered, y)
         same = all(torch.equal(gathered[0], t) for t in gathered)
-        q.put((rank, err, same, pkg.device_status()))
+
+        # ---- libixk's all-reduce against ncclAllReduce, bit for bit on integers
+        comm_mod = importlib.import_module("ixk_b200.comm")
+        comm = comm_mod.Communicator(pkg, rank, world, 16 << 20)
+        checks = {}
+        gi = torch.Generator(device=dev).manual_seed(100 + rank)
+        for name, n in (("one_shot", 64 * 3072), ("two_shot", 3 * 1024 * 1024 + 8), ("tail", 1000 + 3)):
+            for dt in (torch.bfloat16, torch.float32):
+                v = torch.randint(-60, 60, (n,), generator=gi, device=dev).to(dt)
+                slot = comm.view(0, (n,), dt)
+                slot.copy_(v)
+                want_ar = v.clone()
+                dist.all_reduce(want_ar)
+                priv = torch.empty_like(v)
+                comm.all_reduce(slot, out=priv)                # result to a private buffer: one-shot
+                torch.cuda.synchronize()
+                ok_priv = torch.equal(priv, want_ar)
+                comm.all_reduce(slot)                          # in place in the exchange buffer: two-shot when large
+                torch.cuda.synchronize()
+                checks[f"{name}_{dt}"] = ok_priv and torch.equal(slot, want_ar)
+        # many calls back to back (the flags' generation counters, no host sync in between)
+        slot = comm.view(0, (4096,), torch.float32)
+        slot.fill_(1.0)
+        for _ in range(20):
+            comm.all_reduce(slot)
+        torch.cuda.synchronize()
+        checks["repeat"] = bool((slot == float(world) ** 20).all())
+
+        # ---- the GPT-J block again, exchange through libixk
+        y2 = layers.gptj_layer_prefill(x.to(dev), w, layers.KernelOps(pkg), comm=comm)
+        checks["gptj_comm_equals_nccl"] = torch.equal(y, y2)
+
+        # ---- Gemma decode step, TP=2: NCCL exchange, libixk exchange, CUDA-graph replay of the latter
+        hidden, heads, hd, ffn, B, T = 384, 4, 256, 768, 6, 900
+        g = torch.Generator().manual_seed(2)
+        full = {"wqkv": r(hidden, 3 * heads * hd), "wo": r(heads * hd, hidden), "wgate": r(hidden, ffn),
+                "wup": r(hidden, ffn), "wdown": r(ffn, hidden)}
+        xg = torch.randn(B, 1, hidden, generator=g).bfloat16()
+        kc = torch.randn(B, T, heads, hd, generator=g).bfloat16()
+        vc = torch.randn(B, T, heads, hd, generator=g).bfloat16()
+        h0, h1 = layers.shard_range(heads, rank, world)
+        wg = layers.GemmaLayerWeights.shard({k: v.to(dev) for k, v in full.items()}, heads, hd, rank, world)
+        want = layers_oracle.gemma_decode_step(f(xg), {k: f(v) for k, v in full.items()}, f(kc), f(vc), T - 1, heads, hd)
+        ops = layers.KernelOps(pkg)
+        local = lambda c: c[:, :, h0:h1].contiguous().to(dev)
+        y_nccl = layers.gemma_decode_step(xg.to(dev), wg, local(kc), local(vc), T - 1, ops)
+        y_comm = layers.gemma_decode_step(xg.to(dev), wg, local(kc), local(vc), T - 1, ops, comm=comm)
+        err_gemma = float(np.abs(f(y_nccl) - want).max())
+        checks["gemma_comm_equals_nccl"] = torch.equal(y_nccl, y_comm)
+        # the step with its two exchanges inside one CUDA graph, replayed three times
+        kd, vd, xd = local(kc), local(vc), xg.to(dev)
+        ws = torch.empty(8 << 20, dtype=torch.uint8, device=dev)
+        rope = layers.rotary_tables(torch.tensor([T - 1], device=dev), hd)
+        step = lambda: layers.gemma_decode_step(xd, wg, kd, vd, T - 1, ops, workspace=ws, rope=rope, comm=comm)
+        step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        cap = torch.cuda.Stream()
+        cap.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(cap):
+            with torch.cuda.graph(graph, stream=cap, capture_error_mode="thread_local"):
+                y_graph = step()
+        torch.cuda.current_stream().wait_stream(cap)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        checks["gemma_graph_equals_eager"] = torch.equal(y_graph, y_comm)
+        comm.close()
+        q.put((rank, err, same, pkg.device_status(), err_gemma, checks))
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.timeout(600)
-def test_gptj_block_tp2_nccl():
+def test_layers_and_all_reduce_tp2():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     ctx = mp.get_context("spawn")
@@ -67,6 +139,8 @@ def test_gptj_block_tp2_nccl():
     for p in procs:
         p.join(60)
         assert p.exitcode == 0
-    for rank, err, same, status in results:
+    for rank, err, same, status, err_gemma, checks in results:
         assert err < 6e-2, (rank, err)
+        assert err_gemma < 6e-2, (rank, err_gemma)
         assert same and status == 0
+        assert all(checks.values()), (rank, {k: v for k, v in checks.items() if not v})
