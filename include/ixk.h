@@ -53,7 +53,9 @@ typedef enum ixk_dtype {
   IXK_F16 = 1,
   IXK_F32 = 2,
   IXK_F8E4M3 = 3, /* e4m3fn: no inf, max 448   */
-  IXK_F8E5M2 = 4  /* e5m2: IEEE-like, max 57344 */
+  IXK_F8E5M2 = 4, /* e5m2: IEEE-like, max 57344 */
+  IXK_S8 = 5,     /* GEMM operands of the (S8,S8,S32) triple */
+  IXK_S32 = 6     /* its output */
 } ixk_dtype;
 
 /* MatrixLayout::Order as read from the "*_order" attributes
@@ -69,8 +71,9 @@ typedef enum ixk_epilogue {
   IXK_EPILOGUE_BIAS = 3,
   IXK_EPILOGUE_BIAS_RELU = 4,
   IXK_EPILOGUE_BIAS_GELU = 5,
-  IXK_EPILOGUE_GELU_AUX = 6,     /* rejected, as in the reference (onednn_matmul_utils.cc:321-322) */
-  IXK_EPILOGUE_BIAS_GELU_AUX = 7 /* rejected, as above */
+  IXK_EPILOGUE_GELU_AUX = 6,     /* second result: ixk_gemm_aux only (the reference rejects it,
+                                    onednn_matmul_utils.cc:321-322, :452-453) */
+  IXK_EPILOGUE_BIAS_GELU_AUX = 7 /* as above */
 } ixk_epilogue;
 
 /* One operand of the GEMM custom call: the six "{lhs,rhs,output}_*" attributes
@@ -93,8 +96,9 @@ typedef struct ixk_gemm_desc {
   ixk_matrix_layout rhs;    /* B: [K, N] */
   ixk_matrix_layout output; /* D (and C, which XLA aliases with D when beta != 0): [M, N] */
   int64_t batch_size;
-  float alpha;              /* must be 1, as in the reference (onednn_matmul_utils.cc:438) */
-  float beta;               /* D = act(A.B + bias + beta*C); any real value (the reference's
+  float alpha;              /* any finite value (the reference CHECKs alpha == 1,
+                               onednn_matmul_utils.cc:438) */
+  float beta;               /* D = act(alpha*A.B + bias + beta*C); any finite value (the reference's
                                XeTLA path only takes 0 or 1, onednn_matmul_utils.cc:262-270) */
   int32_t epilogue;         /* ixk_epilogue */
   int32_t reserved;         /* must be 0 */
@@ -105,7 +109,7 @@ typedef struct ixk_gemm_desc {
  * (onednn_matmul_utils.cc:533-621) → hgemm_* kernels
  * (xetla/gemm/hgemm_impl.h:101-459) / dnnl::matmul (onednn_matmul_utils.cc:394-491).
  *
- *   D = act(A.B + bias[n] + beta*C)          fp32 accumulate, one rounding to D's type
+ *   D = act(alpha*A.B + bias[n] + beta*C)    fp32 accumulate, one rounding to D's type
  *
  * (the residual is summed before the activation, as oneDNN's append_sum followed
  * by the eltwise post-op does, onednn_matmul_utils.cc:434-449.)
@@ -113,10 +117,15 @@ typedef struct ixk_gemm_desc {
  * of A's type, N being the column count AFTER a column-major output has been
  * rewritten as D^T = B^T.A^T (onednn_matmul_utils.cc:520-530, bias dims :363-365).
  * c may be NULL iff beta == 0; c may alias d.  bias must be non-NULL exactly for
- * the BIAS* epilogues.  Type triples: (BF16,BF16,BF16) (F16,F16,F16)
- * (BF16,BF16,F32) (F16,F16,F32); others → IXK_UNIMPLEMENTED.
+ * the BIAS* epilogues.  Type triples (lhs, rhs, output), the list of RunGemm
+ * (onednn_matmul_utils.cc:605-610): (BF16,BF16,BF16) (F16,F16,F16) (BF16,BF16,F32) (F16,F16,F32);
+ * (F32,F32,F32), computed on the tensor cores in TF32 — operands cut to 10 mantissa bits,
+ * products summed in fp32 — which is the reference's XLA_FP32_MATH_MODE=TF32 setting
+ * (xla/service/onednn_util.h:53-70), there is no full-fp32 mode here; (S8,S8,S32), exact integer
+ * arithmetic, DEFAULT epilogue with alpha = 1 and beta = 0 only.  Others → IXK_UNIMPLEMENTED.
  * Requirements (else IXK_INVALID_ARGUMENT / IXK_UNIMPLEMENTED): pointers 16-byte
- * aligned, leading_dim_stride * sizeof(element) a multiple of 16 for A and B.
+ * aligned, leading_dim_stride * sizeof(element) a multiple of 16 for A and B.  bias has A's
+ * type for 16-bit operands and the output's type otherwise.
  * workspace is optional scratch (the reference hands its scratch allocator down
  * this path, sycl_onednn.h:37).  ixk_gemm_workspace_bytes returns what a problem
  * can use: non-zero only for skinny problems (M <= 128, one batch, a long K),
@@ -127,6 +136,31 @@ int ixk_gemm(const ixk_gemm_desc* desc, const void* a, const void* b,
              const void* c, const void* bias, void* d, void* workspace,
              size_t workspace_bytes, void* cuda_stream);
 size_t ixk_gemm_workspace_bytes(const ixk_gemm_desc* desc);
+
+/* The two epilogues with an auxiliary output (GELU_AUX, BIAS_GELU_AUX of
+ * onednn_matmul_utils.h:42-43, which the reference declares but answers with "Unsupported
+ * Activation mode", onednn_matmul_utils.cc:321-322):
+ *   aux = alpha*A.B + bias[n] + beta*C      (what the activation is applied to, D's type)
+ *   D   = gelu_tanh(aux)
+ * aux has the output's order and shape with its own pitch aux_leading_dim_stride (elements),
+ * batches dense.  Everything else as ixk_gemm (no split-K workspace: the pass is single). */
+int ixk_gemm_aux(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c,
+                 const void* bias, void* d, void* aux, int64_t aux_leading_dim_stride,
+                 void* cuda_stream);
+
+/* Which buffer of the "__cublas$lt$matmul" custom call is which: the operand unpacking of
+ * SyclLtMatmul (sycl_custom_call.cc:167-205) as a plain function, for an XLA FFI handler to
+ * call (csrc/xla_ffi_shim.cc) and for tests without XLA.  Indices into the call's operand list /
+ * result list; -1 = absent. */
+typedef struct ixk_ffi_operands {
+  int32_t lhs_arg, rhs_arg;
+  int32_t c_arg;      /* 2 when beta != 0 (XLA aliases it with the D result) */
+  int32_t bias_arg;   /* 2, or 3 behind C, for the BIAS* epilogues */
+  int32_t d_result;   /* 1 when the epilogue has an auxiliary output, else 0 */
+  int32_t aux_result; /* 0 for the *_AUX epilogues */
+} ixk_ffi_operands;
+int ixk_ffi_select_operands(int epilogue, float beta, int num_args, int num_results,
+                            ixk_ffi_operands* out);
 
 /* fp8 scaled GEMM.  No counterpart kernel exists in the reference (its RunGemm
  * has no fp8 case, onednn_matmul_utils.cc:605-610); the contract is the one of
@@ -202,8 +236,11 @@ size_t ixk_fmha_fwd_workspace_bytes(const ixk_fmha_desc* desc);
  * The call allocates nothing and frees nothing.
  *   - A problem whose ixk_fmha_fwd_workspace_bytes(desc) exceeds IXK_STATIC_SCRATCH_BYTES is
  *     refused with IXK_WORKSPACE_TOO_SMALL and nothing is launched; use ixk_fmha_fwd then.
- *   - The first call on each device looks up the array's device address (a host-side query, no
- *     allocation).  Make that first call outside any stream capture.
+ *   - The first call on each device looks up the array's device address.  The call itself
+ *     allocates nothing, but with CUDA's lazy module loading it can be the moment at which the
+ *     runtime loads the part of the library image that holds the array, i.e. when the device
+ *     memory behind it is actually reserved.  Make that first call at start-up, outside any stream
+ *     capture; from the second call on, the free device memory does not change.
  *   - All calls on a device share the one array, which still holds the previous call's partials:
  *     the kernels overwrite every element they later read, so nothing needs clearing, but two
  *     calls that may overlap on the GPU (different streams, no ordering between them) race on it.

@@ -31,14 +31,14 @@ __all__ = [
 
 IXK_OK, IXK_INVALID_ARGUMENT, IXK_UNIMPLEMENTED, IXK_WORKSPACE_TOO_SMALL = 0, 1, 2, 3
 IXK_CUDA_ERROR, IXK_NO_DEVICE, IXK_DEVICE_TIMEOUT = 4, 5, 6
-IXK_BF16, IXK_F16, IXK_F32, IXK_F8E4M3, IXK_F8E5M2 = 0, 1, 2, 3, 4
+IXK_BF16, IXK_F16, IXK_F32, IXK_F8E4M3, IXK_F8E5M2, IXK_S8, IXK_S32 = 0, 1, 2, 3, 4, 5, 6
 ROW_MAJOR, COL_MAJOR = 0, 1
 # SYCLGemm::GemmBackendEpilogue (xla/service/gpu/onednn_matmul_utils.h:35-44)
 EPILOGUES = ("DEFAULT", "RELU", "GELU", "BIAS", "BIAS_RELU", "BIAS_GELU", "GELU_AUX", "BIAS_GELU_AUX")
 
 _TORCH_TO_IXK = {
     torch.bfloat16: IXK_BF16, torch.float16: IXK_F16, torch.float32: IXK_F32,
-    torch.float8_e4m3fn: IXK_F8E4M3, torch.float8_e5m2: IXK_F8E5M2,
+    torch.float8_e4m3fn: IXK_F8E4M3, torch.float8_e5m2: IXK_F8E5M2, torch.int8: IXK_S8, torch.int32: IXK_S32,
 }
 
 
@@ -60,6 +60,11 @@ class _GemmDesc(ctypes.Structure):
     _fields_ = [("lhs", _MatrixLayout), ("rhs", _MatrixLayout), ("output", _MatrixLayout),
                 ("batch_size", ctypes.c_int64), ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
                 ("epilogue", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
+class _FfiOperands(ctypes.Structure):
+    _fields_ = [("lhs_arg", ctypes.c_int32), ("rhs_arg", ctypes.c_int32), ("c_arg", ctypes.c_int32),
+                ("bias_arg", ctypes.c_int32), ("d_result", ctypes.c_int32), ("aux_result", ctypes.c_int32)]
 
 
 class _FmhaDesc(ctypes.Structure):
@@ -86,6 +91,9 @@ ABI_SYMBOLS = {
     "ixk_version": (ctypes.c_char_p, []),
     "ixk_gemm": (ctypes.c_int, [ctypes.POINTER(_GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "ixk_gemm_workspace_bytes": (_sz, [ctypes.POINTER(_GemmDesc)]),
+    "ixk_gemm_aux": (ctypes.c_int, [ctypes.POINTER(_GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int64, _vp]),
+    "ixk_ffi_select_operands": (ctypes.c_int, [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_int,
+                                               ctypes.POINTER(_FfiOperands)]),
     "ixk_gemm_fp8": (ctypes.c_int, [ctypes.POINTER(_GemmDesc), _vp, _vp, _vp, _vp, _vp, ctypes.c_float,
                                     ctypes.c_float, _vp, _sz, _vp]),
     "ixk_gemm_qkv": (ctypes.c_int, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp, ctypes.c_int64,
@@ -187,17 +195,20 @@ def _require_cuda(*tensors) -> None:
 def run_gemm_custom_call(lhs: torch.Tensor, rhs: torch.Tensor, add: Optional[torch.Tensor],
                          output: torch.Tensor, bias: Optional[torch.Tensor], stream, attrs: dict,
                          epilogue: str, *, inv_scale_a: Optional[float] = None,
-                         inv_scale_b: Optional[float] = None, workspace: Optional[torch.Tensor] = None) -> None:
+                         inv_scale_b: Optional[float] = None, workspace: Optional[torch.Tensor] = None,
+                         aux: Optional[torch.Tensor] = None) -> None:
     """RunGemmCustomCall (xla/service/gpu/sycl_onednn.cc:38-54): buffers + the FFI attribute
     dictionary RunGemm reads (xla/service/gpu/onednn_matmul_utils.cc:543-595).  `attrs` keys:
     {lhs,rhs,output}_{order,num_rows,num_cols,batch_stride,leading_dim_stride,layout_dtype},
     batch_size, alpha, beta.  `add` is the C operand read when beta != 0 (it may be `output`).
     With inv_scale_a/b given the operands are fp8 and the scaled-GEMM entry point is used.
     `workspace` is the scratch the reference's handler passes down (sycl_onednn.h:37): skinny
-    problems (M <= 128) use it to split K over more SMs; see gemm_workspace_bytes()."""
+    problems (M <= 128) use it to split K over more SMs; see gemm_workspace_bytes().  `aux` is the
+    second result of the GELU_AUX / BIAS_GELU_AUX epilogues (the pre-activation values, the
+    output's type, shape and order)."""
     if epilogue not in EPILOGUES:
         raise IxkError(IXK_INVALID_ARGUMENT, "Unknown Epilogue.")  # onednn_matmul_utils.cc:52-54
-    _require_cuda(lhs, rhs, add, output, bias)
+    _require_cuda(lhs, rhs, add, output, bias, aux)
     lib = load_library()
     d = _GemmDesc()
     for name, field in (("lhs", d.lhs), ("rhs", d.rhs), ("output", d.output)):
@@ -214,7 +225,12 @@ def run_gemm_custom_call(lhs: torch.Tensor, rhs: torch.Tensor, add: Optional[tor
     d.reserved = 0
     sp = _stream_ptr(stream)
     ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
-    if inv_scale_a is not None or inv_scale_b is not None:
+    if aux is not None:
+        order = int(attrs["output_order"])
+        aux_ld = aux.stride(-2) if order == ROW_MAJOR else aux.stride(-1)
+        st = lib.ixk_gemm_aux(ctypes.byref(d), _ptr(lhs), _ptr(rhs), _ptr(add), _ptr(bias), _ptr(output), _ptr(aux),
+                              int(aux_ld), sp)
+    elif inv_scale_a is not None or inv_scale_b is not None:
         st = lib.ixk_gemm_fp8(ctypes.byref(d), _ptr(lhs), _ptr(rhs), _ptr(add), _ptr(bias), _ptr(output),
                               float(inv_scale_a), float(inv_scale_b), _ptr(workspace), ws_bytes, sp)
     else:
@@ -254,14 +270,15 @@ def _matrix_attrs(prefix: str, t: torch.Tensor) -> dict:
             f"{prefix}_layout_dtype": _TORCH_TO_IXK[t.dtype]}
 
 
-def gemm_attrs_for(lhs: torch.Tensor, rhs: torch.Tensor, output: torch.Tensor, beta: float = 0.0) -> dict:
+def gemm_attrs_for(lhs: torch.Tensor, rhs: torch.Tensor, output: torch.Tensor, beta: float = 0.0,
+                   alpha: float = 1.0) -> dict:
     """The attribute dictionary XLA's GEMM rewriter would attach for these three tensor views."""
     attrs = {}
     attrs.update(_matrix_attrs("lhs", lhs))
     attrs.update(_matrix_attrs("rhs", rhs))
     attrs.update(_matrix_attrs("output", output))
     attrs["batch_size"] = output.shape[0] if output.dim() == 3 else 1
-    attrs["alpha"] = 1.0
+    attrs["alpha"] = float(alpha)
     attrs["beta"] = float(beta)
     attrs["algorithm"] = 0
     return attrs
@@ -270,14 +287,16 @@ def gemm_attrs_for(lhs: torch.Tensor, rhs: torch.Tensor, output: torch.Tensor, b
 def gemm(lhs: torch.Tensor, rhs: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
          c: Optional[torch.Tensor] = None, beta: float = 0.0, epilogue: str = "DEFAULT",
          out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-         stream=None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out = act(lhs @ rhs + bias + beta*c) through "__cublas$lt$matmul"'s path.  Any mix of
-    row-/column-major 2-D (or batched 3-D) views is passed through as-is, never copied."""
+         stream=None, workspace: Optional[torch.Tensor] = None, alpha: float = 1.0,
+         aux: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = act(alpha * lhs @ rhs + bias + beta*c) through "__cublas$lt$matmul"'s path.  Any mix of
+    row-/column-major 2-D (or batched 3-D) views is passed through as-is, never copied.  With a
+    *_AUX epilogue `aux` receives the values the activation is applied to."""
     if out is None:
         shape = (*lhs.shape[:-1], rhs.shape[-1])
         out = torch.empty(shape, device=lhs.device, dtype=out_dtype or lhs.dtype)
-    attrs = gemm_attrs_for(lhs, rhs, out, beta)
-    run_gemm_custom_call(lhs, rhs, c, out, bias, stream, attrs, epilogue, workspace=workspace)
+    attrs = gemm_attrs_for(lhs, rhs, out, beta, alpha)
+    run_gemm_custom_call(lhs, rhs, c, out, bias, stream, attrs, epilogue, workspace=workspace, aux=aux)
     return out
 
 

@@ -39,7 +39,7 @@ void make_blas_compatible(MatrixDesc& lhs, MatrixDesc& rhs, MatrixDesc& out) {
 }
 
 bool is_fp8(int t) { return t == IXK_F8E4M3 || t == IXK_F8E5M2; }
-int elem_bytes(int t) { return t == IXK_F32 ? 4 : (is_fp8(t) ? 1 : 2); }
+int elem_bytes(int t) { return (t == IXK_F32 || t == IXK_S32) ? 4 : ((is_fp8(t) || t == IXK_S8) ? 1 : 2); }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_layout(const ixk_matrix_layout& l, const char* name) {
@@ -55,7 +55,7 @@ int check_layout(const ixk_matrix_layout& l, const char* name) {
 
 int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, const void* bias,
         void* d, bool fp8_call, float inv_scale_a, float inv_scale_b, void* workspace, size_t workspace_bytes,
-        void* stream) {
+        void* stream, void* aux = nullptr, int64_t aux_ld = 0, bool aux_call = false) {
   clear_error();
   if (desc == nullptr) return fail(IXK_INVALID_ARGUMENT, "desc is NULL");
   if (desc->reserved != 0) return fail(IXK_INVALID_ARGUMENT, "desc.reserved must be 0");
@@ -77,14 +77,21 @@ int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, 
     case IXK_EPILOGUE_BIAS_GELU: wants_bias = true; act = gemm::kActGelu; break;
     case IXK_EPILOGUE_GELU_AUX:
     case IXK_EPILOGUE_BIAS_GELU_AUX:
-      // onednn_matmul_utils.cc:321-322, :452-453: "Unsupported Activation mode".
-      return fail(IXK_UNIMPLEMENTED, "Unsupported Activation mode: *_AUX epilogues have no auxiliary output here");
+      // The reference stops here ("Unsupported Activation mode", onednn_matmul_utils.cc:321-322,
+      // :452-453).  The auxiliary output needs a second result buffer, which only ixk_gemm_aux takes.
+      if (!aux_call)
+        return fail(IXK_UNIMPLEMENTED, "Unsupported Activation mode: the *_AUX epilogues write a second result; call ixk_gemm_aux");
+      wants_bias = desc->epilogue == IXK_EPILOGUE_BIAS_GELU_AUX;
+      act = gemm::kActGelu;
+      break;
     default: return fail(IXK_INVALID_ARGUMENT, "Unknown Epilogue.");
   }
+  if (aux_call && desc->epilogue != IXK_EPILOGUE_GELU_AUX && desc->epilogue != IXK_EPILOGUE_BIAS_GELU_AUX)
+    return fail(IXK_INVALID_ARGUMENT, "ixk_gemm_aux takes the GELU_AUX and BIAS_GELU_AUX epilogues only");
   if (wants_bias != (bias != nullptr))
     return fail(IXK_INVALID_ARGUMENT, "bias must be given exactly for the BIAS* epilogues");
-  if (std::fabs(desc->alpha - 1.0f) >= 1e-6f)
-    return fail(IXK_UNIMPLEMENTED, "alpha must be 1 (onednn_matmul_utils.cc:438 CHECKs the same)");
+  if (!std::isfinite(desc->alpha) || !std::isfinite(desc->beta))
+    return fail(IXK_INVALID_ARGUMENT, "alpha and beta must be finite");
   const bool has_c = desc->beta != 0.0f;
   if (has_c && c == nullptr) return fail(IXK_INVALID_ARGUMENT, "beta != 0 needs the C operand");
 
@@ -98,23 +105,43 @@ int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, 
     if (tc != IXK_BF16 && tc != IXK_F16 && tc != IXK_F32)
       return fail(IXK_UNIMPLEMENTED, "fp8 GEMM output must be BF16, F16 or F32");
     p.fp8 = true;
+    p.kind = gemm::kKindF8;
     p.a_fmt = ta == IXK_F8E4M3 ? 0u : 1u;
     p.b_fmt = tb == IXK_F8E4M3 ? 0u : 1u;
-    p.acc_scale = inv_scale_a * inv_scale_b;
+    p.acc_scale = inv_scale_a * inv_scale_b * desc->alpha;
     p.bias_dtype = tc;
   } else {
-    const bool ok = (ta == IXK_BF16 && tb == IXK_BF16 && (tc == IXK_BF16 || tc == IXK_F32)) ||
-                    (ta == IXK_F16 && tb == IXK_F16 && (tc == IXK_F16 || tc == IXK_F32));
-    if (!ok) {
+    const bool f16_pair = (ta == IXK_BF16 && tb == IXK_BF16 && (tc == IXK_BF16 || tc == IXK_F32)) ||
+                          (ta == IXK_F16 && tb == IXK_F16 && (tc == IXK_F16 || tc == IXK_F32));
+    const bool f32_triple = ta == IXK_F32 && tb == IXK_F32 && tc == IXK_F32;
+    const bool s8_triple = ta == IXK_S8 && tb == IXK_S8 && tc == IXK_S32;
+    if (!f16_pair && !f32_triple && !s8_triple) {
       if (is_fp8(ta) || is_fp8(tb)) return fail(IXK_INVALID_ARGUMENT, "fp8 operands go through ixk_gemm_fp8");
       return fail(IXK_UNIMPLEMENTED,
-                  "Unexpected GEMM lhs/rhs/output types: the tensor-core path takes (BF16,BF16,BF16|F32) and "
-                  "(F16,F16,F16|F32)");
+                  "Unexpected GEMM lhs/rhs/output types: the tensor-core path takes (BF16,BF16,BF16|F32), "
+                  "(F16,F16,F16|F32), (F32,F32,F32) and (S8,S8,S32)");   // onednn_matmul_utils.cc:605-620
     }
-    p.fp8 = false;
-    p.ab_dtype = ta;
-    p.a_fmt = p.b_fmt = (ta == IXK_BF16) ? 1u : 0u;
-    p.bias_dtype = ta;
+    if (f16_pair) {
+      p.fp8 = false;
+      p.kind = gemm::kKindF16;
+      p.ab_dtype = ta;
+      p.a_fmt = p.b_fmt = (ta == IXK_BF16) ? 1u : 0u;
+      p.bias_dtype = ta;
+    } else if (f32_triple) {
+      // TF32 on the tensor cores: the hardware reads the upper 19 bits of each fp32 operand
+      p.fp8 = true;   // (not a 16-bit problem: no split-K)
+      p.kind = gemm::kKindTf32;
+      p.a_fmt = p.b_fmt = 2u;
+      p.bias_dtype = IXK_F32;
+    } else {
+      if (desc->epilogue != IXK_EPILOGUE_DEFAULT || desc->alpha != 1.0f || desc->beta != 0.0f)
+        return fail(IXK_UNIMPLEMENTED, "(S8,S8,S32) takes the DEFAULT epilogue with alpha = 1 and beta = 0 only");
+      p.fp8 = true;
+      p.kind = gemm::kKindI8;
+      p.a_fmt = p.b_fmt = 1u;  // signed 8-bit
+      p.bias_dtype = IXK_S32;
+    }
+    p.acc_scale = desc->alpha;  // the product is scaled in fp32 before bias and residual are added
   }
 
   MatrixDesc lhs = make_desc(desc->lhs, a);
@@ -163,6 +190,16 @@ int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, 
   p.act = act;
   p.beta = desc->beta;
   (void)swapped;
+  if (aux_call) {
+    // aux has the output's type, order and shape (after a column-major output has been rewritten
+    // it is row-major [M,N] like D), its own pitch, and D's batch spacing rule: dense batches.
+    if (aux == nullptr) return fail(IXK_INVALID_ARGUMENT, "aux is NULL");
+    if (aux_ld < p.N) return fail(IXK_INVALID_ARGUMENT, "aux_leading_dim_stride is smaller than the contiguous dimension");
+    if ((reinterpret_cast<uintptr_t>(aux) % elem_bytes(tc)) != 0) return fail(IXK_INVALID_ARGUMENT, "aux is not aligned to its element size");
+    p.aux = aux;
+    p.ld_aux = aux_ld;
+    p.aux_batch_stride = aux_ld * p.M;
+  }
 
   const int es = elem_bytes(ta);
   if (!aligned16(p.a) || !aligned16(p.b))
@@ -180,7 +217,7 @@ int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, 
   if ((rc = get_device_info(&dev)) != IXK_OK) return rc;
   // Skinny problems are cut along K when the caller handed over enough scratch for the partials;
   // without it they run un-split (same result, fewer SMs busy).
-  const int splits = p.force_block_n > 0 ? 1 : gemm::split_k_factor(p.M, p.N, p.K, p.batch, p.fp8);
+  const int splits = (p.force_block_n > 0 || p.aux != nullptr) ? 1 : gemm::split_k_factor(p.M, p.N, p.K, p.batch, p.fp8);
   if (splits > 1 && workspace != nullptr && aligned16(workspace) &&
       workspace_bytes >= gemm::split_k_workspace_bytes(p.M, p.N, splits))
     return gemm::launch_split_k(p, splits, workspace, dev, static_cast<cudaStream_t>(stream));
@@ -275,6 +312,40 @@ int ixk_gemm(const ixk_gemm_desc* desc, const void* a, const void* b, const void
 }
 
 size_t ixk_gemm_workspace_bytes(const ixk_gemm_desc* desc) { return ixk::workspace_query(desc); }
+
+int ixk_gemm_aux(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, const void* bias, void* d,
+                 void* aux, int64_t aux_leading_dim_stride, void* cuda_stream) {
+  return ixk::run(desc, a, b, c, bias, d, /*fp8_call=*/false, 1.0f, 1.0f, nullptr, 0, cuda_stream, aux,
+                  aux_leading_dim_stride, /*aux_call=*/true);
+}
+
+// Which buffer of the "__cublas$lt$matmul" custom call is which (sycl_custom_call.cc:167-205):
+// operands are lhs, rhs, [C when beta != 0], [bias when the epilogue adds one]; the result that
+// receives D is index 1 when the epilogue has an auxiliary output (which is then result 0), else
+// index 0.  XLA aliases operand 2 with the result when beta != 0, so C and D are one buffer there.
+int ixk_ffi_select_operands(int epilogue, float beta, int num_args, int num_results, ixk_ffi_operands* out) {
+  ixk::clear_error();
+  if (out == nullptr) return ixk::fail(IXK_INVALID_ARGUMENT, "out is NULL");
+  if (epilogue < IXK_EPILOGUE_DEFAULT || epilogue > IXK_EPILOGUE_BIAS_GELU_AUX)
+    return ixk::fail(IXK_INVALID_ARGUMENT, "Unknown Epilogue.");   // onednn_matmul_utils.cc:90-110
+  const bool has_bias = epilogue == IXK_EPILOGUE_BIAS || epilogue == IXK_EPILOGUE_BIAS_RELU ||
+                        epilogue == IXK_EPILOGUE_BIAS_GELU || epilogue == IXK_EPILOGUE_BIAS_GELU_AUX;
+  const bool has_aux = epilogue == IXK_EPILOGUE_GELU_AUX || epilogue == IXK_EPILOGUE_BIAS_GELU_AUX;
+  const bool has_c = beta != 0.0f;
+  out->lhs_arg = 0;
+  out->rhs_arg = 1;
+  out->c_arg = has_c ? 2 : -1;
+  out->bias_arg = has_bias ? (has_c ? 3 : 2) : -1;
+  out->d_result = has_aux ? 1 : 0;
+  out->aux_result = has_aux ? 0 : -1;
+  const int need_args = 2 + (has_c ? 1 : 0) + (has_bias ? 1 : 0);
+  if (num_args < need_args)
+    return ixk::fail(IXK_INVALID_ARGUMENT, "the custom call has " + std::to_string(num_args) + " operands, this epilogue and beta need " +
+                                               std::to_string(need_args));
+  if (num_results < out->d_result + 1)
+    return ixk::fail(IXK_INVALID_ARGUMENT, "the custom call has too few results for this epilogue");
+  return IXK_OK;
+}
 
 int ixk_gemm_fp8(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c,
                  const void* bias, void* d, float inv_scale_a, float inv_scale_b, void* workspace,

@@ -14,6 +14,8 @@
 // overlaps the main loop of tile i+1.  Either operand may be K-major or MN-major in global
 // memory; the TMA box shape and the UMMA descriptors follow the operand's major-ness, so no
 // transposed copy is ever made.  Operands are 16-bit (kind::f16) or 8-bit (kind::f8f6f4).
+#include <type_traits>
+
 #include "gemm_sm100.h"
 
 #include <cuda_bf16.h>
@@ -28,6 +30,8 @@ namespace gemm {
 
 namespace {
 
+static_assert(kKindF16 == ptx::kKindF16 && kKindF8 == ptx::kKindF8 && kKindTf32 == ptx::kKindTf32 &&
+              kKindI8 == ptx::kKindI8, "MMA kind codes");
 constexpr int kBlockM = 128;
 constexpr int kSlabBytes = 128;  // bytes of K per shared-memory row (one swizzle span)
 constexpr int kThreads = 192;
@@ -130,7 +134,7 @@ __device__ __forceinline__ void pack_row16(const float (&v)[32], int dtype, uint
 
 __device__ __forceinline__ void store_row(void* base, int64_t elem_off, int dtype, int count,
                                           bool vec_ok, const float (&v)[32]) {
-  if (dtype == IXK_F32) {
+  if (dtype == IXK_F32 || dtype == IXK_S32) {  // 32-bit words, copied bit for bit
     float* p = static_cast<float*>(base) + elem_off;
     if (vec_ok && count == 32) {
 #pragma unroll
@@ -209,6 +213,11 @@ __device__ __forceinline__ void epilogue_tile(const KernelArgs& args, const CUte
       uint32_t r[32];
       ptx::tmem_ld_32x32(tmem_acc + c0, r);
       ptx::tmem_ld_wait();
+      if (args.out_dtype == IXK_S32) {  // integer accumulator (kind::i8): the bits go out as they are
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        return;
+      }
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * args.acc_scale;
       if (args.bias != nullptr) {
@@ -223,6 +232,9 @@ __device__ __forceinline__ void epilogue_tile(const KernelArgs& args, const CUte
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = fmaf(args.beta, cc[i], v[i]);
       }
+      if (args.aux != nullptr && row_ok)  // the value the activation is applied to, as a second output
+        store_row(args.aux, bz * args.aux_batch_stride + static_cast<int64_t>(m) * args.ld_aux + n, args.out_dtype, count,
+                  args.aux_vec_ok != 0, v);
       if (args.act == kActRelu) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
@@ -286,13 +298,13 @@ __device__ __forceinline__ void epilogue_tile(const KernelArgs& args, const CUte
     }
 }
 
-template <int kBlockN, bool kFp8>
+template <int kBlockN, int kKind>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_d, const KernelArgs args) {
   using C = Cfg<kBlockN>;
   constexpr int kStages = C::kStages;
-  constexpr int kElemBytes = kFp8 ? 1 : 2;
+  constexpr int kElemBytes = kKind == ptx::kKindF16 ? 2 : (kKind == ptx::kKindTf32 ? 4 : 1);
   constexpr int kSlabElems = kSlabBytes / kElemBytes;  // K elements per pipeline stage
   constexpr int kUmmaK = 32 / kElemBytes;              // K elements per tcgen05.mma
 
@@ -423,7 +435,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int ks = 0; ks < kSlabElems / kUmmaK; ++ks) {
             const uint64_t da = ptx::umma_smem_desc(a_src + ks * a_kstep, a_lbo, 1024);
             const uint64_t db = ptx::umma_smem_desc(b_src + ks * b_kstep, b_lbo, 1024);
-            ptx::umma_ss_elect<kFp8>(d_tmem, da, db, args.idesc, (kb | ks) != 0 ? 1u : 0u);
+            ptx::umma_ss_elect<kKind>(d_tmem, da, db, args.idesc, (kb | ks) != 0 ? 1u : 0u);
           }
           ptx::umma_commit_elect(empty_bar(stage));
           if (++stage == kStages) {
@@ -489,7 +501,7 @@ struct PairCfg {
 };
 enum : int { kSitePairFull = 111, kSitePairPeer = 112, kSitePairAcc = 113, kSitePairForward = 114 };
 
-template <bool kFp8>
+template <int kKind>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_d, const KernelArgs args) {
@@ -497,7 +509,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   constexpr int kStages = C::kStages;
   constexpr int kBlockN = C::kBlockN;
   constexpr int kHalfN = kBlockN / 2;
-  constexpr int kElemBytes = kFp8 ? 1 : 2;
+  constexpr int kElemBytes = kKind == ptx::kKindF16 ? 2 : (kKind == ptx::kKindTf32 ? 4 : 1);
   constexpr int kSlabElems = kSlabBytes / kElemBytes;
   constexpr int kUmmaK = 32 / kElemBytes;
 
@@ -633,7 +645,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int ks = 0; ks < kSlabElems / kUmmaK; ++ks) {
           const uint64_t da = ptx::umma_smem_desc(a_src + ks * a_kstep, a_lbo, 1024);
           const uint64_t db = ptx::umma_smem_desc(b_src + ks * b_kstep, b_lbo, 1024);
-          ptx::umma_ss_pair_elect<kFp8>(d_tmem, da, db, args.idesc, (kb | ks) != 0 ? 1u : 0u);
+          ptx::umma_ss_pair_elect<kKind>(d_tmem, da, db, args.idesc, (kb | ks) != 0 ? 1u : 0u);
         }
         ptx::umma_commit_pair_elect(empty_bar(stage));  // both CTAs' producers may refill the slot
         if (++stage == kStages) {
@@ -684,11 +696,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   ptx::cluster_sync_all();
 }
 
-template <int kBlockN, bool kFp8>
+template <int kBlockN, int kKind>
 int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const KernelArgs& args,
                int grid, cudaStream_t stream) {
   using C = Cfg<kBlockN>;
-  auto* fn = &gemm_kernel<kBlockN, kFp8>;
+  auto* fn = &gemm_kernel<kBlockN, kKind>;
   static thread_local int configured_device = -1;
   int dev = 0;
   IXK_CUDA_OK(cudaGetDevice(&dev));
@@ -702,10 +714,10 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& 
   return IXK_OK;
 }
 
-template <bool kFp8>
+template <int kKind>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const KernelArgs& args,
                 int pairs, cudaStream_t stream) {
-  auto* fn = &gemm_pair_kernel<kFp8>;
+  auto* fn = &gemm_pair_kernel<kKind>;
   static thread_local int configured_device = -1;
   int dev = 0;
   IXK_CUDA_OK(cudaGetDevice(&dev));
@@ -744,13 +756,13 @@ int pick_block_n(int64_t M, int64_t N, int64_t batch, int sm_count) {
 }
 
 int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
-  const int es = p.fp8 ? 1 : 2;
+  const int es = p.kind == ptx::kKindF16 ? 2 : (p.kind == ptx::kKindTf32 ? 4 : 1);
   const int slab_elems = kSlabBytes / es;
   int bn = p.force_block_n > 0 ? p.force_block_n : pick_block_n(p.M, p.N, p.batch, dev.sm_count);
   if (bn != 64 && bn != 128 && bn != 256) return fail(IXK_INVALID_ARGUMENT, "block_n must be 64, 128 or 256");
   // An MN-major 8-bit B tile is loaded in 128-column boxes (one swizzle span), so it cannot be
   // narrower than 128 columns.
-  if (p.fp8 && p.b_mn_major && bn < 128) bn = 128;
+  if (es == 1 && p.b_mn_major && bn < 128) bn = 128;
 
   // Large problems run on CTA pairs (256 x 256 tiles): worth it once every pair of SMs has a tile.
   const int64_t tiles_m_all = (p.M + kBlockM - 1) / kBlockM;
@@ -759,9 +771,10 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   if (const char* env = std::getenv("IXK_GEMM_PAIR")) pair = pair && std::atoi(env) != 0;
   const int b_box_rows = pair ? 128 : bn;
 
-  const CUtensorMapDataType dt = p.fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                                       : (p.ab_dtype == IXK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  const CUtensorMapDataType dt = es == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : es == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                           : (p.ab_dtype == IXK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   // A is [M,K]: K-major when K is contiguous.  B is [K,N]: MN-major when N is contiguous.
   auto make_map = [&](CUtensorMap* out, const void* base, bool mn_major, int64_t mn, int64_t ld,
                       int64_t batch_stride, int block_mn, bool broadcast) -> int {
@@ -803,7 +816,8 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   k.tiles_n = static_cast<int>((p.N + bn - 1) / bn);
   k.a_mn_major = p.a_mn_major;
   k.b_mn_major = p.b_mn_major;
-  k.idesc = ptx::umma_idesc(p.a_fmt, p.b_fmt, p.a_mn_major ? 1 : 0, p.b_mn_major ? 1 : 0, pair ? 2 * kBlockM : kBlockM, bn);
+  k.idesc = ptx::umma_idesc(p.a_fmt, p.b_fmt, p.a_mn_major ? 1 : 0, p.b_mn_major ? 1 : 0, pair ? 2 * kBlockM : kBlockM, bn,
+                            p.kind == ptx::kKindI8 ? 2u : 1u);
   k.bias = p.bias;
   k.c = (p.beta != 0.0f) ? p.c : nullptr;
   k.d = p.d;
@@ -817,7 +831,7 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   k.acc_scale = p.acc_scale;
   k.beta = p.beta;
   k.status_word = dev.status_word;
-  const int out_es = p.out_dtype == IXK_F32 ? 4 : 2;
+  const int out_es = (p.out_dtype == IXK_F32 || p.out_dtype == IXK_S32) ? 4 : 2;
   const int bias_es = p.bias_dtype == IXK_F32 ? 4 : 2;
   auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
   k.d_vec_ok = aligned16(p.d) && (p.ldd * out_es) % 16 == 0 && (p.d_batch_stride * out_es) % 16 == 0;
@@ -825,10 +839,14 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   k.bias_vec_ok = p.bias && aligned16(p.bias) && (p.bias_batch_stride * bias_es) % 16 == 0;
   k.a_broadcast = p.a_broadcast ? 1 : 0;
   k.bias_batch_stride = p.bias_batch_stride;
+  k.aux = p.aux;
+  k.ld_aux = p.ld_aux;
+  k.aux_batch_stride = p.aux_batch_stride;
+  k.aux_vec_ok = p.aux && aligned16(p.aux) && (p.ld_aux * out_es) % 16 == 0 && (p.aux_batch_stride * out_es) % 16 == 0;
   (void)bias_es;
   // A 16-bit D whose rows start on 16-byte boundaries leaves through shared memory and TMA stores.
   CUtensorMap td = ta;  // placeholder unless D qualifies
-  k.d_tma = (p.out_dtype != IXK_F32 && k.d_vec_ok) ? 1 : 0;
+  k.d_tma = (out_es == 2 && k.d_vec_ok) ? 1 : 0;
   if (k.d_tma) {
     TmapSpec s{};
     s.dtype = p.out_dtype == IXK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -845,20 +863,24 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
     if ((rc = encode_tmap(&td, p.d, s)) != IXK_OK) return rc;
   }
 
-  if (pair) {
-    const int pairs = static_cast<int>(pair_tiles < dev.sm_count / 2 ? pair_tiles : dev.sm_count / 2);
-    return p.fp8 ? launch_pair<true>(ta, tb, td, k, pairs, stream) : launch_pair<false>(ta, tb, td, k, pairs, stream);
+  auto dispatch = [&](auto kind_tag) -> int {
+    constexpr int kKind = decltype(kind_tag)::value;
+    if (pair) {
+      const int pairs = static_cast<int>(pair_tiles < dev.sm_count / 2 ? pair_tiles : dev.sm_count / 2);
+      return launch_pair<kKind>(ta, tb, td, k, pairs, stream);
+    }
+    const int64_t tiles = static_cast<int64_t>(k.tiles_m) * k.tiles_n * k.batch;
+    const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
+    if (bn == 256) return launch_one<256, kKind>(ta, tb, td, k, grid, stream);
+    if (bn == 128) return launch_one<128, kKind>(ta, tb, td, k, grid, stream);
+    return launch_one<64, kKind>(ta, tb, td, k, grid, stream);
+  };
+  switch (p.kind) {
+    case ptx::kKindF8: return dispatch(std::integral_constant<int, ptx::kKindF8>{});
+    case ptx::kKindTf32: return dispatch(std::integral_constant<int, ptx::kKindTf32>{});
+    case ptx::kKindI8: return dispatch(std::integral_constant<int, ptx::kKindI8>{});
+    default: return dispatch(std::integral_constant<int, ptx::kKindF16>{});
   }
-  const int64_t tiles = static_cast<int64_t>(k.tiles_m) * k.tiles_n * k.batch;
-  const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
-  if (p.fp8) {
-    if (bn == 256) return launch_one<256, true>(ta, tb, td, k, grid, stream);
-    if (bn == 128) return launch_one<128, true>(ta, tb, td, k, grid, stream);
-    return launch_one<64, true>(ta, tb, td, k, grid, stream);
-  }
-  if (bn == 256) return launch_one<256, false>(ta, tb, td, k, grid, stream);
-  if (bn == 128) return launch_one<128, false>(ta, tb, td, k, grid, stream);
-  return launch_one<64, false>(ta, tb, td, k, grid, stream);
 }
 
 }  // namespace gemm

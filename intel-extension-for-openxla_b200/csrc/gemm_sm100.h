@@ -8,13 +8,16 @@ namespace ixk {
 namespace gemm {
 
 enum : int { kActNone = 0, kActRelu = 1, kActGelu = 2 };
+// tcgen05.mma kinds (the values of ptx::kKind*, restated for host-only code)
+enum : int { kKindF16 = 0, kKindF8 = 1, kKindTf32 = 2, kKindI8 = 3 };
 
 // A GEMM after normalisation: D is row-major [M,N]; A is [M,K], B is [K,N], each with
 // either dimension contiguous.
 struct Problem {
   int64_t M = 0, N = 0, K = 0, batch = 1;
-  bool fp8 = false;
-  int ab_dtype = IXK_BF16;  // 16-bit operand type when !fp8
+  bool fp8 = false;          // any operand type other than the 16-bit floats (no split-K path)
+  int kind = 0;              // tcgen05.mma kind: kKindF16 / kKindF8 / kKindTf32 / kKindI8
+  int ab_dtype = IXK_BF16;   // 16-bit operand type when kind == kKindF16
   uint32_t a_fmt = 0, b_fmt = 0;  // tcgen05 operand format codes
   bool a_mn_major = false;  // A stored with M contiguous (column-major A)
   bool b_mn_major = false;  // B stored with N contiguous (row-major B)
@@ -26,6 +29,8 @@ struct Problem {
   const void* c = nullptr;
   const void* bias = nullptr;
   void* d = nullptr;
+  void* aux = nullptr;             // pre-activation values (the *_AUX epilogues); D's type and shape
+  int64_t ld_aux = 0, aux_batch_stride = 0;
   int64_t ldc = 0, ldd = 0, c_batch_stride = 0, d_batch_stride = 0;
   int out_dtype = IXK_BF16;
   int bias_dtype = IXK_BF16;
@@ -51,6 +56,9 @@ struct KernelArgs {
   int d_tma;  // 16-bit D with 16-byte-aligned rows: stored through shared memory + TMA
   int a_broadcast;
   int64_t bias_batch_stride;
+  void* aux;
+  int64_t ld_aux, aux_batch_stride;
+  int aux_vec_ok;
   int* status_word;
 };
 

@@ -298,10 +298,20 @@ __device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
       "}\n" ::"r"(bar)
       : "memory");
 }
-template <bool kFp8>
+template <int kKind>
 __device__ __forceinline__ void umma_ss_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                               uint32_t idesc, uint32_t accumulate) {
-  if constexpr (kFp8) {
+  if constexpr (kKind == 0) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }   else if constexpr (kKind == 1) {
     asm volatile(
         "{\n\t"
         ".reg .pred p, e;\n\t"
@@ -311,13 +321,23 @@ __device__ __forceinline__ void umma_ss_elect(uint32_t d_tmem, uint64_t a_desc, 
         "}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
-  } else {
+  }   else if constexpr (kKind == 2) {
     asm volatile(
         "{\n\t"
         ".reg .pred p, e;\n\t"
         "elect.sync _|e, 0xffffffff;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }   else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
         "}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
@@ -365,10 +385,20 @@ __device__ __forceinline__ void umma_commit_pair_elect(uint32_t bar) {
       "}\n" ::"r"(bar)
       : "memory");
 }
-template <bool kFp8>
+template <int kKind>
 __device__ __forceinline__ void umma_ss_pair_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                                    uint32_t idesc, uint32_t accumulate) {
-  if constexpr (kFp8) {
+  if constexpr (kKind == 0) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }   else if constexpr (kKind == 1) {
     asm volatile(
         "{\n\t"
         ".reg .pred p, e;\n\t"
@@ -378,13 +408,23 @@ __device__ __forceinline__ void umma_ss_pair_elect(uint32_t d_tmem, uint64_t a_d
         "}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
-  } else {
+  }   else if constexpr (kKind == 2) {
     asm volatile(
         "{\n\t"
         ".reg .pred p, e;\n\t"
         "elect.sync _|e, 0xffffffff;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "@e tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }   else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
         "}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
@@ -438,10 +478,19 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 }
 
 // D[tmem] (+)= A[smem] . B[smem]; issued by ONE thread.
-template <bool kFp8>
+template <int kKind>
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                         uint32_t idesc, uint32_t accumulate) {
-  if constexpr (kFp8) {
+  if constexpr (kKind == 0) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }   else if constexpr (kKind == 1) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
@@ -450,12 +499,21 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
         "}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
-  } else {
+  }   else if constexpr (kKind == 2) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }   else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
         "}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
@@ -492,13 +550,17 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
-// Instruction descriptor for kind::f16 / kind::f8f6f4 with fp32 accumulation.
-// a_fmt/b_fmt: kind::f16 → 0 = f16, 1 = bf16; kind::f8f6f4 → 0 = e4m3, 1 = e5m2.
+// MMA kinds of the tcgen05.mma wrappers above (their kKind template argument).
+enum : int { kKindF16 = 0, kKindF8 = 1, kKindTf32 = 2, kKindI8 = 3 };
+
+// Instruction descriptor.  a_fmt/b_fmt: kind::f16 → 0 = f16, 1 = bf16; kind::f8f6f4 → 0 = e4m3,
+// 1 = e5m2; kind::tf32 → 2; kind::i8 → 0 = unsigned, 1 = signed.  d_fmt: 1 = f32 accumulator
+// (every floating kind), 2 = s32 (kind::i8).
 // *_mn_major: 0 = operand is K-major in shared memory, 1 = MN-major.
 __host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt, uint32_t b_fmt,
                                                   uint32_t a_mn_major, uint32_t b_mn_major,
-                                                  uint32_t m, uint32_t n) {
-  return (1u << 4)                 // D format: f32
+                                                  uint32_t m, uint32_t n, uint32_t d_fmt = 1) {
+  return (d_fmt << 4)              // D format
          | (a_fmt << 7) | (b_fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) |
          ((n >> 3) << 17) | ((m >> 4) << 24);
 }

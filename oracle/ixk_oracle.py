@@ -156,25 +156,50 @@ def _logical(mat: np.ndarray, layout: dict) -> np.ndarray:
     return out
 
 
-def gemm_epilogue(acc: np.ndarray, bias, c, beta: float, epilogue: str, out_dtype: int) -> np.ndarray:
+def gemm_epilogue(acc: np.ndarray, bias, c, beta: float, epilogue: str, out_dtype: int, alpha: float = 1.0,
+                  with_aux: bool = False):
     """The post-accumulation chain on float32 accumulators, one rounding at the end:
-    bias add (xla/service/gpu/xetla/gemm/epilogue_impl.h:237-241), residual beta*C
-    (:161, onednn append_sum at onednn_matmul_utils.cc:439), activation applied after the
-    sum (:441-449), cast to the output type."""
+    alpha (the addmm form alpha*acc + beta*res, xla/service/gpu/xetla/gemm/epilogue_impl.h:83),
+    bias add (:237-241), residual beta*C (:161, onednn append_sum at onednn_matmul_utils.cc:439),
+    activation applied after the sum (:441-449), cast to the output type.
+    The *_AUX epilogues (declared at onednn_matmul_utils.h:42-43, rejected by the reference's
+    kernels, :321-322) are GELU with the pre-activation values as a second result: with_aux=True
+    returns (D, aux), both rounded to the output type."""
     if epilogue not in EPILOGUES:
         raise ValueError("Unknown Epilogue.")
-    if epilogue.endswith("_AUX"):
+    if epilogue.endswith("_AUX") and not with_aux:
         raise NotImplementedError("Unsupported Activation mode")  # onednn_matmul_utils.cc:321-322
-    v = np.asarray(acc, dtype=np.float32)
+    v = np.asarray(acc, dtype=np.float32) * np.float32(alpha)
     if "BIAS" in epilogue:
         v = v + np.asarray(bias, dtype=np.float32)[None, :]
     if beta != 0.0:
         v = v + np.float32(beta) * np.asarray(c, dtype=np.float32)
+    pre = v
     if epilogue.endswith("RELU"):
         v = np.maximum(v, np.float32(0))
-    elif epilogue.endswith("GELU"):
+    elif "GELU" in epilogue:
         v = gelu_tanh(v)
+    if with_aux:
+        return round_to(v, out_dtype), round_to(pre, out_dtype)
     return round_to(v, out_dtype)
+
+
+def tf32_operand(x: np.ndarray, mode: str = "truncate") -> np.ndarray:
+    """An fp32 GEMM operand as the TF32 math mode sees it (the reference's XLA_FP32_MATH_MODE=TF32,
+    xla/service/onednn_util.h:53-70: 8 exponent bits, 10 mantissa bits): the low 13 mantissa bits are
+    dropped ("truncate", what a tensor core does with fp32 bits) or rounded to nearest, ties away
+    from zero ("round", what a conversion instruction does)."""
+    bits = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    if mode == "round":
+        bits = bits + np.uint32(0x1000)
+    return (bits & np.uint32(0xFFFFE000)).view(np.float32)
+
+
+def gemm_s8(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """(S8,S8,S32) of RunGemm's type list (xla/service/gpu/onednn_matmul_utils.cc:610): exact integer
+    products summed in 32 bits (int64 here, then wrapped, so that overflow behaves as two's complement)."""
+    acc = np.asarray(a, dtype=np.int64) @ np.asarray(b, dtype=np.int64)
+    return acc.astype(np.int32)
 
 
 def gemm_custom_call(attrs: dict, lhs, rhs, c, bias, epilogue: str, out_dtype: int) -> np.ndarray:
@@ -185,8 +210,7 @@ def gemm_custom_call(attrs: dict, lhs, rhs, c, bias, epilogue: str, out_dtype: i
 
     A column-major output is produced as D^T = B^T.A^T (:520-530); the bias then runs along
     the columns of that rewritten problem (:363-365), i.e. along the ORIGINAL rows."""
-    if abs(attrs.get("alpha", 1.0) - 1.0) >= 1e-6:
-        raise NotImplementedError("alpha must be 1")  # onednn_matmul_utils.cc:438
+    alpha = float(attrs.get("alpha", 1.0))   # the reference CHECKs alpha == 1 (onednn_matmul_utils.cc:438)
     batch = attrs.get("batch_size", 1)
 
     def lay(p):
@@ -203,9 +227,9 @@ def gemm_custom_call(attrs: dict, lhs, rhs, c, bias, epilogue: str, out_dtype: i
     for i in range(batch):
         acc = a[i] @ b[i]  # float32 accumulate
         if transposed_out:
-            res = gemm_epilogue(acc.T, bias, None if cc is None else cc[i].T, beta, epilogue, out_dtype).T
+            res = gemm_epilogue(acc.T, bias, None if cc is None else cc[i].T, beta, epilogue, out_dtype, alpha).T
         else:
-            res = gemm_epilogue(acc, bias, None if cc is None else cc[i], beta, epilogue, out_dtype)
+            res = gemm_epilogue(acc, bias, None if cc is None else cc[i], beta, epilogue, out_dtype, alpha)
         out[i] = res
     return out
 

@@ -97,10 +97,15 @@ def test_argument_errors_come_back_as_codes_not_aborts(pkg):
     g = pkg._GemmDesc()
     g.batch_size, g.alpha, g.epilogue = 1, 1.0, 6  # GELU_AUX
     assert lib.ixk_gemm(ctypes.byref(g), None, None, None, None, None, None, 0, None) == pkg.IXK_UNIMPLEMENTED
+    assert b"ixk_gemm_aux" in lib.ixk_last_error()
+    assert lib.ixk_gemm_aux(ctypes.byref(g), None, None, None, None, None, None, 0, None) == pkg.IXK_OK   # an empty problem
     g.epilogue = 42
     assert lib.ixk_gemm(ctypes.byref(g), None, None, None, None, None, None, 0, None) == pkg.IXK_INVALID_ARGUMENT
-    g.epilogue, g.alpha = 0, 2.0
-    assert lib.ixk_gemm(ctypes.byref(g), None, None, None, None, None, None, 0, None) == pkg.IXK_UNIMPLEMENTED
+    g.epilogue = 0
+    assert lib.ixk_gemm_aux(ctypes.byref(g), None, None, None, None, None, None, 0, None) == pkg.IXK_INVALID_ARGUMENT
+    assert b"GELU_AUX" in lib.ixk_last_error()
+    g.alpha = float("nan")
+    assert lib.ixk_gemm(ctypes.byref(g), None, None, None, None, None, None, 0, None) == pkg.IXK_INVALID_ARGUMENT
     f = pkg._FmhaDesc()
     f.dtype, f.dropout_prob = 0, 0.1
     assert lib.ixk_fmha_fwd(ctypes.byref(f), None, None, None, None, None, None, None, 0, None) == pkg.IXK_UNIMPLEMENTED
@@ -176,6 +181,43 @@ def test_python_descriptor_checks_that_shapes_agree(pkg):
         pkg._fmha_desc(q, ke, ke, None, q[:, :2], 1.0, False, 0.0)    # out with fewer heads
     with pytest.raises(pkg.IxkError, match="element type"):
         pkg._fmha_desc(q, ke.half(), ke, None, q, 1.0, False, 0.0)
+
+
+def test_ffi_operand_selection(pkg):
+    """Which buffer of "__cublas$lt$matmul" is which, as SyclLtMatmul unpacks them
+    (sycl_custom_call.cc:167-205): lhs, rhs, [C iff beta != 0], [bias iff the epilogue adds one];
+    D is result 1 when there is an auxiliary output (result 0), else result 0."""
+    lib = pkg.load_library()
+    ops = pkg._FfiOperands()
+    E = {n: i for i, n in enumerate(pkg.EPILOGUES)}
+
+    def pick(epi, beta, n_args, n_res):
+        st = lib.ixk_ffi_select_operands(E[epi], beta, n_args, n_res, ctypes.byref(ops))
+        return st, (ops.lhs_arg, ops.rhs_arg, ops.c_arg, ops.bias_arg, ops.d_result, ops.aux_result)
+
+    assert pick("DEFAULT", 0.0, 2, 1) == (pkg.IXK_OK, (0, 1, -1, -1, 0, -1))
+    assert pick("DEFAULT", 1.0, 3, 1) == (pkg.IXK_OK, (0, 1, 2, -1, 0, -1))
+    assert pick("BIAS_GELU", 0.0, 3, 1) == (pkg.IXK_OK, (0, 1, -1, 2, 0, -1))
+    assert pick("BIAS_RELU", 0.5, 4, 1) == (pkg.IXK_OK, (0, 1, 2, 3, 0, -1))
+    assert pick("GELU_AUX", 0.0, 2, 2) == (pkg.IXK_OK, (0, 1, -1, -1, 1, 0))
+    assert pick("BIAS_GELU_AUX", 1.0, 4, 2) == (pkg.IXK_OK, (0, 1, 2, 3, 1, 0))
+    assert pick("BIAS", 1.0, 3, 1)[0] == pkg.IXK_INVALID_ARGUMENT          # the bias operand is missing
+    assert pick("GELU_AUX", 0.0, 2, 1)[0] == pkg.IXK_INVALID_ARGUMENT      # no second result
+    assert lib.ixk_ffi_select_operands(9, 0.0, 2, 1, ctypes.byref(ops)) == pkg.IXK_INVALID_ARGUMENT
+    assert b"Unknown Epilogue" in lib.ixk_last_error()
+    assert lib.ixk_ffi_select_operands(0, 0.0, 2, 1, None) == pkg.IXK_INVALID_ARGUMENT
+
+
+def test_xla_ffi_shim_is_inert_without_xla_headers(pkg):
+    """csrc/xla_ffi_shim.cc registers the XLA FFI handlers when XLA's headers are on the include
+    path; without them (this repository's own build) it must compile to an empty object."""
+    src = os.path.join(os.path.dirname(pkg.__file__), "csrc", "xla_ffi_shim.cc")
+    with tempfile.TemporaryDirectory() as d:
+        obj = os.path.join(d, "shim.o")
+        subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), "-c", src, "-o", obj],
+                       check=True)
+        syms = subprocess.run(["nm", "--defined-only", obj], check=True, capture_output=True, text=True).stdout
+    assert syms.strip() == ""
 
 
 def test_all_reduce_slices_and_set_up_errors(pkg):

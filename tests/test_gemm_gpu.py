@@ -271,14 +271,128 @@ def test_full_size_on_the_configuration_inputs(pkg, orc, cuda):
         orc.check_close(f32(out[r0:r0 + 128]), want, rtol=2e-2, atol=2e-2, what=f"C1 rows {r0}..{r0 + 127}")
 
 
+@pytest.mark.parametrize("alpha,beta", [(2.0, 0.0), (-0.5, 1.0), (0.25, -1.5)])
+@pytest.mark.parametrize("shape", [(300, 136, 520), (2048, 512, 4096), (64, 4096, 3072)])
+def test_alpha_scales_the_product_before_bias_and_residual(pkg, orc, cuda, shape, alpha, beta):
+    """D = act(alpha*A.B + bias + beta*C) for any alpha (the reference CHECKs alpha == 1,
+    onednn_matmul_utils.cc:438): single-CTA tiles, CTA pairs and the split-K path."""
+    M, K, N = shape
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(K, N, generator=g) * 0.05).bfloat16()
+    b = torch.randn(N, generator=g).bfloat16()
+    c = torch.randn(M, N, generator=g).bfloat16()
+    xd, wd = x.to(cuda), w.to(cuda)
+    need = pkg.gemm_workspace_bytes(xd, wd)
+    ws = torch.empty(need, dtype=torch.uint8, device=cuda) if need else None
+    out = pkg.gemm(xd, wd, bias=b.to(cuda), c=c.to(cuda) if beta else None, beta=beta, alpha=alpha, epilogue="BIAS_GELU",
+                   workspace=ws)
+    want = orc.gemm_epilogue(f32(x) @ f32(w), f32(b), f32(c), beta, "BIAS_GELU", orc.BF16, alpha=alpha)
+    orc.check_close(f32(out), want, rtol=2e-2, atol=2e-2, what=f"alpha {alpha} beta {beta} {shape}")
+
+
+@pytest.mark.parametrize("epilogue", ["GELU_AUX", "BIAS_GELU_AUX"])
+@pytest.mark.parametrize("dtype,out_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float16, torch.float32)])
+@pytest.mark.parametrize("order", ["row", "col"])
+def test_auxiliary_output_epilogues(pkg, orc, cuda, epilogue, dtype, out_dtype, order):
+    """GELU_AUX / BIAS_GELU_AUX (onednn_matmul_utils.h:42-43): D = gelu(z) and the pre-activation z
+    as a second result, for a small and a CTA-pair-sized problem, row- and column-major output."""
+    for (M, K, N) in ((200, 136, 328), (2304, 256, 4352)):
+        g = torch.Generator().manual_seed(N)
+        x = torch.randn(M, K, generator=g).to(dtype)
+        w = (torch.randn(K, N, generator=g) * 0.1).to(dtype)
+        blen = N if order == "row" else M        # the bias follows the columns of the rewritten problem
+        b = torch.randn(blen, generator=g).to(dtype) if "BIAS" in epilogue else None
+        mk = (lambda: torch.full((M, N), float("nan"), dtype=out_dtype, device=cuda)) if order == "row" else \
+             (lambda: torch.full((N, M), float("nan"), dtype=out_dtype, device=cuda).t())
+        out, aux = mk(), mk()
+        pkg.gemm(x.to(cuda), w.to(cuda), bias=None if b is None else b.to(cuda), epilogue=epilogue, out=out, aux=aux)
+        acc = f32(x) @ f32(w)
+        odt = {torch.bfloat16: orc.BF16, torch.float32: orc.F32}[out_dtype]
+        if order == "row":
+            want_d, want_aux = orc.gemm_epilogue(acc, None if b is None else f32(b), None, 0.0, epilogue, odt, with_aux=True)
+        else:
+            d_t, aux_t = orc.gemm_epilogue(acc.T, None if b is None else f32(b), None, 0.0, epilogue, odt, with_aux=True)
+            want_d, want_aux = d_t.T, aux_t.T
+        rtol, atol = TOL[out_dtype]
+        orc.check_close(f32(aux), want_aux, rtol=rtol, atol=atol, what=f"{epilogue} aux {M}x{N} {order}")
+        orc.check_close(f32(out), want_d, rtol=rtol, atol=atol, what=f"{epilogue} d {M}x{N} {order}")
+    with pytest.raises(pkg.IxkError) as e:       # without the second buffer: the reference's answer
+        pkg.gemm(x.to(cuda), w.to(cuda), epilogue="GELU_AUX")
+    assert e.value.status == pkg.IXK_UNIMPLEMENTED
+
+
+@pytest.mark.parametrize("shape", [(128, 64, 256), (200, 136, 328), (2304, 264, 4352), (16, 4096, 1024)])
+@pytest.mark.parametrize("la", ["row", "col"])
+@pytest.mark.parametrize("lb", ["row", "col"])
+def test_fp32_triple_runs_in_tf32(pkg, orc, cuda, shape, la, lb):
+    """(F32,F32,F32) (onednn_matmul_utils.cc:609) on the tensor cores in TF32, the reference's
+    XLA_FP32_MATH_MODE=TF32 (onednn_util.h:53-70).  Bound that holds for any TF32 implementation:
+    each operand is off by < 2^-10 relative, so |D - A.B| <= 2^-9 (|A|.|B|); and the result must be
+    the fp32 sum of products of operands cut to TF32 one way or the other (truncated or rounded)."""
+    M, K, N = shape
+    if (la == "col" and M % 4) or (lb == "row" and N % 4) or K % 4:
+        pytest.skip("pitch not a multiple of 16 bytes")
+    g = torch.Generator().manual_seed(M + K + N)
+    x = torch.randn(M, K, generator=g)
+    w = torch.randn(K, N, generator=g) * 0.1
+    b = torch.randn(N, generator=g)
+    c = torch.randn(M, N, generator=g)
+    out = pkg.gemm(as_layout(x.to(cuda), la), as_layout(w.to(cuda), lb), bias=b.to(cuda), c=c.to(cuda), beta=0.5,
+                   alpha=2.0, epilogue="BIAS")
+    assert out.dtype == torch.float32
+    xn, wn = x.numpy(), w.numpy()
+    exact = 2.0 * (xn.astype(np.float64) @ wn.astype(np.float64)) + b.numpy() + 0.5 * c.numpy()
+    bound = 2.0 * 2.0 ** -9 * (np.abs(xn).astype(np.float64) @ np.abs(wn).astype(np.float64)) + 1e-4
+    got = f32(out).astype(np.float64)
+    assert np.all(np.abs(got - exact) <= bound), float(np.max(np.abs(got - exact) / bound))
+    errs = []
+    for mode in ("truncate", "round"):
+        model = 2.0 * (orc.tf32_operand(xn, mode).astype(np.float64) @ orc.tf32_operand(wn, mode).astype(np.float64)) \
+            + b.numpy() + 0.5 * c.numpy()
+        errs.append(float(np.max(np.abs(got - model))))
+    scale = float(np.max(np.abs(exact)))
+    assert min(errs) <= 2e-5 * scale * np.sqrt(K / 64.0) + 1e-5, errs      # fp32 summation order only
+    # GELU epilogue and a batch, against the oracle's epilogue chain on the TF32 model that matched
+    mode = ("truncate", "round")[int(np.argmin(errs))]
+    xb = torch.randn(3, 64, 96, generator=g)
+    wb = torch.randn(3, 96, 40, generator=g) * 0.2
+    outb = pkg.gemm(xb.to(cuda), wb.to(cuda), epilogue="GELU")
+    for i in range(3):
+        acc = orc.tf32_operand(xb[i].numpy(), mode) @ orc.tf32_operand(wb[i].numpy(), mode)
+        want = orc.gemm_epilogue(acc, None, None, 0.0, "GELU", orc.F32)
+        orc.check_close(f32(outb[i]), want, rtol=1e-3, atol=1e-3, what=f"tf32 batch {i}")
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 256), (200, 144, 336), (2304, 272, 4352), (16, 4096, 1024), (1, 16, 16)])
+@pytest.mark.parametrize("la", ["row", "col"])
+@pytest.mark.parametrize("lb", ["row", "col"])
+def test_int8_triple_is_exact(pkg, orc, cuda, shape, la, lb):
+    """(S8,S8,S32) (onednn_matmul_utils.cc:610): integer products summed in 32 bits, bit for bit,
+    over the whole signed 8-bit range."""
+    M, K, N = shape
+    if (la == "col" and M % 16) or (lb == "row" and N % 16) or K % 16:
+        pytest.skip("pitch not a multiple of 16 bytes")
+    g = torch.Generator().manual_seed(M * 7 + K * 3 + N)
+    x = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8)
+    w = torch.randint(-128, 128, (K, N), generator=g, dtype=torch.int8)
+    out = pkg.gemm(as_layout(x.to(cuda), la), as_layout(w.to(cuda), lb), out_dtype=torch.int32)
+    assert out.dtype == torch.int32
+    assert np.array_equal(out.cpu().numpy(), orc.gemm_s8(x.numpy(), w.numpy()))
+    with pytest.raises(pkg.IxkError) as e:
+        pkg.gemm(x.to(cuda), w.to(cuda), out_dtype=torch.int32, epilogue="RELU")
+    assert e.value.status == pkg.IXK_UNIMPLEMENTED
+
+
 def test_unaligned_pitch_is_rejected(pkg, cuda):
     x = torch.zeros(16, 20, dtype=torch.bfloat16, device=cuda)   # pitch 40 bytes
     w = torch.zeros(20, 16, dtype=torch.bfloat16, device=cuda)
     with pytest.raises(pkg.IxkError) as e:
         pkg.gemm(x, w)
     assert e.value.status == pkg.IXK_UNIMPLEMENTED
-    with pytest.raises(pkg.IxkError) as e:
-        pkg.gemm(torch.zeros(16, 16, dtype=torch.float32, device=cuda), torch.zeros(16, 16, dtype=torch.float32, device=cuda))
+    with pytest.raises(pkg.IxkError) as e:       # a type triple outside RunGemm's list
+        pkg.gemm(torch.zeros(16, 16, dtype=torch.float32, device=cuda), torch.zeros(16, 16, dtype=torch.float32, device=cuda),
+                 out_dtype=torch.bfloat16)
     assert e.value.status == pkg.IXK_UNIMPLEMENTED
 
 

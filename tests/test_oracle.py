@@ -116,14 +116,21 @@ def test_gemm_custom_call_col_major_output_bias_runs_along_rows(orc):
     np.testing.assert_allclose(got[0], a @ b + bias[:, None], rtol=1e-6, atol=1e-6)
 
 
-def test_gemm_custom_call_rejects_aux_and_alpha(orc):
+def test_gemm_custom_call_alpha_aux_and_unknown_epilogue(orc):
     a = np.zeros((2, 2), np.float32)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(NotImplementedError):      # one result only: the reference's answer for *_AUX
         orc.gemm_custom_call(_attrs(2, 2, 2, 0, 0, 0), a, a, None, None, "GELU_AUX", orc.F32)
-    bad = _attrs(2, 2, 2, 0, 0, 0)
-    bad["alpha"] = 2.0
-    with pytest.raises(NotImplementedError):
-        orc.gemm_custom_call(bad, a, a, None, None, "DEFAULT", orc.F32)
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((4, 6)).astype(np.float32)
+    w = rng.standard_normal((6, 3)).astype(np.float32)
+    scaled = _attrs(4, 6, 3, 0, 0, 0)
+    scaled["alpha"] = -0.5
+    got = orc.gemm_custom_call(scaled, x, w, None, None, "DEFAULT", orc.F32)
+    np.testing.assert_allclose(got[0], -0.5 * (x @ w), rtol=1e-6, atol=1e-6)
+    b = rng.standard_normal(3).astype(np.float32)
+    d, aux = orc.gemm_epilogue(x @ w, b, None, 0.0, "BIAS_GELU_AUX", orc.F32, alpha=2.0, with_aux=True)
+    np.testing.assert_allclose(aux, 2.0 * (x @ w) + b, rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(d, orc.gelu_tanh(aux), rtol=1e-6, atol=1e-6)
     with pytest.raises(ValueError):
         orc.gemm_custom_call(_attrs(2, 2, 2, 0, 0, 0), a, a, None, None, "SILU", orc.F32)
 
@@ -234,3 +241,16 @@ def test_fmha_backward_golden(orc):
                                        causal=name == "causal")
         for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
             orc.check_close(got, g[f"{key}_{name}"], rtol=2e-2, atol=2e-2, what=f"golden {key} {name}")
+
+
+def test_tf32_and_int8_models(orc):
+    x = np.array([1.0 + 2.0 ** -11, 1.0 + 2.0 ** -10, -3.0 - 2.0 ** -12, 1e-30], np.float32)
+    t = orc.tf32_operand(x, "truncate")
+    r = orc.tf32_operand(x, "round")
+    assert t[0] == 1.0 and t[1] == np.float32(1.0 + 2.0 ** -10) and t[2] == -3.0
+    assert r[0] == np.float32(1.0 + 2.0 ** -10) and r[2] == -3.0        # half an ulp rounds away; a quarter does not
+    assert np.all((t.view(np.uint32) & 0x1FFF) == 0) and np.all((r.view(np.uint32) & 0x1FFF) == 0)
+    a = np.full((1, 4), -128, np.int8)
+    assert orc.gemm_s8(a, a.T)[0, 0] == 4 * 128 * 128
+    big = np.full((1, 140000), 127, np.int8)        # 140000 * 127^2 > 2^31: wraps like the hardware's 32-bit sum
+    assert orc.gemm_s8(big, big.T)[0, 0] == np.int64(140000 * 127 * 127).astype(np.int32)

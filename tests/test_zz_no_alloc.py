@@ -53,11 +53,19 @@ def test_matches_the_workspace_entry_point_twice_in_a_row(pkg, cuda):
 
             got = torch.full_like(q, float("nan"))
             got_lse = torch.full((B, N, F), float("nan"), dtype=torch.float32, device=cuda)
+            if round_ == 0:
+                # The very first call on a device may be the one that makes the CUDA runtime load the
+                # part of the library image that holds the array (module loading is lazy), so the
+                # steady state is what is measured: one untimed call first.
+                assert _call_static(pkg, q, k, v, got, got_lse, causal) == pkg.IXK_OK
             torch.cuda.synchronize()
-            before = torch.cuda.memory_allocated()
+            free_before, _ = torch.cuda.mem_get_info()           # the driver's view: sees any cudaMalloc, whoever makes it
+            torch_before = torch.cuda.memory_allocated()
             assert _call_static(pkg, q, k, v, got, got_lse, causal) == pkg.IXK_OK
             torch.cuda.synchronize()
-            assert torch.cuda.memory_allocated() == before       # nothing went through torch's allocator
+            free_after, _ = torch.cuda.mem_get_info()
+            assert free_after == free_before                     # no device memory was taken (or given back) by the call
+            assert torch.cuda.memory_allocated() == torch_before  # and nothing went through torch's allocator either
 
             # same kernels, same split count → identical bits; the suite's tolerance (2e-2) as the outer bound
             assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2)
