@@ -419,6 +419,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint32_t b_lbo = args.b_mn_major ? kSlabElems * kSlabBytes : 16;
       const uint32_t a_kstep = args.a_mn_major ? kUmmaK * kSlabBytes : 32;
       const uint32_t b_kstep = args.b_mn_major ? kUmmaK * kSlabBytes : 32;
+      // 32-bit elements, MN-major: the 128-byte swizzle in 32-byte pieces, groups of 4 k rows
+      const bool a_sw32 = kKind == ptx::kKindTf32 && args.a_mn_major, b_sw32 = kKind == ptx::kKindTf32 && args.b_mn_major;
+      const uint32_t a_sbo = a_sw32 ? 512 : 1024, b_sbo = b_sw32 ? 512 : 1024;
+      const uint32_t a_type = a_sw32 ? 1 : 2, b_type = b_sw32 ? 1 : 2;
       for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
         if (!ptx::mbar_wait(acc_empty_bar(buf), acc_phase ^ 1u, ctl, kSiteMmaAcc)) break;
         ptx::tc_fence_after_sync();
@@ -433,8 +437,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const uint32_t b_src = a_src + kATileBytes;
 #pragma unroll
           for (int ks = 0; ks < kSlabElems / kUmmaK; ++ks) {
-            const uint64_t da = ptx::umma_smem_desc(a_src + ks * a_kstep, a_lbo, 1024);
-            const uint64_t db = ptx::umma_smem_desc(b_src + ks * b_kstep, b_lbo, 1024);
+            const uint64_t da = ptx::umma_smem_desc(a_src + ks * a_kstep, a_lbo, a_sbo, a_type);
+            const uint64_t db = ptx::umma_smem_desc(b_src + ks * b_kstep, b_lbo, b_sbo, b_type);
             ptx::umma_ss_elect<kKind>(d_tmem, da, db, args.idesc, (kb | ks) != 0 ? 1u : 0u);
           }
           ptx::umma_commit_elect(empty_bar(stage));
@@ -629,6 +633,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t b_lbo = args.b_mn_major ? kSlabElems * kSlabBytes : 16;
     const uint32_t a_kstep = args.a_mn_major ? kUmmaK * kSlabBytes : 32;
     const uint32_t b_kstep = args.b_mn_major ? kUmmaK * kSlabBytes : 32;
+    // 32-bit elements, MN-major: the 128-byte swizzle in 32-byte pieces, groups of 4 k rows
+    const bool a_sw32 = kKind == ptx::kKindTf32 && args.a_mn_major, b_sw32 = kKind == ptx::kKindTf32 && args.b_mn_major;
+    const uint32_t a_sbo = a_sw32 ? 512 : 1024, b_sbo = b_sw32 ? 512 : 1024;
+    const uint32_t a_type = a_sw32 ? 1 : 2, b_type = b_sw32 ? 1 : 2;
     for (int t = pair_id; t < num_tiles && alive; t += num_pairs) {
       if (!ptx::mbar_wait(acc_empty_bar(buf), acc_phase ^ 1u, ctl, kSitePairAcc)) break;
       ptx::tc_fence_after_sync();
@@ -643,8 +651,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint32_t b_src = a_src + kATileBytes;
 #pragma unroll
         for (int ks = 0; ks < kSlabElems / kUmmaK; ++ks) {
-          const uint64_t da = ptx::umma_smem_desc(a_src + ks * a_kstep, a_lbo, 1024);
-          const uint64_t db = ptx::umma_smem_desc(b_src + ks * b_kstep, b_lbo, 1024);
+          const uint64_t da = ptx::umma_smem_desc(a_src + ks * a_kstep, a_lbo, a_sbo, a_type);
+          const uint64_t db = ptx::umma_smem_desc(b_src + ks * b_kstep, b_lbo, b_sbo, b_type);
           ptx::umma_ss_pair_elect<kKind>(d_tmem, da, db, args.idesc, (kb | ks) != 0 ? 1u : 0u);
         }
         ptx::umma_commit_pair_elect(empty_bar(stage));  // both CTAs' producers may refill the slot
@@ -782,6 +790,7 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
     s.dtype = dt;
     s.rank = 3;
     s.swizzle128 = true;
+    s.swizzle_atom32 = mn_major && es == 4;  // what an MN-major operand of 32-bit elements needs
     if (mn_major) {
       s.dims[0] = mn;
       s.dims[1] = p.K;

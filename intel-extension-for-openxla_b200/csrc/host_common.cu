@@ -86,7 +86,8 @@ int encode_tmap(CUtensorMap* out, const void* base, const TmapSpec& s) {
   }
   CUresult r = g_encode(out, s.dtype, s.rank, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        s.swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        !s.swizzle128 ? CU_TENSOR_MAP_SWIZZLE_NONE
+                        : s.swizzle_atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     std::string m = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(r)) + " (rank " +

@@ -48,6 +48,7 @@ struct TmapSpec {
   uint64_t strides_bytes[3];
   uint32_t box[4];
   bool swizzle128;
+  bool swizzle_atom32 = false;  // with swizzle128: exchange 32-byte pieces (by row modulo 4) instead of 16-byte ones
 };
 int encode_tmap(CUtensorMap* out, const void* base, const TmapSpec& spec);
 

@@ -539,14 +539,17 @@ __device__ __forceinline__ void umma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, ui
 //     8-row groups; LBO is not used by the hardware and set to 1 unit.
 //   MN-major operand (rows of 128 contiguous bytes along M/N, one row per k):
 //     SBO = bytes between 8-k groups, LBO = bytes between 128-byte-wide column blocks.
+// layout_type 1 is the 128-byte swizzle in 32-byte pieces (pieces of a row exchanged by the row
+// index modulo 4): the form an MN-major operand of 32-bit elements must have; its groups are 4 k
+// rows, so SBO = 512 for dense rows.
 __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
+                                                   uint32_t sbo_bytes, uint32_t layout_type = 2) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
   d |= 1ull << 46;
-  d |= 2ull << 61;
+  d |= static_cast<uint64_t>(layout_type) << 61;
   return d;
 }
 
