@@ -262,8 +262,12 @@ int ixk_fmha_fwd_static_scratch(const ixk_fmha_desc* desc, const void* q, const 
  * the forward call; grad_out, dq, dk, dv are [B,N,F|T,H] views with their own strides (elements,
  * innermost 1).  The reference's dp_sum and grad_query_accum scratch arguments are the workspace:
  * ixk_fmha_bwd_workspace_bytes(desc) bytes, 16-byte aligned.  q, k, v, out, grad_out: 16-byte
- * aligned with strides that are multiples of 8; dq, dk, dv likewise.  head_size <= 128 (256 is
- * IXK_UNIMPLEMENTED: the reference's 64x128x256 policy has no counterpart yet). */
+ * aligned with strides that are multiples of 8; dq, dk, dv likewise.  head_size <= 128 runs as one
+ * fused tensor-core kernel between a prepare and a convert pass; 128 < head_size <= 256 (the
+ * reference's 64x128x256 policy, fmha_policy.h:107-116) runs as a chain of batched tensor-core
+ * GEMMs over a group of heads at a time, with the score-sized intermediates (12 bytes per
+ * query-key pair of the group, at most about 192 MB unless one head alone needs more) in the
+ * workspace: same formulas and roundings, more HBM traffic. */
 typedef struct ixk_fmha_bwd_desc {
   ixk_fmha_desc fwd;
   int64_t do_strides[3]; /* B, N, F */

@@ -257,12 +257,6 @@ __device__ __forceinline__ void bwd_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uin
       "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-#ifdef IXK_BWD_TRACE
-__device__ long long g_bwd_trace[4096];
-#define BWD_TRACE(role, ev, it) do { if (blockIdx.x == 0 && (it) < 16) g_bwd_trace[((role) * 16 + (it)) * 8 + (ev)] = clock64(); } while (0)
-#else
-#define BWD_TRACE(role, ev, it) do {} while (0)
-#endif
 
 template <int kHeadDim, bool kBias, bool kBf16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -436,9 +430,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const uint32_t st = it & 1;
         const uint32_t q_addr = stage_q(st), do_addr = do_smem;
         const bool more = it + 1 < n_steps;
-        BWD_TRACE(0, 0, it);
         if (!ptx::mbar_wait(p_ready, it & 1, ctl, kSiteBwdP)) break;
-        BWD_TRACE(0, 1, it);
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < kBlk / 16; ++ks)     // dV += P^T.dO over 16 queries at a time
@@ -450,9 +442,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           ptx::tc_fence_after_sync();
           issue_s(stage_q(st ^ 1));
         }
-        BWD_TRACE(0, 2, it);
         if (!ptx::mbar_wait(ds_ready, it & 1, ctl, kSiteBwdDs)) break;
-        BWD_TRACE(0, 3, it);
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < kBlk / 16; ++ks)     // dQ^T = K^T.dS^T over 16 keys at a time
@@ -468,11 +458,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         ptx::umma_commit_elect(q_empty(st));
         if (more) {
           // dP^T shares its columns with dQ^T at head size 128
-          BWD_TRACE(0, 4, it);
           if (!ptx::mbar_wait(dq_free, it & 1, ctl, kSiteBwdDqFree)) break;
-          BWD_TRACE(0, 5, it);
           if (!ptx::mbar_wait(do_full, (it + 1) & 1, ctl, kSiteBwdQdoFull)) break;
-          BWD_TRACE(0, 6, it);
           ptx::tc_fence_after_sync();
           issue_dp(do_smem);
         }
@@ -492,9 +479,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     for (int it = 0; it < n_steps && alive; ++it) {
       const uint32_t st = it & 1;
       if (!ptx::mbar_wait(q_full(st), (it >> 1) & 1, ctl, kSiteBwdQdoFull)) { alive = false; break; }
-      if (threadIdx.x == 0) BWD_TRACE(1, 0, it);
       if (!ptx::mbar_wait(s_full, it & 1, ctl, kSiteBwdS)) { alive = false; break; }
-      if (threadIdx.x == 0) BWD_TRACE(1, 1, it);
       ptx::tc_fence_after_sync();
       const int q0 = (i0 + it) * kBlk;
       const float* nl = reinterpret_cast<const float*>(smem_raw + rows_off(st)) + 64 * half;
@@ -528,7 +513,6 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         };
         if constexpr (kBias) load_bias(0);
         ptx::tmem_ld_wait();
-        if (threadIdx.x == 0) BWD_TRACE(1, 5, it);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t pw[16];
@@ -567,15 +551,11 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
       };
       if (need_mask) phase_a(std::true_type{}); else phase_a(std::false_type{});
-      if (threadIdx.x == 0) BWD_TRACE(1, 6, it);
       ptx::tmem_st_wait();
-      if (threadIdx.x == 0) BWD_TRACE(1, 7, it);
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(p_ready);
-      if (threadIdx.x == 0) BWD_TRACE(1, 2, it);
       // phase B: dS^T = P^T * (dP^T - D)
       if (!ptx::mbar_wait(dp_full, it & 1, ctl, kSiteBwdDp)) { alive = false; break; }
-      if (threadIdx.x == 0) BWD_TRACE(1, 3, it);
       ptx::tc_fence_after_sync();
       uint32_t dp[2][32];
       ptx::tmem_ld_32x32(tmem_base + lane_addr + C::kTmemDP + 64 * half, dp[0]);
@@ -611,7 +591,6 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(ds_ready);
-      if (threadIdx.x == 0) BWD_TRACE(1, 4, it);
     }
     // epilogue: this thread's row of dV and dK
     const bool have = n_steps > 0 && alive && ptx::mbar_wait(final_bar, 0, ctl, kSiteBwdFinal);
@@ -660,9 +639,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t piece = 0;      // running count of staged pieces: buffer = piece & 1
     for (int it = 0; it < n_steps; ++it) {
-      if (d == 0) BWD_TRACE(2, 0, it);
       if (!ptx::mbar_wait(dq_full, it & 1, ctl, kSiteBwdDqFull)) break;
-      if (d == 0) BWD_TRACE(2, 1, it);
       ptx::tc_fence_after_sync();
       const int q0 = (i0 + it) * kBlk;
       float* dst = args.dq_acc + (static_cast<int64_t>(bn) * args.f_pad + q0) * kHeadDim;
@@ -675,7 +652,6 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // the columns are free once they sit in registers
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(dq_free);
-      if (d == 0) BWD_TRACE(2, 2, it);
       // Pieces of 16 query rows in four staging buffers: transpose through shared memory into the accumulator's
       // [query][head dim] order (conflict-free: a warp writes 32 consecutive floats of one row),
       // then one bulk reduction per piece adds the contiguous block to global memory.
@@ -699,7 +675,6 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           ptx::bulk_commit_group();
         }
       }
-      if (d == 0) BWD_TRACE(2, 3, it);
     }
     if (threadIdx.x == kReduceWarp * 32) ptx::bulk_wait_group<0>();   // all additions performed before the CTA exits
   } else {
@@ -801,20 +776,23 @@ int f_pad_of(int F) { return (F + kBlk - 1) / kBlk * kBlk; }
 }  // namespace
 
 size_t bwd_workspace_bytes(const Problem& p) {
-  if (p.B == 0 || p.N == 0 || p.F == 0 || p.H > 128) return 0;
+  if (p.B == 0 || p.N == 0 || p.F == 0) return 0;
+  if (p.H > 128) {  // the two per-row arrays (256-byte aligned end) + the score-sized scratch of one group of heads
+    const size_t rows = (static_cast<size_t>(p.B) * p.N * f_pad_of(p.F) * 2 * sizeof(float) + 255) / 256 * 256;
+    return rows + bwd_wide_scratch_bytes(p);
+  }
   return static_cast<size_t>(p.B) * p.N * f_pad_of(p.F) * (head_pad_of(p.H) + 2) * sizeof(float);
 }
 
 int launch_bwd(const BwdProblem& bp, const DeviceInfo& dev, void* workspace, size_t workspace_bytes,
                cudaStream_t stream) {
   const Problem& p = bp.fwd;
-  if (p.H > 128)
-    return fail(IXK_UNIMPLEMENTED, "attention backward covers head_size <= 128 (dK and dV of a 256-wide head fill tensor memory)");
   const size_t need = bwd_workspace_bytes(p);
   if (workspace == nullptr || workspace_bytes < need)
     return fail(IXK_WORKSPACE_TOO_SMALL, "attention backward needs ixk_fmha_bwd_workspace_bytes(desc) bytes of workspace");
   if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return fail(IXK_INVALID_ARGUMENT, "workspace must be 16-byte aligned");
-  const int f_pad = f_pad_of(p.F), head_pad = head_pad_of(p.H);
+  const bool wide = p.H > 128;
+  const int f_pad = f_pad_of(p.F), head_pad = wide ? 0 : head_pad_of(p.H);   // (no fp32 dQ accumulator on the wide path)
   const int64_t rows = static_cast<int64_t>(p.B) * p.N * f_pad;
   float* neg_lse2 = static_cast<float*>(workspace);
   float* delta = neg_lse2 + rows;
@@ -838,6 +816,10 @@ int launch_bwd(const BwdProblem& bp, const DeviceInfo& dev, void* workspace, siz
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
 
+  if (wide) {
+    unsigned char* scratch = static_cast<unsigned char*>(workspace) + (static_cast<size_t>(rows) * 2 * sizeof(float) + 255) / 256 * 256;
+    return launch_bwd_wide(bp, dev, neg_lse2, delta, f_pad, scratch, stream);
+  }
   int rc;
   const bool bias = p.bias != nullptr;
   if (head_pad == 64) {
@@ -864,8 +846,3 @@ int launch_bwd(const BwdProblem& bp, const DeviceInfo& dev, void* workspace, siz
 }  // namespace fmha
 }  // namespace ixk
 
-#ifdef IXK_BWD_TRACE
-extern "C" int ixk_debug_bwd_trace(long long* host_out, int count) {
-  return cudaMemcpyFromSymbol(host_out, ixk::fmha::g_bwd_trace, sizeof(long long) * count) == cudaSuccess ? 0 : 1;
-}
-#endif

@@ -126,41 +126,6 @@ __device__ __forceinline__ float unpack_hi(uint32_t w, bool bf16) {
   return bf16 ? __uint_as_float(w & 0xffff0000u) : __half2float(__ushort_as_half(static_cast<uint16_t>(w >> 16)));
 }
 
-// Optional self-timing, compiled in only with -DIXK_FMHA_TRACE (pipeline studies; never part of
-// the shipped library).  CTA 0 stamps clock64() into a device array of [10 kinds][32 rows][8
-// events] that ixk_debug_fmha_trace() copies out:
-//   kinds 0-7  softmax warp w, row = 16 * (item - 1) + key block, for the CTA's 2nd and 3rd item
-//   kind  8    the MMA issuer, same rows
-//   kind  9    row = item: issuer loop-top (event 0; event 1 for the last CTA) and producer events
-//              4-7; rows 8 + key block of the 2nd item: issuer bookkeeping between two key blocks
-// The macros use the enclosing scope's `it` (item counter) and, for IXK_TRACE, `trace_on`.
-#ifdef IXK_FMHA_TRACE
-__device__ long long g_fmha_trace[10 * 32 * 8];
-#define IXK_TRACE(kind, j, ev)                                                                \
-  do {                                                                                         \
-    if (blockIdx.x == 0 && (j) < 16 && trace_on)                                               \
-      g_fmha_trace[((kind)*32 + (it - 1) * 16 + (j)) * 8 + (ev)] = clock64();                  \
-  } while (0)
-#define IXK_HTRACE(jj, col)                                                                    \
-  do {                                                                                         \
-    if (blockIdx.x == 0 && it == 1 && (jj) < 16) g_fmha_trace[(9 * 32 + 8 + (jj)) * 8 + (col)] = clock64(); \
-  } while (0)
-#define IXK_PTRACE(col)                                                                        \
-  do {                                                                                         \
-    if (blockIdx.x == 0 && it < 8) g_fmha_trace[(9 * 32 + it) * 8 + (col)] = clock64();        \
-  } while (0)
-#else
-#define IXK_TRACE(kind, j, ev) \
-  do {                         \
-  } while (0)
-#define IXK_HTRACE(jj, col) \
-  do {                      \
-  } while (0)
-#define IXK_PTRACE(col) \
-  do {                  \
-  } while (0)
-#endif
-
 // One unit of work: a (batch, head, query block) triple and how many key blocks each of its
 // query tiles visits.
 struct Item {
@@ -180,14 +145,28 @@ struct Item {
 
 template <int kQTiles>
 __device__ __forceinline__ Item get_item(const KernelArgs& args, int w) {
-  // Items are ordered heaviest first: under a causal mask the last query block sees the most keys.
+  // Causal: items are ordered heaviest first (the last query block sees the most keys), query
+  // block by query block over all (batch, head) pairs, which the alternating deal below balances.
+  // Non-causal: every item weighs the same, so the order is free and is chosen for L2: the query
+  // blocks of one (batch, head) are neighbours, then the heads of one batch.  The CTAs of a round
+  // then work on about a batch's worth of pairs at a time: K and V of a pair (and a bias slab
+  // shared by the heads of a batch) come from HBM once and are found in L2 by the other query
+  // blocks, instead of every pair's K and V being streamed again for every query block.
   const int pairs = args.N * args.B;
-  const int rank = w / pairs;
-  const int rest = w - rank * pairs;
   Item it;
-  it.head = rest % args.N;
-  it.batch = rest / args.N;
-  const int qb = args.causal ? (args.num_qblocks - 1 - rank) : rank;
+  int qb;
+  if (args.causal) {
+    const int rank = w / pairs;
+    const int rest = w - rank * pairs;
+    it.head = rest % args.N;
+    it.batch = rest / args.N;
+    qb = args.num_qblocks - 1 - rank;
+  } else {
+    const int pair = w / args.num_qblocks;
+    qb = w - pair * args.num_qblocks;
+    it.head = pair % args.N;
+    it.batch = pair / args.N;
+  }
   it.q0 = qb * (kBlockQ * kQTiles);
   const int kv_blocks_all = (args.T + kBlockKV - 1) / kBlockKV;
   it.nblk0 = it.nblk1 = 0;
@@ -349,7 +328,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       uint32_t it = 0;
       for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
         const Item item = get_item<kQTiles>(args, w);
-        IXK_PTRACE(7);
         // Q of tile t, once the tile's last S of the previous item has been issued.  A tile with
         // no rows in this item still completes its phase, so that parities follow the item count.
         auto load_q = [&](int t) {
@@ -371,13 +349,11 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const int first_tile = (kQTiles == 2 && item.reversed) ? 1 : 0;
         load_q(first_tile);
         if (!alive) break;
-        IXK_PTRACE(4);
         const int loads = 2 * item.nblk_max;
         for (int i = 0; i < loads; ++i, ++load_idx) {
           if (kQTiles == 2 && i == 1) {  // order: Q_0, K_0, Q_1, V_0, K_1, ...
             load_q(1 - first_tile);
             if (!alive) break;
-            IXK_PTRACE(5);
           }
           const int slot = load_idx % kSlots;
           const uint32_t use = load_idx / kSlots;
@@ -385,7 +361,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             alive = false;
             break;
           }
-          if (i == 0) IXK_PTRACE(6);
           const CUtensorMap* map = (i & 1) ? &tmap_v : &tmap_k;
           const int kv_head = item.head * ((i & 1) ? args.v_head_mul : args.k_head_mul);
           const int kv_batch = item.batch * ((i & 1) ? args.v_batch_mul : args.k_batch_mul);
@@ -484,11 +459,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       };
       for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it), q_par ^= 1u) {
         const Item item = get_item<kQTiles>(args, w);
-        [[maybe_unused]] const bool trace_on = (it == 1 || it == 2) && lane == 0;
-#ifdef IXK_FMHA_TRACE
-        if (it < 8 && lane == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
-          g_fmha_trace[(9 * 32 + it) * 8 + (blockIdx.x == 0 ? 0 : 1)] = clock64();
-#endif
         const int nblk_max = item.nblk_max;
         const int first0 = item.first(0), end0 = first0 + item.nblk0;
         const int first1 = item.first(1), end1 = first1 + item.nblk1;
@@ -507,7 +477,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             for (int part = 0; part < kParts; ++part) {
               if (!wait(p_part(t, part), p_par, kSiteMmaP)) return;
               ptx::tc_fence_after_sync();
-              IXK_TRACE(8, j, t * 4 + (part == 0 ? 0 : 1));
 #pragma unroll
               for (int q4 = 0; q4 < 4 / kParts; ++q4) {
                 const int quarter = part * (4 / kParts) + q4;
@@ -515,7 +484,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
               }
             }
             p_par ^= 1u;
-            if (j > 0 && t == 0) IXK_TRACE(8, j, 3);
           }
           if (next_s) {
             if (!active) {  // the tile joins at the next step: its Q is first needed here
@@ -528,16 +496,12 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             }
             issue_s(t, k_slot);
             ptx::umma_commit_elect(s_full(t));
-            IXK_TRACE(8, j, t * 4 + 2);
           }
           // Both slots go back behind the last tile's MMAs (a commit covers everything this
           // thread has issued so far, the other tile's work included).
           if (t == kQTiles - 1) {
-            IXK_HTRACE(j, 0);
             ptx::umma_commit_elect(kv_empty(v_slot));
-            IXK_HTRACE(j, 1);
             if (more) ptx::umma_commit_elect(kv_empty(k_slot));
-            IXK_HTRACE(j, 2);
           }
           if (active && !next_s) {
             ptx::umma_commit_elect(o_final(t));
@@ -550,7 +514,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if ((t == 0 ? first0 : first1) == 0 && item.nblk(t) > 0) {  // a tile's Q is awaited where its first S is issued
             if (!wait(q_full(t), q_par, kSiteMmaQ)) return;
             ptx::tc_fence_after_sync();
-            IXK_TRACE(8, 0, 3);
             issue_s(t, k_slot);
             ptx::umma_commit_elect(s_full(t));
           }
@@ -560,7 +523,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         {
           if (!wait(kv_full(slot), slot_par, kSiteMmaKV)) break;
           ptx::tc_fence_after_sync();
-          IXK_TRACE(8, 0, 7);
           first_s(std::integral_constant<int, 0>{}, slot);
           if (kQTiles == 2 && alive) first_s(std::integral_constant<int, kQTiles - 1>{}, slot);
           advance();
@@ -570,21 +532,17 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           // V_j and K_{j+1} are both needed in this step; asking for them here, where the issuer
           // would otherwise idle until P arrives, keeps the round trips off the MMA sequence.
           const uint32_t v_slot = slot;
-          if (j > 0) IXK_HTRACE(j - 1, 3);
           if (!wait(kv_full(v_slot), slot_par, kSiteMmaKV)) break;
           advance();
           const uint32_t k_slot = slot;  // K_{j+1}, present when `more`
           const uint32_t k_par = slot_par;
-          if (j > 0) IXK_HTRACE(j - 1, 4);
           if (more) {
             // (with a two-slot ring K_{j+1} was only requested when K_j's S had been issued: there
             // the wait stays behind P.V_j, where the load has had time to land)
             if (kSlots > 2 && !wait(kv_full(k_slot), k_par, kSiteMmaKV)) break;
             advance();
           }
-          if (j > 0) IXK_HTRACE(j - 1, 5);
           ptx::tc_fence_after_sync();
-          if (j > 0) IXK_TRACE(8, j, 7);
           tile_turn(std::integral_constant<int, 0>{}, j, more, v_slot, k_slot, k_par);
           if (kQTiles == 2 && alive) tile_turn(std::integral_constant<int, kQTiles - 1>{}, j, more, v_slot, k_slot, k_par);
         }
@@ -728,7 +686,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       uint32_t it = 0;
       for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
         const Item item = get_item<kQTiles>(args, w);
-        [[maybe_unused]] const bool trace_on = (it == 1 || it == 2) && lane == 0;
         const int my_blocks = item.nblk(t);
         if (my_blocks == 0) continue;
         const int q0 = item.q0, head = item.head, batch = item.batch;
@@ -747,12 +704,10 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           }
           ++n_s;
           ptx::tc_fence_after_sync();
-          IXK_TRACE(warp, j, 0);
           uint32_t r[4][32];
 #pragma unroll
           for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32(s_addr + c * 32, r[c]);
           ptx::tmem_ld_wait();
-          IXK_TRACE(warp, j, 1);
           const int kv0 = (item.reversed ? my_blocks - 1 - j : j) * kBlockKV;
           // Scores enter the exponential as x = r * mult - m.  Fast path: r is the raw Q.K^T and
           // mult = head_scale * log2(e) (> 0, so the row maximum can be taken on r).  With a
@@ -883,7 +838,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
               ptx::tmem_st_32x32(o_addr + c * 32, o);
             }
           }
-          IXK_TRACE(warp, j, 2);
           const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
           const uint64_t mult2 = ptx::f32x2(mult, mult);
           // bf16 P is made by truncating the fp32 bit pattern (one byte-permute per pair) instead of
@@ -923,12 +877,9 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             ptx::tmem_st_32x16(s_addr + c * 16, pk);
             if ((c + 1) % (4 / kParts) == 0) {
               // hand over this part of P
-              if (j + 2 < my_blocks) IXK_TRACE(warp, j, c == 1 ? 3 : 5);
               ptx::tmem_st_wait();
-              if (j + 2 < my_blocks && c == 3) IXK_TRACE(warp, j, 7);
               ptx::tc_fence_before_sync();
               ptx::mbar_arrive(p_part(t, c / (4 / kParts)));
-              IXK_TRACE(warp, j, 3 + c);
             }
           }
           };
@@ -1072,9 +1023,6 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   if (items > 0x7fffffff) return fail(IXK_UNIMPLEMENTED, "too many (batch, head, query block) work items");
   a.num_items = static_cast<int>(items);
   int grid = a.num_items < dev.sm_count ? a.num_items : dev.sm_count;
-#ifdef IXK_FMHA_TRACE
-  if (const char* e = std::getenv("IXK_FMHA_GRID")) grid = std::min(grid, std::max(1, std::atoi(e)));
-#endif
   fn<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tbias, to, a);
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
@@ -1120,8 +1068,3 @@ int launch_prefill(const Problem& p, const DeviceInfo& dev, cudaStream_t stream)
 }  // namespace fmha
 }  // namespace ixk
 
-#ifdef IXK_FMHA_TRACE
-extern "C" int ixk_debug_fmha_trace(long long* host_out, int count) {
-  return cudaMemcpyFromSymbol(host_out, ixk::fmha::g_fmha_trace, sizeof(long long) * count) == cudaSuccess ? 0 : 1;
-}
-#endif

@@ -57,5 +57,12 @@ size_t bwd_workspace_bytes(const Problem& p);
 int launch_bwd(const BwdProblem& p, const DeviceInfo& dev, void* workspace, size_t workspace_bytes,
                cudaStream_t stream);
 
+// ---- head sizes above 128 (fmha_bwd_wide.cu): the same gradients as a chain of batched GEMMs
+// over a group of heads at a time, with the score-sized intermediates in `scratch`
+// (bwd_wide_scratch_bytes); neg_lse2 / delta are the prepare kernel's per-row arrays [B*N, f_pad].
+size_t bwd_wide_scratch_bytes(const Problem& p);
+int launch_bwd_wide(const BwdProblem& p, const DeviceInfo& dev, const float* neg_lse2, const float* delta, int f_pad,
+                    void* scratch, cudaStream_t stream);
+
 }  // namespace fmha
 }  // namespace ixk

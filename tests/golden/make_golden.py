@@ -5,6 +5,7 @@ toolchain and XeTLA / oneDNN), so these stand in for them.
 
     python tests/golden/make_golden.py            # all files
     python tests/golden/make_golden.py backward   # only fmha_bwd_bf16.npz
+    python tests/golden/make_golden.py backward256  # only fmha_bwd_h256_bf16.npz
 """
 import os
 
@@ -18,12 +19,13 @@ def bits(t: torch.Tensor) -> np.ndarray:
     return t.contiguous().view(torch.uint16).numpy().copy()
 
 
-def backward():
+def backward(H=64, seed=4321, shape=(1, 2, 140, 150), filename="fmha_bwd_bf16.npz"):
     """Attention gradients by autograd over plain fp32 attention: causal, and non-causal with a
-    head-broadcast additive bias; ragged sizes."""
-    torch.manual_seed(4321)
+    head-broadcast additive bias; ragged sizes.  Head size 64, and 256 (the head size of the two
+    decoder-layer configurations) in a file of its own."""
+    torch.manual_seed(seed)
     torch.set_num_threads(1)
-    B, Nh, F, T, H = 1, 2, 140, 150, 64
+    B, Nh, F, T = shape
     scale = H ** -0.5
     q, k, v = (torch.randn(B, Nh, S, H).bfloat16() for S in (F, T, T))
     do = torch.randn(B, Nh, F, H).bfloat16()
@@ -40,7 +42,11 @@ def backward():
         o.backward(do.float())
         out.update({f"o_{name}": o.detach().numpy(), f"lse_{name}": torch.logsumexp(s, dim=-1).detach().numpy(),
                     f"dq_{name}": qf.grad.numpy(), f"dk_{name}": kf.grad.numpy(), f"dv_{name}": vf.grad.numpy()})
-    np.savez_compressed(os.path.join(HERE, "fmha_bwd_bf16.npz"), **out)
+    np.savez_compressed(os.path.join(HERE, filename), **out)
+
+
+def backward256():
+    backward(H=256, seed=8765, shape=(1, 2, 72, 90), filename="fmha_bwd_h256_bf16.npz")
 
 
 def main():
@@ -114,6 +120,9 @@ if __name__ == "__main__":
     import sys
     if sys.argv[1:] == ["backward"]:
         backward()
+    elif sys.argv[1:] == ["backward256"]:
+        backward256()
     else:
         main()
         backward()
+        backward256()

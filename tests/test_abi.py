@@ -83,8 +83,12 @@ def test_workspace_queries_need_no_gpu(pkg):
     assert lib.ixk_fmha_bwd_workspace_bytes(ctypes.byref(bd)) == 2 * 3 * 256 * (128 + 2) * 4
     bd.fwd.head_size = 64
     assert lib.ixk_fmha_bwd_workspace_bytes(ctypes.byref(bd)) == 2 * 3 * 256 * (64 + 2) * 4
-    bd.fwd.head_size = 256       # not covered by the backward kernels
-    assert lib.ixk_fmha_bwd_workspace_bytes(ctypes.byref(bd)) == 0
+    # head sizes above 128: the two per-row arrays (rounded up to 256 bytes) + fp32 and 16-bit scores of
+    # one group of heads, key pitch rounded up to 8 (here all 3 heads fit one group)
+    bd.fwd.head_size = 256
+    rows = 2 * 3 * 256 * 2 * 4
+    assert rows % 256 == 0
+    assert lib.ixk_fmha_bwd_workspace_bytes(ctypes.byref(bd)) == rows + 3 * 200 * 80 * 4 + 3 * 200 * 80 * 2
     assert lib.ixk_fmha_bwd_workspace_bytes(None) == 0
 
 

@@ -17,7 +17,7 @@ def f32(t):
 
 
 def run_case(pkg, orc, cuda, *, B, N, F, T, H, causal=False, bias_shape=None, dtype=torch.bfloat16, seed=0,
-             seq_major=False):
+             seq_major=False, launches_expected=3):
     g = torch.Generator().manual_seed(seed)
 
     def make(S):
@@ -37,7 +37,7 @@ def run_case(pkg, orc, cuda, *, B, N, F, T, H, causal=False, bias_shape=None, dt
     launches = pkg.launch_count()
     pkg.fmha_backward_kernel(None, q, k, v, out, bias, do, lse, dq, dk, dv, scale, causal=causal)
     torch.cuda.synchronize()
-    assert pkg.launch_count() - launches == 3
+    assert pkg.launch_count() - launches == launches_expected
     assert pkg.device_status() == 0
     odt = orc.BF16 if dtype == torch.bfloat16 else orc.F16
     wq, wk, wv = orc.fmha_backward(f32(q), f32(k), f32(v), f32(out), f32(do), f32(lse),
@@ -80,13 +80,50 @@ def test_fp16_and_sequence_major_storage(pkg, orc, cuda):
     run_case(pkg, orc, cuda, B=2, N=4, F=384, T=384, H=64, causal=True, seq_major=True, seed=4)
 
 
+@pytest.mark.parametrize("causal", [False, True], ids=["full", "causal"])
+@pytest.mark.parametrize("case", [dict(B=1, N=1, F=128, T=128, H=256), dict(B=2, N=3, F=200, T=330, H=256),
+                                  dict(B=1, N=2, F=300, T=77, H=160), dict(B=2, N=2, F=5, T=260, H=256),
+                                  dict(B=1, N=4, F=384, T=384, H=256, seq_major=True),
+                                  dict(B=2, N=2, F=260, T=200, H=256, bias_shape=(2, 1)),
+                                  dict(B=1, N=2, F=256, T=256, H=192, dtype=torch.float16)],
+                         ids=lambda c: "B{B}N{N}F{F}T{T}H{H}".format(**c) + ("sm" if c.get("seq_major") else "") +
+                         ("b" if c.get("bias_shape") else "") + ("f16" if c.get("dtype") else ""))
+def test_heads_wider_than_128(pkg, orc, cuda, case, causal):
+    """Head sizes 129..256 (the reference's 64x128x256 backward policy, fmha_policy.h:107-116; both
+    decoder-layer configurations have 256-wide heads): the GEMM-chain path, one group of heads per
+    batch element here: prepare + 5 products + 2 score passes per group."""
+    if case.get("bias_shape") and causal:
+        pytest.skip("one mask at a time")
+    run_case(pkg, orc, cuda, causal=causal, seed=case["F"] + case["H"], launches_expected=1 + 7 * case["B"], **case)
+
+
+def test_wide_heads_in_several_groups(pkg, orc, cuda):
+    """Scores of all heads that do not fit the per-group scratch budget (192 MB) are processed a
+    group of heads at a time: 8 heads of 2304 x 2304 scores (32 MB each) run as groups of 6 and 2."""
+    B, N, F, T, H = 1, 8, 2304, 2304, 256
+    g = torch.Generator(device="cuda").manual_seed(5)
+    mk = lambda S: torch.randn(B, N, S, H, generator=g, device=cuda).bfloat16()
+    q, k, v, do = mk(F), mk(T), mk(T), mk(F)
+    scale = H ** -0.5
+    out = torch.empty_like(q)
+    lse = torch.empty(B, N, F, dtype=torch.float32, device=cuda)
+    pkg.fmha_forward_kernel(None, q, k, v, None, None, 0.0, out, lse, scale, True, causal=True)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    n0 = pkg.launch_count()
+    pkg.fmha_backward_kernel(None, q, k, v, out, None, do, lse, dq, dk, dv, scale, causal=True)
+    assert pkg.launch_count() - n0 == 1 + 7 * 2 and pkg.device_status() == 0
+    mask = torch.ones(F, T, dtype=torch.bool, device=cuda).tril()
+    for n in (0, 7):
+        qq, kk, vv = (t[:, n:n + 1].float().requires_grad_() for t in (q, k, v))
+        ref = torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, attn_mask=mask, scale=scale)
+        ref.backward(do[:, n:n + 1].float())
+        for name, got, want in (("dq", dq, qq.grad), ("dk", dk, kk.grad), ("dv", dv, vv.grad)):
+            rel = ((got[:, n:n + 1].float() - want).norm() / want.norm()).item()
+            assert rel < 1e-2, f"{name}[{n}]: relative error {rel:.3e}"
+
+
 def test_rejections(pkg, cuda):
-    q = torch.randn(1, 1, 128, 256, device=cuda).bfloat16()
     lse = torch.zeros(1, 1, 128, device=cuda)
-    with pytest.raises(pkg.IxkError) as e:
-        pkg.fmha_backward_kernel(None, q, q, q, q, None, q, lse, torch.empty_like(q), torch.empty_like(q),
-                                 torch.empty_like(q), 1.0)
-    assert e.value.status == pkg.IXK_UNIMPLEMENTED
     q = torch.randn(1, 1, 128, 64, device=cuda).bfloat16()
     with pytest.raises(pkg.IxkError):      # gradient buffer of the wrong shape
         pkg.fmha_backward_kernel(None, q, q, q, q, None, q, lse, torch.empty(1, 1, 64, 64, device=cuda).bfloat16(),
@@ -96,10 +133,12 @@ def test_rejections(pkg, cuda):
                                  torch.empty_like(q), 1.0)
 
 
-def test_golden_vectors(pkg, orc, cuda):
-    """Gradients made by autograd over fp32 attention on the CPU (tests/golden/make_golden.py)."""
+@pytest.mark.parametrize("fname", ["fmha_bwd_bf16.npz", "fmha_bwd_h256_bf16.npz"])
+def test_golden_vectors(pkg, orc, cuda, fname):
+    """Gradients made by autograd over fp32 attention on the CPU (tests/golden/make_golden.py),
+    head size 64 (fused kernel) and 256 (GEMM-chain path)."""
     import os
-    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "fmha_bwd_bf16.npz"))
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", fname))
     t = lambda name: torch.from_numpy(g[name].view(np.int16)).view(torch.bfloat16).to(cuda)
     q, k, v, do, bias = (t(n) for n in ("q", "k", "v", "do", "bias"))
     scale = float(g["scale"])

@@ -230,9 +230,11 @@ def test_fmha_backward_matches_autograd(orc):
             np.testing.assert_allclose(got, want.numpy(), rtol=2e-4, atol=2e-5)
 
 
-def test_fmha_backward_golden(orc):
-    """Backward oracle (bf16 operand rounding on) against autograd gradients of fp32 attention."""
-    g = np.load(os.path.join(GOLDEN, "fmha_bwd_bf16.npz"))
+@pytest.mark.parametrize("fname", ["fmha_bwd_bf16.npz", "fmha_bwd_h256_bf16.npz"])
+def test_fmha_backward_golden(orc, fname):
+    """Backward oracle (bf16 operand rounding on) against autograd gradients of fp32 attention,
+    at head size 64 and at 256."""
+    g = np.load(os.path.join(GOLDEN, fname))
     q, k, v, do = (orc.bf16_to_f32(g[n]) for n in ("q", "k", "v", "do"))
     bias = orc.bf16_to_f32(g["bias"])
     for name in ("causal", "bias"):
