@@ -36,6 +36,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <type_traits>
 
@@ -109,6 +110,7 @@ struct KernelArgs {
   // 0 where K / V is one tensor broadcast over heads / batches (stride 0: multi-query attention),
   // 1 otherwise: multiplies the head / batch coordinate of the K and V loads
   int k_head_mul, k_batch_mul, v_head_mul, v_batch_mul;
+  int use_schedule;  // the CTAs walk the host-made work list instead of the dealing formula
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
@@ -190,10 +192,24 @@ __device__ __forceinline__ Item get_item(const KernelArgs& args, int w) {
   return it;
 }
 
-// The i-th work item of a CTA.  Items are dealt in rounds of gridDim.x, alternating direction
-// (0..G-1, then G-1..0, ...), so that a CTA that drew a heavy item in one round draws a light one
-// in the next: with items sorted by weight this keeps the per-CTA totals within a few percent.
-__device__ __forceinline__ int item_of(uint32_t round) {
+// A host-made work list: for every CTA the items it walks, in order.  Used for causal problems
+// small enough for the table to travel as a kernel parameter (it lives in the parameter bank,
+// nothing is allocated): the host deals the items so that the CTAs finish together AND so that the
+// CTAs running at one time work on few (batch, head) pairs, whose K and V then stay in L2.
+constexpr int kSchedMaxCtas = 148;
+constexpr int kSchedMaxPerCta = 16;
+struct Schedule {
+  uint16_t count[kSchedMaxCtas];
+  uint16_t item[kSchedMaxCtas * kSchedMaxPerCta];
+};
+
+// The i-th work item of a CTA.  With a work list: its i-th entry.  Otherwise items are dealt in
+// rounds of gridDim.x, alternating direction (0..G-1, then G-1..0, ...), so that a CTA that drew a
+// heavy item in one round draws a light one in the next: with items sorted by weight this keeps
+// the per-CTA totals within a few percent.
+__device__ __forceinline__ int item_of(const KernelArgs& args, const Schedule& sched, uint32_t round) {
+  if (args.use_schedule)
+    return round < sched.count[blockIdx.x] ? sched.item[blockIdx.x * kSchedMaxPerCta + round] : args.num_items;
   const int g = static_cast<int>(gridDim.x);
   const int c = static_cast<int>(blockIdx.x);
   return static_cast<int>(round) * g + ((round & 1u) ? (g - 1 - c) : c);
@@ -242,7 +258,8 @@ template <int kHeadDim, int kQTiles, int kPolyOf4, bool kBias>
 __global__ void __launch_bounds__(kThreads, 1)
 fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_bias,
-                    const __grid_constant__ CUtensorMap tmap_o, const KernelArgs args) {
+                    const __grid_constant__ CUtensorMap tmap_o, const __grid_constant__ KernelArgs args,
+                    const __grid_constant__ Schedule sched) {
   using C = Cfg<kHeadDim, kQTiles, kBias>;
   constexpr int kSlots = C::kKvSlots;
 
@@ -326,7 +343,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       [[maybe_unused]] uint32_t n_bias0 = 0, n_bias1 = 0;  // bias tiles loaded per query tile
       bool alive = true;
       uint32_t it = 0;
-      for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
+      for (int w = item_of(args, sched, 0); w < args.num_items && alive; w = item_of(args, sched, ++it)) {
         const Item item = get_item<kQTiles>(args, w);
         // Q of tile t, once the tile's last S of the previous item has been issued.  A tile with
         // no rows in this item still completes its phase, so that parities follow the item count.
@@ -457,7 +474,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (!ptx::mbar_wait(bar, parity, ctl, site)) alive = false;
         return alive;
       };
-      for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it), q_par ^= 1u) {
+      for (int w = item_of(args, sched, 0); w < args.num_items && alive; w = item_of(args, sched, ++it), q_par ^= 1u) {
         const Item item = get_item<kQTiles>(args, w);
         const int nblk_max = item.nblk_max;
         const int first0 = item.first(0), end0 = first0 + item.nblk0;
@@ -567,7 +584,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     uint32_t n_sync0 = 0, n_sync1 = 0;  // rendezvous of the four warps around a tile's staging box
     bool alive = true;
     uint32_t it = 0;
-    for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
+    for (int w = item_of(args, sched, 0); w < args.num_items && alive; w = item_of(args, sched, ++it)) {
       const Item item = get_item<kQTiles>(args, w);
       for (int tt = 0; tt < kQTiles && alive; ++tt) {
         const int t = item.reversed ? kQTiles - 1 - tt : tt;  // the tile that started first is served first
@@ -684,7 +701,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       [[maybe_unused]] uint32_t n_bias = 0;  // bias tiles consumed
       bool alive = true;
       uint32_t it = 0;
-      for (int w = item_of(0); w < args.num_items && alive; w = item_of(++it)) {
+      for (int w = item_of(args, sched, 0); w < args.num_items && alive; w = item_of(args, sched, ++it)) {
         const Item item = get_item<kQTiles>(args, w);
         const int my_blocks = item.nblk(t);
         if (my_blocks == 0) continue;
@@ -919,6 +936,52 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   }
 }
 
+// Work list for a causal launch.  Items are taken in an order made for L2 — the (batch, head)
+// pairs in groups of 16, inside a group query block by query block from the heaviest down, so
+// that a group's K and V are in use by many CTAs at once — and each goes to the CTA with the least
+// work so far (cost = key blocks + 1.5 for the item's fixed part).  The two lightest query-block
+// ranks of ALL pairs are held back to the end, where they fill the gaps the heavy items left:
+// without them the finish times spread by up to a heavy item.  Returns false (formula dealing) for
+// non-causal launches and for problems whose list does not fit the table.
+template <int kQTiles>
+bool build_schedule(const KernelArgs& a, int grid, Schedule* out) {
+  if (!a.causal || grid > kSchedMaxCtas || a.num_items > 0xffff || a.num_items > grid * kSchedMaxPerCta) return false;
+  const int pairs = a.N * a.B, nq = a.num_qblocks;
+  if (nq < 3) return false;
+  const int rows_per_item = kBlockQ * kQTiles;
+  const int kv_blocks_all = (a.T + kBlockKV - 1) / kBlockKV;
+  auto cost = [&](int qb) {   // in key-block steps, as get_item counts them (the later tile of the item sees the most keys)
+    const int last_row0 = std::min(qb * rows_per_item + (kQTiles - 1) * kBlockQ, ((a.F - 1) / kBlockQ) * kBlockQ);
+    const int n = std::min(kv_blocks_all, (last_row0 + kBlockQ - 1) / kBlockKV + 1);
+    return 2 * n + 3;         // (doubled: 1.5 steps of fixed cost per item)
+  };
+  int load[kSchedMaxCtas];
+  for (int c = 0; c < grid; ++c) {
+    load[c] = 0;
+    out->count[c] = 0;
+  }
+  bool ok = true;
+  auto give = [&](int pair, int qb) {
+    int best = 0;
+    for (int c = 1; c < grid; ++c)
+      if (load[c] < load[best]) best = c;
+    if (out->count[best] >= kSchedMaxPerCta) {
+      ok = false;
+      return;
+    }
+    const int rank = nq - 1 - qb;   // the item numbering of get_item: rank-major, heaviest query block first
+    out->item[best * kSchedMaxPerCta + out->count[best]++] = static_cast<uint16_t>(rank * pairs + pair);
+    load[best] += cost(qb);
+  };
+  constexpr int kGroup = 16, kHeldBack = 2;
+  for (int p0 = 0; p0 < pairs && ok; p0 += kGroup)
+    for (int qb = nq - 1; qb >= kHeldBack && ok; --qb)
+      for (int pr = p0; pr < std::min(pairs, p0 + kGroup) && ok; ++pr) give(pr, qb);
+  for (int qb = kHeldBack - 1; qb >= 0 && ok; --qb)
+    for (int pr = 0; pr < pairs && ok; ++pr) give(pr, qb);
+  return ok;
+}
+
 template <int kHeadDim, int kQTiles, int kPolyOf4, bool kBias>
 int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   using C = Cfg<kHeadDim, kQTiles, kBias>;
@@ -1023,7 +1086,18 @@ int launch_cfg(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   if (items > 0x7fffffff) return fail(IXK_UNIMPLEMENTED, "too many (batch, head, query block) work items");
   a.num_items = static_cast<int>(items);
   int grid = a.num_items < dev.sm_count ? a.num_items : dev.sm_count;
-  fn<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tbias, to, a);
+  // (5 KB: kept off the stack.  The list depends on the shape only, so a thread that launches the
+  // same problem again, as a layer or a benchmark loop does, reuses the one it has.)
+  static thread_local Schedule sched;
+  static thread_local int sched_key[6] = {-1, -1, -1, -1, -1, -1};
+  static thread_local bool sched_ok = false;
+  const int key[6] = {a.B, a.N, a.F, a.T, a.causal, grid};
+  if (!std::equal(key, key + 6, sched_key)) {
+    sched_ok = build_schedule<kQTiles>(a, grid, &sched);
+    std::copy(key, key + 6, sched_key);
+  }
+  a.use_schedule = sched_ok ? 1 : 0;
+  fn<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tbias, to, a, sched);
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
   return IXK_OK;
