@@ -71,6 +71,7 @@ enum : int { kSiteLoad = 201, kSiteMmaQ = 202, kSiteMmaKV = 203, kSiteMmaP = 204
               kSiteLoadQ = 207, kSiteMmaO = 208, kSiteLoadBias = 209, kSiteSoftmaxBias = 210 };
 
 constexpr int kBiasTileBytes = 2 * kChunkBytes;  // 128 query rows x 128 keys, 16-bit, as two swizzled boxes
+constexpr int kBiasPrefetch = 8;  // 16-byte groups of a bias row (the first box) read before the scores arrive
 
 template <int kHeadDim, int kQTiles, bool kBias>
 struct Cfg {
@@ -715,6 +716,21 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         float m_run = -INFINITY;
         float l_run = 0.0f;
         for (int j = 0; j < my_blocks; ++j) {
+          // The bias tile of this block is in shared memory before the scores are ready: its first
+          // box (keys 0-63) goes into registers while S is still on its way.
+          [[maybe_unused]] uint4 bw[kBiasPrefetch];
+          [[maybe_unused]] const uint8_t* bias_tile =
+              smem_gen + (bias_smem - smem_base) + t * kBiasTileBytes + row_in_tile * 128;
+          if constexpr (kBias) {
+            if (!ptx::mbar_wait(bias_full(t), n_bias & 1u, ctl, kSiteSoftmaxBias)) {
+              alive = false;
+              break;
+            }
+            ++n_bias;
+#pragma unroll
+            for (int grp = 0; grp < kBiasPrefetch; ++grp)
+              bw[grp] = *reinterpret_cast<const uint4*>(bias_tile + ((grp ^ (row_in_tile & 7)) << 4));
+          }
           if (!ptx::mbar_wait(s_full(t), n_s & 1u, ctl, kSiteSoftmaxS)) {
             alive = false;
             break;
@@ -747,19 +763,16 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
               // The bias tile was brought in by TMA as two 128-byte-swizzled boxes of 64 keys; this
               // thread reads its own row, 16 bytes at a time (8 consecutive rows touch 8 different
               // 16-byte columns, so the reads are bank-conflict free).
-              if (!ptx::mbar_wait(bias_full(t), n_bias & 1u, ctl, kSiteSoftmaxBias)) {
-                alive = false;
-                break;
-              }
-              ++n_bias;
-              const uint8_t* tile = smem_gen + (bias_smem - smem_base) + t * kBiasTileBytes + row_in_tile * 128;
+              const uint8_t* tile = bias_tile;
 #pragma unroll
               for (int c = 0; c < 4; ++c) {
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                   const int grp = c * 4 + g;  // 16-byte group of 8 keys
-                  const uint4 w = *reinterpret_cast<const uint4*>(tile + (grp >> 3) * kChunkBytes +
-                                                                  (((grp & 7) ^ (row_in_tile & 7)) << 4));
+                  const uint4 w = grp < kBiasPrefetch
+                                      ? bw[grp < kBiasPrefetch ? grp : 0]
+                                      : *reinterpret_cast<const uint4*>(tile + (grp >> 3) * kChunkBytes +
+                                                                        (((grp & 7) ^ (row_in_tile & 7)) << 4));
                   const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {
@@ -769,7 +782,11 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                   }
                 }
               }
-              ptx::mbar_arrive(bias_empty(t));  // release semantics: the reads above are done
+              // The next tile is written by TMA, i.e. through the async proxy: this thread's reads
+              // (generic proxy) have to be fenced against it, the barrier alone does not order them
+              // (seen with an earlier hand-back: single rows picked up the next tile's values).
+              ptx::fence_proxy_async_smem();
+              ptx::mbar_arrive(bias_empty(t));
             } else if (bias_row != nullptr) {
               const uint16_t* bp = bias_row + kv0;
               const int count = min(kBlockKV, args.T - kv0);
