@@ -370,6 +370,17 @@ int ixk_all_reduce(ixk_comm* comm, int dtype, int kind, size_t in_offset, void* 
 int ixk_all_reduce_residual(ixk_comm* comm, int dtype, size_t in_offset, const void* x,
                             const void* bias, void* out, int64_t rows, int64_t cols,
                             void* cuda_stream);
+/* The two halves of the two-shot all-reduce as calls of their own (sycl_reduce_scatter /
+ * sycl_allgather, ccl_ops.h:49-68; kernels ccl_ops.cc:518-559, :268-294).  count_per_rank elements
+ * must be a whole number of 16-byte vectors.
+ * Reduce-scatter: every rank's contribution is world * count_per_rank elements at in_offset of its
+ * exchange buffer; rank r receives the combination of slice r in `out` (any local buffer).
+ * All-gather: rank r's piece `in` (any local buffer) lands at out_offset + r * piece of EVERY
+ * rank's exchange buffer.  Ordering rules as for ixk_all_reduce. */
+int ixk_reduce_scatter(ixk_comm* comm, int dtype, int kind, size_t in_offset, void* out,
+                       size_t count_per_rank, void* cuda_stream);
+int ixk_all_gather(ixk_comm* comm, int dtype, const void* in, size_t out_offset,
+                   size_t count_per_rank, void* cuda_stream);
 /* [begin, end) in elements of the slice rank `rank` reduces in the two-shot scheme: whole 16-byte
  * vectors split evenly, the last rank takes the remainder (ccl_ops.cc:103-114).  Host arithmetic. */
 int ixk_all_reduce_slice(int dtype, size_t count, int rank, int world, size_t* begin, size_t* end);

@@ -119,6 +119,8 @@ ABI_SYMBOLS = {
     "ixk_comm_destroy": (ctypes.c_int, [_vp]),
     "ixk_all_reduce": (ctypes.c_int, [_vp, ctypes.c_int, ctypes.c_int, _sz, _vp, _sz, _vp]),
     "ixk_all_reduce_residual": (ctypes.c_int, [_vp, ctypes.c_int, _sz, _vp, _vp, _vp, ctypes.c_int64, ctypes.c_int64, _vp]),
+    "ixk_reduce_scatter": (ctypes.c_int, [_vp, ctypes.c_int, ctypes.c_int, _sz, _vp, _sz, _vp]),
+    "ixk_all_gather": (ctypes.c_int, [_vp, ctypes.c_int, _vp, _sz, _sz, _vp]),
     "ixk_all_reduce_slice": (ctypes.c_int, [ctypes.c_int, _sz, ctypes.c_int, ctypes.c_int, ctypes.POINTER(_sz),
                                             ctypes.POINTER(_sz)]),
     "ixk_selftest_bounded_wait": (ctypes.c_int, [ctypes.c_longlong, _vp, _vp]),

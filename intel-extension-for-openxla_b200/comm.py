@@ -89,6 +89,23 @@ class Communicator:
         self.pkg._check(st)
         return out
 
+    def reduce_scatter(self, contribution: torch.Tensor, out: torch.Tensor, kind: str = "SUM", stream=None) -> torch.Tensor:
+        """`contribution`: a view of the exchange buffer holding world * out.numel() elements (the same
+        offset on every rank); `out` (any dense local tensor) receives the combination of slice `rank`."""
+        st = self.lib.ixk_reduce_scatter(self._comm, self.pkg._TORCH_TO_IXK[contribution.dtype], REDUCE_KINDS.index(kind),
+                                         self.offset_of(contribution), out.data_ptr(), out.numel(),
+                                         self.pkg._stream_ptr(stream))
+        self.pkg._check(st)
+        return out
+
+    def all_gather(self, piece: torch.Tensor, gathered: torch.Tensor, stream=None) -> torch.Tensor:
+        """`piece` (any dense local tensor) lands at slot `rank` of `gathered`, a view of the exchange
+        buffer with world * piece.numel() elements, on every rank."""
+        st = self.lib.ixk_all_gather(self._comm, self.pkg._TORCH_TO_IXK[piece.dtype], piece.data_ptr(),
+                                     self.offset_of(gathered), piece.numel(), self.pkg._stream_ptr(stream))
+        self.pkg._check(st)
+        return gathered
+
     def set_wait_limit(self, cycles: int) -> None:
         self.pkg._check(self.lib.ixk_comm_set_wait_limit(self._comm, cycles))
 

@@ -189,11 +189,18 @@ __device__ __forceinline__ float combine(float a, float b, int kind) {
   }
 }
 
+enum : int { kOneShot = 0, kTwoShotMode = 1, kReduceScatter = 2, kAllGather = 3 };
+
 // kWorld > 0: the rank loop is unrolled and all loads of a vector are in flight together;
 // kWorld == 0: any world size up to kMaxRanks.  Ranks are always combined in the order
 // 0, 1, ..., world - 1, so every rank computes the same bits.
-template <typename T, int kWorld, bool kTwoShot>
+// kMode: one-shot all-reduce (every rank reads everything), two-shot all-reduce (reduce a slice,
+// write it to all ranks), reduce-scatter (the first half of the two-shot: rank r keeps the sum of
+// slice r; reducescatter_dpcpp, ccl_ops.cc:518-559) and all-gather (the second half: rank r's
+// piece goes to slot r of every rank's buffer; ccl_ops.cc:268-294).
+template <typename T, int kWorld, int kMode>
 __global__ void __launch_bounds__(kThreads) all_reduce_kernel(const Args a) {
+  constexpr bool kTwoShot = kMode == kTwoShotMode;
   using V = Vec<T>;
   constexpr int E = V::kElems;
   __shared__ int abort_smem;
@@ -210,6 +217,20 @@ __global__ void __launch_bounds__(kThreads) all_reduce_kernel(const Args a) {
     v_end = a.rank == world - 1 ? vecs : v_begin + per;
   }
   const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  if (kMode == kAllGather) {
+    // a.count = elements per rank (whole vectors); in[0] is this rank's piece, out[r] every rank's gathered buffer
+    for (size_t v = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; v < vecs; v += stride) {
+      const uint4 piece = static_cast<const uint4*>(a.in[0])[v];
+      for (int r = 0; r < world; ++r) static_cast<uint4*>(a.out[r])[static_cast<size_t>(a.rank) * vecs + v] = piece;
+    }
+    if (world > 1 && !exchange(a, kPhaseDone, gen, kSiteEnd, &abort_smem)) return;
+    if (threadIdx.x == 0) a.flags[a.rank]->counter[blockIdx.x] = gen;
+    return;
+  }
+  if (kMode == kReduceScatter) {  // a.count = elements per rank: slice r of every contribution is [r * count, (r + 1) * count)
+    v_begin = static_cast<size_t>(a.rank) * vecs;
+    v_end = v_begin + vecs;
+  }
   for (size_t v = v_begin + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; v < v_end; v += stride) {
     float acc[E];
     if (kWorld > 0) {
@@ -236,6 +257,8 @@ __global__ void __launch_bounds__(kThreads) all_reduce_kernel(const Args a) {
     if (kTwoShot) {
       const uint4 packed = V::pack(acc);
       for (int r = 0; r < world; ++r) static_cast<uint4*>(a.out[r])[v] = packed;
+    } else if (kMode == kReduceScatter) {
+      static_cast<uint4*>(a.out[0])[v - v_begin] = V::pack(acc);
     } else {
       if (a.x != nullptr) {
         // out = x + round(sum + bias): the inner sum is rounded to the storage type first, so that
@@ -255,7 +278,7 @@ __global__ void __launch_bounds__(kThreads) all_reduce_kernel(const Args a) {
     }
   }
   // elements behind the last whole 16-byte vector (one thread of the rank that owns the tail)
-  if (blockIdx.x == 0 && threadIdx.x == 0 && (!kTwoShot || a.rank == world - 1)) {
+  if (kMode != kReduceScatter && blockIdx.x == 0 && threadIdx.x == 0 && (!kTwoShot || a.rank == world - 1)) {
     for (size_t i = vecs * E; i < a.count; ++i) {
       float s = V::load1(a.in[0], i);
       for (int r = 1; r < world; ++r) s = combine(s, V::load1(a.in[r], i), a.kind);
@@ -304,21 +327,29 @@ int grid_for(size_t vecs) {
   return static_cast<int>(g);
 }
 
-template <typename T, bool kTwoShot>
+template <typename T, int kMode>
 void launch_world(const Args& a, int grid, cudaStream_t stream) {
+  if (kMode == kAllGather) {  // no arithmetic: one instantiation serves every world size
+    all_reduce_kernel<T, 0, kMode><<<grid, kThreads, 0, stream>>>(a);
+    return;
+  }
   switch (a.world) {
-    case 2: all_reduce_kernel<T, 2, kTwoShot><<<grid, kThreads, 0, stream>>>(a); break;
-    case 4: all_reduce_kernel<T, 4, kTwoShot><<<grid, kThreads, 0, stream>>>(a); break;
-    case 8: all_reduce_kernel<T, 8, kTwoShot><<<grid, kThreads, 0, stream>>>(a); break;
-    default: all_reduce_kernel<T, 0, kTwoShot><<<grid, kThreads, 0, stream>>>(a); break;
+    case 2: all_reduce_kernel<T, 2, kMode><<<grid, kThreads, 0, stream>>>(a); break;
+    case 4: all_reduce_kernel<T, 4, kMode><<<grid, kThreads, 0, stream>>>(a); break;
+    case 8: all_reduce_kernel<T, 8, kMode><<<grid, kThreads, 0, stream>>>(a); break;
+    default: all_reduce_kernel<T, 0, kMode><<<grid, kThreads, 0, stream>>>(a); break;
   }
 }
 
-template <bool kTwoShot>
+template <int kMode>
 void launch_dtype(int dtype, const Args& a, int grid, cudaStream_t stream) {
-  if (dtype == IXK_BF16) launch_world<__nv_bfloat16, kTwoShot>(a, grid, stream);
-  else if (dtype == IXK_F16) launch_world<__half, kTwoShot>(a, grid, stream);
-  else launch_world<float, kTwoShot>(a, grid, stream);
+  if (kMode == kAllGather) {  // bytes are bytes
+    launch_world<float, kMode>(a, grid, stream);
+    return;
+  }
+  if (dtype == IXK_BF16) launch_world<__nv_bfloat16, kMode>(a, grid, stream);
+  else if (dtype == IXK_F16) launch_world<__half, kMode>(a, grid, stream);
+  else launch_world<float, kMode>(a, grid, stream);
 }
 
 int run(ixk_comm* c, int dtype, int kind, size_t in_offset, const void* x, const void* bias, long long cols, void* out,
@@ -383,8 +414,54 @@ int run(ixk_comm* c, int dtype, int kind, size_t in_offset, const void* x, const
   a.status_word = dev.status_word;
   const size_t vecs = bytes / 16;
   const int grid = grid_for(two_shot ? vecs / c->world : vecs);
-  if (two_shot) launch_dtype<true>(dtype, a, grid, stream);
-  else launch_dtype<false>(dtype, a, grid, stream);
+  if (two_shot) launch_dtype<kTwoShotMode>(dtype, a, grid, stream);
+  else launch_dtype<kOneShot>(dtype, a, grid, stream);
+  IXK_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return IXK_OK;
+}
+
+// The two halves of the two-shot all-reduce as calls of their own.  `count` = elements per rank, a
+// whole number of 16-byte vectors.
+int run_half(ixk_comm* c, int dtype, int kind, bool gather, size_t comm_offset, void* local, size_t count,
+             cudaStream_t stream) {
+  if (c == nullptr) return fail(IXK_INVALID_ARGUMENT, "comm is NULL");
+  if (dtype != IXK_BF16 && dtype != IXK_F16 && dtype != IXK_F32)
+    return fail(IXK_UNIMPLEMENTED, "reduce-scatter / all-gather: BF16, F16 and F32 only");
+  if (!gather && (kind < IXK_REDUCE_SUM || kind > IXK_REDUCE_MAX)) return fail(IXK_INVALID_ARGUMENT, "unknown reduction kind");
+  if (count == 0) return IXK_OK;
+  if (local == nullptr) return fail(IXK_INVALID_ARGUMENT, "the local buffer is NULL");
+  if (!c->connected) return fail(IXK_INVALID_ARGUMENT, "the communicator has not been connected to its peers");
+  const size_t piece = count * elem_size(dtype);
+  if (piece % 16 != 0) return fail(IXK_UNIMPLEMENTED, "the per-rank piece must be a whole number of 16-byte vectors");
+  const size_t total = piece * static_cast<size_t>(c->world);
+  if (comm_offset % 16 != 0 || comm_offset > c->data_bytes || total > c->data_bytes - comm_offset)
+    return fail(IXK_INVALID_ARGUMENT, "[offset, offset + world * piece) must lie inside the communicator's buffer, 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(local) & 15u) != 0) return fail(IXK_INVALID_ARGUMENT, "the local buffer must be 16-byte aligned");
+  unsigned char* data = c->base + kHeaderBytes;
+  unsigned char* l = static_cast<unsigned char*>(local);
+  if (l < data + comm_offset + total && data + comm_offset < l + piece)
+    return fail(IXK_INVALID_ARGUMENT, "the local buffer overlaps the exchanged range");
+  DeviceInfo dev;
+  int rc = get_device_info(&dev);
+  if (rc != IXK_OK) return rc;
+  if (dev.device != c->device) return fail(IXK_INVALID_ARGUMENT, "the communicator belongs to another device");
+  Args a{};
+  for (int r = 0; r < c->world; ++r) {
+    a.flags[r] = reinterpret_cast<Flags*>(c->peer[r]);
+    a.in[r] = gather ? nullptr : c->peer[r] + kHeaderBytes + comm_offset;
+    a.out[r] = gather ? c->peer[r] + kHeaderBytes + comm_offset : nullptr;
+  }
+  if (gather) a.in[0] = local; else a.out[0] = local;
+  a.count = count;
+  a.rank = c->rank;
+  a.world = c->world;
+  a.kind = kind;
+  a.wait_limit = c->wait_limit;
+  a.status_word = dev.status_word;
+  const int grid = grid_for(piece / 16);
+  if (gather) launch_dtype<kAllGather>(dtype, a, grid, stream);
+  else launch_dtype<kReduceScatter>(dtype, a, grid, stream);
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
   return IXK_OK;
@@ -395,6 +472,17 @@ int run(ixk_comm* c, int dtype, int kind, size_t in_offset, const void* x, const
 }  // namespace ixk
 
 extern "C" {
+
+int ixk_reduce_scatter(ixk_comm* c, int dtype, int kind, size_t in_offset, void* out, size_t count_per_rank, void* cuda_stream) {
+  ixk::clear_error();
+  return ixk::comm::run_half(c, dtype, kind, false, in_offset, out, count_per_rank, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int ixk_all_gather(ixk_comm* c, int dtype, const void* in, size_t out_offset, size_t count_per_rank, void* cuda_stream) {
+  ixk::clear_error();
+  return ixk::comm::run_half(c, dtype, IXK_REDUCE_SUM, true, out_offset, const_cast<void*>(in), count_per_rank,
+                             static_cast<cudaStream_t>(cuda_stream));
+}
 
 int ixk_comm_create(int rank, int world, size_t buffer_bytes, ixk_comm** comm, void* handle_out) {
   ixk::clear_error();

@@ -129,6 +129,51 @@ def test_two_ranks_on_one_device_without_any_wait(pkg, cuda, monkeypatch, algo, 
         b.close()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32], ids=["bf16", "f32"])
+def test_reduce_scatter_and_all_gather_two_ranks_without_any_wait(pkg, cuda, dtype):
+    """The two halves of the two-shot all-reduce as calls of their own (ccl_ops.cc:518-559, :268-294),
+    with the same no-wait arrangement: flags written from the host, rank 0 first, then rank 1."""
+    per_rank = 40000                                     # elements per rank: whole 16-byte vectors
+    a, b = RawComm(pkg, 0, 2, 4 << 20, cuda), RawComm(pkg, 1, 2, 4 << 20, cuda)
+    try:
+        a.connect([a, b])
+        b.connect([a, b])
+        lib, k = a.lib, pkg._TORCH_TO_IXK[dtype]
+        stream = torch.cuda.current_stream().cuda_stream
+        g = torch.Generator(device="cuda").manual_seed(3)
+        va = torch.randint(-50, 50, (2 * per_rank,), generator=g, device=cuda).to(dtype)
+        vb = torch.randint(-50, 50, (2 * per_rank,), generator=g, device=cuda).to(dtype)
+        a.view(0, 2 * per_rank, dtype).copy_(va)
+        b.view(0, 2 * per_rank, dtype).copy_(vb)
+        want = (va.float() + vb.float()).to(dtype)
+        oa = torch.zeros(per_rank, dtype=dtype, device=cuda)
+        ob = torch.zeros(per_rank, dtype=dtype, device=cuda)
+        a.flags[:, :, 1] = 1                             # generation 1: reduce-scatter
+        torch.cuda.synchronize()
+        assert lib.ixk_reduce_scatter(a.h, k, 0, 0, oa.data_ptr(), per_rank, stream) == pkg.IXK_OK
+        torch.cuda.synchronize()
+        assert lib.ixk_reduce_scatter(b.h, k, 0, 0, ob.data_ptr(), per_rank, stream) == pkg.IXK_OK
+        torch.cuda.synchronize()
+        assert torch.equal(oa, want[:per_rank]) and torch.equal(ob, want[per_rank:])
+        # generation 2: all-gather of the two reduced pieces = the all-reduce result on both ranks
+        off = 2 << 20
+        a.flags[:, :, 1] = 2
+        torch.cuda.synchronize()
+        assert lib.ixk_all_gather(a.h, k, oa.data_ptr(), off, per_rank, stream) == pkg.IXK_OK
+        torch.cuda.synchronize()
+        assert lib.ixk_all_gather(b.h, k, ob.data_ptr(), off, per_rank, stream) == pkg.IXK_OK
+        torch.cuda.synchronize()
+        assert pkg.device_status() == 0
+        assert torch.equal(a.view(off, 2 * per_rank, dtype), want) and torch.equal(b.view(off, 2 * per_rank, dtype), want)
+        # a piece that is not a whole number of vectors, and a local buffer inside the exchanged range
+        assert lib.ixk_reduce_scatter(a.h, k, 0, 0, oa.data_ptr(), 3, stream) == pkg.IXK_UNIMPLEMENTED
+        inside = a.view(0, per_rank, dtype)
+        assert lib.ixk_reduce_scatter(a.h, k, 0, 0, inside.data_ptr(), per_rank, stream) == pkg.IXK_INVALID_ARGUMENT
+    finally:
+        a.close()
+        b.close()
+
+
 def test_a_peer_that_never_arrives_ends_in_a_timeout_status(pkg, cuda):
     """The wait for a peer is bounded: with nobody on the other side the kernel gives up after its
     cycle budget, reports where, and leaves the device usable."""

@@ -71,6 +71,22 @@ def _worker(rank, world, port, q):
                 comm.all_reduce(slot)                          # in place in the exchange buffer: two-shot when large
                 torch.cuda.synchronize()
                 checks[f"{name}_{dt}"] = ok_priv and torch.equal(slot, want_ar)
+        # the two halves as calls of their own, against NCCL's
+        n = 8 * 4096
+        v = torch.randint(-60, 60, (world * n,), generator=gi, device=dev).to(torch.bfloat16)
+        slot = comm.view(0, (world * n,), torch.bfloat16)
+        slot.copy_(v)
+        mine = torch.empty(n, dtype=torch.bfloat16, device=dev)
+        comm.reduce_scatter(slot, mine)
+        want_rs = torch.empty(n, dtype=torch.bfloat16, device=dev)
+        dist.reduce_scatter_tensor(want_rs, v)
+        gathered = comm.view(8 << 20, (world * n,), torch.bfloat16)
+        comm.all_gather(mine, gathered)
+        want_ag = torch.empty(world * n, dtype=torch.bfloat16, device=dev)
+        dist.all_gather_into_tensor(want_ag, want_rs)
+        torch.cuda.synchronize()
+        checks["reduce_scatter"] = torch.equal(mine, want_rs)
+        checks["all_gather"] = torch.equal(gathered, want_ag)
         # many calls back to back (the flags' generation counters, no host sync in between)
         slot = comm.view(0, (4096,), torch.float32)
         slot.fill_(1.0)
