@@ -453,7 +453,7 @@ int run_half(ixk_comm* c, int dtype, int kind, bool gather, size_t comm_offset, 
     a.out[r] = gather ? c->peer[r] + kHeaderBytes + comm_offset : nullptr;
   }
   if (gather) a.in[0] = local; else a.out[0] = local;
-  a.count = count;
+  a.count = gather ? piece / 4 : count;   // the gather kernel is instantiated for 4-byte words whatever the type
   a.rank = c->rank;
   a.world = c->world;
   a.kind = kind;
