@@ -45,10 +45,13 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each workload's dominant kernel, from
 # one ncu capture of that kernel at this size (absent: no capture of that kernel exists).
 NCU_TRAFFIC_BYTES = {
+    "fmha_causal": 267.1e6,
+    "fmha_bias": 319.8e6,
+    "fmha_bwd_causal": 829.4e6,    # the main kernel of the three
     "fmha_bwd_full": 626.8e6,
-    "fmha_causal": 493.8e6,
-    "fmha_bias": 1.110e9,
-    "gemm_bias_gelu": 0.909e9,
+    "gemm_bias_gelu": 0.985e9,
+    "gemm_fp8": 1.137e9,
+    "gemm_fp8_e5m2": 1.137e9,      # same kernel and shape; captured with e4m3 x e4m3
     "decode_attn": 4.30e9,
 }
 
