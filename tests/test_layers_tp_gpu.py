@@ -29,6 +29,7 @@ def _worker(rank, world, port, q):
     import torch.distributed as dist
     import __graft_entry__ as entry
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # a rank sits an exchange out below: no NVLink multicast objects around it
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -135,6 +136,21 @@ def _worker(rank, world, port, q):
             graph.replay()
         torch.cuda.synchronize()
         checks["gemma_graph_equals_eager"] = torch.equal(y_graph, y_comm)
+        # ---- a peer that does not show up: rank 1 sits this exchange out (it is between steps, nothing
+        # of its own in flight); rank 0's kernel gives up after its cycle budget, reports where, and
+        # the GPU stays usable.  The ranks then meet on the host and take the communicator down.
+        torch.cuda.synchronize()
+        dist.barrier()
+        comm.set_wait_limit(20_000_000)                # about 10 ms
+        if rank == 0:
+            comm.all_reduce(comm.view(0, (4096,), torch.float32), out=torch.empty(4096, device=dev))
+            try:
+                pkg.device_status()
+                checks["absent_peer_times_out"] = False
+            except pkg.IxkError as e:
+                checks["absent_peer_times_out"] = e.status == pkg.IXK_DEVICE_TIMEOUT and "301" in str(e)
+            xs = torch.ones(64, 64, dtype=torch.bfloat16, device=dev)
+            checks["usable_after_timeout"] = bool((pkg.gemm(xs, xs) == 64).all()) and pkg.device_status() == 0
         comm.close()
         q.put((rank, err, same, pkg.device_status(), err_gemma, checks))
     finally:
