@@ -762,7 +762,7 @@ def run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=Tru
     # ---- exchange: libixk's NVLink all-reduce where the buffers can be shared, else NCCL
     comm, comm_note = None, None
     if world > 1 and not args.nccl:
-        nbytes = 4 * 2048 * 4096 * 2 if args.workload == "gptj_layer" else 1 << 20
+        nbytes = 2 * 4 * 2048 * 4096 * 2 if args.workload == "gptj_layer" else 1 << 20   # GPT-J: the slots + the result
         try:
             comm = comm_mod.Communicator(pkg, rank, world, nbytes)
         except Exception as ex:  # noqa: BLE001 - e.g. CUDA IPC not permitted between the ranks' containers
@@ -780,7 +780,8 @@ def run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=Tru
         x_host = torch.randn(B, S, 4096, generator=g).bfloat16().pin_memory()
         x = x_host.to(dev)
         rope = layers.rotary_tables(torch.arange(S, device=dev), 64)
-        step = lambda reduce=None: layers.gptj_layer_prefill(x, w, ops, rope=rope, reduce=reduce, comm=comm)
+        step = lambda reduce=None: layers.gptj_layer_prefill(x, w, ops, rope=rope, reduce=reduce, comm=comm,
+                                                             fused_exchange=not args.unfused_exchange)
         work, div, unit, bound = layers.gptj_layer_flops(B, S), 1e12, "TFLOP/s", "tensor"
         peak = peaks["bf16_tflops"] * world
         if world > 1:   # once, outside the timed region: the sharded step against the un-sharded layer, same inputs
@@ -936,6 +937,8 @@ def run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=Tru
     config["exchange"] = ("none (one GPU)" if world == 1 else
                           "libixk NVLink all-reduce (peer loads/stores, device-side flags)" if comm is not None else
                           (comm_note or "NCCL all-reduce"))
+    if comm is not None and args.workload == "gptj_layer" and not args.unfused_exchange:
+        config["exchange"] += "; the down projection stores its row blocks into the owners' buffers as it computes"
     line = {
         "metric": LAYER_METRIC[args.workload], "value": value, "unit": unit, "n_gpus": world, "per_gpu_value": value / world,
         "steps": args.steps, "warmup": args.warmup,
@@ -1018,6 +1021,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="layer workloads: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--nccl", action="store_true",
                     help="layer workloads at N > 1: exchange through NCCL instead of libixk's NVLink all-reduce")
+    ap.add_argument("--unfused-exchange", action="store_true",
+                    help="GPT-J layer at N > 1 with libixk's exchange: down projection, all-reduce and residual add as "
+                         "three launches instead of the projection that scatters its result + one exchange kernel")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-timed steps only (no e2e, no CPU baseline): the command profiled under ncu")
     args = ap.parse_args()

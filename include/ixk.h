@@ -364,7 +364,7 @@ int ixk_comm_destroy(ixk_comm* comm);
 int ixk_all_reduce(ixk_comm* comm, int dtype, int kind, size_t in_offset, void* out,
                    size_t count, void* cuda_stream);
 /* All-reduce fused with the residual add that follows a row-parallel projection:
- *   out = x + round(sum over ranks [+ bias[col]])      [rows, cols] dense
+ *   out = x + round(round(sum over ranks) [+ bias[col]])      [rows, cols] dense
  * the same bits as ixk_all_reduce followed by ixk_residual_add.  out may alias x, but not the
  * contribution. */
 int ixk_all_reduce_residual(ixk_comm* comm, int dtype, size_t in_offset, const void* x,
@@ -381,6 +381,30 @@ int ixk_reduce_scatter(ixk_comm* comm, int dtype, int kind, size_t in_offset, vo
                        size_t count_per_rank, void* cuda_stream);
 int ixk_all_gather(ixk_comm* comm, int dtype, const void* in, size_t out_offset,
                    size_t count_per_rank, void* cuda_stream);
+/* A row-parallel projection fused with the first half of its all-reduce, then the second half
+ * fused with the residual add (the reference runs the projection, sycl_allreduce and the add as
+ * three steps: sycl_custom_call.cc:154-221, ccl_ops.cc:604-789).
+ * ixk_gemm_scatter computes D = alpha * A.B [+ beta * C] [+ bias] as ixk_gemm does (desc.output
+ * describes the whole [M, N] result: row-major, dense, 16-bit, batch 1; `c`, when beta != 0, is a
+ * local [M, N] matrix of that layout), but stores row block o of D (rows [o * M / world,
+ * (o + 1) * M / world)) straight into rank o's exchange buffer: slot `rank` of the `world` slots
+ * of M / world x N elements that start at slots_offset.  The stores cross NVLink while the
+ * tensor cores work on the following tiles.  Shapes: M a multiple of 128 * world, N of 8, and a
+ * problem of at least 74 tiles of 256 x 256 (else IXK_UNIMPLEMENTED: use ixk_gemm +
+ * ixk_all_reduce).  No waiting on peers inside this call.
+ * ixk_all_reduce_scattered then, on every rank: waits for all ranks' projections, adds up the
+ * slots of the rows this rank owns (in rank order, fp32), applies
+ *   out = x + round(round(sum) [+ bias[col]])          (x == NULL: out = round(sum))
+ * and writes those rows to the result at out_offset of EVERY rank's exchange buffer; when the
+ * call has completed there, each rank holds the whole [rows, cols] result: the bits of ixk_gemm +
+ * ixk_all_reduce + ixk_residual_add.  x ([rows, cols] dense) and bias are local; slots and result
+ * must not overlap.  Ordering rules and time-outs as for ixk_all_reduce; the next
+ * ixk_gemm_scatter on the same slots may be issued right after it on the same stream. */
+int ixk_gemm_scatter(ixk_comm* comm, const ixk_gemm_desc* desc, const void* a, const void* b,
+                     const void* c, const void* bias, size_t slots_offset, void* cuda_stream);
+int ixk_all_reduce_scattered(ixk_comm* comm, int dtype, size_t slots_offset, const void* x,
+                             const void* bias, size_t out_offset, int64_t rows, int64_t cols,
+                             void* cuda_stream);
 /* [begin, end) in elements of the slice rank `rank` reduces in the two-shot scheme: whole 16-byte
  * vectors split evenly, the last rank takes the remainder (ccl_ops.cc:103-114).  Host arithmetic. */
 int ixk_all_reduce_slice(int dtype, size_t count, int rank, int world, size_t* begin, size_t* end);

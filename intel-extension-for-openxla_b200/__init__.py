@@ -121,6 +121,8 @@ ABI_SYMBOLS = {
     "ixk_all_reduce_residual": (ctypes.c_int, [_vp, ctypes.c_int, _sz, _vp, _vp, _vp, ctypes.c_int64, ctypes.c_int64, _vp]),
     "ixk_reduce_scatter": (ctypes.c_int, [_vp, ctypes.c_int, ctypes.c_int, _sz, _vp, _sz, _vp]),
     "ixk_all_gather": (ctypes.c_int, [_vp, ctypes.c_int, _vp, _sz, _sz, _vp]),
+    "ixk_gemm_scatter": (ctypes.c_int, [_vp, ctypes.POINTER(_GemmDesc), _vp, _vp, _vp, _vp, _sz, _vp]),
+    "ixk_all_reduce_scattered": (ctypes.c_int, [_vp, ctypes.c_int, _sz, _vp, _vp, _sz, ctypes.c_int64, ctypes.c_int64, _vp]),
     "ixk_all_reduce_slice": (ctypes.c_int, [ctypes.c_int, _sz, ctypes.c_int, ctypes.c_int, ctypes.POINTER(_sz),
                                             ctypes.POINTER(_sz)]),
     "ixk_selftest_bounded_wait": (ctypes.c_int, [ctypes.c_longlong, _vp, _vp]),
@@ -194,6 +196,26 @@ def _require_cuda(*tensors) -> None:
 
 # ----------------------------------------------------------------------------- GEMM
 
+def gemm_desc_from_attrs(attrs: dict, epilogue: str) -> "_GemmDesc":
+    """The C descriptor for the attribute dictionary of a GEMM custom call."""
+    if epilogue not in EPILOGUES:
+        raise IxkError(IXK_INVALID_ARGUMENT, "Unknown Epilogue.")  # onednn_matmul_utils.cc:52-54
+    d = _GemmDesc()
+    for name, field in (("lhs", d.lhs), ("rhs", d.rhs), ("output", d.output)):
+        field.order = int(attrs[f"{name}_order"])
+        field.dtype = int(attrs[f"{name}_layout_dtype"])
+        field.num_rows = int(attrs[f"{name}_num_rows"])
+        field.num_cols = int(attrs[f"{name}_num_cols"])
+        field.batch_stride = int(attrs[f"{name}_batch_stride"])
+        field.leading_dim_stride = int(attrs[f"{name}_leading_dim_stride"])
+    d.batch_size = int(attrs["batch_size"])
+    d.alpha = float(attrs.get("alpha", 1.0))
+    d.beta = float(attrs.get("beta", 0.0))
+    d.epilogue = EPILOGUES.index(epilogue)
+    d.reserved = 0
+    return d
+
+
 def run_gemm_custom_call(lhs: torch.Tensor, rhs: torch.Tensor, add: Optional[torch.Tensor],
                          output: torch.Tensor, bias: Optional[torch.Tensor], stream, attrs: dict,
                          epilogue: str, *, inv_scale_a: Optional[float] = None,
@@ -212,19 +234,7 @@ def run_gemm_custom_call(lhs: torch.Tensor, rhs: torch.Tensor, add: Optional[tor
         raise IxkError(IXK_INVALID_ARGUMENT, "Unknown Epilogue.")  # onednn_matmul_utils.cc:52-54
     _require_cuda(lhs, rhs, add, output, bias, aux)
     lib = load_library()
-    d = _GemmDesc()
-    for name, field in (("lhs", d.lhs), ("rhs", d.rhs), ("output", d.output)):
-        field.order = int(attrs[f"{name}_order"])
-        field.dtype = int(attrs[f"{name}_layout_dtype"])
-        field.num_rows = int(attrs[f"{name}_num_rows"])
-        field.num_cols = int(attrs[f"{name}_num_cols"])
-        field.batch_stride = int(attrs[f"{name}_batch_stride"])
-        field.leading_dim_stride = int(attrs[f"{name}_leading_dim_stride"])
-    d.batch_size = int(attrs["batch_size"])
-    d.alpha = float(attrs.get("alpha", 1.0))
-    d.beta = float(attrs.get("beta", 0.0))
-    d.epilogue = EPILOGUES.index(epilogue)
-    d.reserved = 0
+    d = gemm_desc_from_attrs(attrs, epilogue)
     sp = _stream_ptr(stream)
     ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     if aux is not None:

@@ -106,6 +106,35 @@ class Communicator:
         self.pkg._check(st)
         return gathered
 
+    def gemm_scatter(self, lhs: torch.Tensor, rhs: torch.Tensor, slots_offset: int, *, c: Optional[torch.Tensor] = None,
+                     beta: float = 0.0, bias: Optional[torch.Tensor] = None, epilogue: str = "DEFAULT", stream=None) -> None:
+        """This rank's partial lhs @ rhs (+ beta * c) of a row-parallel projection, row block o stored
+        straight into rank o's exchange buffer (slot `rank` of the slots at slots_offset) while the
+        following tiles are computed.  all_reduce_scattered finishes the exchange."""
+        m, n = lhs.shape[-2], rhs.shape[-1]
+        shape_only = torch.empty((m, n), device="meta", dtype=lhs.dtype)   # carries the result's layout; no memory
+        attrs = self.pkg.gemm_attrs_for(lhs, rhs, shape_only, beta)
+        d = self.pkg.gemm_desc_from_attrs(attrs, epilogue)
+        ptr = lambda t: None if t is None else t.data_ptr()
+        st = self.lib.ixk_gemm_scatter(self._comm, ctypes.byref(d), ptr(lhs), ptr(rhs), ptr(c), ptr(bias), slots_offset,
+                                       self.pkg._stream_ptr(stream))
+        self.pkg._check(st)
+
+    def all_reduce_scattered(self, slots_offset: int, out: torch.Tensor, x: Optional[torch.Tensor] = None,
+                             bias: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """Adds up the slots gemm_scatter filled (the rows this rank owns), applies
+        x + round(round(sum) + bias) and writes the rows into `out` — a [rows, cols] view of the
+        exchange buffer at the same offset on every rank — of every rank."""
+        rows, cols = out.numel() // out.shape[-1], out.shape[-1]
+        if x is not None and (x.numel() != out.numel() or not x.is_contiguous()):
+            raise self.pkg.IxkError(self.pkg.IXK_INVALID_ARGUMENT, "x must be dense and of the result's size")
+        st = self.lib.ixk_all_reduce_scattered(self._comm, self.pkg._TORCH_TO_IXK[out.dtype], slots_offset,
+                                               None if x is None else x.data_ptr(),
+                                               None if bias is None else bias.data_ptr(), self.offset_of(out),
+                                               rows, cols, self.pkg._stream_ptr(stream))
+        self.pkg._check(st)
+        return out
+
     def set_wait_limit(self, cycles: int) -> None:
         self.pkg._check(self.lib.ixk_comm_set_wait_limit(self._comm, cycles))
 

@@ -55,7 +55,8 @@ int check_layout(const ixk_matrix_layout& l, const char* name) {
 
 int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, const void* bias,
         void* d, bool fp8_call, float inv_scale_a, float inv_scale_b, void* workspace, size_t workspace_bytes,
-        void* stream, void* aux = nullptr, int64_t aux_ld = 0, bool aux_call = false) {
+        void* stream, void* aux = nullptr, int64_t aux_ld = 0, bool aux_call = false,
+        ixk_comm* scatter_comm = nullptr, size_t slots_offset = 0) {
   clear_error();
   if (desc == nullptr) return fail(IXK_INVALID_ARGUMENT, "desc is NULL");
   if (desc->reserved != 0) return fail(IXK_INVALID_ARGUMENT, "desc.reserved must be 0");
@@ -161,7 +162,7 @@ int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, 
     return fail(IXK_INVALID_ARGUMENT, "lhs [M,K], rhs [K,N] and output [M,N] shapes do not agree");
   p.batch = desc->batch_size;
   if (p.M == 0 || p.N == 0) return IXK_OK;  // nothing to write; pointers may be NULL
-  if (a == nullptr || b == nullptr || d == nullptr)
+  if (a == nullptr || b == nullptr || (d == nullptr && scatter_comm == nullptr))
     return fail(IXK_INVALID_ARGUMENT, "a, b and d must be non-NULL");
   if (p.K == 0) return fail(IXK_UNIMPLEMENTED, "K == 0 is not supported");
   if (p.M > INT32_MAX || p.N > INT32_MAX || p.K > INT32_MAX)
@@ -210,6 +211,18 @@ int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, 
     return fail(IXK_UNIMPLEMENTED, "batch_stride * element size must be a multiple of 16 bytes for lhs and rhs (TMA)");
   if ((reinterpret_cast<uintptr_t>(p.d) % elem_bytes(tc)) != 0)
     return fail(IXK_INVALID_ARGUMENT, "d is not aligned to its element size");
+  if (scatter_comm != nullptr) {
+    // D leaves in row blocks, one per rank, for the exchange buffers of the ranks that own them
+    if (swapped || p.batch != 1 || p.ldd != p.N || elem_bytes(tc) != 2)
+      return fail(IXK_UNIMPLEMENTED, "a scattered output is row-major, dense, un-batched and 16-bit");
+    if ((rc = comm::scatter_targets(scatter_comm, slots_offset, p.M, static_cast<size_t>(p.N) * 2, p.scatter_dest,
+                                    &p.scatter_world)) != IXK_OK)
+      return rc;
+    p.d = p.scatter_dest[0];
+    DeviceInfo dev;
+    if ((rc = get_device_info(&dev)) != IXK_OK) return rc;
+    return gemm::launch(p, dev, static_cast<cudaStream_t>(stream));
+  }
 
   if (const char* env = std::getenv("IXK_GEMM_BLOCK_N")) p.force_block_n = std::atoi(env);
 
@@ -345,6 +358,15 @@ int ixk_ffi_select_operands(int epilogue, float beta, int num_args, int num_resu
   if (num_results < out->d_result + 1)
     return ixk::fail(IXK_INVALID_ARGUMENT, "the custom call has too few results for this epilogue");
   return IXK_OK;
+}
+
+int ixk_gemm_scatter(ixk_comm* comm, const ixk_gemm_desc* desc, const void* a, const void* b, const void* c,
+                     const void* bias, size_t slots_offset, void* cuda_stream) {
+  if (comm == nullptr) {
+    ixk::clear_error();
+    return ixk::fail(IXK_INVALID_ARGUMENT, "comm is NULL");
+  }
+  return ixk::run(desc, a, b, c, bias, nullptr, false, 1.0f, 1.0f, nullptr, 0, cuda_stream, nullptr, 0, false, comm, slots_offset);
 }
 
 int ixk_gemm_fp8(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c,

@@ -54,7 +54,7 @@ struct Args {
   Flags* flags[kMaxRanks];
   const void* in[kMaxRanks];
   void* out[kMaxRanks];  // two-shot: every rank's output; one-shot: out[0] is this rank's output
-  const void* x;         // one-shot epilogue: out = x + round(sum [+ bias[col]]); nullptr = plain sum
+  const void* x;         // epilogue: out = x + round(round(sum) [+ bias[col]]); nullptr = plain sum
   const void* bias;
   long long cols;
   size_t count;          // elements
@@ -254,26 +254,28 @@ __global__ void __launch_bounds__(kThreads) all_reduce_kernel(const Args a) {
         for (int i = 0; i < E; ++i) acc[i] = combine(acc[i], f[i], a.kind);
       }
     }
+    if (kMode != kReduceScatter && a.x != nullptr) {
+      // out = x + round(round(sum) + bias): every intermediate is rounded to the storage type, so
+      // that the result has the bits of an all-reduce followed by the separate residual add
+      float xf[E];
+      V::unpack(static_cast<const uint4*>(a.x)[v], xf);
+#pragma unroll
+      for (int i = 0; i < E; ++i) acc[i] = V::round1(acc[i]);
+      if (a.bias != nullptr) {
+        float bf[E];
+        V::unpack(static_cast<const uint4*>(a.bias)[(v * E % a.cols) / E], bf);
+#pragma unroll
+        for (int i = 0; i < E; ++i) acc[i] = V::round1(acc[i] + bf[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < E; ++i) acc[i] += xf[i];
+    }
     if (kTwoShot) {
       const uint4 packed = V::pack(acc);
       for (int r = 0; r < world; ++r) static_cast<uint4*>(a.out[r])[v] = packed;
     } else if (kMode == kReduceScatter) {
       static_cast<uint4*>(a.out[0])[v - v_begin] = V::pack(acc);
     } else {
-      if (a.x != nullptr) {
-        // out = x + round(sum + bias): the inner sum is rounded to the storage type first, so that
-        // the result equals an all-reduce followed by the separate residual add
-        float xf[E];
-        V::unpack(static_cast<const uint4*>(a.x)[v], xf);
-        if (a.bias != nullptr) {
-          float bf[E];
-          V::unpack(static_cast<const uint4*>(a.bias)[(v * E % a.cols) / E], bf);
-#pragma unroll
-          for (int i = 0; i < E; ++i) acc[i] += bf[i];
-        }
-#pragma unroll
-        for (int i = 0; i < E; ++i) acc[i] = xf[i] + V::round1(acc[i]);
-      }
       static_cast<uint4*>(a.out[0])[v] = V::pack(acc);
     }
   }
@@ -286,8 +288,9 @@ __global__ void __launch_bounds__(kThreads) all_reduce_kernel(const Args a) {
         for (int r = 0; r < world; ++r) V::store1(a.out[r], i, s);
       } else {
         if (a.x != nullptr) {
-          if (a.bias != nullptr) s += V::load1(a.bias, i % a.cols);
-          s = V::load1(a.x, i) + V::round1(s);
+          s = V::round1(s);
+          if (a.bias != nullptr) s = V::round1(s + V::load1(a.bias, i % a.cols));
+          s += V::load1(a.x, i);
         }
         V::store1(a.out[0], i, s);
       }
@@ -467,11 +470,87 @@ int run_half(ixk_comm* c, int dtype, int kind, bool gather, size_t comm_offset, 
   return IXK_OK;
 }
 
+// Second half of a projection whose output was scattered (gemm::Problem::scatter_*): slot s of
+// this rank's `world` slots holds rank s's partial sums of the rows this rank owns.  The two-shot
+// kernel does the rest: its "contributions" are the local slots (addressed so that the kernel's
+// slice index lands inside them), its outputs every rank's result buffer.
+int run_scattered(ixk_comm* c, int dtype, size_t slots_offset, const void* x, const void* bias, size_t out_offset,
+                  long long rows, long long cols, cudaStream_t stream) {
+  if (c == nullptr) return fail(IXK_INVALID_ARGUMENT, "comm is NULL");
+  if (dtype != IXK_BF16 && dtype != IXK_F16) return fail(IXK_UNIMPLEMENTED, "scattered all-reduce: BF16 and F16 only");
+  if (rows < 0 || cols < 0) return fail(IXK_INVALID_ARGUMENT, "negative size");
+  if (rows == 0 || cols == 0) return IXK_OK;
+  if (!c->connected) return fail(IXK_INVALID_ARGUMENT, "the communicator has not been connected to its peers");
+  if (rows % c->world != 0 || cols % 8 != 0)
+    return fail(IXK_UNIMPLEMENTED, "rows must divide among the ranks and cols be a multiple of 8");
+  const size_t bytes = static_cast<size_t>(rows) * cols * 2;
+  const size_t slot_bytes = bytes / c->world;
+  auto inside = [&](size_t off) { return off % 16 == 0 && off <= c->data_bytes && bytes <= c->data_bytes - off; };
+  if (!inside(slots_offset) || !inside(out_offset))
+    return fail(IXK_INVALID_ARGUMENT, "slots and result must lie inside the communicator's buffer, 16-byte aligned");
+  if (slots_offset < out_offset + bytes && out_offset < slots_offset + bytes)
+    return fail(IXK_INVALID_ARGUMENT, "the result overlaps the slots");
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0 || (reinterpret_cast<uintptr_t>(bias) & 15u) != 0)
+    return fail(IXK_INVALID_ARGUMENT, "x and bias must be 16-byte aligned");
+  if (bias != nullptr && x == nullptr) return fail(IXK_INVALID_ARGUMENT, "bias comes with the residual x only");
+  DeviceInfo dev;
+  int rc = get_device_info(&dev);
+  if (rc != IXK_OK) return rc;
+  if (dev.device != c->device) return fail(IXK_INVALID_ARGUMENT, "the communicator belongs to another device");
+  Args a{};
+  const uintptr_t slots = reinterpret_cast<uintptr_t>(c->base + kHeaderBytes + slots_offset);
+  for (int r = 0; r < c->world; ++r) {
+    a.flags[r] = reinterpret_cast<Flags*>(c->peer[r]);
+    // the kernel reads in[s] + (this rank's slice begin + i): make that slot s, element i
+    a.in[r] = reinterpret_cast<const void*>(slots + static_cast<uintptr_t>(r) * slot_bytes -
+                                            static_cast<uintptr_t>(c->rank) * slot_bytes);
+    a.out[r] = c->peer[r] + kHeaderBytes + out_offset;
+  }
+  a.x = x;
+  a.bias = bias;
+  a.cols = cols;
+  a.count = static_cast<size_t>(rows) * cols;
+  a.rank = c->rank;
+  a.world = c->world;
+  a.kind = IXK_REDUCE_SUM;
+  a.wait_limit = c->wait_limit;
+  a.status_word = dev.status_word;
+  const int grid = grid_for(slot_bytes / 16);
+  launch_dtype<kTwoShotMode>(dtype, a, grid, stream);
+  IXK_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return IXK_OK;
+}
+
 }  // namespace
+
+int scatter_targets(ixk_comm* c, size_t slots_offset, long long rows, size_t row_bytes, void** dest, int* world) {
+  if (c == nullptr) return fail(IXK_INVALID_ARGUMENT, "comm is NULL");
+  if (!c->connected) return fail(IXK_INVALID_ARGUMENT, "the communicator has not been connected to its peers");
+  if (rows <= 0 || rows % c->world != 0) return fail(IXK_UNIMPLEMENTED, "the rows must divide among the ranks");
+  const size_t slot_bytes = static_cast<size_t>(rows / c->world) * row_bytes;
+  const size_t total = slot_bytes * c->world;
+  if (slots_offset % 16 != 0 || slot_bytes % 16 != 0 || slots_offset > c->data_bytes || total > c->data_bytes - slots_offset)
+    return fail(IXK_INVALID_ARGUMENT, "the slots must lie inside the communicator's buffer, 16-byte aligned");
+  int device = -1;
+  IXK_CUDA_OK(cudaGetDevice(&device));
+  if (device != c->device) return fail(IXK_INVALID_ARGUMENT, "the communicator belongs to another device");
+  for (int o = 0; o < c->world; ++o)
+    dest[o] = c->peer[o] + kHeaderBytes + slots_offset + static_cast<size_t>(c->rank) * slot_bytes;
+  *world = c->world;
+  return IXK_OK;
+}
+
 }  // namespace comm
 }  // namespace ixk
 
 extern "C" {
+
+int ixk_all_reduce_scattered(ixk_comm* c, int dtype, size_t slots_offset, const void* x, const void* bias,
+                             size_t out_offset, int64_t rows, int64_t cols, void* cuda_stream) {
+  ixk::clear_error();
+  return ixk::comm::run_scattered(c, dtype, slots_offset, x, bias, out_offset, rows, cols, static_cast<cudaStream_t>(cuda_stream));
+}
 
 int ixk_reduce_scatter(ixk_comm* c, int dtype, int kind, size_t in_offset, void* out, size_t count_per_rank, void* cuda_stream) {
   ixk::clear_error();

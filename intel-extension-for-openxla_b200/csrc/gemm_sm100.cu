@@ -30,8 +30,8 @@ namespace gemm {
 
 namespace {
 
-static_assert(kKindF16 == ptx::kKindF16 && kKindF8 == ptx::kKindF8 && kKindTf32 == ptx::kKindTf32 &&
-              kKindI8 == ptx::kKindI8, "MMA kind codes");
+static_assert(int(kKindF16) == int(ptx::kKindF16) && int(kKindF8) == int(ptx::kKindF8) &&
+              int(kKindTf32) == int(ptx::kKindTf32) && int(kKindI8) == int(ptx::kKindI8), "MMA kind codes");
 constexpr int kBlockM = 128;
 constexpr int kSlabBytes = 128;  // bytes of K per shared-memory row (one swizzle span)
 constexpr int kThreads = 192;
@@ -197,7 +197,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 template <int kBlockN>
 __device__ __forceinline__ void epilogue_tile(const KernelArgs& args, const CUtensorMap* tmap_d_ptr, uint32_t tmem_acc,
                                               uint32_t stage_smem, int bz, int bm, int bn, int quarter, int lane,
-                                              uint32_t& n_store) {
+                                              uint32_t& n_store, int d_row_shift = 0) {
   const CUtensorMap& tmap_d = *tmap_d_ptr;
   if (bm * kBlockM >= args.M) return;  // a CTA pair's second half past the last row block
   const int row_in_tile = quarter * 32 + lane;
@@ -280,7 +280,7 @@ __device__ __forceinline__ void epilogue_tile(const KernelArgs& args, const CUte
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          ptx::tma_store_3d(&tmap_d, box, n, bm * kBlockM + quarter * 32, bz);
+          ptx::tma_store_3d(&tmap_d, box, n, bm * kBlockM + quarter * 32 - d_row_shift, bz);
           ptx::bulk_commit_group();
         }
         ++n_store;
@@ -505,10 +505,17 @@ struct PairCfg {
 };
 enum : int { kSitePairFull = 111, kSitePairPeer = 112, kSitePairAcc = 113, kSitePairForward = 114 };
 
-template <int kKind>
+// The tensor maps of D: one, or one per destination of a scattered output (rows of D dealt out
+// in equal blocks to up to kMaxScatter buffers, each a dense [M / kDests', N] matrix).
+template <int kDests>
+struct OutputMaps {
+  CUtensorMap m[kDests];
+};
+
+template <int kKind, int kDests>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_d, const KernelArgs args) {
+                 const __grid_constant__ OutputMaps<kDests> tmaps_d, const KernelArgs args) {
   using C = PairCfg;
   constexpr int kStages = C::kStages;
   constexpr int kBlockN = C::kBlockN;
@@ -552,7 +559,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     ptx::fence_mbar_init();
     ptx::prefetch_tmap(&tmap_a);
     ptx::prefetch_tmap(&tmap_b);
-    if (args.d_tma) ptx::prefetch_tmap(&tmap_d);
+    if (args.d_tma) ptx::prefetch_tmap(&tmaps_d.m[0]);
   }
   __syncthreads();
   ptx::cluster_sync_all();  // both CTAs' barriers exist before anyone arrives on them remotely
@@ -677,8 +684,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tile_coords(t, tiles_m2, args.tiles_n, bz, bm2, bn);
       if (!ptx::mbar_wait(acc_full_bar(buf), acc_phase, ctl, kSiteEpilogue)) break;
       ptx::tc_fence_after_sync();
-      epilogue_tile<kBlockN>(args, &tmap_d, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBlockN,
-                             stage_smem, bz, bm2 * 2 + static_cast<int>(rank), bn, quarter, lane, n_store);
+      const int bm = bm2 * 2 + static_cast<int>(rank);
+      // scattered output: this row block's destination and the row that destination starts at
+      const int dest = kDests > 1 ? (bm * kBlockM) / args.scatter_rows : 0;
+      epilogue_tile<kBlockN>(args, &tmaps_d.m[dest], tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBlockN,
+                             stage_smem, bz, bm, bn, quarter, lane, n_store, kDests > 1 ? dest * args.scatter_rows : 0);
       ptx::tc_fence_before_sync();
       if (rank == 0) {
         ptx::mbar_arrive(acc_empty_bar(buf));
@@ -688,7 +698,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       buf ^= 1;
       if (buf == 0) acc_phase ^= 1u;
     }
-    if (args.d_tma && lane == 0) ptx::bulk_wait_group<0>();
+    if (args.d_tma && lane == 0) {
+      ptx::bulk_wait_group<0>();
+      if (kDests > 1) {  // the stores went to other GPUs: complete at system scope before the kernel ends
+        ptx::fence_proxy_async_all();
+        __threadfence_system();
+      }
+    }
   }
 
   // Teardown: neither CTA may leave while its partner can still read its shared memory or arrive
@@ -722,10 +738,10 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& 
   return IXK_OK;
 }
 
-template <int kKind>
-int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const KernelArgs& args,
+template <int kKind, int kDests>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const OutputMaps<kDests>& td, const KernelArgs& args,
                 int pairs, cudaStream_t stream) {
-  auto* fn = &gemm_pair_kernel<kKind>;
+  auto* fn = &gemm_pair_kernel<kKind, kDests>;
   static thread_local int configured_device = -1;
   int dev = 0;
   IXK_CUDA_OK(cudaGetDevice(&dev));
@@ -778,6 +794,19 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
   bool pair = bn == 256 && tiles_m_all >= 2 && pair_tiles >= dev.sm_count / 2;
   if (const char* env = std::getenv("IXK_GEMM_PAIR")) pair = pair && std::atoi(env) != 0;
   const int b_box_rows = pair ? 128 : bn;
+  if (p.scatter_world > 0) {
+    // Only the kernel that large projections run on stores to several destinations, and only
+    // whole row blocks of one CTA.
+    if (p.scatter_world > kMaxScatter) return fail(IXK_INVALID_ARGUMENT, "too many destinations");
+    if (!pair || p.kind != ptx::kKindF16 || p.batch != 1 || p.out_dtype == IXK_F32 || p.aux != nullptr ||
+        p.M % (static_cast<int64_t>(p.scatter_world) * kBlockM) != 0 || p.N % 8 != 0)
+      return fail(IXK_UNIMPLEMENTED,
+                  "a scattered output needs a 16-bit, un-batched problem large enough for the CTA-pair kernel "
+                  "(at least 74 tiles of 256 x 256), M a multiple of 128 x destinations and N a multiple of 8");
+    for (int o = 0; o < p.scatter_world; ++o)
+      if (p.scatter_dest[o] == nullptr || (reinterpret_cast<uintptr_t>(p.scatter_dest[o]) & 15u) != 0)
+        return fail(IXK_INVALID_ARGUMENT, "a destination of the scattered output is NULL or not 16-byte aligned");
+  }
 
   const CUtensorMapDataType dt = es == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : es == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
@@ -871,12 +900,36 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream) {
     s.strides_bytes[1] = p.batch > 1 ? static_cast<uint64_t>(p.d_batch_stride) * 2 : s.strides_bytes[0] * s.dims[1];
     if ((rc = encode_tmap(&td, p.d, s)) != IXK_OK) return rc;
   }
+  OutputMaps<kMaxScatter> td_scatter;
+  if (p.scatter_world > 0) {
+    k.d_tma = 1;
+    k.scatter_rows = static_cast<int>(p.M / p.scatter_world);
+    TmapSpec s{};
+    s.dtype = p.out_dtype == IXK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    s.rank = 3;
+    s.swizzle128 = true;
+    s.dims[0] = p.N;
+    s.dims[1] = k.scatter_rows;
+    s.dims[2] = 1;
+    s.box[0] = 64;
+    s.box[1] = 32;
+    s.box[2] = 1;
+    s.strides_bytes[0] = static_cast<uint64_t>(p.N) * 2;
+    s.strides_bytes[1] = s.strides_bytes[0] * s.dims[1];
+    for (int o = 0; o < kMaxScatter; ++o)
+      if ((rc = encode_tmap(&td_scatter.m[o], p.scatter_dest[o < p.scatter_world ? o : 0], s)) != IXK_OK) return rc;
+  }
 
   auto dispatch = [&](auto kind_tag) -> int {
     constexpr int kKind = decltype(kind_tag)::value;
     if (pair) {
       const int pairs = static_cast<int>(pair_tiles < dev.sm_count / 2 ? pair_tiles : dev.sm_count / 2);
-      return launch_pair<kKind>(ta, tb, td, k, pairs, stream);
+      if (p.scatter_world > 0) {
+        if constexpr (kKind == ptx::kKindF16) return launch_pair<kKind, kMaxScatter>(ta, tb, td_scatter, k, pairs, stream);
+      }
+      OutputMaps<1> one;
+      one.m[0] = td;
+      return launch_pair<kKind, 1>(ta, tb, one, k, pairs, stream);
     }
     const int64_t tiles = static_cast<int64_t>(k.tiles_m) * k.tiles_n * k.batch;
     const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);

@@ -10,6 +10,7 @@ namespace gemm {
 enum : int { kActNone = 0, kActRelu = 1, kActGelu = 2 };
 // tcgen05.mma kinds (the values of ptx::kKind*, restated for host-only code)
 enum : int { kKindF16 = 0, kKindF8 = 1, kKindTf32 = 2, kKindI8 = 3 };
+constexpr int kMaxScatter = 8;  // destinations of a scattered output (= the most ranks a communicator has)
 
 // A GEMM after normalisation: D is row-major [M,N]; A is [M,K], B is [K,N], each with
 // either dimension contiguous.
@@ -38,6 +39,11 @@ struct Problem {
   float acc_scale = 1.0f;
   float beta = 0.0f;
   int force_block_n = 0;  // tuning override; 0 = heuristic
+  // Scattered output (row-parallel projection feeding an all-reduce): row block o of D, rows
+  // [o * M / scatter_world, (o + 1) * M / scatter_world), is stored dense ([M / world, N], pitch N)
+  // at scatter_dest[o], which may be another GPU's memory.  0 = D goes to `d` as usual.
+  int scatter_world = 0;
+  void* scatter_dest[kMaxScatter] = {};
 };
 
 // Kernel parameter block (passed by value).
@@ -59,6 +65,7 @@ struct KernelArgs {
   void* aux;
   int64_t ld_aux, aux_batch_stride;
   int aux_vec_ok;
+  int scatter_rows;  // rows per destination of a scattered output; 0 = one destination
   int* status_word;
 };
 

@@ -52,4 +52,11 @@ struct TmapSpec {
 };
 int encode_tmap(CUtensorMap* out, const void* base, const TmapSpec& spec);
 
+namespace comm {
+// Where a rank's scattered output goes: dest[o] = slot `rank` of the `world` slots ([rows / world]
+// rows of row_bytes each) that start at slots_offset in rank o's exchange buffer.  Checks that the
+// slots fit and that the communicator is connected and belongs to the current device.
+int scatter_targets(ixk_comm* c, size_t slots_offset, long long rows, size_t row_bytes, void** dest, int* world);
+}  // namespace comm
+
 }  // namespace ixk

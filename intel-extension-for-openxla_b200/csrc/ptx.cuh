@@ -136,6 +136,9 @@ __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// Orders this thread's completed async-proxy (TMA) accesses to any memory ahead of its later
+// generic-proxy accesses and fences.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before_sync() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }

@@ -171,7 +171,7 @@ class GptJLayerWeights:
 
 
 def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None, rope=None, reduce=None,
-                       comm=None) -> torch.Tensor:
+                       comm=None, fused_exchange: bool = False) -> torch.Tensor:
     """GPT-J block, prefill: y = x + Attn(LN(x)) + MLP(LN(x)), x [B, S, hidden] replicated on every
     rank.  The attention-output and MLP-down partial sums are added locally (the second GEMM takes
     the first as its C operand with beta = 1), so the block needs ONE all-reduce.  `rope` may carry
@@ -180,19 +180,30 @@ def gptj_layer_prefill(x: torch.Tensor, w: GptJLayerWeights, ops, group=None, ro
     records the step in pieces around the exchange passes its own).  With `comm` (a
     comm.Communicator) the partial sum is produced straight into the NVLink exchange buffer and
     reduced there by libixk's own all-reduce kernel: no NCCL call, so the whole step is one stream of
-    kernel launches that a CUDA graph can hold."""
+    kernel launches that a CUDA graph can hold.  With `fused_exchange` as well, the down projection
+    stores each row block of its result into the exchange buffer of the rank that owns it while it
+    computes the next tiles, and the rest of the exchange (sum of the slots, bias, residual add,
+    rows written to every rank) is one more kernel; the result is then a view of the exchange buffer
+    (valid until the next step) with the same bits as the other paths."""
     B, S, hidden = x.shape
     hl, hd = w.heads_local, w.head_dim
-    h = _glue(ops, "layer_norm", layer_norm)(x).view(B * S, hidden)
+    rows = B * S
+    fused = comm is not None and fused_exchange and comm.world > 1
+    h = _glue(ops, "layer_norm", layer_norm)(x).view(rows, hidden)
     qkv = ops.gemm(h, w.wqkv).view(B, S, 3, hl, hd)
     cos, sin = rope if rope is not None else rotary_tables(torch.arange(S, device=x.device), w.rotary_dim)
     _glue(ops, "rotary_qk_", _rotary_qk_torch_)(qkv, cos, sin, w.rotary_dim)
     q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))        # [B, hl, S, hd] views, no copies
     ctx = torch.empty(B, S, hl, hd, dtype=x.dtype, device=x.device)
     ops.attention(q, k, v, ctx.permute(0, 2, 1, 3), scale=1.0 / math.sqrt(hd), causal=True)
-    slot = comm.view(0, (B * S, hidden), x.dtype) if comm is not None else None
-    attn_partial = ops.gemm(ctx.view(B * S, hl * hd), w.wo, out=slot)
+    slot = comm.view(0, (rows, hidden), x.dtype) if comm is not None and not fused else None
+    attn_partial = ops.gemm(ctx.view(rows, hl * hd), w.wo, out=slot)
     up = ops.gemm(h, w.w1, bias=w.b1, epilogue="BIAS_GELU")
+    if fused:
+        nbytes = rows * hidden * x.element_size()
+        comm.gemm_scatter(up, w.w2, 0, c=attn_partial, beta=1.0)          # slots at [0, nbytes) of every rank's buffer
+        y = comm.all_reduce_scattered(0, comm.view(nbytes, (rows, hidden), x.dtype), x=x.view(rows, hidden), bias=w.b2)
+        return y.view(B, S, hidden)
     partial = ops.gemm(up, w.w2, c=attn_partial, beta=1.0, out=attn_partial)   # in place: C aliases D
     if comm is not None:
         partial = comm.all_reduce(partial)              # in place in the exchange buffer

@@ -174,6 +174,73 @@ def test_reduce_scatter_and_all_gather_two_ranks_without_any_wait(pkg, cuda, dty
         b.close()
 
 
+def test_projection_scattered_into_the_owners_slots_then_reduced_two_ranks_without_any_wait(pkg, cuda):
+    """ixk_gemm_scatter + ixk_all_reduce_scattered against ixk_gemm + sum + ixk_residual_add, bit for
+    bit.  Both ranks' projections run first (they wait for nobody), then the second halves in the
+    no-wait arrangement."""
+    M, N, K = 2560, 2048, 512                       # 10 x 8 tiles of 256 x 256: the CTA-pair kernel
+    slots_off, out_off = 0, M * N * 2
+    a, b = RawComm(pkg, 0, 2, 2 * M * N * 2, cuda), RawComm(pkg, 1, 2, 2 * M * N * 2, cuda)
+    try:
+        a.connect([a, b])
+        b.connect([a, b])
+        g = torch.Generator(device="cuda").manual_seed(4)
+        rnd = lambda *shape, s=1.0: (torch.randn(*shape, generator=g, device=cuda) * s).bfloat16()
+        lhs, rhs, add = [rnd(M, K), rnd(M, K)], [rnd(K, N, s=0.05), rnd(K, N, s=0.05)], [rnd(M, N), rnd(M, N)]
+        x, bias = rnd(M, N), rnd(N)
+        stream = torch.cuda.current_stream().cuda_stream
+        for c in (a, b):
+            c.data.zero_()
+        for r, c in enumerate((a, b)):
+            attrs = pkg.gemm_attrs_for(lhs[r], rhs[r], torch.empty((M, N), device="meta", dtype=torch.bfloat16), 1.0)
+            d = pkg.gemm_desc_from_attrs(attrs, "DEFAULT")
+            st = c.lib.ixk_gemm_scatter(c.h, ctypes.byref(d), lhs[r].data_ptr(), rhs[r].data_ptr(), add[r].data_ptr(), None,
+                                        slots_off, stream)
+            assert st == pkg.IXK_OK, a.lib.ixk_last_error().decode()
+        torch.cuda.synchronize()
+        assert pkg.device_status() == 0
+        part = [pkg.gemm(lhs[r], rhs[r], c=add[r], beta=1.0) for r in range(2)]
+        half = M // 2
+        # rank o's slot s = rows [o * half, (o + 1) * half) of rank s's partial
+        for o, c in enumerate((a, b)):
+            for src in range(2):
+                slot = c.view(slots_off + src * half * N * 2, half * N, torch.bfloat16).view(half, N)
+                assert torch.equal(slot, part[src][o * half:(o + 1) * half]), f"slot {src} of rank {o}"
+        total = (part[0].float() + part[1].float()).bfloat16()
+        want = pkg.residual_add(x, total, bias)
+        k = pkg._TORCH_TO_IXK[torch.bfloat16]
+        a.flags[:, :, 1] = 1
+        torch.cuda.synchronize()
+        for c in (a, b):
+            assert c.lib.ixk_all_reduce_scattered(c.h, k, slots_off, x.data_ptr(), bias.data_ptr(), out_off, M, N,
+                                                  stream) == pkg.IXK_OK, a.lib.ixk_last_error().decode()
+            torch.cuda.synchronize()
+            assert pkg.device_status() == 0
+        for c in (a, b):
+            assert torch.equal(c.view(out_off, M * N, torch.bfloat16).view(M, N), want)
+        # without the residual: the plain sum
+        a.flags[:, :, 1] = 2
+        torch.cuda.synchronize()
+        for c in (a, b):
+            assert c.lib.ixk_all_reduce_scattered(c.h, k, slots_off, None, None, out_off, M, N, stream) == pkg.IXK_OK
+            torch.cuda.synchronize()
+        assert torch.equal(a.view(out_off, M * N, torch.bfloat16).view(M, N), total)
+        assert torch.equal(b.view(out_off, M * N, torch.bfloat16).view(M, N), total)
+        # shapes the scattered store does not take; ranges that do not fit
+        small = pkg.gemm_desc_from_attrs(pkg.gemm_attrs_for(lhs[0][:256], rhs[0], torch.empty((256, N), device="meta",
+                                                                                             dtype=torch.bfloat16)), "DEFAULT")
+        assert a.lib.ixk_gemm_scatter(a.h, ctypes.byref(small), lhs[0].data_ptr(), rhs[0].data_ptr(), None, None, 0,
+                                      stream) == pkg.IXK_UNIMPLEMENTED
+        assert a.lib.ixk_gemm_scatter(a.h, ctypes.byref(d), lhs[0].data_ptr(), rhs[0].data_ptr(), add[0].data_ptr(), None,
+                                      out_off + 16, stream) == pkg.IXK_INVALID_ARGUMENT
+        assert a.lib.ixk_all_reduce_scattered(a.h, k, slots_off, None, None, out_off - 16, M, N, stream) == pkg.IXK_INVALID_ARGUMENT
+        assert a.lib.ixk_gemm_scatter(None, ctypes.byref(d), lhs[0].data_ptr(), rhs[0].data_ptr(), None, None, 0,
+                                      stream) == pkg.IXK_INVALID_ARGUMENT
+    finally:
+        a.close()
+        b.close()
+
+
 def test_a_peer_that_never_arrives_ends_in_a_timeout_status(pkg, cuda):
     """The wait for a peer is bounded: with nobody on the other side the kernel gives up after its
     cycle budget, reports where, and leaves the device usable."""

@@ -55,7 +55,7 @@ def _worker(rank, world, port, q):
 
         # ---- libixk's all-reduce against ncclAllReduce, bit for bit on integers
         comm_mod = importlib.import_module("ixk_b200.comm")
-        comm = comm_mod.Communicator(pkg, rank, world, 16 << 20)
+        comm = comm_mod.Communicator(pkg, rank, world, 32 << 20)
         checks = {}
         gi = torch.Generator(device=dev).manual_seed(100 + rank)
         for name, n in (("one_shot", 64 * 3072), ("two_shot", 3 * 1024 * 1024 + 8), ("tail", 1000 + 3)):
@@ -99,6 +99,19 @@ def _worker(rank, world, port, q):
         # ---- the GPT-J block again, exchange through libixk
         y2 = layers.gptj_layer_prefill(x.to(dev), w, layers.KernelOps(pkg), comm=comm)
         checks["gptj_comm_equals_nccl"] = torch.equal(y, y2)
+        # the projection that scatters its result + one exchange kernel (needs the CTA-pair GEMM: a wider case)
+        hidden2, ffn2, B2, S2 = 2048, 2048, 2, 1280
+        g2 = torch.Generator().manual_seed(5)
+        r2 = lambda *s: (torch.randn(*s, generator=g2) * 0.02).bfloat16()
+        full2 = {"wqkv": r2(hidden2, 3 * 16 * 128), "wo": r2(16 * 128, hidden2), "w1": r2(hidden2, ffn2), "b1": r2(ffn2),
+                 "w2": r2(ffn2, hidden2), "b2": r2(hidden2)}
+        w2 = layers.GptJLayerWeights.shard({k_: v_.to(dev) for k_, v_ in full2.items()}, 16, 128, rot, rank, world)
+        x2 = (torch.randn(B2, S2, hidden2, generator=torch.Generator().manual_seed(6)) * 0.5).bfloat16().to(dev)
+        y_unfused = layers.gptj_layer_prefill(x2, w2, layers.KernelOps(pkg), comm=comm).clone()
+        y_fused = layers.gptj_layer_prefill(x2, w2, layers.KernelOps(pkg), comm=comm, fused_exchange=True).clone()
+        torch.cuda.synchronize()
+        checks["gptj_fused_exchange_equals_unfused"] = torch.equal(y_unfused, y_fused)
+        checks["gptj_fused_exchange_finite"] = bool(torch.isfinite(y_fused.float()).all())
 
         # ---- Gemma decode step, TP=2: NCCL exchange, libixk exchange, CUDA-graph replay of the latter
         hidden, heads, hd, ffn, B, T = 384, 4, 256, 768, 6, 900
