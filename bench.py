@@ -718,7 +718,8 @@ def _layer_weights(name, seed=7):
         return {"wqkv": r(4096, 12288), "wo": r(4096, 4096), "w1": r(4096, 16384), "b1": r(16384),
                 "w2": r(16384, 4096), "b2": r(4096)}
     return {"wqkv": r(3072, 12288), "wo": r(4096, 3072), "wgate": r(3072, 24576), "wup": r(3072, 24576),
-            "wdown": r(24576, 3072)}   # Gemma-7B shape: hidden 3072, 16 heads x 256, GeGLU 24576
+            "wdown": r(24576, 3072),   # Gemma-7B shape: hidden 3072, 16 heads x 256, GeGLU 24576
+            "norm_attn": r(3072), "norm_mlp": r(3072)}   # the RMSNorm scales w, applied as (1 + w)
 
 
 LAYER_METRIC = {

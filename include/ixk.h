@@ -296,6 +296,11 @@ typedef enum ixk_norm_kind { IXK_NORM_LAYER = 0, IXK_NORM_RMS = 1 } ixk_norm_kin
  * cols <= 8192 (else IXK_UNIMPLEMENTED).  x and y may be the same buffer. */
 int ixk_row_norm(int dtype, int kind, int64_t rows, int64_t cols, const void* x,
                  int64_t ldx, void* y, int64_t ldy, float eps, void* cuda_stream);
+/* The same with a learned gain: y = normalised * (gain_offset + gain[col]), gain [cols] of the
+ * input type; gain_offset = 1 gives the (1 + w) scale of Gemma's RMSNorm, 0 the usual w. */
+int ixk_row_norm_gain(int dtype, int kind, int64_t rows, int64_t cols, const void* x, int64_t ldx,
+                      const void* gain, float gain_offset, void* y, int64_t ldy, float eps,
+                      void* cuda_stream);
 /* Rotary position embedding in place, GPT-J convention: elements (2i, 2i+1),
  * 2i < rotary_dim, of every head rotate by the angle whose cosine / sine is
  * cos_table / sin_table[position, i] (fp32 tables [seq_len, rotary_dim/2]).
@@ -303,6 +308,12 @@ int ixk_row_norm(int dtype, int kind, int64_t rows, int64_t cols, const void* x,
  * sits at position t % seq_len.  Giving heads = 2 * heads_local and x = the
  * fused [tokens, 3, heads_local, head_dim] projection rotates q and k at once. */
 int ixk_rotary_interleaved(int dtype, void* x, int64_t tokens, int64_t seq_len,
+                           int64_t heads, int64_t rotary_dim, int64_t token_stride,
+                           int64_t head_stride, const float* cos_table,
+                           const float* sin_table, void* cuda_stream);
+/* The half-split convention (Gemma, Llama): element i < rotary_dim/2 pairs with element
+ * i + rotary_dim/2, same tables; rotary_dim a multiple of 16. */
+int ixk_rotary_half(int dtype, void* x, int64_t tokens, int64_t seq_len,
                            int64_t heads, int64_t rotary_dim, int64_t token_stride,
                            int64_t head_stride, const float* cos_table,
                            const float* sin_table, void* cuda_stream);

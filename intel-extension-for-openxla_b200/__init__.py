@@ -106,6 +106,10 @@ ABI_SYMBOLS = {
                                     _vp, ctypes.c_int64, ctypes.c_float, _vp]),
     "ixk_rotary_interleaved": (ctypes.c_int, [ctypes.c_int, _vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                               ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp, _vp, _vp]),
+    "ixk_row_norm_gain": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, _vp, ctypes.c_int64,
+                                         _vp, ctypes.c_float, _vp, ctypes.c_int64, ctypes.c_float, _vp]),
+    "ixk_rotary_half": (ctypes.c_int, [ctypes.c_int, _vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                       ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp, _vp, _vp]),
     "ixk_residual_add": (ctypes.c_int, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, _vp, _vp, _vp, _vp, _vp]),
     "ixk_fmha_fwd_workspace_bytes": (_sz, [ctypes.POINTER(_FmhaDesc)]),
     "ixk_fmha_fwd_static_scratch": (ctypes.c_int, [ctypes.POINTER(_FmhaDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
@@ -369,8 +373,9 @@ NORM_LAYER, NORM_RMS = 0, 1
 
 
 def row_norm(x: torch.Tensor, *, kind: int = NORM_LAYER, eps: float = 1e-5, out: Optional[torch.Tensor] = None,
-             stream=None) -> torch.Tensor:
-    """LayerNorm (unit gain, zero shift) or RMSNorm over the last dimension of a dense tensor."""
+             stream=None, gain: Optional[torch.Tensor] = None, gain_offset: float = 0.0) -> torch.Tensor:
+    """LayerNorm (zero shift) or RMSNorm over the last dimension of a dense tensor; with `gain` [cols]
+    the normalised row is multiplied by (gain_offset + gain) before the one rounding."""
     if not x.is_contiguous():
         raise IxkError(IXK_INVALID_ARGUMENT, "row_norm wants a contiguous tensor")
     out = torch.empty_like(x) if out is None else out
@@ -378,16 +383,22 @@ def row_norm(x: torch.Tensor, *, kind: int = NORM_LAYER, eps: float = 1e-5, out:
         raise IxkError(IXK_INVALID_ARGUMENT, "out must match x")
     cols = x.shape[-1]
     rows = x.numel() // cols if cols else 0
+    if gain is not None:
+        if gain.shape != (cols,) or gain.dtype != x.dtype or not gain.is_contiguous():
+            raise IxkError(IXK_INVALID_ARGUMENT, "gain must be a dense [cols] vector of the input type")
+        _check(load_library().ixk_row_norm_gain(_TORCH_TO_IXK[x.dtype], kind, rows, cols, x.data_ptr(), cols, gain.data_ptr(),
+                                                float(gain_offset), out.data_ptr(), cols, eps, _stream_ptr(stream)))
+        return out
     _check(load_library().ixk_row_norm(_TORCH_TO_IXK[x.dtype], kind, rows, cols, x.data_ptr(), cols, out.data_ptr(),
                                        cols, eps, _stream_ptr(stream)))
     return out
 
 
 def rotary_interleaved_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_len: int, rotary_dim: int,
-                        stream=None) -> torch.Tensor:
+                        stream=None, half_split: bool = False) -> torch.Tensor:
     """In place on x [tokens, heads, head_dim] (any token pitch, unit element stride): pairs (2i, 2i+1)
-    of the first rotary_dim elements of every head, token t at position t % seq_len; cos/sin fp32
-    [seq_len, rotary_dim/2]."""
+    of the first rotary_dim elements of every head (half_split: pairs (i, i + rotary_dim/2)), token
+    t at position t % seq_len; cos/sin fp32 [seq_len, rotary_dim/2]."""
     if x.dim() != 3 or x.stride(2) != 1:
         raise IxkError(IXK_INVALID_ARGUMENT, "x must be [tokens, heads, head_dim] with unit element stride")
     if cos.dtype != torch.float32 or sin.dtype != torch.float32 or not cos.is_contiguous() or not sin.is_contiguous() \
@@ -395,10 +406,15 @@ def rotary_interleaved_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, s
         raise IxkError(IXK_INVALID_ARGUMENT, "cos/sin must be contiguous fp32 [seq_len, rotary_dim/2]")
     if rotary_dim > x.shape[2]:
         raise IxkError(IXK_INVALID_ARGUMENT, "rotary_dim exceeds head_dim")
-    _check(load_library().ixk_rotary_interleaved(_TORCH_TO_IXK[x.dtype], x.data_ptr(), x.shape[0], seq_len, x.shape[1],
-                                                 rotary_dim, x.stride(0), x.stride(1), cos.data_ptr(), sin.data_ptr(),
-                                                 _stream_ptr(stream)))
+    fn = load_library().ixk_rotary_half if half_split else load_library().ixk_rotary_interleaved
+    _check(fn(_TORCH_TO_IXK[x.dtype], x.data_ptr(), x.shape[0], seq_len, x.shape[1], rotary_dim, x.stride(0), x.stride(1),
+              cos.data_ptr(), sin.data_ptr(), _stream_ptr(stream)))
     return x
+
+
+def rotary_half_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_len: int, rotary_dim: int, stream=None):
+    """The half-split convention of the Gemma family: see rotary_interleaved_."""
+    return rotary_interleaved_(x, cos, sin, seq_len, rotary_dim, stream, half_split=True)
 
 
 def residual_add(x: torch.Tensor, partial: torch.Tensor, bias: Optional[torch.Tensor] = None,

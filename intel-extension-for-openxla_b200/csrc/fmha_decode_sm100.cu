@@ -3,7 +3,7 @@
 // (xla/service/gpu/xetla/sdp/fmha_policy.h:35-83 via fmha_forward.h:621-646); here the step is
 // what it is on the hardware: a stream of K and V through the SMs at HBM speed.
 //
-//   grid  (splits * F, N, B)   one (batch, head, query, key-split) per CTA, 8 warps
+//   grid  (splits * ceil(F / rows), N, B)   one (batch, head, pair of queries, key-split) per CTA, 8 warps
 //   lane  owns 8 consecutive head-dim elements: one 128-bit load per key for K, one for V
 //   score dot product finished with warp-shuffle reductions over the lanes sharing a key
 //   softmax online (running max / sum in fp32, exp2 with head_scale*log2(e) folded in)
@@ -73,19 +73,22 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
   return r;
 }
 
-// kLanesPerKey lanes cooperate on one key (kLanesPerKey * 8 >= head size).
-template <int kLanesPerKey>
-__global__ void __launch_bounds__(kThreads)
+// kLanesPerKey lanes cooperate on one key (kLanesPerKey * 8 >= head size).  A CTA serves kQ
+// consecutive query rows: every K and V vector is loaded once and used for all of them, so a
+// step with a few query rows per sequence (2 <= F <= 16) streams the cache ceil(F / kQ) times,
+// not F times.
+template <int kLanesPerKey, int kQ>
+__global__ void __launch_bounds__(kThreads, 2)
 fmha_decode_kernel(const DecodeArgs a) {
   constexpr int kGroups = 32 / kLanesPerKey;  // keys handled side by side in one warp
   constexpr int kHPad = kLanesPerKey * 8;
-  __shared__ float sm_acc[kWarps][kHPad];
-  __shared__ float sm_m[kWarps];
-  __shared__ float sm_l[kWarps];
+  __shared__ float sm_acc[kWarps][kQ][kHPad];
+  __shared__ float sm_m[kWarps][kQ];
+  __shared__ float sm_l[kWarps][kQ];
 
   const bool bf16 = a.is_bf16 != 0;
   const int split = blockIdx.x % a.splits;
-  const int f = blockIdx.x / a.splits;
+  const int f0 = (blockIdx.x / a.splits) * kQ;  // first query row of this CTA
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
   const int warp = threadIdx.x >> 5;
@@ -97,29 +100,37 @@ fmha_decode_kernel(const DecodeArgs a) {
 
   int t_begin = split * a.keys_per_split;
   int t_end = min(a.T, t_begin + a.keys_per_split);
-  if (a.causal) t_end = min(t_end, f + 1);  // keys t <= f are visible (top-left anchored)
+  // keys t <= f are visible to row f (top-left anchored): the CTA streams up to its last row's limit
+  if (a.causal) t_end = min(t_end, min(f0 + kQ, a.F));
 
-  float qf[8];
-  {
+  float qf[kQ][8];
+  const uint16_t* bias_row[kQ];
+#pragma unroll
+  for (int r = 0; r < kQ; ++r) {
+    const int f = f0 + r;
     uint4 w = make_uint4(0, 0, 0, 0);
-    if (dim_ok)
+    if (dim_ok && f < a.F)
       w = *reinterpret_cast<const uint4*>(a.q + batch * a.q_strides[0] + head * a.q_strides[1] +
                                           static_cast<int64_t>(f) * a.q_strides[2] + d0);
-    unpack8(w, bf16, qf);
+    unpack8(w, bf16, qf[r]);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) qf[i] *= a.scale_log2;
+    for (int i = 0; i < 8; ++i) qf[r][i] *= a.scale_log2;
+    bias_row[r] = nullptr;
+    if (a.bias != nullptr && f < a.F)
+      bias_row[r] = a.bias + batch * a.bias_strides[0] + head * a.bias_strides[1] + static_cast<int64_t>(f) * a.bias_strides[2];
   }
   const uint16_t* kbase = a.k + batch * a.k_strides[0] + head * a.k_strides[1] + d0;
   const uint16_t* vbase = a.v + batch * a.v_strides[0] + head * a.v_strides[1] + d0;
-  const uint16_t* bias_row = nullptr;
-  if (a.bias != nullptr)
-    bias_row = a.bias + batch * a.bias_strides[0] + head * a.bias_strides[1] + static_cast<int64_t>(f) * a.bias_strides[2];
 
-  float m_run = -INFINITY;
-  float l_run = 0.0f;
-  float acc[8];
+  float m_run[kQ], l_run[kQ];
+  float acc[kQ][8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  for (int r = 0; r < kQ; ++r) {
+    m_run[r] = -INFINITY;
+    l_run[r] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[r][i] = 0.0f;
+  }
 
   // Key index of this lane group: warps interleave, groups inside a warp interleave.  The loop
   // bound is warp-uniform (the shuffles below need every lane); `ok` masks the ragged end.
@@ -139,93 +150,110 @@ fmha_decode_kernel(const DecodeArgs a) {
         vw[u] = ld_stream(vbase + static_cast<int64_t>(t) * a.v_strides[2]);
       }
     }
-    float x[kUnroll];
+    float x[kQ][kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       float kf[8];
       unpack8(kw[u], bf16, kf);
-      float s = 0.0f;
+      const int t = t0 + u * kStride;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) s = fmaf(qf[i], kf[i], s);
+      for (int r = 0; r < kQ; ++r) {
+        float s = 0.0f;
 #pragma unroll
-      for (int off = kLanesPerKey / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-      if (ok[u] && bias_row != nullptr) s = fmaf(to_f32(__ldg(bias_row + t0 + u * kStride), bf16), kLog2e, s);
-      x[u] = ok[u] ? s : -INFINITY;
+        for (int i = 0; i < 8; ++i) s = fmaf(qf[r][i], kf[i], s);
+#pragma unroll
+        for (int off = kLanesPerKey / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        const bool seen = ok[u] && (kQ == 1 || !a.causal || t <= f0 + r);
+        if (seen && bias_row[r] != nullptr) s = fmaf(to_f32(__ldg(bias_row[r] + t), bf16), kLog2e, s);
+        x[r][u] = seen ? s : -INFINITY;
+      }
     }
-    float mx = x[0];
+    float vf[kUnroll][8];
 #pragma unroll
-    for (int u = 1; u < kUnroll; ++u) mx = fmaxf(mx, x[u]);
-    if (mx > m_run) {
-      const float corr = ptx::ex2_approx(m_run - mx);  // 0 when m_run = -inf
-      l_run *= corr;
+    for (int u = 0; u < kUnroll; ++u) unpack8(vw[u], bf16, vf[u]);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] *= corr;
-      m_run = mx;
-    }
-    if (m_run != -INFINITY) {
+    for (int r = 0; r < kQ; ++r) {
+      float mx = x[r][0];
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const float p = ptx::ex2_approx(x[u] - m_run);  // 0 for masked / absent keys
-        l_run += p;
-        float vf[8];
-        unpack8(vw[u], bf16, vf);
+      for (int u = 1; u < kUnroll; ++u) mx = fmaxf(mx, x[r][u]);
+      if (mx > m_run[r]) {
+        const float corr = ptx::ex2_approx(m_run[r] - mx);  // 0 when m_run = -inf
+        l_run[r] *= corr;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[i], acc[i]);
+        for (int i = 0; i < 8; ++i) acc[r][i] *= corr;
+        m_run[r] = mx;
+      }
+      if (m_run[r] != -INFINITY) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const float p = ptx::ex2_approx(x[r][u] - m_run[r]);  // 0 for masked / absent keys
+          l_run[r] += p;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[r][i] = fmaf(p, vf[u][i], acc[r][i]);
+        }
       }
     }
   }
 
   // Merge the lane groups of the warp (butterfly over the group index).
 #pragma unroll
-  for (int off = kLanesPerKey; off < 32; off <<= 1) {
-    const float m_o = __shfl_xor_sync(0xffffffffu, m_run, off);
-    const float l_o = __shfl_xor_sync(0xffffffffu, l_run, off);
-    const float m_new = fmaxf(m_run, m_o);
-    const float c_s = (m_run == -INFINITY) ? 0.0f : ptx::ex2_approx(m_run - m_new);
-    const float c_o = (m_o == -INFINITY) ? 0.0f : ptx::ex2_approx(m_o - m_new);
-    l_run = l_run * c_s + l_o * c_o;
+  for (int r = 0; r < kQ; ++r) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float a_o = __shfl_xor_sync(0xffffffffu, acc[i], off);
-      acc[i] = acc[i] * c_s + a_o * c_o;
+    for (int off = kLanesPerKey; off < 32; off <<= 1) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m_run[r], off);
+      const float l_o = __shfl_xor_sync(0xffffffffu, l_run[r], off);
+      const float m_new = fmaxf(m_run[r], m_o);
+      const float c_s = (m_run[r] == -INFINITY) ? 0.0f : ptx::ex2_approx(m_run[r] - m_new);
+      const float c_o = (m_o == -INFINITY) ? 0.0f : ptx::ex2_approx(m_o - m_new);
+      l_run[r] = l_run[r] * c_s + l_o * c_o;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float a_o = __shfl_xor_sync(0xffffffffu, acc[r][i], off);
+        acc[r][i] = acc[r][i] * c_s + a_o * c_o;
+      }
+      m_run[r] = m_new;
     }
-    m_run = m_new;
-  }
-  if (group == 0) {
+    if (group == 0) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) sm_acc[warp][d0 + i] = acc[i];
-    if (sub == 0) {
-      sm_m[warp] = m_run;
-      sm_l[warp] = l_run;
+      for (int i = 0; i < 8; ++i) sm_acc[warp][r][d0 + i] = acc[r][i];
+      if (sub == 0) {
+        sm_m[warp][r] = m_run[r];
+        sm_l[warp][r] = l_run[r];
+      }
     }
   }
   __syncthreads();
 
   // Merge the warps; thread d owns head-dim element d.
   const int d = threadIdx.x;
-  float m_all = -INFINITY;
 #pragma unroll
-  for (int w = 0; w < kWarps; ++w) m_all = fmaxf(m_all, sm_m[w]);
-  float l_all = 0.0f;
-  float o = 0.0f;
+  for (int r = 0; r < kQ; ++r) {
+    const int f = f0 + r;
+    if (f >= a.F) break;
+    float m_all = -INFINITY;
 #pragma unroll
-  for (int w = 0; w < kWarps; ++w) {
-    const float c = (sm_m[w] == -INFINITY) ? 0.0f : ptx::ex2_approx(sm_m[w] - m_all);
-    l_all += sm_l[w] * c;
-    if (d < kHPad) o += sm_acc[w][d] * c;
-  }
-  const int64_t row = (static_cast<int64_t>(batch) * a.N + head) * a.F + f;
-  if (a.splits == 1) {
-    if (d < a.H)
-      a.out[batch * a.o_strides[0] + head * a.o_strides[1] + static_cast<int64_t>(f) * a.o_strides[2] + d] =
-          from_f32(o / l_all, bf16);
-    if (d == 0 && a.lse != nullptr) a.lse[row] = (m_all + log2f(l_all)) * kLn2;
-  } else {
-    float* part = a.partial + (row * a.splits + split) * (a.H + 2);
-    if (d < a.H) part[d] = o;
-    if (d == 0) {
-      part[a.H] = m_all;
-      part[a.H + 1] = l_all;
+    for (int w = 0; w < kWarps; ++w) m_all = fmaxf(m_all, sm_m[w][r]);
+    float l_all = 0.0f;
+    float o = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float c = (sm_m[w][r] == -INFINITY) ? 0.0f : ptx::ex2_approx(sm_m[w][r] - m_all);
+      l_all += sm_l[w][r] * c;
+      if (d < kHPad) o += sm_acc[w][r][d] * c;
+    }
+    const int64_t row = (static_cast<int64_t>(batch) * a.N + head) * a.F + f;
+    if (a.splits == 1) {
+      if (d < a.H)
+        a.out[batch * a.o_strides[0] + head * a.o_strides[1] + static_cast<int64_t>(f) * a.o_strides[2] + d] =
+            from_f32(o / l_all, bf16);
+      if (d == 0 && a.lse != nullptr) a.lse[row] = (m_all + log2f(l_all)) * kLn2;
+    } else {
+      float* part = a.partial + (row * a.splits + split) * (a.H + 2);
+      if (d < a.H) part[d] = o;
+      if (d == 0) {
+        part[a.H] = m_all;
+        part[a.H + 1] = l_all;
+      }
     }
   }
 }
@@ -261,8 +289,14 @@ __global__ void fmha_decode_combine_kernel(const DecodeArgs a) {
 
 }  // namespace
 
+// Query rows one CTA serves.  Two rows share every K and V load; with four the kernel is bound by
+// instruction issue (the per-row dot products and their shuffle reductions) and by the registers
+// of four accumulators (one CTA per SM), and ran slower than two passes of two rows.
+int decode_rows_per_cta(int F) { return F >= 2 ? 2 : 1; }
+
 int decode_splits(const Problem& p, int /*sm_count*/) {
-  const int64_t base = static_cast<int64_t>(p.B) * p.N * p.F;
+  const int rows = decode_rows_per_cta(p.F);
+  const int64_t base = static_cast<int64_t>(p.B) * p.N * ((p.F + rows - 1) / rows);
   int64_t want = (kTargetCtas + base - 1) / base;
   const int64_t max_splits = (p.T + kMinKeysPerSplit - 1) / kMinKeysPerSplit;
   if (want > max_splits) want = max_splits;
@@ -320,13 +354,16 @@ int launch_decode(const Problem& p, const DeviceInfo& dev, void* workspace, size
     a.o_strides[i] = p.o_strides[i];
     a.bias_strides[i] = p.bias_strides[i];
   }
-  dim3 grid(splits * p.F, p.N, p.B);
-  if (p.H <= 64)
-    fmha_decode_kernel<8><<<grid, kThreads, 0, stream>>>(a);
-  else if (p.H <= 128)
-    fmha_decode_kernel<16><<<grid, kThreads, 0, stream>>>(a);
-  else
-    fmha_decode_kernel<32><<<grid, kThreads, 0, stream>>>(a);
+  const int rows_per_cta = decode_rows_per_cta(p.F);
+  dim3 grid(splits * ((p.F + rows_per_cta - 1) / rows_per_cta), p.N, p.B);
+  auto launch_lanes = [&](auto lanes_tag) {
+    constexpr int kLanes = decltype(lanes_tag)::value;
+    if (rows_per_cta == 1) fmha_decode_kernel<kLanes, 1><<<grid, kThreads, 0, stream>>>(a);
+    else fmha_decode_kernel<kLanes, 2><<<grid, kThreads, 0, stream>>>(a);
+  };
+  if (p.H <= 64) launch_lanes(std::integral_constant<int, 8>{});
+  else if (p.H <= 128) launch_lanes(std::integral_constant<int, 16>{});
+  else launch_lanes(std::integral_constant<int, 32>{});
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
   if (splits > 1) {

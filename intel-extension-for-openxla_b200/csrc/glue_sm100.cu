@@ -1,6 +1,7 @@
 // The memory-bound steps between the custom calls of a decoder layer: row normalisation
-// (LayerNorm / RMSNorm without learned gain), interleaved-pair rotary embedding applied in place
-// to the q and k slices of a fused QKV projection, and the residual add that closes the block.
+// (LayerNorm / RMSNorm, with or without a learned gain), rotary embedding (interleaved pairs as in
+// GPT-J, or half-split pairs as in Gemma) applied in place to the q and k slices of a fused QKV
+// projection, and the residual add that closes the block.
 // XLA emits these as loop fusions around the custom calls (they are not custom calls in the
 // reference); they live here so that a layer built from the library's GEMM and attention calls is
 // not dominated by many small framework kernels.  Each is one pass over its operands with 16-byte
@@ -57,9 +58,11 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 // One CTA per row; the row stays in registers between the statistics and the write.
+// `gain` (may be null): y = normalised * (gain_offset + gain[col]), one rounding.
 template <bool kBf16, bool kRms>
 __global__ void __launch_bounds__(kNormThreads) row_norm_kernel(const uint4* x, uint4* y,  // may be one buffer: no __restrict__
-                                                                int cols, int64_t ldx_vec, int64_t ldy_vec, float eps) {
+                                                                int cols, int64_t ldx_vec, int64_t ldy_vec, float eps,
+                                                                const uint4* __restrict__ gain, float gain_offset) {
   __shared__ float scratch[kNormThreads / 32];
   const int nvec = cols / kVecElems;
   const uint4* xr = x + static_cast<int64_t>(blockIdx.x) * ldx_vec;
@@ -108,9 +111,20 @@ __global__ void __launch_bounds__(kNormThreads) row_norm_kernel(const uint4* x, 
     const int idx = threadIdx.x + i * kNormThreads;
     if (idx < nvec) {
       uint32_t words[4];
+      if (gain != nullptr) {
+        const uint4 gw = gain[idx];
+        const uint32_t gwords[4] = {gw.x, gw.y, gw.z, gw.w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        words[j] = pack2<kBf16>((v[i][2 * j] - mean) * rstd, (v[i][2 * j + 1] - mean) * rstd);
+        for (int j = 0; j < 4; ++j) {
+          const float2 g = unpack2<kBf16>(gwords[j]);
+          words[j] = pack2<kBf16>((v[i][2 * j] - mean) * rstd * (gain_offset + g.x),
+                                  (v[i][2 * j + 1] - mean) * rstd * (gain_offset + g.y));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          words[j] = pack2<kBf16>((v[i][2 * j] - mean) * rstd, (v[i][2 * j + 1] - mean) * rstd);
+      }
       yr[idx] = make_uint4(words[0], words[1], words[2], words[3]);
     }
   }
@@ -141,6 +155,41 @@ __global__ void rotary_kernel(uint4* __restrict__ x, const float4* __restrict__ 
       out[j] = pack2<kBf16>(f.x * cs[j] - f.y * sn[j], f.x * sn[j] + f.y * cs[j]);
     }
     *p = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
+// Half-split rotary (the convention of the Gemma and Llama families): element i < rotary_dim / 2
+// pairs with element i + rotary_dim / 2.  One thread per 16-byte vector of the first half and its
+// partner vector in the second half.
+template <bool kBf16>
+__global__ void rotary_half_kernel(uint4* __restrict__ x, const float4* __restrict__ cos_t, const float4* __restrict__ sin_t,
+                                   int64_t total_vecs, int vecs_per_half, int heads, int seq_len,
+                                   int64_t token_stride_vec, int64_t head_stride_vec) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vecs;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int vec = static_cast<int>(i % vecs_per_half);
+    const int64_t th = i / vecs_per_half;
+    const int head = static_cast<int>(th % heads);
+    const int64_t token = th / heads;
+    const int pos = static_cast<int>(token % seq_len);
+    uint4* p1 = x + token * token_stride_vec + head * head_stride_vec + vec;
+    uint4* p2 = p1 + vecs_per_half;
+    const uint4 w1 = *p1, w2 = *p2;
+    // 8 angles per vector: two float4 of the [seq_len, rotary_dim / 2] tables
+    const int64_t t = (static_cast<int64_t>(pos) * vecs_per_half + vec) * 2;
+    const float4 c0 = cos_t[t], c1 = cos_t[t + 1], s0 = sin_t[t], s1 = sin_t[t + 1];
+    const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const uint32_t a[4] = {w1.x, w1.y, w1.z, w1.w}, b[4] = {w2.x, w2.y, w2.z, w2.w};
+    uint32_t o1[4], o2[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f1 = unpack2<kBf16>(a[j]), f2 = unpack2<kBf16>(b[j]);
+      o1[j] = pack2<kBf16>(f1.x * cs[2 * j] - f2.x * sn[2 * j], f1.y * cs[2 * j + 1] - f2.y * sn[2 * j + 1]);
+      o2[j] = pack2<kBf16>(f2.x * cs[2 * j] + f1.x * sn[2 * j], f2.y * cs[2 * j + 1] + f1.y * sn[2 * j + 1]);
+    }
+    *p1 = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+    *p2 = make_uint4(o2[0], o2[1], o2[2], o2[3]);
   }
 }
 
@@ -187,9 +236,10 @@ using namespace ixk;
 
 extern "C" {
 
-int ixk_row_norm(int dtype, int kind, int64_t rows, int64_t cols, const void* x, int64_t ldx, void* y, int64_t ldy,
-                 float eps, void* stream) {
+static int row_norm_impl(int dtype, int kind, int64_t rows, int64_t cols, const void* x, int64_t ldx, void* y, int64_t ldy,
+                         float eps, const void* gain, float gain_offset, void* stream) {
   clear_error();
+  if (gain != nullptr && !glue::aligned16(gain)) return fail(IXK_INVALID_ARGUMENT, "row_norm: gain must be 16-byte aligned");
   if (dtype != IXK_BF16 && dtype != IXK_F16) return fail(IXK_UNIMPLEMENTED, "row_norm: dtype must be BF16 or F16");
   if (kind != IXK_NORM_LAYER && kind != IXK_NORM_RMS) return fail(IXK_INVALID_ARGUMENT, "row_norm: unknown kind");
   if (rows < 0 || cols <= 0 || (rows > 0 && (x == nullptr || y == nullptr)))
@@ -207,24 +257,41 @@ int ixk_row_norm(int dtype, int kind, int64_t rows, int64_t cols, const void* x,
   auto s = static_cast<cudaStream_t>(stream);
   const uint4* xv = static_cast<const uint4*>(x);
   uint4* yv = static_cast<uint4*>(y);
+  const uint4* gv = static_cast<const uint4*>(gain);
   const int64_t lx = ldx / glue::kVecElems, ly = ldy / glue::kVecElems;
   const int c = static_cast<int>(cols);
   if (dtype == IXK_BF16) {
-    if (kind == IXK_NORM_RMS) glue::row_norm_kernel<true, true><<<grid, glue::kNormThreads, 0, s>>>(xv, yv, c, lx, ly, eps);
-    else glue::row_norm_kernel<true, false><<<grid, glue::kNormThreads, 0, s>>>(xv, yv, c, lx, ly, eps);
+    if (kind == IXK_NORM_RMS) glue::row_norm_kernel<true, true><<<grid, glue::kNormThreads, 0, s>>>(xv, yv, c, lx, ly, eps, gv, gain_offset);
+    else glue::row_norm_kernel<true, false><<<grid, glue::kNormThreads, 0, s>>>(xv, yv, c, lx, ly, eps, gv, gain_offset);
   } else {
-    if (kind == IXK_NORM_RMS) glue::row_norm_kernel<false, true><<<grid, glue::kNormThreads, 0, s>>>(xv, yv, c, lx, ly, eps);
-    else glue::row_norm_kernel<false, false><<<grid, glue::kNormThreads, 0, s>>>(xv, yv, c, lx, ly, eps);
+    if (kind == IXK_NORM_RMS) glue::row_norm_kernel<false, true><<<grid, glue::kNormThreads, 0, s>>>(xv, yv, c, lx, ly, eps, gv, gain_offset);
+    else glue::row_norm_kernel<false, false><<<grid, glue::kNormThreads, 0, s>>>(xv, yv, c, lx, ly, eps, gv, gain_offset);
   }
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
   return IXK_OK;
 }
 
-int ixk_rotary_interleaved(int dtype, void* x, int64_t tokens, int64_t seq_len, int64_t heads, int64_t rotary_dim,
-                           int64_t token_stride, int64_t head_stride, const float* cos_table, const float* sin_table,
-                           void* stream) {
+int ixk_row_norm(int dtype, int kind, int64_t rows, int64_t cols, const void* x, int64_t ldx, void* y, int64_t ldy,
+                 float eps, void* stream) {
+  return row_norm_impl(dtype, kind, rows, cols, x, ldx, y, ldy, eps, nullptr, 0.0f, stream);
+}
+
+int ixk_row_norm_gain(int dtype, int kind, int64_t rows, int64_t cols, const void* x, int64_t ldx, const void* gain,
+                      float gain_offset, void* y, int64_t ldy, float eps, void* stream) {
+  if (gain == nullptr) {
+    clear_error();
+    return fail(IXK_INVALID_ARGUMENT, "row_norm: gain is NULL");
+  }
+  return row_norm_impl(dtype, kind, rows, cols, x, ldx, y, ldy, eps, gain, gain_offset, stream);
+}
+
+static int rotary_impl(bool half_split, int dtype, void* x, int64_t tokens, int64_t seq_len, int64_t heads, int64_t rotary_dim,
+                       int64_t token_stride, int64_t head_stride, const float* cos_table, const float* sin_table,
+                       void* stream) {
   clear_error();
+  if (half_split && rotary_dim % (2 * glue::kVecElems))
+    return fail(IXK_INVALID_ARGUMENT, "rotary: the half-split form needs rotary_dim to be a multiple of 16 elements");
   if (dtype != IXK_BF16 && dtype != IXK_F16) return fail(IXK_UNIMPLEMENTED, "rotary: dtype must be BF16 or F16");
   if (tokens < 0 || seq_len <= 0 || heads <= 0 || rotary_dim <= 0 ||
       (tokens > 0 && (x == nullptr || cos_table == nullptr || sin_table == nullptr)))
@@ -235,7 +302,7 @@ int ixk_rotary_interleaved(int dtype, void* x, int64_t tokens, int64_t seq_len, 
     return fail(IXK_INVALID_ARGUMENT, "rotary: rotary_dim and strides must be multiples of 8 elements, pointers 16-byte aligned");
   DeviceInfo info;
   if (int st = get_device_info(&info)) return st;
-  const int vph = static_cast<int>(rotary_dim / glue::kVecElems);
+  const int vph = static_cast<int>(rotary_dim / glue::kVecElems) / (half_split ? 2 : 1);
   const int64_t total = tokens * heads * vph;
   if (total == 0) return IXK_OK;
   const int grid = glue::elementwise_grid(total, 256, info.sm_count);
@@ -243,15 +310,30 @@ int ixk_rotary_interleaved(int dtype, void* x, int64_t tokens, int64_t seq_len, 
   auto* xv = static_cast<uint4*>(x);
   auto* cv = reinterpret_cast<const float4*>(cos_table);
   auto* sv = reinterpret_cast<const float4*>(sin_table);
-  if (dtype == IXK_BF16)
-    glue::rotary_kernel<true><<<grid, 256, 0, s>>>(xv, cv, sv, total, vph, static_cast<int>(heads), static_cast<int>(seq_len),
-                                                   token_stride / glue::kVecElems, head_stride / glue::kVecElems);
-  else
-    glue::rotary_kernel<false><<<grid, 256, 0, s>>>(xv, cv, sv, total, vph, static_cast<int>(heads), static_cast<int>(seq_len),
-                                                    token_stride / glue::kVecElems, head_stride / glue::kVecElems);
+  const int h = static_cast<int>(heads), sl = static_cast<int>(seq_len);
+  const int64_t ts = token_stride / glue::kVecElems, hs = head_stride / glue::kVecElems;
+  if (half_split) {
+    if (dtype == IXK_BF16) glue::rotary_half_kernel<true><<<grid, 256, 0, s>>>(xv, cv, sv, total, vph, h, sl, ts, hs);
+    else glue::rotary_half_kernel<false><<<grid, 256, 0, s>>>(xv, cv, sv, total, vph, h, sl, ts, hs);
+  } else {
+    if (dtype == IXK_BF16) glue::rotary_kernel<true><<<grid, 256, 0, s>>>(xv, cv, sv, total, vph, h, sl, ts, hs);
+    else glue::rotary_kernel<false><<<grid, 256, 0, s>>>(xv, cv, sv, total, vph, h, sl, ts, hs);
+  }
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
   return IXK_OK;
+}
+
+int ixk_rotary_interleaved(int dtype, void* x, int64_t tokens, int64_t seq_len, int64_t heads, int64_t rotary_dim,
+                           int64_t token_stride, int64_t head_stride, const float* cos_table, const float* sin_table,
+                           void* stream) {
+  return rotary_impl(false, dtype, x, tokens, seq_len, heads, rotary_dim, token_stride, head_stride, cos_table, sin_table, stream);
+}
+
+int ixk_rotary_half(int dtype, void* x, int64_t tokens, int64_t seq_len, int64_t heads, int64_t rotary_dim,
+                    int64_t token_stride, int64_t head_stride, const float* cos_table, const float* sin_table,
+                    void* stream) {
+  return rotary_impl(true, dtype, x, tokens, seq_len, heads, rotary_dim, token_stride, head_stride, cos_table, sin_table, stream);
 }
 
 int ixk_residual_add(int dtype, int64_t rows, int64_t cols, const void* x, const void* partial, const void* bias,

@@ -43,15 +43,16 @@ class KernelOps:
     def layer_norm(self, x, eps=1e-5):
         return self.pkg.row_norm(x, kind=self.pkg.NORM_LAYER, eps=eps)
 
-    def rms_norm(self, x, eps=1e-6):
-        return self.pkg.row_norm(x, kind=self.pkg.NORM_RMS, eps=eps)
+    def rms_norm(self, x, eps=1e-6, gain=None):
+        """`gain`: Gemma's learned scale w, applied as (1 + w)."""
+        return self.pkg.row_norm(x, kind=self.pkg.NORM_RMS, eps=eps, gain=gain, gain_offset=1.0)
 
-    def rotary_qk_(self, qkv, cos, sin, rotary_dim):
+    def rotary_qk_(self, qkv, cos, sin, rotary_dim, half_split=False):
         """qkv [B, S, 3, heads_local, head_dim] dense: rotates the q and k slices in place (they are
         2 * heads_local consecutive heads of every token)."""
         B, S, _, hl, hd = qkv.shape
         qk = qkv.view(B * S, 3 * hl, hd)[:, :2 * hl]
-        self.pkg.rotary_interleaved_(qk, cos, sin, S, rotary_dim)
+        self.pkg.rotary_interleaved_(qk, cos, sin, S, rotary_dim, half_split=half_split)
         return qkv
 
     def residual_add(self, x, partial, bias=None, out=None):
@@ -108,9 +109,11 @@ def layer_norm(x: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
     return ((xf - mu) * torch.rsqrt(var + eps)).to(x.dtype)
 
 
-def rms_norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+def rms_norm(x: torch.Tensor, eps: float = 1e-6, gain: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMSNorm; `gain` is Gemma's learned scale w, applied as (1 + w) before the one rounding."""
     xf = x.float()
-    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (y if gain is None else y * (1.0 + gain.float())).to(x.dtype)
 
 
 def rotary_tables(positions: torch.Tensor, rotary_dim: int, base: float = 10000.0):
@@ -131,9 +134,21 @@ def apply_rotary_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rotary_
     return x
 
 
-def _rotary_qk_torch_(qkv, cos, sin, rotary_dim):
-    apply_rotary_(qkv[:, :, 0], cos, sin, rotary_dim)
-    apply_rotary_(qkv[:, :, 1], cos, sin, rotary_dim)
+def apply_rotary_half_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rotary_dim: int) -> torch.Tensor:
+    """In place, Gemma convention: element i < rotary_dim/2 pairs with element i + rotary_dim/2
+    (keras_nlp's CachedGemmaAttention._apply_rope, which example/gemma/keras_nlp.patch:6-23 calls)."""
+    half = rotary_dim // 2
+    x1, x2 = x[..., :half].float(), x[..., half:rotary_dim].float()
+    c, s = cos[:, None, :], sin[:, None, :]
+    x[..., :half] = (x1 * c - x2 * s).to(x.dtype)
+    x[..., half:rotary_dim] = (x2 * c + x1 * s).to(x.dtype)
+    return x
+
+
+def _rotary_qk_torch_(qkv, cos, sin, rotary_dim, half_split=False):
+    fn = apply_rotary_half_ if half_split else apply_rotary_
+    fn(qkv[:, :, 0], cos, sin, rotary_dim)
+    fn(qkv[:, :, 1], cos, sin, rotary_dim)
     return qkv
 
 
@@ -223,7 +238,8 @@ def gptj_layer_flops(B, S, hidden=4096, heads=16, head_dim=256, ffn=16384):
 @dataclass
 class GemmaLayerWeights:
     """This rank's shard.  Full shapes: wqkv [3072, 12288], wo [4096, 3072], wgate/wup [3072, 24576],
-    wdown [24576, 3072]."""
+    wdown [24576, 3072]; norm_attn / norm_mlp [3072]: the learned scales w of the two RMSNorms,
+    applied as (1 + w), replicated on every rank (None = unit gain)."""
     wqkv: torch.Tensor
     wo: torch.Tensor
     wgate: torch.Tensor
@@ -231,6 +247,8 @@ class GemmaLayerWeights:
     wdown: torch.Tensor
     heads_local: int
     head_dim: int
+    norm_attn: Optional[torch.Tensor] = None
+    norm_mlp: Optional[torch.Tensor] = None
 
     @staticmethod
     def shard(full: dict, num_heads: int, head_dim: int, rank: int, world: int):
@@ -240,7 +258,8 @@ class GemmaLayerWeights:
             wgate=shard_columns(full["wgate"], rank, world),
             wup=shard_columns(full["wup"], rank, world),
             wdown=shard_rows(full["wdown"], rank, world),
-            heads_local=num_heads // world, head_dim=head_dim)
+            heads_local=num_heads // world, head_dim=head_dim,
+            norm_attn=full.get("norm_attn"), norm_mlp=full.get("norm_mlp"))
 
 
 def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -252,15 +271,16 @@ def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tens
     With `comm` (a comm.Communicator) each row-parallel projection writes its partial into the
     NVLink exchange buffer and one libixk kernel does the exchange and the residual add that
     follows it (the two partials use different offsets, so the second exchange never waits for
-    readers of the first)."""
+    readers of the first).  Numerics are the Gemma block's: RMSNorm with the (1 + w) scale,
+    rotary embedding on half-split pairs over the whole head, GeGLU with the tanh GELU."""
     B, _, hidden = x.shape
     hl, hd = w.heads_local, w.head_dim
     norm = _glue(ops, "rms_norm", rms_norm)
     add = _glue(ops, "residual_add", _residual_add_torch)
-    h = norm(x).view(B, hidden)
+    h = norm(x, gain=w.norm_attn).view(B, hidden)
     qkv = ops.gemm(h, w.wqkv).view(B, 1, 3, hl, hd)
     cos, sin = rope if rope is not None else rotary_tables(torch.tensor([position], device=x.device), hd)
-    _glue(ops, "rotary_qk_", _rotary_qk_torch_)(qkv, cos, sin, hd)
+    _glue(ops, "rotary_qk_", _rotary_qk_torch_)(qkv, cos, sin, hd, half_split=True)
     k_cache[:, position] = qkv[:, 0, 1]
     v_cache[:, position] = qkv[:, 0, 2]
     T = position + 1
@@ -275,7 +295,7 @@ def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tens
         x1 = comm.all_reduce_residual(part, x)
     else:
         x1 = add(x, reduce(ops.gemm(ctx.view(B, hl * hd), w.wo), group))
-    h2 = norm(x1).view(B, hidden)
+    h2 = norm(x1, gain=w.norm_mlp).view(B, hidden)
     gate = ops.gemm(h2, w.wgate, epilogue="GELU")
     up = ops.gemm(h2, w.wup)
     if comm is not None:

@@ -27,9 +27,11 @@ def layer_norm(x, eps=1e-5):
     return _r((x - mu) / np.sqrt(var + eps))
 
 
-def rms_norm(x, eps=1e-6):
+def rms_norm(x, eps=1e-6, gain=None):
+    """`gain`: the learned scale w of Gemma's RMSNorm, applied as (1 + w) before the one rounding."""
     x = np.asarray(x, np.float32)
-    return _r(x / np.sqrt((x * x).mean(-1, keepdims=True) + eps))
+    y = x / np.sqrt((x * x).mean(-1, keepdims=True) + eps)
+    return _r(y if gain is None else y * (1.0 + np.asarray(gain, np.float32)))
 
 
 def rotary(x, positions, rotary_dim, base=10000.0):
@@ -41,6 +43,21 @@ def rotary(x, positions, rotary_dim, base=10000.0):
     x1, x2 = x[..., 0:rotary_dim:2].copy(), x[..., 1:rotary_dim:2].copy()
     x[..., 0:rotary_dim:2] = x1 * c - x2 * s
     x[..., 1:rotary_dim:2] = x1 * s + x2 * c
+    return _r(x)
+
+
+def rotary_half(x, positions, rotary_dim, base=10000.0):
+    """Half-split rotary (Gemma): element i < rotary_dim/2 pairs with i + rotary_dim/2; the published
+    form of keras_nlp's CachedGemmaAttention._apply_rope, which the reference's Gemma example runs
+    (example/gemma/keras_nlp.patch:6-23 calls it; keras_nlp itself is not part of the reference)."""
+    x = np.array(x, np.float32)
+    half = rotary_dim // 2
+    inv = 1.0 / (base ** (np.arange(0, rotary_dim, 2, dtype=np.float32) / rotary_dim))
+    ang = np.asarray(positions, np.float32)[:, None] * inv[None, :]
+    c, s = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+    x1, x2 = x[..., :half].copy(), x[..., half:rotary_dim].copy()
+    x[..., :half] = x1 * c - x2 * s
+    x[..., half:rotary_dim] = x2 * c + x1 * s
     return _r(x)
 
 
@@ -65,11 +82,11 @@ def gptj_layer_prefill(x, w, num_heads, head_dim, rotary_dim):
 def gemma_decode_step(x, w, k_cache, v_cache, position, num_heads, head_dim):
     """x [B,1,hidden]; caches [B,T,heads,head_dim] (updated copies are used, inputs untouched)."""
     B, _, hidden = x.shape
-    h = rms_norm(x).reshape(B, hidden)
+    h = rms_norm(x, gain=w.get("norm_attn")).reshape(B, hidden)
     qkv = _r(h @ w["wqkv"]).reshape(B, 1, 3, num_heads, head_dim)
     pos = np.array([position])
-    q = rotary(qkv[:, :, 0], pos, head_dim).transpose(0, 2, 1, 3)
-    k_new = rotary(qkv[:, :, 1], pos, head_dim)[:, 0]
+    q = rotary_half(qkv[:, :, 0], pos, head_dim).transpose(0, 2, 1, 3)
+    k_new = rotary_half(qkv[:, :, 1], pos, head_dim)[:, 0]
     k_cache = np.array(k_cache, np.float32)
     v_cache = np.array(v_cache, np.float32)
     k_cache[:, position] = k_new
@@ -79,7 +96,7 @@ def gemma_decode_step(x, w, k_cache, v_cache, position, num_heads, head_dim):
                               head_scale=1.0 / math.sqrt(head_dim))
     ctx = ctx.transpose(0, 2, 1, 3).reshape(B, num_heads * head_dim)
     x1 = _r(np.asarray(x, np.float32) + _r(ctx @ w["wo"]).reshape(B, 1, hidden))
-    h2 = rms_norm(x1).reshape(B, hidden)
+    h2 = rms_norm(x1, gain=w.get("norm_mlp")).reshape(B, hidden)
     gate = orc.gemm_epilogue(h2 @ w["wgate"], None, None, 0.0, "GELU", orc.BF16)
     up = _r(h2 @ w["wup"])
     down = _r(_r(gate * up) @ w["wdown"])

@@ -116,6 +116,11 @@ DECODE_CASES = [
     (2, 3, 2, 1000, 64, False, "btnh", True),
     (1, 1, 16, 130, 128, True, "bnth", True),
     (3, 2, 1, 1, 256, False, "bnth", False),
+    # two query rows per CTA share one pass over the cache
+    (2, 2, 5, 4096, 256, False, "btnh", False),     # two pairs and a single row, several key splits
+    (1, 3, 6, 700, 64, True, "bnth", False),
+    (2, 2, 16, 2048, 256, False, "btnh", True),
+    (1, 2, 4, 3, 128, True, "bnth", False),         # fewer keys than rows
 ]
 
 

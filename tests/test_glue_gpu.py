@@ -39,6 +39,26 @@ def test_row_norm(pkg, orc, cuda, dtype, kind, rows, cols):
         orc.check_close(f32(got), ref, rtol=ULP[dtype], atol=ULP[dtype], what=f"row_norm {kind} vs layer oracle")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (37, 3072), (5, 8192), (300, 520)])
+def test_rms_norm_with_the_one_plus_w_scale(pkg, orc, cuda, dtype, rows, cols):
+    """Gemma's RMSNorm: normalised * (1 + w), one rounding (and offset 0: the usual learned gain)."""
+    from oracle import layers_oracle
+    g = torch.Generator().manual_seed(rows * 7 + cols)
+    x = (torch.randn(rows, cols, generator=g) * 1.7 + 0.3).to(dtype)
+    w = (torch.randn(cols, generator=g) * 0.3).to(dtype)
+    xf, wf = f32(x), f32(w)
+    normed = xf / np.sqrt((xf * xf).mean(-1, keepdims=True) + 1e-6)
+    got = pkg.row_norm(x.to(cuda), kind=pkg.NORM_RMS, eps=1e-6, gain=w.to(cuda), gain_offset=1.0)
+    orc.check_close(f32(got), normed * (1.0 + wf), rtol=ULP[dtype], atol=ULP[dtype], what="rms norm (1 + w)")
+    if dtype == torch.bfloat16:
+        orc.check_close(f32(got), layers_oracle.rms_norm(xf, gain=wf), rtol=ULP[dtype], atol=ULP[dtype], what="vs layer oracle")
+    got0 = pkg.row_norm(x.to(cuda), kind=pkg.NORM_RMS, eps=1e-6, gain=w.to(cuda))
+    orc.check_close(f32(got0), normed * wf, rtol=ULP[dtype], atol=ULP[dtype], what="rms norm w")
+    with pytest.raises(pkg.IxkError):
+        pkg.row_norm(x.to(cuda), kind=pkg.NORM_RMS, gain=w[:-1].contiguous().to(cuda))     # wrong length
+
+
 def test_row_norm_in_place_and_rejections(pkg, cuda):
     x = torch.randn(16, 256).bfloat16().to(cuda)
     want = pkg.row_norm(x)
@@ -79,6 +99,40 @@ def test_rotary_on_fused_qkv(pkg, orc, cuda, dtype, B, S, heads, hd, rot):
         orc.check_close(f32(dev[:, :, i]), exact, rtol=ULP[dtype], atol=ULP[dtype], what="rotary")
         if want is not None:        # the oracle builds its own tables in numpy: table rounding adds an ulp
             orc.check_close(f32(dev[:, :, i]), want, rtol=2 * ULP[dtype], atol=2 * ULP[dtype], what="rotary vs layer oracle")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,S,heads,hd,rot", [(2, 37, 2, 256, 256), (1, 1, 4, 256, 256), (3, 128, 3, 64, 32),
+                                              (5, 1, 2, 128, 128), (1, 700, 1, 256, 16)])
+def test_rotary_half_split_on_fused_qkv(pkg, orc, cuda, dtype, B, S, heads, hd, rot):
+    """The Gemma convention: element i pairs with element i + rot/2."""
+    from oracle import layers_oracle
+    layers = __import__("importlib").import_module("ixk_b200.layers")
+    g = torch.Generator().manual_seed(B * 999 + S)
+    qkv = torch.randn(B, S, 3, heads, hd, generator=g).to(dtype)
+    cos, sin = layers.rotary_tables(torch.arange(S), rot)
+    dev = qkv.to(cuda)
+    layers.KernelOps(pkg).rotary_qk_(dev, cos.to(cuda), sin.to(cuda), rot, half_split=True)
+    xf = f32(qkv)
+    assert torch.equal(dev[:, :, 2].cpu(), qkv[:, :, 2])
+    assert torch.equal(dev[..., rot:].cpu(), qkv[..., rot:])
+    half = rot // 2
+    for i in range(2):
+        c, s = f32(cos)[:, None, :], f32(sin)[:, None, :]
+        x1, x2 = xf[:, :, i, :, :half], xf[:, :, i, :, half:rot]
+        exact = xf[:, :, i].copy()
+        exact[..., :half] = x1 * c - x2 * s
+        exact[..., half:rot] = x2 * c + x1 * s
+        orc.check_close(f32(dev[:, :, i]), exact, rtol=ULP[dtype], atol=ULP[dtype], what="rotary, half-split")
+        if dtype == torch.bfloat16:
+            want = layers_oracle.rotary_half(xf[:, :, i], np.arange(S), rot)
+            orc.check_close(f32(dev[:, :, i]), want, rtol=2 * ULP[dtype], atol=2 * ULP[dtype], what="vs layer oracle")
+    # the torch stand-in the CPU tests use computes the same thing
+    ref = qkv.clone()
+    layers._rotary_qk_torch_(ref, cos, sin, rot, half_split=True)
+    orc.check_close(f32(dev), f32(ref), rtol=ULP[dtype], atol=ULP[dtype], what="kernel vs torch stand-in")
+    with pytest.raises(pkg.IxkError):
+        pkg.rotary_half_(dev.view(B * S, 3 * heads, hd), cos[:, :4].contiguous().to(cuda), sin[:, :4].contiguous().to(cuda), S, 8)
 
 
 def test_rotary_rejections(pkg, cuda):

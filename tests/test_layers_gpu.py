@@ -37,7 +37,8 @@ def test_gemma_decode_step(pkg, orc, cuda):
     g = torch.Generator().manual_seed(2)
     r = lambda *s: (torch.randn(*s, generator=g) * 0.02).bfloat16()
     full = {"wqkv": r(hidden, 3 * heads * hd), "wo": r(heads * hd, hidden), "wgate": r(hidden, ffn),
-            "wup": r(hidden, ffn), "wdown": r(ffn, hidden)}
+            "wup": r(hidden, ffn), "wdown": r(ffn, hidden),
+            "norm_attn": r(hidden), "norm_mlp": r(hidden)}
     x = torch.randn(B, 1, hidden, generator=g).bfloat16()
     kc = torch.randn(B, T, heads, hd, generator=g).bfloat16()
     vc = torch.randn(B, T, heads, hd, generator=g).bfloat16()
@@ -77,7 +78,8 @@ def test_gemma_decode_step_at_full_width(pkg, orc, cuda):
     g = torch.Generator().manual_seed(4)
     r = lambda *s: (torch.randn(*s, generator=g) * 0.02).bfloat16()
     full = {"wqkv": r(hidden, 3 * heads * hd), "wo": r(heads * hd, hidden), "wgate": r(hidden, ffn),
-            "wup": r(hidden, ffn), "wdown": r(ffn, hidden)}
+            "wup": r(hidden, ffn), "wdown": r(ffn, hidden),
+            "norm_attn": r(hidden), "norm_mlp": r(hidden)}
     x = torch.randn(B, 1, hidden, generator=g).bfloat16()
     kc = torch.randn(B, T, heads, hd, generator=g).bfloat16()
     vc = torch.randn(B, T, heads, hd, generator=g).bfloat16()

@@ -48,7 +48,8 @@ def _make_weights(seed, hidden, heads, head_dim, ffn, gemma):
     r = lambda *shape: (torch.randn(*shape, generator=g) * 0.05).bfloat16()
     if gemma:
         return {"wqkv": r(hidden, 3 * heads * head_dim), "wo": r(heads * head_dim, hidden), "wgate": r(hidden, ffn),
-                "wup": r(hidden, ffn), "wdown": r(ffn, hidden)}
+                "wup": r(hidden, ffn), "wdown": r(ffn, hidden),
+            "norm_attn": r(hidden), "norm_mlp": r(hidden)}
     return {"wqkv": r(hidden, 3 * heads * head_dim), "wo": r(heads * head_dim, hidden), "w1": r(hidden, ffn),
             "b1": r(ffn), "w2": r(ffn, hidden), "b2": r(hidden)}
 

@@ -117,7 +117,8 @@ def _worker(rank, world, port, q):
         hidden, heads, hd, ffn, B, T = 384, 4, 256, 768, 6, 900
         g = torch.Generator().manual_seed(2)
         full = {"wqkv": r(hidden, 3 * heads * hd), "wo": r(heads * hd, hidden), "wgate": r(hidden, ffn),
-                "wup": r(hidden, ffn), "wdown": r(ffn, hidden)}
+                "wup": r(hidden, ffn), "wdown": r(ffn, hidden),
+            "norm_attn": r(hidden), "norm_mlp": r(hidden)}
         xg = torch.randn(B, 1, hidden, generator=g).bfloat16()
         kc = torch.randn(B, T, heads, hd, generator=g).bfloat16()
         vc = torch.randn(B, T, heads, hd, generator=g).bfloat16()

@@ -11,6 +11,7 @@ problem is refused, and that the call really allocates nothing.
 The file name sorts last on purpose: a run that stops at the first failure has then already run
 every other test.  It also passes when run alone in a fresh process."""
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -58,6 +59,7 @@ def test_matches_the_workspace_entry_point_twice_in_a_row(pkg, cuda):
                 # part of the library image that holds the array (module loading is lazy), so the
                 # steady state is what is measured: one untimed call first.
                 assert _call_static(pkg, q, k, v, got, got_lse, causal) == pkg.IXK_OK
+            gc.collect()                                         # tensors of earlier tests that sit in reference cycles go now, not mid-measurement
             torch.cuda.synchronize()
             free_before, _ = torch.cuda.mem_get_info()           # the driver's view: sees any cudaMalloc, whoever makes it
             torch_before = torch.cuda.memory_allocated()
