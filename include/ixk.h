@@ -215,7 +215,11 @@ typedef struct ixk_fmha_desc {
 
 /* Replaces fmha_forward_kernel_bf16 / _fp16 (sdp_forward.cc:34-84):
  *   O[b,n,f,:] = softmax_t( head_scale * Q[b,n,f,:].K[b,n,t,:] + bias[b,n,f,t] ) . V[b,n,t,:]
- * with the softmax statistics in fp32.  lse (may be NULL) receives
+ * with the softmax statistics in fp32.  One stated deviation in the prefill path for BF16: the
+ * probabilities handed to the P.V product are cut to bf16 by truncation, with the mean loss
+ * (0.28 %) put back through the exponent and taken out of the row sum again, where the reference
+ * rounds P to the storage type (fmha_forward.h:364-382); results agree within the 2e-2 the
+ * parity tests allow, F16 and the decode path round to nearest.  lse (may be NULL) receives
  * m + ln(l) per row — the reference's "activation" output when is_training
  * (fmha_forward.h:433-450).  workspace must hold ixk_fmha_fwd_workspace_bytes(desc)
  * bytes (non-zero only for the split-key decode path, F <= 16). */
@@ -432,6 +436,8 @@ int ixk_device_status(int* status_word);
  * device is as usable as before.  cycles_out_device (device memory, may be NULL) receives the
  * cycles the CTA spent.  No counterpart in the reference, whose kernels have no device-side waits. */
 int ixk_selftest_bounded_wait(long long limit_cycles, long long* cycles_out_device, void* cuda_stream);
+/* With IXK_NVTX=1 in the environment every entry point that launches work is wrapped in an NVTX
+ * range of its own name (for timelines of the calling program); off by default. */
 /* Number of kernels this library has launched from this process (all threads). */
 uint64_t ixk_launch_count(void);
 

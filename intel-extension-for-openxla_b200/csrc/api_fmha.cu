@@ -89,6 +89,7 @@ size_t ixk_fmha_fwd_workspace_bytes(const ixk_fmha_desc* desc) {
 
 int ixk_fmha_fwd(const ixk_fmha_desc* desc, const void* q, const void* k, const void* v, const void* bias,
                  void* out, float* lse, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  IXK_API_RANGE("ixk_fmha_fwd");
   ixk::clear_error();
   ixk::fmha::Problem p;
   int rc = ixk::make_problem(desc, q, k, v, bias, out, lse, &p, true);
@@ -119,6 +120,7 @@ size_t ixk_fmha_bwd_workspace_bytes(const ixk_fmha_bwd_desc* desc) {
 int ixk_fmha_bwd(const ixk_fmha_bwd_desc* desc, const void* q, const void* k, const void* v, const void* out,
                  const void* bias, const void* grad_out, const float* lse, void* dq, void* dk, void* dv,
                  void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  IXK_API_RANGE("ixk_fmha_bwd");
   ixk::clear_error();
   if (desc == nullptr) return ixk::fail(IXK_INVALID_ARGUMENT, "desc is NULL");
   ixk::fmha::BwdProblem bp;

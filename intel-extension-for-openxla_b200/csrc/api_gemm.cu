@@ -321,6 +321,7 @@ extern "C" {
 
 int ixk_gemm(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c,
              const void* bias, void* d, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  IXK_API_RANGE("ixk_gemm");
   return ixk::run(desc, a, b, c, bias, d, /*fp8_call=*/false, 1.0f, 1.0f, workspace, workspace_bytes, cuda_stream);
 }
 
@@ -328,6 +329,7 @@ size_t ixk_gemm_workspace_bytes(const ixk_gemm_desc* desc) { return ixk::workspa
 
 int ixk_gemm_aux(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, const void* bias, void* d,
                  void* aux, int64_t aux_leading_dim_stride, void* cuda_stream) {
+  IXK_API_RANGE("ixk_gemm_aux");
   return ixk::run(desc, a, b, c, bias, d, /*fp8_call=*/false, 1.0f, 1.0f, nullptr, 0, cuda_stream, aux,
                   aux_leading_dim_stride, /*aux_call=*/true);
 }
@@ -362,6 +364,7 @@ int ixk_ffi_select_operands(int epilogue, float beta, int num_args, int num_resu
 
 int ixk_gemm_scatter(ixk_comm* comm, const ixk_gemm_desc* desc, const void* a, const void* b, const void* c,
                      const void* bias, size_t slots_offset, void* cuda_stream) {
+  IXK_API_RANGE("ixk_gemm_scatter");
   if (comm == nullptr) {
     ixk::clear_error();
     return ixk::fail(IXK_INVALID_ARGUMENT, "comm is NULL");
@@ -372,6 +375,7 @@ int ixk_gemm_scatter(ixk_comm* comm, const ixk_gemm_desc* desc, const void* a, c
 int ixk_gemm_fp8(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c,
                  const void* bias, void* d, float inv_scale_a, float inv_scale_b, void* workspace,
                  size_t workspace_bytes, void* cuda_stream) {
+  IXK_API_RANGE("ixk_gemm_fp8");
   return ixk::run(desc, a, b, c, bias, d, /*fp8_call=*/true, inv_scale_a, inv_scale_b, workspace, workspace_bytes,
                   cuda_stream);
 }
@@ -379,6 +383,7 @@ int ixk_gemm_fp8(const ixk_gemm_desc* desc, const void* a, const void* b, const 
 int ixk_gemm_qkv(int dtype, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, const void* b,
                  int64_t ldb, const void* bias, void* out0, void* out1, void* out2, int64_t ldc,
                  void* cuda_stream) {
+  IXK_API_RANGE("ixk_gemm_qkv");
   return ixk::run_qkv(dtype, m, n, k, a, lda, b, ldb, bias, out0, out1, out2, ldc, cuda_stream);
 }
 

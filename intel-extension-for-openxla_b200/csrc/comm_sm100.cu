@@ -548,22 +548,26 @@ extern "C" {
 
 int ixk_all_reduce_scattered(ixk_comm* c, int dtype, size_t slots_offset, const void* x, const void* bias,
                              size_t out_offset, int64_t rows, int64_t cols, void* cuda_stream) {
+  IXK_API_RANGE("ixk_all_reduce_scattered");
   ixk::clear_error();
   return ixk::comm::run_scattered(c, dtype, slots_offset, x, bias, out_offset, rows, cols, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int ixk_reduce_scatter(ixk_comm* c, int dtype, int kind, size_t in_offset, void* out, size_t count_per_rank, void* cuda_stream) {
+  IXK_API_RANGE("ixk_reduce_scatter");
   ixk::clear_error();
   return ixk::comm::run_half(c, dtype, kind, false, in_offset, out, count_per_rank, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int ixk_all_gather(ixk_comm* c, int dtype, const void* in, size_t out_offset, size_t count_per_rank, void* cuda_stream) {
+  IXK_API_RANGE("ixk_all_gather");
   ixk::clear_error();
   return ixk::comm::run_half(c, dtype, IXK_REDUCE_SUM, true, out_offset, const_cast<void*>(in), count_per_rank,
                              static_cast<cudaStream_t>(cuda_stream));
 }
 
 int ixk_comm_create(int rank, int world, size_t buffer_bytes, ixk_comm** comm, void* handle_out) {
+  IXK_API_RANGE("ixk_comm_create");
   ixk::clear_error();
   if (comm == nullptr) return ixk::fail(IXK_INVALID_ARGUMENT, "comm is NULL");
   *comm = nullptr;
@@ -604,6 +608,7 @@ int ixk_comm_create(int rank, int world, size_t buffer_bytes, ixk_comm** comm, v
 }
 
 int ixk_comm_connect_ipc(ixk_comm* c, const void* handles) {
+  IXK_API_RANGE("ixk_comm_connect_ipc");
   ixk::clear_error();
   if (c == nullptr || handles == nullptr) return ixk::fail(IXK_INVALID_ARGUMENT, "comm or handles is NULL");
   if (c->connected) return ixk::fail(IXK_INVALID_ARGUMENT, "already connected");
@@ -625,6 +630,7 @@ int ixk_comm_connect_ipc(ixk_comm* c, const void* handles) {
 }
 
 int ixk_comm_connect_pointers(ixk_comm* c, void* const* peer_bases) {
+  IXK_API_RANGE("ixk_comm_connect_pointers");
   ixk::clear_error();
   if (c == nullptr || peer_bases == nullptr) return ixk::fail(IXK_INVALID_ARGUMENT, "comm or peer_bases is NULL");
   if (c->connected) return ixk::fail(IXK_INVALID_ARGUMENT, "already connected");
@@ -649,6 +655,7 @@ int ixk_comm_set_wait_limit(ixk_comm* c, long long cycles) {
 }
 
 int ixk_comm_destroy(ixk_comm* c) {
+  IXK_API_RANGE("ixk_comm_destroy");
   ixk::clear_error();
   if (c == nullptr) return IXK_OK;
   cudaError_t first = cudaSuccess;
@@ -671,12 +678,14 @@ int ixk_comm_destroy(ixk_comm* c) {
 }
 
 int ixk_all_reduce(ixk_comm* c, int dtype, int kind, size_t in_offset, void* out, size_t count, void* cuda_stream) {
+  IXK_API_RANGE("ixk_all_reduce");
   ixk::clear_error();
   return ixk::comm::run(c, dtype, kind, in_offset, nullptr, nullptr, 0, out, count, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int ixk_all_reduce_residual(ixk_comm* c, int dtype, size_t in_offset, const void* x, const void* bias, void* out,
                             int64_t rows, int64_t cols, void* cuda_stream) {
+  IXK_API_RANGE("ixk_all_reduce_residual");
   ixk::clear_error();
   if (x == nullptr) return ixk::fail(IXK_INVALID_ARGUMENT, "x is NULL");
   if (rows < 0 || cols < 0) return ixk::fail(IXK_INVALID_ARGUMENT, "negative size");

@@ -146,40 +146,39 @@ __device__ __forceinline__ float2 unpack16(uint32_t w, int is_bf16) {
   return __half22float2(*reinterpret_cast<const __half2*>(&w));
 }
 
-// One warp per (batch, head, padded query row), four rows in flight per warp; a lane takes 8 head
-// elements (16 bytes) of O and dO and one float4 per 128 floats of the accumulator row.
+// One warp per group of four consecutive padded query rows of one (batch, head) (the padded row
+// count is a multiple of 128, so a group never straddles two heads): a lane takes 8 head elements
+// (16 bytes) of O and dO and one float4 per 128 floats of each accumulator row.  The row -> (batch,
+// head, query) arithmetic is done once per group: with one 64-bit division chain per ROW the
+// kernel was bound by instruction issue (about 400 instructions per row) at 2.5 TB/s.
 __global__ void bwd_prepare_kernel(const PrepArgs a) {
   constexpr int kRows = 4;
   const int lane = threadIdx.x & 31;
-  const int64_t rows = static_cast<int64_t>(a.B) * a.N * a.f_pad;
+  const int64_t groups = static_cast<int64_t>(a.B) * a.N * (a.f_pad / kRows);
   const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
-  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row0 < rows;
-       row0 += warps * kRows) {
+  const int groups_per_head = a.f_pad / kRows;
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); g < groups; g += warps) {
+    const int64_t bn = g / groups_per_head;
+    const int f0 = static_cast<int>(g - bn * groups_per_head) * kRows;
+    const int n = static_cast<int>(bn % a.N), b = static_cast<int>(bn / a.N);
+    const int64_t row0 = bn * a.f_pad + f0;
+    const uint16_t* o_base = a.out + b * a.o_strides[0] + n * a.o_strides[1] + lane * 8;
+    const uint16_t* g_base = a.grad_out + b * a.do_strides[0] + n * a.do_strides[1] + lane * 8;
     uint4 ow[kRows], gw[kRows];
-    bool live[kRows];
 #pragma unroll
     for (int r = 0; r < kRows; ++r) {
-      const int64_t row = row0 + r * warps;
       ow[r] = gw[r] = make_uint4(0u, 0u, 0u, 0u);
-      live[r] = false;
-      if (row < rows) {
-        const int f = static_cast<int>(row % a.f_pad);
-        const int64_t bn = row / a.f_pad;
-        const int n = static_cast<int>(bn % a.N), b = static_cast<int>(bn / a.N);
-        live[r] = f < a.F;
-        if (live[r] && lane * 8 < a.H) {      // head sizes up to 256 fit one 16-byte load per lane
-          ow[r] = *reinterpret_cast<const uint4*>(a.out + b * a.o_strides[0] + n * a.o_strides[1] + f * a.o_strides[2] + lane * 8);
-          gw[r] = *reinterpret_cast<const uint4*>(a.grad_out + b * a.do_strides[0] + n * a.do_strides[1] +
-                                                  f * a.do_strides[2] + lane * 8);
-        }
-        float* acc = a.dq_acc + row * a.head_pad;
-        for (int h = lane * 4; h < a.head_pad; h += 128) *reinterpret_cast<float4*>(acc + h) = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (f0 + r < a.F && lane * 8 < a.H) {      // head sizes up to 256 fit one 16-byte load per lane
+        ow[r] = *reinterpret_cast<const uint4*>(o_base + static_cast<int64_t>(f0 + r) * a.o_strides[2]);
+        gw[r] = *reinterpret_cast<const uint4*>(g_base + static_cast<int64_t>(f0 + r) * a.do_strides[2]);
       }
     }
+    // the group's accumulator rows are contiguous: kRows * head_pad floats
+    float* acc = a.dq_acc + row0 * a.head_pad;
+    for (int h = lane * 4; h < kRows * a.head_pad; h += 128) *reinterpret_cast<float4*>(acc + h) = make_float4(0.f, 0.f, 0.f, 0.f);
+    float sums[kRows];
 #pragma unroll
     for (int r = 0; r < kRows; ++r) {
-      const int64_t row = row0 + r * warps;
-      if (row >= rows) break;
       const uint32_t ov[4] = {ow[r].x, ow[r].y, ow[r].z, ow[r].w}, gv[4] = {gw[r].x, gw[r].y, gw[r].z, gw[r].w};
       float sum = 0.0f;
 #pragma unroll
@@ -190,10 +189,15 @@ __global__ void bwd_prepare_kernel(const PrepArgs a) {
       }
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-      if (lane == 0) {
-        a.delta[row] = sum;
-        a.neg_lse2[row] = live[r] ? -a.lse[(row / a.f_pad) * a.F + row % a.f_pad] * kLog2e : -INFINITY;
-      }
+      sums[r] = sum;
+    }
+    if (lane < kRows) {
+      float mine = sums[0];
+#pragma unroll
+      for (int r = 1; r < kRows; ++r) mine = lane == r ? sums[r] : mine;
+      const int f = f0 + lane;
+      a.delta[row0 + lane] = mine;
+      a.neg_lse2[row0 + lane] = f < a.F ? -a.lse[bn * a.F + f] * kLog2e : -INFINITY;
     }
   }
 }
@@ -811,7 +815,7 @@ int launch_bwd(const BwdProblem& bp, const DeviceInfo& dev, void* workspace, siz
   pa.neg_lse2 = neg_lse2;
   pa.delta = delta;
   pa.dq_acc = dq_acc;
-  const int prep_grid = static_cast<int>(std::min<int64_t>((rows + 7) / 8, static_cast<int64_t>(dev.sm_count) * 8));
+  const int prep_grid = static_cast<int>(std::min<int64_t>((rows / 4 + 7) / 8, static_cast<int64_t>(dev.sm_count) * 8));
   bwd_prepare_kernel<<<prep_grid, 256, 0, stream>>>(pa);
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();

@@ -59,6 +59,7 @@ extern "C" {
 
 int ixk_fmha_fwd_static_scratch(const ixk_fmha_desc* desc, const void* q, const void* k, const void* v,
                                 const void* bias, void* out, float* lse, void* cuda_stream) {
+  IXK_API_RANGE("ixk_fmha_fwd_static_scratch");
   ixk::clear_error();
   if (desc == nullptr) return ixk::fail(IXK_INVALID_ARGUMENT, "desc is NULL");
   const size_t need = ixk_fmha_fwd_workspace_bytes(desc);

@@ -274,11 +274,13 @@ static int row_norm_impl(int dtype, int kind, int64_t rows, int64_t cols, const 
 
 int ixk_row_norm(int dtype, int kind, int64_t rows, int64_t cols, const void* x, int64_t ldx, void* y, int64_t ldy,
                  float eps, void* stream) {
+  IXK_API_RANGE("ixk_row_norm");
   return row_norm_impl(dtype, kind, rows, cols, x, ldx, y, ldy, eps, nullptr, 0.0f, stream);
 }
 
 int ixk_row_norm_gain(int dtype, int kind, int64_t rows, int64_t cols, const void* x, int64_t ldx, const void* gain,
                       float gain_offset, void* y, int64_t ldy, float eps, void* stream) {
+  IXK_API_RANGE("ixk_row_norm_gain");
   if (gain == nullptr) {
     clear_error();
     return fail(IXK_INVALID_ARGUMENT, "row_norm: gain is NULL");
@@ -327,17 +329,20 @@ static int rotary_impl(bool half_split, int dtype, void* x, int64_t tokens, int6
 int ixk_rotary_interleaved(int dtype, void* x, int64_t tokens, int64_t seq_len, int64_t heads, int64_t rotary_dim,
                            int64_t token_stride, int64_t head_stride, const float* cos_table, const float* sin_table,
                            void* stream) {
+  IXK_API_RANGE("ixk_rotary_interleaved");
   return rotary_impl(false, dtype, x, tokens, seq_len, heads, rotary_dim, token_stride, head_stride, cos_table, sin_table, stream);
 }
 
 int ixk_rotary_half(int dtype, void* x, int64_t tokens, int64_t seq_len, int64_t heads, int64_t rotary_dim,
                     int64_t token_stride, int64_t head_stride, const float* cos_table, const float* sin_table,
                     void* stream) {
+  IXK_API_RANGE("ixk_rotary_half");
   return rotary_impl(true, dtype, x, tokens, seq_len, heads, rotary_dim, token_stride, head_stride, cos_table, sin_table, stream);
 }
 
 int ixk_residual_add(int dtype, int64_t rows, int64_t cols, const void* x, const void* partial, const void* bias,
                      void* out, void* stream) {
+  IXK_API_RANGE("ixk_residual_add");
   clear_error();
   if (dtype != IXK_BF16 && dtype != IXK_F16) return fail(IXK_UNIMPLEMENTED, "residual_add: dtype must be BF16 or F16");
   if (rows < 0 || cols <= 0 || (rows > 0 && (x == nullptr || partial == nullptr || out == nullptr)))

@@ -1,6 +1,9 @@
 #include "host_common.h"
 
+#include <nvtx3/nvToolsExt.h>
+
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 namespace ixk {
@@ -40,6 +43,22 @@ int fail(int code, const std::string& msg) {
 }
 void clear_error() { tl_last_error.clear(); }
 void count_launch(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+namespace {
+bool nvtx_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("IXK_NVTX");
+    return e != nullptr && e[0] != '\0' && e[0] != '0';
+  }();
+  return on;
+}
+}  // namespace
+ApiRange::ApiRange(const char* name) : on(nvtx_enabled()) {
+  if (on) nvtxRangePushA(name);
+}
+ApiRange::~ApiRange() {
+  if (on) nvtxRangePop();
+}
 
 int get_device_info(DeviceInfo* info) {
   int dev = -1;
@@ -126,6 +145,7 @@ const char* ixk_last_error(void) { return ixk::tl_last_error.c_str(); }
 const char* ixk_version(void) { return "0.1.0"; }
 
 int ixk_device_status(int* status_word) {
+  IXK_API_RANGE("ixk_device_status");
   ixk::clear_error();
   if (status_word == nullptr) return ixk::fail(IXK_INVALID_ARGUMENT, "status_word is NULL");
   ixk::DeviceInfo dev;

@@ -38,6 +38,18 @@ int get_device_info(DeviceInfo* info);
 
 void count_launch(uint64_t n = 1);
 
+// A named NVTX range around an entry point, for timelines of a host program that calls the library
+// (the reference marks its thunks through its profiler plug-in instead).  Off unless the
+// environment has IXK_NVTX=1 when the library is first used; costs one branch when off.
+struct ApiRange {
+  explicit ApiRange(const char* name);
+  ~ApiRange();
+  ApiRange(const ApiRange&) = delete;
+  ApiRange& operator=(const ApiRange&) = delete;
+  bool on;
+};
+#define IXK_API_RANGE(name) ::ixk::ApiRange ixk_api_range_(name)
+
 // 2-D .. 4-D tiled tensor map with 128-byte swizzle (or none when box_inner_bytes < 128 is
 // impossible to swizzle).  dims/strides innermost first; strides[0] is implied (= elem size),
 // strides_bytes[i] is the pitch of dimension i+1.
