@@ -414,7 +414,11 @@ int ixk_all_gather(ixk_comm* comm, int dtype, const void* in, size_t out_offset,
  * call has completed there, each rank holds the whole [rows, cols] result: the bits of ixk_gemm +
  * ixk_all_reduce + ixk_residual_add.  x ([rows, cols] dense) and bias are local; slots and result
  * must not overlap.  Ordering rules and time-outs as for ixk_all_reduce; the next
- * ixk_gemm_scatter on the same slots may be issued right after it on the same stream. */
+ * ixk_gemm_scatter on the same slots may be issued right after it on the same stream.
+ * The scattered stores arrive in the peers' slots without any handshake: from the moment a peer
+ * may reach its ixk_gemm_scatter, nothing else on this rank may still use the slot range (the pair
+ * of calls itself is safe back to back, because ixk_all_reduce_scattered returns only when every
+ * rank has read its slots; a range that other calls used before needs the ranks to meet first). */
 int ixk_gemm_scatter(ixk_comm* comm, const ixk_gemm_desc* desc, const void* a, const void* b,
                      const void* c, const void* bias, size_t slots_offset, void* cuda_stream);
 int ixk_all_reduce_scattered(ixk_comm* comm, int dtype, size_t slots_offset, const void* x,

@@ -108,7 +108,16 @@ def _worker(rank, world, port, q):
         w2 = layers.GptJLayerWeights.shard({k_: v_.to(dev) for k_, v_ in full2.items()}, 16, 128, rot, rank, world)
         x2 = (torch.randn(B2, S2, hidden2, generator=torch.Generator().manual_seed(6)) * 0.5).bfloat16().to(dev)
         y_unfused = layers.gptj_layer_prefill(x2, w2, layers.KernelOps(pkg), comm=comm).clone()
+        # The scattered stores of the fused form land in the peers' buffers with no handshake (that is
+        # the point), in the range the unfused step above still reads after its exchange: the ranks
+        # meet before the range changes hands.  Steps of one form need no such meeting.
+        torch.cuda.synchronize()
+        dist.barrier()
         y_fused = layers.gptj_layer_prefill(x2, w2, layers.KernelOps(pkg), comm=comm, fused_exchange=True).clone()
+        y_fused2 = layers.gptj_layer_prefill(x2, w2, layers.KernelOps(pkg), comm=comm, fused_exchange=True).clone()
+        torch.cuda.synchronize()
+        dist.barrier()
+        checks["gptj_fused_exchange_twice_in_a_row"] = torch.equal(y_fused, y_fused2)
         torch.cuda.synchronize()
         checks["gptj_fused_exchange_equals_unfused"] = torch.equal(y_unfused, y_fused)
         checks["gptj_fused_exchange_finite"] = bool(torch.isfinite(y_fused.float()).all())
