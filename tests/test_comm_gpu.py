@@ -241,6 +241,96 @@ def test_projection_scattered_into_the_owners_slots_then_reduced_two_ranks_witho
         b.close()
 
 
+def test_eight_ranks_on_one_device_without_any_wait(pkg, cuda):
+    """The widest communicator (8 ranks: the unrolled kernels, the slice and slot arithmetic, eight
+    output tensor maps of the scattered projection), as eight communicators on one device run one
+    after the other with every flag written from the host beforehand, so that no kernel waits."""
+    world = 8
+    M, N, K = 2048, 2560, 256                       # 8 x 10 tiles of 256 x 256: the CTA-pair kernel; 256 rows per rank
+    slots_off, out_off = 0, M * N * 2
+    ranks = [RawComm(pkg, r, world, 2 * M * N * 2, cuda) for r in range(world)]
+    try:
+        for c in ranks:
+            c.connect(ranks)
+        stream = torch.cuda.current_stream().cuda_stream
+        k = pkg._TORCH_TO_IXK[torch.bfloat16]
+        g = torch.Generator(device="cuda").manual_seed(8)
+
+        def preset():
+            """Every CTA slot of every rank finds every peer at the generation it is about to use
+            (one more than the slot's own counter, which sits behind the flags in the header; the
+            ranks have made the same calls, so their counters agree)."""
+            for c in ranks:
+                counters = c.mem[2 * MAX_BLOCKS * MAX_RANKS * 4:2 * MAX_BLOCKS * MAX_RANKS * 4 + MAX_BLOCKS * 4].view(torch.int32)
+                c.flags[:, :, :] = (counters + 1)[None, :, None]
+            torch.cuda.synchronize()
+
+        def in_rank_order(parts):                    # fp32 sum in rank order, rounded once: what the kernels compute
+            acc = parts[0].float()
+            for p_ in parts[1:]:
+                acc = acc + p_.float()
+            return acc
+
+        # one-shot (a decode step's partial) with the residual epilogue, and the plain sum to a private buffer
+        rows, cols = 64, 3072
+        parts = [torch.randn(rows, cols, generator=g, device=cuda).bfloat16() for _ in range(world)]
+        x = torch.randn(rows, cols, generator=g, device=cuda).bfloat16()
+        for c, p_ in zip(ranks, parts):
+            c.view(0, rows * cols, torch.bfloat16).copy_(p_.flatten())
+        total = in_rank_order(parts).bfloat16()
+        preset()
+        for c in ranks:
+            got = torch.empty_like(x)
+            assert c.lib.ixk_all_reduce_residual(c.h, k, 0, x.data_ptr(), None, got.data_ptr(), rows, cols, stream) == pkg.IXK_OK
+            torch.cuda.synchronize()
+            assert torch.equal(got, (x.float() + total.float()).bfloat16()), f"one-shot, rank {c.rank}"
+        # two-shot, in place: rank r reduces slice r and writes it into every rank's buffer
+        n = 3 * 1024 * 1024 + 8 * 5                  # the last rank's slice is longer than the others'
+        big = [torch.randint(-20, 20, (n,), generator=g, device=cuda).bfloat16() for _ in range(world)]
+        for c, p_ in zip(ranks, big):
+            c.view(0, n, torch.bfloat16).copy_(p_)
+        preset()
+        for c in ranks:
+            assert c.all_reduce(torch.bfloat16, 0, c.view(0, n, torch.bfloat16), n) == pkg.IXK_OK
+            torch.cuda.synchronize()
+        want = in_rank_order(big).bfloat16()
+        for c in ranks:
+            assert torch.equal(c.view(0, n, torch.bfloat16), want), f"two-shot, rank {c.rank}"
+        assert pkg.device_status() == 0
+
+        # the projection scattered over eight owners, then the second half with bias and residual
+        lhs = [torch.randn(M, K, generator=g, device=cuda).bfloat16() for _ in range(world)]
+        rhs = [(torch.randn(K, N, generator=g, device=cuda) * 0.06).bfloat16() for _ in range(world)]
+        xr = torch.randn(M, N, generator=g, device=cuda).bfloat16()
+        bias = torch.randn(N, generator=g, device=cuda).bfloat16()
+        for c in ranks:
+            c.data.zero_()
+        for c in ranks:
+            attrs = pkg.gemm_attrs_for(lhs[c.rank], rhs[c.rank], torch.empty((M, N), device="meta", dtype=torch.bfloat16))
+            d = pkg.gemm_desc_from_attrs(attrs, "DEFAULT")
+            assert c.lib.ixk_gemm_scatter(c.h, ctypes.byref(d), lhs[c.rank].data_ptr(), rhs[c.rank].data_ptr(), None, None,
+                                          slots_off, stream) == pkg.IXK_OK, c.lib.ixk_last_error().decode()
+        torch.cuda.synchronize()
+        part = [pkg.gemm(lhs[r], rhs[r]) for r in range(world)]
+        per = M // world
+        for o, c in enumerate(ranks):                # rank o's slot s = rows [o * per, (o + 1) * per) of rank s's partial
+            for src in (0, 3, 7):
+                slot = c.view(slots_off + src * per * N * 2, per * N, torch.bfloat16).view(per, N)
+                assert torch.equal(slot, part[src][o * per:(o + 1) * per]), f"slot {src} of rank {o}"
+        want = pkg.residual_add(xr, in_rank_order(part).bfloat16(), bias)
+        preset()
+        for c in ranks:
+            assert c.lib.ixk_all_reduce_scattered(c.h, k, slots_off, xr.data_ptr(), bias.data_ptr(), out_off, M, N,
+                                                  stream) == pkg.IXK_OK, c.lib.ixk_last_error().decode()
+            torch.cuda.synchronize()
+        for c in ranks:
+            assert torch.equal(c.view(out_off, M * N, torch.bfloat16).view(M, N), want), f"scattered, rank {c.rank}"
+        assert pkg.device_status() == 0
+    finally:
+        for c in ranks:
+            c.close()
+
+
 def test_a_peer_that_never_arrives_ends_in_a_timeout_status(pkg, cuda):
     """The wait for a peer is bounded: with nobody on the other side the kernel gives up after its
     cycle budget, reports where, and leaves the device usable."""
