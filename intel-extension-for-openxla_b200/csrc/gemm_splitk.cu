@@ -51,20 +51,51 @@ struct ReduceArgs {
   float beta;
 };
 
+__device__ __forceinline__ void reduce_epilogue_store(const ReduceArgs& a, int m, int n, float v) {
+  if (a.bias != nullptr) v += load_as_f32(a.bias, n, a.bias_dtype);
+  if (a.c != nullptr) v = fmaf(a.beta, load_as_f32(a.c, static_cast<int64_t>(m) * a.ldc + n, a.out_dtype), v);
+  if (a.act == kActRelu) v = fmaxf(v, 0.0f);
+  if (a.act == kActGelu) v = gelu_tanh_f(v);
+  store_from_f32(a.d, static_cast<int64_t>(m) * a.ldd + n, a.out_dtype, v);
+}
+
+// A thread sums four consecutive columns of one row over the chunks, in chunk order, with the
+// loads of all chunks in flight together (kVec: N is a multiple of 4, so the partial planes can be
+// read 16 bytes at a time); otherwise one element per thread.
+template <bool kVec>
 __global__ void splitk_reduce_kernel(const ReduceArgs a) {
-  const int64_t total = static_cast<int64_t>(a.M) * a.N;
-  const int64_t plane = total;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+  const int64_t plane = static_cast<int64_t>(a.M) * a.N;
+  if (kVec) {
+    const int64_t total = plane / 4;
+    const int n4 = a.N / 4;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+      const int m = static_cast<int>(i / n4);
+      const int n = static_cast<int>(i - static_cast<int64_t>(m) * n4) * 4;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4* src = reinterpret_cast<const float4*>(a.partial) + i;
+#pragma unroll 4
+      for (int s = 0; s < a.splits; ++s) {
+        const float4 v = __ldg(src + s * (plane / 4));
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+      }
+      reduce_epilogue_store(a, m, n, acc.x);
+      reduce_epilogue_store(a, m, n + 1, acc.y);
+      reduce_epilogue_store(a, m, n + 2, acc.z);
+      reduce_epilogue_store(a, m, n + 3, acc.w);
+    }
+    return;
+  }
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < plane;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int m = static_cast<int>(i / a.N);
     const int n = static_cast<int>(i - static_cast<int64_t>(m) * a.N);
     float v = 0.0f;
     for (int s = 0; s < a.splits; ++s) v += a.partial[s * plane + i];
-    if (a.bias != nullptr) v += load_as_f32(a.bias, n, a.bias_dtype);
-    if (a.c != nullptr) v = fmaf(a.beta, load_as_f32(a.c, static_cast<int64_t>(m) * a.ldc + n, a.out_dtype), v);
-    if (a.act == kActRelu) v = fmaxf(v, 0.0f);
-    if (a.act == kActGelu) v = gelu_tanh_f(v);
-    store_from_f32(a.d, static_cast<int64_t>(m) * a.ldd + n, a.out_dtype, v);
+    reduce_epilogue_store(a, m, n, v);
   }
 }
 
@@ -118,11 +149,13 @@ int launch_split_k(const Problem& p, int splits, void* workspace, const DeviceIn
   r.bias_dtype = p.bias_dtype;
   r.act = p.act;
   r.beta = p.beta;
-  const int64_t total = p.M * p.N;
+  const bool vec = p.N % 4 == 0 && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0;
+  const int64_t total = vec ? p.M * p.N / 4 : p.M * p.N;
   const int threads = 256;
   int64_t blocks = (total + threads - 1) / threads;
-  if (blocks > 4 * dev.sm_count) blocks = 4 * dev.sm_count;
-  splitk_reduce_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(r);
+  if (blocks > 8 * dev.sm_count) blocks = 8 * dev.sm_count;
+  if (vec) splitk_reduce_kernel<true><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(r);
+  else splitk_reduce_kernel<false><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(r);
   IXK_CUDA_OK(cudaGetLastError());
   count_launch();
   return IXK_OK;
