@@ -104,12 +104,27 @@ __global__ void splitk_reduce_kernel(const ReduceArgs a) {
 int split_k_factor(int64_t M, int64_t N, int64_t K, int64_t batch, bool fp8) {
   if (batch != 1 || M > 128 || fp8) return 1;
   const int64_t tiles = (N + 127) / 128;  // one row of 128 x 128 tiles
-  int64_t want = (5 * kAssumedSms / 2 + tiles - 1) / tiles;  // ~2.5 work units per SM
-  const int64_t cap = K / kMinChunk;
-  if (want > cap) want = cap;
-  // every chunk must be a whole number of pipeline slabs so that no chunk reads into the next
-  while (want > 1 && K % (want * kSlabElems16) != 0) --want;
-  return want < 2 ? 1 : static_cast<int>(want);
+  if (K % kSlabElems16 != 0) return 1;
+  // One CTA per SM at this kernel's shared-memory size, so tiles x chunks run in waves of the SM
+  // count: pick the chunk count whose last wave is fullest, charging every further wave for the
+  // CTAs' fixed part (set-up, pipeline fill, epilogue).  Every chunk is a whole number of pipeline
+  // slabs (no chunk reads into the next) of at least kMinChunk elements; at most four waves.
+  auto score = [&](int64_t ctas) {
+    const int64_t waves = (ctas + kAssumedSms - 1) / kAssumedSms;
+    return static_cast<double>(ctas) / static_cast<double>(waves * kAssumedSms) - 0.04 * static_cast<double>(waves - 1);
+  };
+  int best = 1;
+  double best_score = score(tiles);
+  for (int s = 2; s <= 16; ++s) {
+    if (K % (static_cast<int64_t>(s) * kSlabElems16) != 0 || K / s < kMinChunk) continue;
+    const int64_t ctas = tiles * s;
+    if ((ctas + kAssumedSms - 1) / kAssumedSms > 4) continue;
+    if (score(ctas) >= best_score - 1e-9) {
+      best = s;
+      best_score = score(ctas);
+    }
+  }
+  return best;
 }
 
 size_t split_k_workspace_bytes(int64_t M, int64_t N, int splits) {
