@@ -65,7 +65,7 @@ __device__ __forceinline__ void reduce_epilogue_store(const ReduceArgs& a, int m
 template <bool kVec>
 __global__ void splitk_reduce_kernel(const ReduceArgs a) {
   const int64_t plane = static_cast<int64_t>(a.M) * a.N;
-  if (kVec) {
+  if constexpr (kVec) {
     const int64_t total = plane / 4;
     const int n4 = a.N / 4;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -87,15 +87,15 @@ __global__ void splitk_reduce_kernel(const ReduceArgs a) {
       reduce_epilogue_store(a, m, n + 2, acc.z);
       reduce_epilogue_store(a, m, n + 3, acc.w);
     }
-    return;
-  }
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < plane;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int m = static_cast<int>(i / a.N);
-    const int n = static_cast<int>(i - static_cast<int64_t>(m) * a.N);
-    float v = 0.0f;
-    for (int s = 0; s < a.splits; ++s) v += a.partial[s * plane + i];
-    reduce_epilogue_store(a, m, n, v);
+  } else {
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < plane;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+      const int m = static_cast<int>(i / a.N);
+      const int n = static_cast<int>(i - static_cast<int64_t>(m) * a.N);
+      float v = 0.0f;
+      for (int s = 0; s < a.splits; ++s) v += a.partial[s * plane + i];
+      reduce_epilogue_store(a, m, n, v);
+    }
   }
 }
 
