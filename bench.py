@@ -843,7 +843,7 @@ def run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=Tru
 
     def warm_up_and_check():
         """Warm-up steps, then (N > 1) the sharded result against the un-sharded layer and the device
-        status word; the verdict is the same on every rank."""
+        status word; the outcome is the same on every rank."""
         for _ in range(args.warmup):
             out = step()
             flush_l2(flush_buf)
