@@ -782,6 +782,7 @@ def run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=Tru
     comm, comm_note = None, None
     if world > 1 and not args.nccl:
         nbytes = 2 * 4 * 2048 * 4096 * 2 if args.workload == "gptj_layer" else 1 << 20   # GPT-J: the slots + the result
+        nbytes += 4096                                  # + the slot of the per-step alignment exchange (see the timed loop)
         try:
             comm = comm_mod.Communicator(pkg, rank, world, nbytes)
         except Exception as ex:  # noqa: BLE001 - e.g. CUDA IPC not permitted between the ranks' containers
@@ -946,14 +947,31 @@ def run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=Tru
     n0 = pkg.launch_count()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    # N > 1: the L2 flush between steps takes a slightly different time on every GPU, and a rank that
+    # is through earlier would otherwise spend the difference waiting inside its step's first
+    # exchange, i.e. inside its timed region.  A tiny exchange after the flush lines the ranks up
+    # before the start event; it is not part of the step and not timed.
+    if world > 1:
+        if comm is not None:
+            align_slot = comm.view(comm.buffer_bytes - 4096, (1024,), torch.float32)
+            align_slot.zero_()
+            align_out = torch.empty(1024, dtype=torch.float32, device=dev)
+            align = lambda: comm.all_reduce(align_slot, out=align_out)
+        else:
+            align_t = torch.zeros(1024, device=dev)
+            align = lambda: dist.all_reduce(align_t)
+        barrier()
+    else:
+        align = lambda: None
     with ClockSampler(local) as clk:
         for i in range(args.steps):
             flush_l2(flush_buf)      # first, so that the host enqueues the step while the flush runs
+            align()
             starts[i].record()
             y = step()
             ends[i].record()
         torch.cuda.synchronize()
-    launches = pkg.launch_count() - n0
+    launches = pkg.launch_count() - n0 - (args.steps if (world > 1 and comm is not None) else 0)   # without the alignment launches
     if launches_per_step is not None:
         launches = launches_per_step * args.steps   # replayed from the graph
     total_ms = float(sum(s.elapsed_time(e) for s, e in zip(starts, ends)))
