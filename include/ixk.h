@@ -321,6 +321,16 @@ int ixk_rotary_half(int dtype, void* x, int64_t tokens, int64_t seq_len,
                            int64_t heads, int64_t rotary_dim, int64_t token_stride,
                            int64_t head_stride, const float* cos_table,
                            const float* sin_table, void* cuda_stream);
+/* This step's keys and values into a KV cache, both tensors in one launch (the slice_update of
+ * the reference's Gemma example, example/gemma/keras_nlp.patch:15-17, which XLA compiles as a
+ * dynamic-update-slice): cache[b, position, n, :] = new[b, n, :].  Strides in elements (the
+ * cache's token stride lets [B,T,N,H] and [B,N,T,H] caches both work); the same strides for K and
+ * V.  k_new / v_new may be slices of a fused QKV projection. */
+int ixk_kv_append(int dtype, int64_t batch, int64_t heads, int64_t head_dim, const void* k_new,
+                  const void* v_new, int64_t new_batch_stride, int64_t new_head_stride,
+                  void* k_cache, void* v_cache, int64_t cache_batch_stride,
+                  int64_t cache_token_stride, int64_t cache_head_stride, int64_t position,
+                  void* cuda_stream);
 /* out = x + partial                      (bias NULL)
  * out = x + round(partial + bias[col])   (bias given; the inner sum is rounded
  * to dtype before the residual add).  All [rows, cols] dense; out may alias x

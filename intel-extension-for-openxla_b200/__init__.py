@@ -110,6 +110,8 @@ ABI_SYMBOLS = {
                                          _vp, ctypes.c_float, _vp, ctypes.c_int64, ctypes.c_float, _vp]),
     "ixk_rotary_half": (ctypes.c_int, [ctypes.c_int, _vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                        ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp, _vp, _vp]),
+    "ixk_kv_append": (ctypes.c_int, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp, _vp, ctypes.c_int64,
+                                     ctypes.c_int64, _vp, _vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp]),
     "ixk_residual_add": (ctypes.c_int, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, _vp, _vp, _vp, _vp, _vp]),
     "ixk_fmha_fwd_workspace_bytes": (_sz, [ctypes.POINTER(_FmhaDesc)]),
     "ixk_fmha_fwd_static_scratch": (ctypes.c_int, [ctypes.POINTER(_FmhaDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
@@ -415,6 +417,22 @@ def rotary_interleaved_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, s
 def rotary_half_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_len: int, rotary_dim: int, stream=None):
     """The half-split convention of the Gemma family: see rotary_interleaved_."""
     return rotary_interleaved_(x, cos, sin, seq_len, rotary_dim, stream, half_split=True)
+
+
+def kv_append_(k_cache: torch.Tensor, v_cache: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, position: int,
+               stream=None) -> None:
+    """k_cache / v_cache [B, T, heads, head_dim] (any strides with unit element stride, the same for
+    both): cache[:, position] = new, new [B, heads, head_dim] views (e.g. slices of a fused QKV
+    projection), both tensors in one launch."""
+    B, T, N, H = k_cache.shape
+    if v_cache.shape != k_cache.shape or v_cache.stride() != k_cache.stride() or k_new.shape != (B, N, H) or \
+            v_new.shape != (B, N, H) or k_new.stride() != v_new.stride() or k_cache.stride(3) != 1 or k_new.stride(2) != 1:
+        raise IxkError(IXK_INVALID_ARGUMENT, "caches [B,T,N,H] and new rows [B,N,H] of matching shapes and strides are expected")
+    if not 0 <= position < T:
+        raise IxkError(IXK_INVALID_ARGUMENT, "position outside the cache")
+    _check(load_library().ixk_kv_append(_TORCH_TO_IXK[k_cache.dtype], B, N, H, k_new.data_ptr(), v_new.data_ptr(),
+                                        k_new.stride(0), k_new.stride(1), k_cache.data_ptr(), v_cache.data_ptr(),
+                                        k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), position, _stream_ptr(stream)))
 
 
 def residual_add(x: torch.Tensor, partial: torch.Tensor, bias: Optional[torch.Tensor] = None,

@@ -193,6 +193,27 @@ __global__ void rotary_half_kernel(uint4* __restrict__ x, const float4* __restri
   }
 }
 
+// This step's keys and values into the cache (the dynamic-update-slice of a decode step): one
+// thread per 16-byte vector of one (batch, head) row of K or V.
+__global__ void kv_append_kernel(const uint4* __restrict__ k_new, const uint4* __restrict__ v_new, uint4* __restrict__ k_cache,
+                                 uint4* __restrict__ v_cache, int64_t total_vecs, int vecs_per_head, int heads,
+                                 int64_t new_batch_vec, int64_t new_head_vec, int64_t cache_batch_vec, int64_t cache_head_vec,
+                                 int64_t cache_offset_vec) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < 2 * total_vecs;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const bool is_v = i >= total_vecs;
+    const int64_t j = is_v ? i - total_vecs : i;
+    const int vec = static_cast<int>(j % vecs_per_head);
+    const int64_t bh = j / vecs_per_head;
+    const int head = static_cast<int>(bh % heads);
+    const int64_t b = bh / heads;
+    const int64_t src = b * new_batch_vec + head * new_head_vec + vec;
+    const int64_t dst = cache_offset_vec + b * cache_batch_vec + head * cache_head_vec + vec;
+    if (is_v) v_cache[dst] = v_new[src];
+    else k_cache[dst] = k_new[src];
+  }
+}
+
 // out = x + round(partial + bias): the sum with the bias is rounded to the storage type first,
 // like a framework that materialises (partial + bias) before the residual add.
 template <bool kBf16>
@@ -338,6 +359,36 @@ int ixk_rotary_half(int dtype, void* x, int64_t tokens, int64_t seq_len, int64_t
                     void* stream) {
   IXK_API_RANGE("ixk_rotary_half");
   return rotary_impl(true, dtype, x, tokens, seq_len, heads, rotary_dim, token_stride, head_stride, cos_table, sin_table, stream);
+}
+
+int ixk_kv_append(int dtype, int64_t batch, int64_t heads, int64_t head_dim, const void* k_new, const void* v_new,
+                  int64_t new_batch_stride, int64_t new_head_stride, void* k_cache, void* v_cache, int64_t cache_batch_stride,
+                  int64_t cache_token_stride, int64_t cache_head_stride, int64_t position, void* stream) {
+  IXK_API_RANGE("ixk_kv_append");
+  clear_error();
+  if (dtype != IXK_BF16 && dtype != IXK_F16) return fail(IXK_UNIMPLEMENTED, "kv_append: dtype must be BF16 or F16");
+  if (batch < 0 || heads <= 0 || head_dim <= 0 || position < 0 ||
+      (batch > 0 && (k_new == nullptr || v_new == nullptr || k_cache == nullptr || v_cache == nullptr)))
+    return fail(IXK_INVALID_ARGUMENT, "kv_append: null or negative argument");
+  if (head_dim % glue::kVecElems || new_batch_stride % glue::kVecElems || new_head_stride % glue::kVecElems ||
+      cache_batch_stride % glue::kVecElems || cache_token_stride % glue::kVecElems || cache_head_stride % glue::kVecElems ||
+      new_head_stride < head_dim || cache_head_stride < head_dim || !glue::aligned16(k_new) || !glue::aligned16(v_new) ||
+      !glue::aligned16(k_cache) || !glue::aligned16(v_cache))
+    return fail(IXK_INVALID_ARGUMENT, "kv_append: head_dim and strides must be multiples of 8 elements, pointers 16-byte aligned");
+  DeviceInfo info;
+  if (int st = get_device_info(&info)) return st;
+  const int vph = static_cast<int>(head_dim / glue::kVecElems);
+  const int64_t total = batch * heads * vph;
+  if (total == 0) return IXK_OK;
+  const int grid = glue::elementwise_grid(2 * total, 256, info.sm_count);
+  glue::kv_append_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(k_new), static_cast<const uint4*>(v_new), static_cast<uint4*>(k_cache),
+      static_cast<uint4*>(v_cache), total, vph, static_cast<int>(heads), new_batch_stride / glue::kVecElems,
+      new_head_stride / glue::kVecElems, cache_batch_stride / glue::kVecElems, cache_head_stride / glue::kVecElems,
+      position * (cache_token_stride / glue::kVecElems));
+  IXK_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return IXK_OK;
 }
 
 int ixk_residual_add(int dtype, int64_t rows, int64_t cols, const void* x, const void* partial, const void* bias,

@@ -58,6 +58,9 @@ class KernelOps:
     def residual_add(self, x, partial, bias=None, out=None):
         return self.pkg.residual_add(x, partial, bias, out=out)
 
+    def kv_append_(self, k_cache, v_cache, k_new, v_new, position):
+        self.pkg.kv_append_(k_cache, v_cache, k_new, v_new, position)
+
 
 def _glue(ops, name, fallback):
     return getattr(ops, name, None) or fallback
@@ -150,6 +153,11 @@ def _rotary_qk_torch_(qkv, cos, sin, rotary_dim, half_split=False):
     fn(qkv[:, :, 0], cos, sin, rotary_dim)
     fn(qkv[:, :, 1], cos, sin, rotary_dim)
     return qkv
+
+
+def _kv_append_torch_(k_cache, v_cache, k_new, v_new, position):
+    k_cache[:, position] = k_new
+    v_cache[:, position] = v_new
 
 
 def _residual_add_torch(x, partial, bias=None, out=None):
@@ -281,8 +289,7 @@ def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tens
     qkv = ops.gemm(h, w.wqkv).view(B, 1, 3, hl, hd)
     cos, sin = rope if rope is not None else rotary_tables(torch.tensor([position], device=x.device), hd)
     _glue(ops, "rotary_qk_", _rotary_qk_torch_)(qkv, cos, sin, hd, half_split=True)
-    k_cache[:, position] = qkv[:, 0, 1]
-    v_cache[:, position] = qkv[:, 0, 2]
+    _glue(ops, "kv_append_", _kv_append_torch_)(k_cache, v_cache, qkv[:, 0, 1], qkv[:, 0, 2], position)
     T = position + 1
     q = qkv[:, :, 0].permute(0, 2, 1, 3)                                   # [B, hl, 1, hd]
     ctx = torch.empty(B, 1, hl, hd, dtype=x.dtype, device=x.device)

@@ -135,6 +135,31 @@ def test_rotary_half_split_on_fused_qkv(pkg, orc, cuda, dtype, B, S, heads, hd, 
         pkg.rotary_half_(dev.view(B * S, 3 * heads, hd), cos[:, :4].contiguous().to(cuda), sin[:, :4].contiguous().to(cuda), S, 8)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("layout", ["btnh", "bnth"])
+def test_kv_append(pkg, cuda, dtype, layout):
+    """The step's keys and values land at `position` of both caches, nothing else changes; the new
+    rows are slices of a fused QKV projection (strided views), the cache in either layout."""
+    B, T, N, H, pos = 3, 37, 4, 256, 21
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(B, 1, 3, N, H, generator=g).to(dtype).to(cuda)
+    if layout == "btnh":
+        kc, vc = (torch.randn(B, T, N, H, generator=g).to(dtype).to(cuda) for _ in range(2))
+    else:
+        kc, vc = (torch.randn(B, N, T, H, generator=g).to(dtype).to(cuda).permute(0, 2, 1, 3) for _ in range(2))
+    want_k, want_v = kc.clone(), vc.clone()
+    want_k[:, pos] = qkv[:, 0, 1]
+    want_v[:, pos] = qkv[:, 0, 2]
+    n0 = pkg.launch_count()
+    pkg.kv_append_(kc, vc, qkv[:, 0, 1], qkv[:, 0, 2], pos)
+    assert pkg.launch_count() == n0 + 1
+    assert torch.equal(kc, want_k) and torch.equal(vc, want_v)
+    with pytest.raises(pkg.IxkError):
+        pkg.kv_append_(kc, vc, qkv[:, 0, 1], qkv[:, 0, 2], T)                 # position outside the cache
+    with pytest.raises(pkg.IxkError):
+        pkg.kv_append_(kc, vc, qkv[:, 0, 1, :2], qkv[:, 0, 2, :2], pos)       # head count differs
+
+
 def test_rotary_rejections(pkg, cuda):
     x = torch.randn(8, 2, 64).bfloat16().to(cuda)
     cos = torch.ones(8, 16, device=cuda)
