@@ -882,6 +882,7 @@ def run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=Tru
         raise RuntimeError(f"tensor-parallel {args.workload} disagrees with the un-sharded layer: {tp_check} {why}")
     if world > 1:
         del y_ref
+    y_eager = y.clone()      # the checked result, to be met again by the last timed (replayed) step
     # A layer step is a fixed sequence of ~10-15 library kernels: it is captured once into a CUDA
     # graph and replayed, which removes the launch gaps (the decode step is launch-bound otherwise).
     # With libixk's all-reduce the exchange is an ordinary kernel inside that graph.  With NCCL the
@@ -975,6 +976,13 @@ def run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=Tru
     if launches_per_step is not None:
         launches = launches_per_step * args.steps   # replayed from the graph
     total_ms = float(sum(s.elapsed_time(e) for s, e in zip(starts, ends)))
+    # the steps are deterministic (fixed inputs, sums in rank order): the last timed step, launched the
+    # way the timed steps are, must reproduce the checked warm-up result bit for bit
+    same = torch.tensor([1 if torch.equal(y, y_eager) else 0], device=dev)
+    if world > 1:
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    timed_equals_checked = bool(int(same.item()))
+    del y_eager
     # end to end: host x in, host y out
     y_host = torch.empty(y.shape, dtype=y.dtype).pin_memory()
     e2e_steps = max(3, min(args.steps, 10))
@@ -1016,6 +1024,7 @@ def run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=Tru
                      "peak_source": f"{world} x {peaks['source']} single-GPU peak"},
         "device_status": status,
     }
+    line["config"]["timed_step_equals_checked_step"] = timed_equals_checked
     if tp_check is not None:
         line["tp_check"] = tp_check
     if with_cpu and rank == 0 and world == 1:
