@@ -174,6 +174,20 @@ int ixk_gemm_fp8(const ixk_gemm_desc* desc, const void* a, const void* b,
                  float inv_scale_b, void* workspace, size_t workspace_bytes,
                  void* cuda_stream);
 
+/* Gate and up projections of a GeGLU MLP in one product (the reference's Gemma example runs them
+ * as two dots, a GELU and a multiply that XLA fuses, example/gemma/keras_nlp.patch:53-63 for the
+ * block): b is [K, 2 N'] with the gate weights in the first N' columns and the up weights in the
+ * last; desc describes the [M, 2 N'] product (row-major, dense, 16-bit, DEFAULT epilogue, alpha 1,
+ * beta 0, batch 1, M <= 128: decode); out [M, N'] receives
+ *   round(gelu_tanh(gate)) * round(up)   rounded once more,
+ * the bits of a gate GEMM with the GELU epilogue, an up GEMM and an elementwise product.  The
+ * product itself (split along K where that helps) lives in the workspace, which must hold
+ * ixk_gemm_geglu_workspace_bytes(desc) bytes.  Other shapes: IXK_UNIMPLEMENTED (use the calls above). */
+int ixk_gemm_geglu(const ixk_gemm_desc* desc, const void* a, const void* b, void* out,
+                   int64_t out_leading_dim_stride, void* workspace, size_t workspace_bytes,
+                   void* cuda_stream);
+size_t ixk_gemm_geglu_workspace_bytes(const ixk_gemm_desc* desc);
+
 /* Three projections of one input (the QKV-fusion pass).  Replaces
  * XetlaQKVGemmKernel::run (xetla/gemm/gemm.h:111-171) → HGEMM_QKV_KERNEL /
  * HGEMM_QKV_BIAS_KERNEL (xetla/gemm/hgemm_impl.h:461-608):

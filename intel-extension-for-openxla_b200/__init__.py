@@ -94,6 +94,8 @@ ABI_SYMBOLS = {
     "ixk_gemm_aux": (ctypes.c_int, [ctypes.POINTER(_GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int64, _vp]),
     "ixk_ffi_select_operands": (ctypes.c_int, [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_int,
                                                ctypes.POINTER(_FfiOperands)]),
+    "ixk_gemm_geglu": (ctypes.c_int, [ctypes.POINTER(_GemmDesc), _vp, _vp, _vp, ctypes.c_int64, _vp, _sz, _vp]),
+    "ixk_gemm_geglu_workspace_bytes": (_sz, [ctypes.POINTER(_GemmDesc)]),
     "ixk_gemm_fp8": (ctypes.c_int, [ctypes.POINTER(_GemmDesc), _vp, _vp, _vp, _vp, _vp, ctypes.c_float,
                                     ctypes.c_float, _vp, _sz, _vp]),
     "ixk_gemm_qkv": (ctypes.c_int, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp, ctypes.c_int64,
@@ -315,6 +317,24 @@ def gemm(lhs: torch.Tensor, rhs: torch.Tensor, *, bias: Optional[torch.Tensor] =
         out = torch.empty(shape, device=lhs.device, dtype=out_dtype or lhs.dtype)
     attrs = gemm_attrs_for(lhs, rhs, out, beta, alpha)
     run_gemm_custom_call(lhs, rhs, c, out, bias, stream, attrs, epilogue, workspace=workspace, aux=aux)
+    return out
+
+
+def gemm_geglu(x: torch.Tensor, w_gate_up: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+               workspace: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """gelu_tanh(x @ w[:, :N']) * (x @ w[:, N':]) for x [M <= 128, K] and w [K, 2 N'] in one GEMM and one
+    combining pass (decode-time GeGLU).  `workspace`: uint8 scratch of gemm_geglu_workspace_bytes()
+    bytes (allocated here when absent)."""
+    m, n2 = x.shape[-2], w_gate_up.shape[-1]
+    if out is None:
+        out = torch.empty((m, n2 // 2), device=x.device, dtype=x.dtype)
+    d = gemm_desc_from_attrs(gemm_attrs_for(x, w_gate_up, torch.empty((m, n2), device="meta", dtype=x.dtype)), "DEFAULT")
+    lib = load_library()
+    need = int(lib.ixk_gemm_geglu_workspace_bytes(ctypes.byref(d)))
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    _check(lib.ixk_gemm_geglu(ctypes.byref(d), _ptr(x), _ptr(w_gate_up), _ptr(out), out.stride(-2), _ptr(workspace),
+                              workspace.numel() * workspace.element_size(), _stream_ptr(stream)))
     return out
 
 

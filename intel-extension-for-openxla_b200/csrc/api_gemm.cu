@@ -56,7 +56,7 @@ int check_layout(const ixk_matrix_layout& l, const char* name) {
 int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, const void* bias,
         void* d, bool fp8_call, float inv_scale_a, float inv_scale_b, void* workspace, size_t workspace_bytes,
         void* stream, void* aux = nullptr, int64_t aux_ld = 0, bool aux_call = false,
-        ixk_comm* scatter_comm = nullptr, size_t slots_offset = 0) {
+        ixk_comm* scatter_comm = nullptr, size_t slots_offset = 0, bool geglu = false, int64_t geglu_ld = 0) {
   clear_error();
   if (desc == nullptr) return fail(IXK_INVALID_ARGUMENT, "desc is NULL");
   if (desc->reserved != 0) return fail(IXK_INVALID_ARGUMENT, "desc.reserved must be 0");
@@ -224,6 +224,23 @@ int run(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c, 
     return gemm::launch(p, dev, static_cast<cudaStream_t>(stream));
   }
 
+  if (geglu) {
+    // [gate | up] halves of one product, combined by the pass that follows the GEMM
+    if (swapped || p.kind != gemm::kKindF16 || p.batch != 1 || p.M > 128 || desc->epilogue != IXK_EPILOGUE_DEFAULT ||
+        desc->beta != 0.0f || desc->alpha != 1.0f || elem_bytes(tc) != 2 || p.ldd != p.N || p.N % 16 != 0)
+      return fail(IXK_UNIMPLEMENTED, "GeGLU projection: 16-bit row-major problem with M <= 128, DEFAULT epilogue, alpha 1, "
+                                     "beta 0, a dense [M, 2 N'] product with N' a multiple of 8");
+    if (geglu_ld < p.N / 2) return fail(IXK_INVALID_ARGUMENT, "out_leading_dim_stride is smaller than N'");
+    DeviceInfo dev;
+    if ((rc = get_device_info(&dev)) != IXK_OK) return rc;
+    const int splits = gemm::split_k_factor(p.M, p.N, p.K, p.batch, p.fp8);
+    const size_t need = static_cast<size_t>(splits) * p.M * p.N * sizeof(float);
+    if (workspace == nullptr || !aligned16(workspace) || workspace_bytes < need)
+      return fail(IXK_WORKSPACE_TOO_SMALL, "GeGLU projection: need " + std::to_string(need) + " bytes of 16-byte aligned scratch");
+    p.ldd = geglu_ld;   // of the [M, N'] result; the product itself goes to the scratch
+    return gemm::launch_split_k(p, splits, workspace, dev, static_cast<cudaStream_t>(stream), true);
+  }
+
   if (const char* env = std::getenv("IXK_GEMM_BLOCK_N")) p.force_block_n = std::atoi(env);
 
   DeviceInfo dev;
@@ -370,6 +387,20 @@ int ixk_gemm_scatter(ixk_comm* comm, const ixk_gemm_desc* desc, const void* a, c
     return ixk::fail(IXK_INVALID_ARGUMENT, "comm is NULL");
   }
   return ixk::run(desc, a, b, c, bias, nullptr, false, 1.0f, 1.0f, nullptr, 0, cuda_stream, nullptr, 0, false, comm, slots_offset);
+}
+
+int ixk_gemm_geglu(const ixk_gemm_desc* desc, const void* a, const void* b, void* out, int64_t out_leading_dim_stride,
+                   void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  IXK_API_RANGE("ixk_gemm_geglu");
+  return ixk::run(desc, a, b, nullptr, nullptr, out, false, 1.0f, 1.0f, workspace, workspace_bytes, cuda_stream, nullptr, 0, false,
+                  nullptr, 0, /*geglu=*/true, out_leading_dim_stride);
+}
+
+size_t ixk_gemm_geglu_workspace_bytes(const ixk_gemm_desc* desc) {
+  if (desc == nullptr) return 0;
+  const int64_t M = desc->output.num_rows, N = desc->output.num_cols, K = desc->lhs.num_cols;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  return static_cast<size_t>(ixk::gemm::split_k_factor(M, N, K, desc->batch_size, false)) * M * N * sizeof(float);
 }
 
 int ixk_gemm_fp8(const ixk_gemm_desc* desc, const void* a, const void* b, const void* c,

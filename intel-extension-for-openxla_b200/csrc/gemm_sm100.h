@@ -77,7 +77,10 @@ int launch(const Problem& p, const DeviceInfo& dev, cudaStream_t stream);
 // takes, and the two-kernel launch (partial GEMMs as a batch, then reduce + epilogue).
 int split_k_factor(int64_t M, int64_t N, int64_t K, int64_t batch, bool fp8);
 size_t split_k_workspace_bytes(int64_t M, int64_t N, int splits);
-int launch_split_k(const Problem& p, int splits, void* workspace, const DeviceInfo& dev, cudaStream_t stream);
+// (geglu: the N columns are [gate | up]; the reduce writes gelu(gate) * up, N / 2 columns, to p.d / p.ldd;
+// splits may be 1 then: one GEMM into the scratch + the GeGLU pass)
+int launch_split_k(const Problem& p, int splits, void* workspace, const DeviceInfo& dev, cudaStream_t stream,
+                   bool geglu = false);
 
 }  // namespace gemm
 }  // namespace ixk

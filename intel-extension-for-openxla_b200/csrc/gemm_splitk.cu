@@ -49,6 +49,7 @@ struct ReduceArgs {
   int64_t ldc, ldd;
   int out_dtype, bias_dtype, act;
   float beta;
+  int geglu;   // the N columns are [gate | up] halves: out[m, n] = round(gelu(gate)) * round(up), N / 2 columns
 };
 
 __device__ __forceinline__ void reduce_epilogue_store(const ReduceArgs& a, int m, int n, float v) {
@@ -62,6 +63,40 @@ __device__ __forceinline__ void reduce_epilogue_store(const ReduceArgs& a, int m
 // A thread sums four consecutive columns of one row over the chunks, in chunk order, with the
 // loads of all chunks in flight together (kVec: N is a multiple of 4, so the partial planes can be
 // read 16 bytes at a time); otherwise one element per thread.
+__device__ __forceinline__ float round_to(float v, int dtype) {
+  if (dtype == IXK_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+  if (dtype == IXK_F16) return __half2float(__float2half_rn(v));
+  return v;
+}
+
+// GeGLU over the two halves of a [M, 2 N'] product: thread = four consecutive output columns; the
+// gate is activated and rounded, the up half rounded, then multiplied (the values a gate GEMM with
+// a GELU epilogue, an up GEMM and an elementwise product would have produced one after the other).
+__global__ void splitk_reduce_geglu_kernel(const ReduceArgs a) {
+  const int half = a.N / 2, h4 = half / 4;
+  const int64_t plane4 = static_cast<int64_t>(a.M) * a.N / 4;
+  const int64_t total = static_cast<int64_t>(a.M) * h4;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int m = static_cast<int>(i / h4);
+    const int n = static_cast<int>(i - static_cast<int64_t>(m) * h4) * 4;
+    const float4* gsrc = reinterpret_cast<const float4*>(a.partial) + (static_cast<int64_t>(m) * a.N + n) / 4;
+    const float4* usrc = gsrc + h4;
+    float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+#pragma unroll 4
+    for (int s = 0; s < a.splits; ++s) {
+      const float4 gv = __ldg(gsrc + s * plane4), uv = __ldg(usrc + s * plane4);
+      g.x += gv.x; g.y += gv.y; g.z += gv.z; g.w += gv.w;
+      u.x += uv.x; u.y += uv.y; u.z += uv.z; u.w += uv.w;
+    }
+    const float gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      store_from_f32(a.d, static_cast<int64_t>(m) * a.ldd + n + e, a.out_dtype,
+                     round_to(gelu_tanh_f(gs[e]), a.out_dtype) * round_to(us[e], a.out_dtype));
+  }
+}
+
 template <bool kVec>
 __global__ void splitk_reduce_kernel(const ReduceArgs a) {
   const int64_t plane = static_cast<int64_t>(a.M) * a.N;
@@ -131,7 +166,7 @@ size_t split_k_workspace_bytes(int64_t M, int64_t N, int splits) {
   return splits <= 1 ? 0 : static_cast<size_t>(splits) * M * N * sizeof(float);
 }
 
-int launch_split_k(const Problem& p, int splits, void* workspace, const DeviceInfo& dev, cudaStream_t stream) {
+int launch_split_k(const Problem& p, int splits, void* workspace, const DeviceInfo& dev, cudaStream_t stream, bool geglu) {
   const int64_t chunk = p.K / splits;
   Problem part = p;
   part.K = chunk;
@@ -164,6 +199,16 @@ int launch_split_k(const Problem& p, int splits, void* workspace, const DeviceIn
   r.bias_dtype = p.bias_dtype;
   r.act = p.act;
   r.beta = p.beta;
+  r.geglu = geglu ? 1 : 0;
+  if (geglu) {
+    const int64_t total = p.M * (p.N / 8);
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 8 * dev.sm_count) blocks = 8 * dev.sm_count;
+    splitk_reduce_geglu_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(r);
+    IXK_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return IXK_OK;
+  }
   const bool vec = p.N % 4 == 0 && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0;
   const int64_t total = vec ? p.M * p.N / 4 : p.M * p.N;
   const int threads = 256;

@@ -34,6 +34,18 @@ class KernelOps:
         return self.pkg.gemm(x, w, bias=bias, c=c, beta=beta, epilogue=epilogue, out=out,
                              workspace=self.gemm_workspace)
 
+    def gemm_geglu(self, x, w_gate_up):
+        """gelu(x @ gate) * (x @ up) with [gate | up] as one weight: one GEMM + one combining pass (decode
+        shapes; needs the scratch).  None when the library does not take the shape."""
+        if x.shape[-2] > 128 or self.gemm_workspace is None:
+            return None
+        try:
+            return self.pkg.gemm_geglu(x, w_gate_up, workspace=self.gemm_workspace)
+        except self.pkg.IxkError as ex:
+            if ex.status in (self.pkg.IXK_UNIMPLEMENTED, self.pkg.IXK_WORKSPACE_TOO_SMALL):
+                return None
+            raise
+
     def attention(self, q, k, v, out, *, scale, causal, workspace=None):
         """q/out [B,N,F,H] views, k/v [B,N,T,H] views."""
         self.pkg.fmha_forward_kernel(None, q, k, v, None, None, 0.0, out, None, scale, False, causal=causal,
@@ -247,24 +259,32 @@ def gptj_layer_flops(B, S, hidden=4096, heads=16, head_dim=256, ffn=16384):
 class GemmaLayerWeights:
     """This rank's shard.  Full shapes: wqkv [3072, 12288], wo [4096, 3072], wgate/wup [3072, 24576],
     wdown [24576, 3072]; norm_attn / norm_mlp [3072]: the learned scales w of the two RMSNorms,
-    applied as (1 + w), replicated on every rank (None = unit gain)."""
+    applied as (1 + w), replicated on every rank (None = unit gain).  The gate and up shards are
+    kept side by side in one matrix (wgateup [3072, 2 * columns]: one GEMM serves both); wgate and
+    wup are its two halves as views."""
     wqkv: torch.Tensor
     wo: torch.Tensor
-    wgate: torch.Tensor
-    wup: torch.Tensor
+    wgateup: torch.Tensor
     wdown: torch.Tensor
     heads_local: int
     head_dim: int
     norm_attn: Optional[torch.Tensor] = None
     norm_mlp: Optional[torch.Tensor] = None
 
+    @property
+    def wgate(self) -> torch.Tensor:
+        return self.wgateup[:, :self.wgateup.shape[1] // 2]
+
+    @property
+    def wup(self) -> torch.Tensor:
+        return self.wgateup[:, self.wgateup.shape[1] // 2:]
+
     @staticmethod
     def shard(full: dict, num_heads: int, head_dim: int, rank: int, world: int):
         return GemmaLayerWeights(
             wqkv=shard_qkv_weight(full["wqkv"], num_heads, head_dim, rank, world),
             wo=shard_rows(full["wo"], rank, world),
-            wgate=shard_columns(full["wgate"], rank, world),
-            wup=shard_columns(full["wup"], rank, world),
+            wgateup=torch.cat((shard_columns(full["wgate"], rank, world), shard_columns(full["wup"], rank, world)), dim=1),
             wdown=shard_rows(full["wdown"], rank, world),
             heads_local=num_heads // world, head_dim=head_dim,
             norm_attn=full.get("norm_attn"), norm_mlp=full.get("norm_mlp"))
@@ -303,12 +323,14 @@ def gemma_decode_step(x: torch.Tensor, w: GemmaLayerWeights, k_cache: torch.Tens
     else:
         x1 = add(x, reduce(ops.gemm(ctx.view(B, hl * hd), w.wo), group))
     h2 = norm(x1, gain=w.norm_mlp).view(B, hidden)
-    gate = ops.gemm(h2, w.wgate, epilogue="GELU")
-    up = ops.gemm(h2, w.wup)
+    fused = getattr(ops, "gemm_geglu", None)
+    act = fused(h2, w.wgateup) if fused is not None else None     # one GEMM for gate and up, GeGLU in its second pass
+    if act is None:
+        act = ops.gemm(h2, w.wgate, epilogue="GELU") * ops.gemm(h2, w.wup)
     if comm is not None:
-        part = ops.gemm(gate * up, w.wdown, out=comm.view(nbytes, (B, hidden), x.dtype))
+        part = ops.gemm(act, w.wdown, out=comm.view(nbytes, (B, hidden), x.dtype))
         return comm.all_reduce_residual(part, x1)
-    return add(x1, reduce(ops.gemm(gate * up, w.wdown), group))
+    return add(x1, reduce(ops.gemm(act, w.wdown), group))
 
 
 def gemma_decode_bytes(B, T, hidden=3072, heads=16, head_dim=256, ffn=24576, elem=2):

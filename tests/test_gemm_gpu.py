@@ -432,3 +432,33 @@ def test_split_k_skinny(pkg, orc, cuda, shape, lb):
     n1 = pkg.launch_count()
     small = pkg.gemm(xd, wd, workspace=ws[:64])
     assert pkg.launch_count() == n1 + 1 and small.shape == (M, N)
+
+
+@pytest.mark.parametrize("shape", [(64, 3072, 2 * 6144), (8, 512, 2 * 128), (128, 1024, 2 * 1024), (64, 3072, 2 * 24576)],
+                         ids=lambda s: "M{}K{}N{}".format(*s))
+def test_geglu_projection_in_one_product(pkg, orc, cuda, shape):
+    """ixk_gemm_geglu: gate and up weights side by side, one GEMM (split along K where that helps) and
+    one combining pass, against the three separate steps (gate GEMM with the GELU epilogue, up GEMM,
+    elementwise product) and the oracle."""
+    M, K, N2 = shape
+    half = N2 // 2
+    g = torch.Generator().manual_seed(M + K + N2)
+    x = torch.randn(M, K, generator=g).bfloat16().to(cuda)
+    w = (torch.randn(K, N2, generator=g) * 0.03).bfloat16().to(cuda)
+    n0 = pkg.launch_count()
+    got = pkg.gemm_geglu(x, w)
+    assert pkg.launch_count() - n0 == 2 and got.shape == (M, half)
+    gate = pkg.gemm(x, w[:, :half], epilogue="GELU")
+    up = pkg.gemm(x, w[:, half:])
+    # the same roundings in the same places; the products may differ in summation order (other K cuts)
+    orc.check_close(f32(got), f32(gate * up), rtol=2e-2, atol=2e-3, what=f"geglu vs three steps {shape}")
+    xf, wf = f32(x), f32(w)
+    want = orc.round_bf16(orc.gemm_epilogue(xf @ wf[:, :half], None, None, 0.0, "GELU", orc.BF16) * orc.round_bf16(xf @ wf[:, half:]))
+    orc.check_close(f32(got), want, rtol=2e-2, atol=2e-3, what=f"geglu vs oracle {shape}")
+    # shapes it does not take
+    with pytest.raises(pkg.IxkError) as e:
+        pkg.gemm_geglu(torch.zeros(256, K, dtype=torch.bfloat16, device=cuda), w)
+    assert e.value.status == pkg.IXK_UNIMPLEMENTED
+    with pytest.raises(pkg.IxkError) as e:
+        pkg.gemm_geglu(x, w, workspace=torch.empty(16, dtype=torch.uint8, device=cuda))
+    assert e.value.status == pkg.IXK_WORKSPACE_TOO_SMALL
