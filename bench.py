@@ -823,6 +823,8 @@ def run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=Tru
         v_cache = v_full[:, :, h0:h0 + hl].contiguous() if world > 1 else v_full
         ws = torch.empty(8 << 20, dtype=torch.uint8, device=dev)
         rope = layers.rotary_tables(torch.tensor([T - 1], device=dev), 256)
+        if comm is not None:
+            comm.set_alternating(True)   # the step's two exchanges (and the alignment one) use three different ranges in turn
         step = lambda reduce=None: layers.gemma_decode_step(x, w, k_cache, v_cache, T - 1, ops, workspace=ws, rope=rope,
                                                             reduce=reduce, comm=comm)
         work, div, unit, bound = layers.gemma_decode_bytes(B, T), 1e9, "GB/s", "hbm"

@@ -398,6 +398,14 @@ void* ixk_comm_base(ixk_comm* comm);
 void* ixk_comm_buffer(ixk_comm* comm);
 size_t ixk_comm_buffer_bytes(ixk_comm* comm);
 int ixk_comm_set_wait_limit(ixk_comm* comm, long long cycles);
+/* A promise by the caller that lets the one-shot form (ixk_all_reduce to a buffer outside the
+ * exchange buffer, ixk_all_reduce_residual) leave without its second meeting with the peers: no two
+ * CONSECUTIVE calls on this communicator (of any kind, on any rank: the ranks issue the same
+ * sequence) use overlapping contribution ranges.  Then a rank can only rewrite a range after it
+ * has passed the first meeting of the call in between, i.e. after every peer has finished reading
+ * the range.  A decode step with two exchanges at two offsets satisfies this by construction.
+ * Off by default; the two-shot and scattered forms always keep both meetings. */
+int ixk_comm_set_alternating(ixk_comm* comm, int on);
 int ixk_comm_destroy(ixk_comm* comm);
 /* dtype in {BF16, F16, F32}; kind: ixk_reduce_kind; count in elements. */
 int ixk_all_reduce(ixk_comm* comm, int dtype, int kind, size_t in_offset, void* out,

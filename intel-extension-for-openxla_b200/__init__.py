@@ -124,6 +124,7 @@ ABI_SYMBOLS = {
     "ixk_comm_buffer": (_vp, [_vp]),
     "ixk_comm_buffer_bytes": (_sz, [_vp]),
     "ixk_comm_set_wait_limit": (ctypes.c_int, [_vp, ctypes.c_longlong]),
+    "ixk_comm_set_alternating": (ctypes.c_int, [_vp, ctypes.c_int]),
     "ixk_comm_destroy": (ctypes.c_int, [_vp]),
     "ixk_all_reduce": (ctypes.c_int, [_vp, ctypes.c_int, ctypes.c_int, _sz, _vp, _sz, _vp]),
     "ixk_all_reduce_residual": (ctypes.c_int, [_vp, ctypes.c_int, _sz, _vp, _vp, _vp, ctypes.c_int64, ctypes.c_int64, _vp]),

@@ -135,6 +135,11 @@ class Communicator:
         self.pkg._check(st)
         return out
 
+    def set_alternating(self, on: bool = True) -> None:
+        """Promise that consecutive calls never use overlapping contribution ranges: the one-shot form
+        then skips its second meeting with the peers (see ixk_comm_set_alternating)."""
+        self.pkg._check(self.lib.ixk_comm_set_alternating(self._comm, 1 if on else 0))
+
     def set_wait_limit(self, cycles: int) -> None:
         self.pkg._check(self.lib.ixk_comm_set_wait_limit(self._comm, cycles))
 

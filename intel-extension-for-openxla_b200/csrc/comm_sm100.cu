@@ -59,6 +59,7 @@ struct Args {
   long long cols;
   size_t count;          // elements
   int rank, world, kind;
+  int skip_end;          // one-shot only: leave without waiting for the peers (see ixk_comm_set_alternating)
   long long wait_limit;
   int* status_word;
 };
@@ -92,7 +93,9 @@ __device__ __forceinline__ bool exchange(const Args& a, int phase, uint32_t gen,
     const uint32_t* mine = &a.flags[a.rank]->sig[phase][blockIdx.x][peer];
     const long long t0 = clock64();
     uint32_t spins = 0;
-    while (ld_acquire_sys(mine) != gen) {
+    // (>=, wrap-safe: a peer that left without the second meeting may already have announced the
+    // next generation here)
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - gen) < 0) {
       if ((++spins & 63u) == 0 && clock64() - t0 > a.wait_limit) {
         atomicCAS(a.status_word, 0, site);
         *abort_smem = 1;
@@ -296,7 +299,7 @@ __global__ void __launch_bounds__(kThreads) all_reduce_kernel(const Args a) {
       }
     }
   }
-  if (world > 1 && !exchange(a, kPhaseDone, gen, kSiteEnd, &abort_smem)) return;
+  if (world > 1 && !(kMode == kOneShot && a.skip_end) && !exchange(a, kPhaseDone, gen, kSiteEnd, &abort_smem)) return;
   if (threadIdx.x == 0) a.flags[a.rank]->counter[blockIdx.x] = gen;
 }
 
@@ -314,6 +317,7 @@ struct ixk_comm {
   bool connected = false;
   long long wait_limit = ixk::comm::kDefaultWaitCycles;
   int force_algo = 0;                                   // 0 = by size, 1 = one-shot, 2 = two-shot
+  bool alternating = false;                             // the caller never reuses a contribution range in consecutive calls
 };
 
 namespace ixk {
@@ -413,6 +417,7 @@ int run(ixk_comm* c, int dtype, int kind, size_t in_offset, const void* x, const
   a.rank = c->rank;
   a.world = c->world;
   a.kind = kind;
+  a.skip_end = (c->alternating && !two_shot) ? 1 : 0;
   a.wait_limit = c->wait_limit;
   a.status_word = dev.status_word;
   const size_t vecs = bytes / 16;
@@ -651,6 +656,13 @@ int ixk_comm_set_wait_limit(ixk_comm* c, long long cycles) {
   ixk::clear_error();
   if (c == nullptr || cycles <= 0) return ixk::fail(IXK_INVALID_ARGUMENT, "comm is NULL or cycles <= 0");
   c->wait_limit = cycles;
+  return IXK_OK;
+}
+
+int ixk_comm_set_alternating(ixk_comm* c, int on) {
+  ixk::clear_error();
+  if (c == nullptr) return ixk::fail(IXK_INVALID_ARGUMENT, "comm is NULL");
+  c->alternating = on != 0;
   return IXK_OK;
 }
 

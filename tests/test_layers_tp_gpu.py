@@ -159,6 +159,25 @@ def _worker(rank, world, port, q):
             graph.replay()
         torch.cuda.synchronize()
         checks["gemma_graph_equals_eager"] = torch.equal(y_graph, y_comm)
+        # the same step with the promise that consecutive exchanges never share a range (its two use
+        # two offsets): the one-shot kernels then leave without their second meeting; 40 replays back
+        # to back, where a rank that runs ahead would be caught rewriting a range still being read
+        # (the promise is read when a call is issued: a new capture)
+        comm.set_alternating(True)
+        torch.cuda.synchronize()
+        dist.barrier()
+        cap.wait_stream(torch.cuda.current_stream())
+        graph2 = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(cap):
+            with torch.cuda.graph(graph2, stream=cap, capture_error_mode="thread_local"):
+                y_alt = step()
+        torch.cuda.current_stream().wait_stream(cap)
+        for _ in range(40):
+            graph2.replay()
+        torch.cuda.synchronize()
+        checks["gemma_alternating_equals_eager"] = torch.equal(y_alt, y_comm) and pkg.device_status() == 0
+        comm.set_alternating(False)
+        dist.barrier()
         # ---- a peer that does not show up: rank 1 sits this exchange out (it is between steps, nothing
         # of its own in flight); rank 0's kernel gives up after its cycle budget, reports where, and
         # the GPU stays usable.  The ranks then meet on the host and take the communicator down.
