@@ -246,6 +246,20 @@ def test_all_reduce_slices_and_set_up_errors(pkg):
         assert lib.ixk_selftest_bounded_wait(1000, None, None) == pkg.IXK_NO_DEVICE
     assert lib.ixk_all_reduce(None, 0, 0, 0, None, 16, None) == pkg.IXK_INVALID_ARGUMENT
     assert lib.ixk_comm_destroy(None) == pkg.IXK_OK
+    # the calls that came with the fused projection + exchange and the decode step: a NULL
+    # communicator, a NULL descriptor and an unsupported type are answered with codes, GPU or not
+    assert lib.ixk_comm_set_alternating(None, 1) == pkg.IXK_INVALID_ARGUMENT
+    assert lib.ixk_all_reduce_scattered(None, pkg.IXK_BF16, 0, None, None, 0, 8, 8, None) == pkg.IXK_INVALID_ARGUMENT
+    assert lib.ixk_reduce_scatter(None, pkg.IXK_BF16, 0, 0, None, 8, None) == pkg.IXK_INVALID_ARGUMENT
+    assert lib.ixk_all_gather(None, pkg.IXK_BF16, None, 0, 8, None) == pkg.IXK_INVALID_ARGUMENT
+    d = pkg._GemmDesc()
+    assert lib.ixk_gemm_scatter(None, ctypes.byref(d), None, None, None, None, 0, None) == pkg.IXK_INVALID_ARGUMENT
+    assert lib.ixk_gemm_geglu(None, None, None, None, 0, None, 0, None) == pkg.IXK_INVALID_ARGUMENT
+    assert lib.ixk_gemm_geglu_workspace_bytes(None) == 0
+    assert lib.ixk_kv_append(pkg.IXK_F32, 1, 1, 8, None, None, 8, 8, None, None, 8, 8, 8, 0, None) == pkg.IXK_UNIMPLEMENTED
+    assert lib.ixk_kv_append(pkg.IXK_BF16, 1, 1, 8, None, None, 8, 8, None, None, 8, 8, 8, 0, None) == pkg.IXK_INVALID_ARGUMENT
+    assert lib.ixk_row_norm_gain(pkg.IXK_BF16, pkg.NORM_RMS, 1, 8, None, 8, None, 1.0, None, 8, 1e-6, None) == pkg.IXK_INVALID_ARGUMENT
+    assert lib.ixk_rotary_half(pkg.IXK_F32, None, 1, 1, 1, 16, 16, 16, None, None, None) == pkg.IXK_UNIMPLEMENTED
 
 
 def test_missing_library_fails_loudly(pkg, monkeypatch):
