@@ -679,6 +679,11 @@ def run_ours(args, rank, world):
                 if world > 1:
                     raise      # a rank that leaves a collective workload alone would strand the others
                 others.append({"workload": lname, "error": repr(ex)})
+        if world > 1 and not args.nccl:
+            try:
+                others.append(run_all_reduce(rank, world, pkg, dev))
+            except Exception as ex:  # noqa: BLE001 - e.g. CUDA IPC refused: every rank fails at the same (collective) point
+                others.append({"workload": "all_reduce", "error": repr(ex)[:300]})
         line["others"] = others
     if world > 1:
         import torch.distributed as dist
@@ -753,6 +758,50 @@ def layer_config(name, world):
         wname = f"gemma_decode_B64_T4096_hidden3072_heads16x256_mlp24576_tp{world}"
     return {"workload": wname, "parallelism": f"tp{world} by heads / MLP columns, all-reduce after row-parallel GEMMs",
             "l2": "L2 flushed (512 MB read+write) between timed steps"}
+
+
+def run_all_reduce(rank, world, pkg, dev, calls=40):
+    """The exchange of the tensor-parallel layers on its own: libixk's NVLink all-reduce at the two
+    message sizes of configurations 5 and 4 (393 KB: one-shot to a private buffer; 67 MB: two-shot in
+    place), `calls` back to back between one pair of CUDA events, max over ranks, with
+    ncclAllReduce timed the same way beside it.  Bus bandwidth = 2 (N - 1) / N x bytes / time."""
+    import importlib
+    import torch.distributed as dist
+    comm_mod = importlib.import_module(entry.PKG_NAME + ".comm")
+    sizes = (("393 KB (decode partial), one-shot", 64 * 3072), ("67 MB (prefill partial), two-shot in place", 8192 * 4096))
+    comm = comm_mod.Communicator(pkg, rank, world, sizes[-1][1] * 2)
+    rows = []
+    try:
+        for label, n in sizes:
+            slot = comm.view(0, (n,), torch.bfloat16)
+            slot.normal_()
+            private = torch.empty(n, dtype=torch.bfloat16, device=dev)
+            mine = (lambda: comm.all_reduce(slot, out=private)) if n * 2 < (1 << 20) else (lambda: comm.all_reduce(slot))
+            ref_t = torch.randn(n, device=dev).bfloat16()
+            theirs = lambda: dist.all_reduce(ref_t)
+            out = {}
+            for name, fn in (("libixk", mine), ("nccl", theirs)):
+                for _ in range(5):
+                    fn()
+                torch.cuda.synchronize()
+                dist.barrier()
+                s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s_ev.record()
+                for _ in range(calls):
+                    fn()
+                e_ev.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([s_ev.elapsed_time(e_ev) / calls], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                us = float(t.item()) * 1e3
+                out[name] = {"us_per_call": us, "bus_gbs": 2.0 * (world - 1) / world * n * 2 / (us * 1e-6) / 1e9}
+            rows.append({"message": label, "bytes": n * 2, **out})
+        status = pkg.device_status()
+    finally:
+        comm.close()
+    return {"workload": f"all_reduce_bf16_{world}_ranks", "metric": "all-reduce time per call, back to back (us) and bus bandwidth (GB/s)",
+            "n_gpus": world, "sizes": rows, "device_status": status,
+            "note": "NVLink peer loads / stores with device-side flags (libixk) against ncclAllReduce, same buffers sizes and timing"}
 
 
 def run_layer(args, rank, world, pkg, dev, local, peaks, flush_buf, with_cpu=True):
